@@ -1,0 +1,211 @@
+"""The cache: a slot per live sequence, keys and values per cache, state per slot.
+
+A model's schedule names caches (``ScheduleEntry.cache``); the mixer that writes a
+cache says what it needs (``KVCacheRequest`` or ``StateRequest``). Caches with the
+same needs form a *group* with storage of its own:
+
+* a KV group owns pools ``k``/``v`` [caches, pages, kv heads, page_size, head_dim] and
+  a page allocator. A sequence holds ceil(len / page_size) pages of the group, taken
+  when it grows and returned when its slot is released. A windowed group returns
+  pages that have fallen wholly out of the window after each step.
+* a state group owns ``state`` [caches, slots, *shape]; a slot's rows are zeroed when
+  the slot is acquired.
+
+The reference keeps one append-only array per layer for its single sequence
+(crates/spissa-runtime/src/rotary.rs:195-318: append checks capacity before it
+changes anything, truncate undoes). Here all lengths live on the host; a step first
+reserves everything it needs and changes nothing if that fails.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..parts.base import KVCacheRequest, StateRequest
+from .slots import CacheFull, CacheMisuse, IndexPool
+from .views import KVLayerView, StateLayerView
+
+
+@dataclass
+class SequenceState:
+    slot: int
+    length: int = 0
+    pages: dict = field(default_factory=dict)         # kv group name -> list of pages (None = returned)
+
+
+class KVGroup:
+    def __init__(self, name, request: KVCacheRequest, cache_ids, n_pages, page_size, dtype, device,
+                 allocate=True):
+        self.name, self.request, self.cache_ids = name, request, list(cache_ids)
+        self.page_size, self.n_pages = page_size, n_pages
+        self.pages = IndexPool(n_pages, f"page of cache group {name}")
+        shape = (len(self.cache_ids), n_pages, request.num_kv_heads, page_size, request.head_dim)
+        self.k = torch.empty(shape, dtype=dtype, device=device) if allocate else None
+        self.v = torch.empty(shape, dtype=dtype, device=device) if allocate else None
+        self.index = {c: i for i, c in enumerate(self.cache_ids)}
+
+    def pages_for(self, length: int) -> int:
+        return (length + self.page_size - 1) // self.page_size
+
+    def bytes(self) -> int:
+        return 0 if self.k is None else 2 * self.k.numel() * self.k.element_size()
+
+
+class StateGroup:
+    def __init__(self, name, request: StateRequest, cache_ids, n_slots, device, allocate=True):
+        self.name, self.request, self.cache_ids = name, request, list(cache_ids)
+        shape = (len(self.cache_ids), n_slots) + tuple(request.shape)
+        self.state = torch.zeros(shape, dtype=request.dtype, device=device) if allocate else None
+        self.index = {c: i for i, c in enumerate(self.cache_ids)}
+
+
+class CacheManager:
+    """Slots, page accounting and storage for one model.
+
+    ``requests``: cache id -> request of the mixer that writes it (None: no cache).
+    ``max_tokens``: tokens all live sequences may hold together, each sequence rounded
+    up to whole pages. ``max_seqs``: slots.
+    """
+
+    def __init__(self, requests: dict, max_tokens: int, max_seqs: int, page_size: int, dtype, device,
+                 allocate: bool = True):
+        if page_size <= 0 or max_tokens <= 0 or max_seqs <= 0:
+            raise ValueError("page_size, max_tokens and max_seqs must be positive")
+        self.page_size = page_size
+        self.n_pages = (max_tokens + page_size - 1) // page_size
+        self.max_seqs = max_seqs
+        self.slots = IndexPool(max_seqs, "slot")
+        self.seqs: dict = {}
+        self.kv_groups: dict = {}
+        self.state_groups: dict = {}
+        self.cache_group: dict = {}
+        by_need: dict = {}
+        for cid, req in requests.items():
+            if req is None:
+                continue
+            by_need.setdefault(req, []).append(cid)
+        for req, cids in by_need.items():
+            if isinstance(req, KVCacheRequest):
+                name = f"kv{len(self.kv_groups)}" + (f"_w{req.window}" if req.window else "")
+                self.kv_groups[name] = KVGroup(name, req, cids, self.n_pages, page_size, dtype, device, allocate)
+            elif isinstance(req, StateRequest):
+                name = f"state{len(self.state_groups)}"
+                self.state_groups[name] = StateGroup(name, req, cids, max_seqs, device, allocate)
+            else:
+                raise TypeError(f"unknown cache request {req!r}")
+            for c in cids:
+                self.cache_group[c] = name
+
+    # ------------------------------------------------------------------ slots
+    def acquire(self) -> int:
+        slot = self.slots.acquire()
+        self.seqs[slot] = SequenceState(slot, 0, {g: [] for g in self.kv_groups})
+        for g in self.state_groups.values():
+            if g.state is not None:
+                g.state[:, slot].zero_()
+        return slot
+
+    def release(self, slot: int) -> None:
+        if slot not in self.seqs:
+            raise CacheMisuse(f"slot {slot} is released but not held")
+        seq = self.seqs.pop(slot)
+        for gname, pages in seq.pages.items():
+            pool = self.kv_groups[gname].pages
+            for p in pages:
+                if p is not None:
+                    pool.release(p)
+        self.slots.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self._seq(slot).length
+
+    def _seq(self, slot: int) -> SequenceState:
+        try:
+            return self.seqs[slot]
+        except KeyError:
+            raise CacheMisuse(f"slot {slot} is not held") from None
+
+    def free_tokens(self) -> int:
+        """Tokens that could still be stored if given to one new sequence."""
+        if not self.kv_groups:
+            return 1 << 60
+        return min(g.pages.free_count for g in self.kv_groups.values()) * self.page_size
+
+    # ------------------------------------------------------------------ a step
+    def reserve(self, slot_counts: list) -> dict:
+        """Take the pages that ``[(slot, new_tokens)]`` need. All or nothing.
+
+        Returns kv group name -> per entry the sequence's page list (returned pages as 0).
+        """
+        seen = set()
+        for slot, n in slot_counts:
+            self._seq(slot)
+            if slot in seen:
+                raise CacheMisuse(f"slot {slot} appears twice in one step")
+            seen.add(slot)
+            if n <= 0:
+                raise ValueError("every sequence of a step brings at least one token")
+        for g in self.kv_groups.values():
+            need = sum(g.pages_for(self.seqs[s].length + n) - len(self.seqs[s].pages[g.name])
+                       for s, n in slot_counts)
+            if need > g.pages.free_count:
+                raise CacheFull(f"cache group {g.name}: the step needs {need} more pages of {self.page_size} "
+                                f"tokens, {g.pages.free_count} of {g.n_pages} are free")
+        tables = {}
+        for g in self.kv_groups.values():
+            rows = []
+            for s, n in slot_counts:
+                seq = self.seqs[s]
+                have = seq.pages[g.name]
+                want = g.pages_for(seq.length + n)
+                have.extend(g.pages.acquire_many(want - len(have)))
+                rows.append([p if p is not None else 0 for p in have])
+            tables[g.name] = rows
+        return tables
+
+    def commit(self, slot_counts: list) -> None:
+        """The step ran: lengths grow; windowed groups return pages no key can be read from."""
+        for slot, n in slot_counts:
+            seq = self.seqs[slot]
+            seq.length += n
+            for g in self.kv_groups.values():
+                w = g.request.window
+                if not w:
+                    continue
+                # the next query stands at seq.length and sees keys ≥ seq.length - w + 1
+                first_needed = max(0, seq.length - w + 1) // self.page_size
+                pages = seq.pages[g.name]
+                for i in range(min(first_needed, len(pages))):
+                    if pages[i] is not None:
+                        g.pages.release(pages[i])
+                        pages[i] = None
+
+    # ------------------------------------------------------------------ views
+    def view(self, cache_id: int, step, writes: bool):
+        gname = self.cache_group.get(cache_id)
+        if gname is None:
+            return None
+        if gname in self.kv_groups:
+            g = self.kv_groups[gname]
+            i = g.index[cache_id]
+            return KVLayerView(g.k[i], g.v[i], step.page_tables[gname], self.page_size, step.token_seq,
+                               step.positions, step.seq_row, g.request.window, writes)
+        g = self.state_groups[gname]
+        return StateLayerView(g.state[g.index[cache_id]], writes)
+
+    def check(self) -> None:
+        """No slot or page lost, held twice or freed twice."""
+        self.slots.check()
+        if sorted(self.seqs) != self.slots.held():
+            raise CacheMisuse("the slots held and the sequences known differ")
+        for g in self.kv_groups.values():
+            g.pages.check()
+            owned = [p for s in self.seqs.values() for p in s.pages[g.name] if p is not None]
+            if len(owned) != len(set(owned)):
+                raise CacheMisuse(f"a page of group {g.name} belongs to two sequences")
+            if sorted(owned) != g.pages.held():
+                raise CacheMisuse(f"pages held and pages owned differ in group {g.name}")
+
+    def bytes(self) -> int:
+        return sum(g.bytes() for g in self.kv_groups.values())

@@ -1,0 +1,154 @@
+"""Compiles the CUDA sources of this folder for sm_100a into shared libraries.
+
+One library per source file, named after a hash of the source, the shared headers
+and the flags, so a changed file is rebuilt and an unchanged one is reused. The
+libraries land in ``csrc/_build`` inside the package (or, when that is not
+writable, in ``$SPISSA_B200_BUILD_DIR`` or a per-user folder under the system's
+temporary directory). Only ``nvcc`` is needed: the libraries export plain C
+functions and are loaded with ``ctypes``.
+"""
+from __future__ import annotations
+
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+CSRC = Path(__file__).resolve().parent
+HEADERS = ["common.cuh"]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo", "--shared",
+    "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+]
+# module name -> source file
+MODULES = {
+    "generic": "generic_kernels.cu",
+    "sampling": "sampling_kernels.cu",
+}
+
+
+class BuildError(RuntimeError):
+    pass
+
+
+def _say(msg: str) -> None:
+    print(f"[spissa_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def find_nvcc() -> str:
+    cand = [os.environ.get("SPISSA_B200_NVCC"), shutil.which("nvcc"),
+            os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"),
+            "/usr/local/cuda/bin/nvcc"]
+    for c in cand:
+        if c and os.path.isfile(c) and os.access(c, os.X_OK):
+            return c
+    raise BuildError("nvcc was not found (looked at $SPISSA_B200_NVCC, PATH, $CUDA_HOME/bin, "
+                     "/usr/local/cuda/bin); the CUDA kernels cannot be built")
+
+
+def _writable_dir(p: Path) -> bool:
+    try:
+        p.mkdir(parents=True, exist_ok=True)
+        probe = p / f".probe_{os.getpid()}"
+        probe.write_bytes(b"")
+        probe.unlink()
+        return True
+    except OSError:
+        return False
+
+
+def build_dir() -> Path:
+    env = os.environ.get("SPISSA_B200_BUILD_DIR")
+    if env and _writable_dir(Path(env)):
+        return Path(env)
+    local = CSRC / "_build"
+    if _writable_dir(local):
+        return local
+    fallback = Path(tempfile.gettempdir()) / f"spissa_b200_build_{os.getuid()}"
+    if _writable_dir(fallback):
+        return fallback
+    raise BuildError(f"no writable folder for built kernels (tried {local} and {fallback})")
+
+
+def _digest(source: str) -> str:
+    h = hashlib.sha256()
+    for name in [source] + HEADERS:
+        h.update(name.encode())
+        h.update((CSRC / name).read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def library_path(module: str, folder: Path | None = None) -> Path:
+    source = MODULES[module]
+    return (folder or build_dir()) / f"libspissa_{module}_{_digest(source)}.so"
+
+
+def find_built(module: str) -> Path | None:
+    """An up-to-date library of ``module`` in any of the known folders, if there is one."""
+    name = f"libspissa_{module}_{_digest(MODULES[module])}.so"
+    folders = [CSRC / "_build", Path(tempfile.gettempdir()) / f"spissa_b200_build_{os.getuid()}"]
+    env = os.environ.get("SPISSA_B200_BUILD_DIR")
+    if env:
+        folders.insert(0, Path(env))
+    for f in folders:
+        if (f / name).is_file():
+            return f / name
+    return None
+
+
+def build_module(module: str, verbose: bool = True, extra_flags=()) -> Path:
+    """Compile ``module`` if no up-to-date library exists; return the library's path."""
+    if module not in MODULES:
+        raise BuildError(f"unknown kernel module {module!r}; known: {sorted(MODULES)}")
+    have = find_built(module)
+    if have is not None:
+        return have
+    out = library_path(module)
+    nvcc = find_nvcc()
+    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / MODULES[module])]
+    if verbose:
+        _say(f"compiling {MODULES[module]} for sm_100a (first use) ...")
+    t0 = time.time()
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                            env=dict(os.environ, TMPDIR=str(out.parent)))
+    last = t0
+    while True:
+        try:
+            log, _ = proc.communicate(timeout=5)
+            break
+        except subprocess.TimeoutExpired:
+            if verbose and time.time() - last >= 10:
+                _say(f"  still compiling {MODULES[module]} ({time.time() - t0:.0f} s)")
+                last = time.time()
+    if proc.returncode != 0:
+        try:
+            tmp.unlink()
+        except OSError:
+            pass
+        raise BuildError(f"nvcc failed on {MODULES[module]}:\n{log}")
+    os.replace(tmp, out)
+    for old in out.parent.glob(f"libspissa_{module}_*.so"):
+        if old != out:
+            try:
+                old.unlink()
+            except OSError:
+                pass
+    if verbose:
+        _say(f"built {out.name} in {time.time() - t0:.1f} s")
+    return out
+
+
+def build_all(verbose: bool = True) -> dict:
+    return {m: build_module(m, verbose) for m in MODULES}
+
+
+if __name__ == "__main__":
+    for m, p in build_all().items():
+        print(m, p)

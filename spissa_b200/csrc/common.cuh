@@ -1,0 +1,80 @@
+// Shared helpers for every kernel file: element loads and stores by storage type,
+// warp and block reductions with a fixed order, launch-error reporting.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define SP_DT_F32 0
+#define SP_DT_BF16 1
+
+#define SP_API extern "C" __attribute__((visibility("default")))
+
+// ---------------------------------------------------------------- error text
+// Each library keeps the text of its last refusal; the host reads it after a
+// non-zero return code. Nothing here aborts the process.
+static thread_local char sp_error_text[512];
+
+#define SP_FAIL(...)                                              \
+    do {                                                          \
+        snprintf(sp_error_text, sizeof(sp_error_text), __VA_ARGS__); \
+        return 1;                                                 \
+    } while (0)
+
+#define SP_CHECK_LAUNCH(name)                                                      \
+    do {                                                                           \
+        cudaError_t e_ = cudaGetLastError();                                       \
+        if (e_ != cudaSuccess) SP_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+// ---------------------------------------------------------------- element access
+__device__ __forceinline__ float sp_ld(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float sp_ld(const __nv_bfloat16* p, size_t i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void sp_st(float* p, size_t i, float v) { p[i] = v; }
+__device__ __forceinline__ void sp_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float sp_ld_dt(const void* p, int dt, size_t i) {
+    return dt == SP_DT_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+}
+__device__ __forceinline__ void sp_st_dt(void* p, int dt, size_t i, float v) {
+    if (dt == SP_DT_F32) ((float*)p)[i] = v;
+    else ((__nv_bfloat16*)p)[i] = __float2bfloat16_rn(v);
+}
+
+// ---------------------------------------------------------------- reductions
+__device__ __forceinline__ float sp_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float sp_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. ``scratch``
+// holds 32 floats. The order of additions depends only on blockDim.
+__device__ __forceinline__ float sp_block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = sp_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? scratch[lane] : 0.0f;
+    r = sp_warp_sum(r);
+    return r;
+}
+__device__ __forceinline__ float sp_block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = sp_warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nw = (blockDim.x + 31) >> 5;
+    float r = (lane < nw) ? scratch[lane] : -INFINITY;
+    r = sp_warp_max(r);
+    return r;
+}

@@ -1,0 +1,433 @@
+// Generic kernels: every op of the forward pass for every storage type and every size.
+//
+// These are the true 32-bit path of the whole model (plain FFMA, accurate expf /
+// sqrtf / division, no tensor cores, no reduced-precision matrix mode) and the
+// fallback for sizes that a specialised kernel refuses. Each output element is
+// reduced in an order that depends only on its own row, never on what else is in
+// the batch, so that cutting the same tokens into other steps changes no bit.
+//
+// Formulas follow the reference runtime (paths within Erik-cpu-create/spissa):
+//   embedding       crates/spissa-runtime/src/ops.rs:6-30
+//   rms norm        crates/spissa-runtime/src/ops.rs:159-179
+//   linear          crates/spissa-runtime/src/ops.rs:62-105   (y = x·Wᵀ, W [out,in])
+//   rotate-half     crates/spissa-runtime/src/rotary.rs:98-123, :454-481
+//   attention       crates/spissa-runtime/src/rotary.rs:335-415, :549-569
+//   silu            crates/spissa-runtime/src/ops.rs:192-194
+//   argmax          crates/spissa-runtime/src/ops.rs:309-324  (first maximum wins)
+#include "common.cuh"
+
+SP_API const char* sp_generic_last_error() { return sp_error_text; }
+
+// ============================================================== embedding
+template <typename TW>
+__global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int T, int H, int V, int* status) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int id = ids[t];
+    const bool ok = (id >= 0 && id < V);
+    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    for (int c = threadIdx.x; c < H; c += blockDim.x)
+        out[(size_t)t * H + c] = ok ? sp_ld(table, (size_t)id * H + c) : 0.0f;
+}
+
+SP_API int sp_embed_gather(const void* table, int table_dt, const int* ids, float* out,
+                           int T, int H, int V, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dt == SP_DT_F32)
+        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, T, H, V, status);
+    else if (table_dt == SP_DT_BF16)
+        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, T, H, V, status);
+    else
+        SP_FAIL("embed_gather: unsupported table dtype code %d", table_dt);
+    SP_CHECK_LAUNCH("embed_gather");
+    return 0;
+}
+
+// ============================================================== rms norm
+// One block per output row. ``rows`` (optional) gathers input rows: out row r is the
+// norm of x row rows[r]. Statistics and the product are 32-bit; the result is rounded
+// once, on the store.
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt,
+                               void* __restrict__ out, int out_dt, const int* __restrict__ rows,
+                               int n_rows, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    if (r >= n_rows) return;
+    const size_t src = (size_t)(rows ? rows[r] : r) * H;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = x[src + c];
+        ss = fmaf(v, v, ss);
+    }
+    ss = sp_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = x[src + c] * inv * sp_ld_dt(w, w_dt, c);
+        sp_st_dt(out, out_dt, (size_t)r * H + c, v);
+    }
+}
+
+SP_API int sp_rmsnorm(const float* x, const void* w, int w_dt, void* out, int out_dt, const int* rows,
+                      int n_rows, int H, float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if ((w_dt | out_dt) & ~1) SP_FAIL("rmsnorm: unsupported dtype code");
+    // a fixed block size: the order of the row sum must not depend on the batch
+    rmsnorm_kernel<<<n_rows, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps);
+    SP_CHECK_LAUNCH("rmsnorm");
+    return 0;
+}
+
+// ============================================================== matrix product
+// C[M,N] (+)= A[M,K] · W[N,K]ᵀ, FFMA, 64x64 tile, 16-deep slices, 4x4 per thread.
+// Each output's sum runs over k = 0..K-1 in order, whatever M is.
+#define GG_BM 64
+#define GG_BN 64
+#define GG_BK 16
+
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256)
+gemm_generic_kernel(const TA* __restrict__ A, const TW* __restrict__ W, void* __restrict__ C, int c_dt,
+                    int M, int N, int K, int lda, int ldw, int ldc, int accumulate) {
+    __shared__ float As[GG_BK][GG_BM + 4];
+    __shared__ float Ws[GG_BK][GG_BN + 4];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+    for (int k0 = 0; k0 < K; k0 += GG_BK) {
+        // 64 rows x 16 k = 1024 elements per operand, 4 per thread; k runs fastest in memory
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int e = threadIdx.x + i * 256;
+            const int r = e >> 4, kk = e & 15;
+            const int gm = m0 + r, gn = n0 + r, gk = k0 + kk;
+            As[kk][r] = (gm < M && gk < K) ? sp_ld(A, (size_t)gm * lda + gk) : 0.0f;
+            Ws[kk][r] = (gn < N && gk < K) ? sp_ld(W, (size_t)gn * ldw + gk) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GG_BK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gm = m0 + ty * 4 + i;
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            const size_t o = (size_t)gm * ldc + gn;
+            float v = acc[i][j];
+            if (accumulate) v += ((float*)C)[o];
+            sp_st_dt(C, c_dt, o, v);
+        }
+    }
+}
+
+SP_API int sp_gemm_generic(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt,
+                           int M, int N, int K, int lda, int ldw, int ldc, int accumulate,
+                           cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0) SP_FAIL("gemm: K must be positive, got %d", K);
+    if (accumulate && c_dt != SP_DT_F32) SP_FAIL("gemm: accumulation needs a 32-bit output");
+    dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM);
+    if (grid.y > 65535) SP_FAIL("gemm: M=%d is beyond this kernel's grid", M);
+#define GG_LAUNCH(TA, TW) \
+    gemm_generic_kernel<TA, TW><<<grid, 256, 0, stream>>>((const TA*)A, (const TW*)W, C, c_dt, M, N, K, lda, ldw, ldc, accumulate)
+    if (a_dt == SP_DT_F32 && w_dt == SP_DT_F32) GG_LAUNCH(float, float);
+    else if (a_dt == SP_DT_F32 && w_dt == SP_DT_BF16) GG_LAUNCH(float, __nv_bfloat16);
+    else if (a_dt == SP_DT_BF16 && w_dt == SP_DT_F32) GG_LAUNCH(__nv_bfloat16, float);
+    else if (a_dt == SP_DT_BF16 && w_dt == SP_DT_BF16) GG_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else SP_FAIL("gemm: unsupported dtype codes %d/%d", a_dt, w_dt);
+#undef GG_LAUNCH
+    SP_CHECK_LAUNCH("gemm_generic");
+    return 0;
+}
+
+// ============================================================== rope + cache write
+// qkv row t = [q heads | k heads | v heads]. Rotates q and k (rotate-half over the
+// first ``rd`` dims of each head, angle = position · inv_freq[i], all 32-bit), stores
+// q to ``q_out`` and k, v to the paged cache at the token's position.
+// Cache layout per layer: [page][kv head][page_size][hd].
+struct KvPlace {
+    const int* token_seq;     // [T] sequence index of each token
+    const int* positions;     // [T] absolute position of each token
+    const int* seq_slot;      // [B] slot of each sequence
+    const int* page_table;    // [slots][max_pages]
+    int max_pages;
+    int page_size;
+};
+
+template <typename TIN, typename TQ, typename TC>
+__global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict__ q_out,
+                                     TC* __restrict__ kpool, TC* __restrict__ vpool, KvPlace pl,
+                                     const float* __restrict__ inv_freq, int T, int nh, int nkv, int hd,
+                                     int rd, int write_kv) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int pos = pl.positions[t];
+    const int half = rd >> 1;
+    const int row = (nh + 2 * nkv) * hd;
+    const TIN* src = qkv + (size_t)t * row;
+    int page = 0, off = 0;
+    if (write_kv) {
+        const int slot = pl.seq_slot[pl.token_seq[t]];
+        page = pl.page_table[(size_t)slot * pl.max_pages + pos / pl.page_size];
+        off = pos % pl.page_size;
+    }
+    const int n_rot_heads = nh + nkv;
+    // rotated heads: one thread per (head, pair) and per unrotated tail element
+    for (int e = threadIdx.x; e < n_rot_heads * hd; e += blockDim.x) {
+        const int h = e / hd, d = e % hd;
+        float v;
+        if (d < rd) {
+            const int i = d < half ? d : d - half;
+            const float ang = (float)pos * inv_freq[i];
+            const float c = cosf(ang), s = sinf(ang);
+            const float a = sp_ld(src, (size_t)h * hd + i);
+            const float b = sp_ld(src, (size_t)h * hd + i + half);
+            v = d < half ? a * c - b * s : b * c + a * s;
+        } else {
+            v = sp_ld(src, (size_t)h * hd + d);
+        }
+        if (h < nh) {
+            sp_st(q_out, (size_t)t * nh * hd + (size_t)h * hd + d, v);
+        } else if (write_kv) {
+            const int g = h - nh;
+            sp_st(kpool, (((size_t)page * nkv + g) * pl.page_size + off) * hd + d, v);
+        }
+    }
+    if (write_kv) {
+        for (int e = threadIdx.x; e < nkv * hd; e += blockDim.x) {
+            const int g = e / hd, d = e % hd;
+            const float v = sp_ld(src, (size_t)(nh + nkv) * hd + e);
+            sp_st(vpool, (((size_t)page * nkv + g) * pl.page_size + off) * hd + d, v);
+        }
+    }
+}
+
+SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, void* kpool, void* vpool,
+                            int cache_dt, const int* token_seq, const int* positions, const int* seq_slot,
+                            const int* page_table, int max_pages, int page_size, const float* inv_freq,
+                            int T, int nh, int nkv, int hd, int rd, int write_kv, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rd < 0 || rd > hd || (rd & 1)) SP_FAIL("rope: rotary_dim %d must be even and at most head_dim %d", rd, hd);
+    if (rd > 0 && !inv_freq) SP_FAIL("rope: a frequency table is needed when rotary_dim > 0");
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
+    const int threads = 256;
+#define RK_LAUNCH(TIN, TQ, TC) \
+    rope_kv_write_kernel<TIN, TQ, TC><<<T, threads, 0, stream>>>((const TIN*)qkv, (TQ*)q_out, (TC*)kpool, (TC*)vpool, pl, inv_freq, T, nh, nkv, hd, rd, write_kv)
+    const int key = in_dt * 4 + q_dt * 2 + cache_dt;
+    switch (key) {
+        case 0: RK_LAUNCH(float, float, float); break;
+        case 1: RK_LAUNCH(float, float, __nv_bfloat16); break;
+        case 2: RK_LAUNCH(float, __nv_bfloat16, float); break;
+        case 3: RK_LAUNCH(float, __nv_bfloat16, __nv_bfloat16); break;
+        case 4: RK_LAUNCH(__nv_bfloat16, float, float); break;
+        case 5: RK_LAUNCH(__nv_bfloat16, float, __nv_bfloat16); break;
+        case 6: RK_LAUNCH(__nv_bfloat16, __nv_bfloat16, float); break;
+        case 7: RK_LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16); break;
+        default: SP_FAIL("rope: unsupported dtype codes");
+    }
+#undef RK_LAUNCH
+    SP_CHECK_LAUNCH("rope_kv_write");
+    return 0;
+}
+
+// ============================================================== attention over the cache
+// One warp per (token, query head). Keys are visited in chunks of 32 from the first
+// visible position; lane j scores key j, the softmax runs online in 32-bit, and lane d
+// owns output dims d, d+32, ... . A token at position p sees keys lo..p with
+// lo = max(0, p-window+1) when window > 0, else 0. All keys, this step's included,
+// are read from the cache.
+#define AG_WARPS 4
+#define AG_MAX_HD 256
+
+template <typename TQ, typename TC>
+__global__ void __launch_bounds__(AG_WARPS * 32)
+attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
+                         TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int window,
+                         float scale) {
+    __shared__ float qs[AG_WARPS][AG_MAX_HD];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long gw = (long long)blockIdx.x * AG_WARPS + warp;
+    if (gw >= (long long)T * nh) return;
+    const int t = (int)(gw / nh), h = (int)(gw % nh);
+    const int g = h / (nh / nkv);
+    const int p = pl.positions[t];
+    const int slot = pl.seq_slot[pl.token_seq[t]];
+    const int* pt = pl.page_table + (size_t)slot * pl.max_pages;
+    const int ps = pl.page_size;
+
+    for (int d = lane; d < hd; d += 32) qs[warp][d] = sp_ld(q, (size_t)t * nh * hd + (size_t)h * hd + d);
+    __syncwarp();
+
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    float m = -INFINITY, l = 0.0f;
+    float acc[AG_MAX_HD / 32];
+#pragma unroll
+    for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.0f;
+
+    for (int j0 = lo; j0 <= p; j0 += 32) {
+        const int j = j0 + lane;
+        const bool valid = j <= p;
+        float s = -INFINITY;
+        int my_page = 0, my_off = 0;
+        if (valid) {
+            my_page = pt[j / ps];
+            my_off = j % ps;
+            const TC* kr = kpool + (((size_t)my_page * nkv + g) * ps + my_off) * hd;
+            float dot = 0.0f;
+            for (int d = 0; d < hd; ++d) dot = fmaf(qs[warp][d], sp_ld(kr, d), dot);
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, sp_warp_max(s));
+        const float e = valid ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);              // first chunk: exp(-inf) = 0
+        l = l * corr + sp_warp_sum(e);
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= corr;
+        const int n_valid = min(32, p - j0 + 1);
+        for (int jj = 0; jj < n_valid; ++jj) {
+            const float pj = __shfl_sync(0xffffffffu, e, jj);
+            const int pg = __shfl_sync(0xffffffffu, my_page, jj);
+            const int of = __shfl_sync(0xffffffffu, my_off, jj);
+            const TC* vr = vpool + (((size_t)pg * nkv + g) * ps + of) * hd;
+#pragma unroll
+            for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(pj, sp_ld(vr, d), acc[i]);
+            }
+        }
+        m = m_new;
+    }
+#pragma unroll
+    for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) sp_st(out, (size_t)t * nh * hd + (size_t)h * hd + d, acc[i] / l);
+    }
+}
+
+SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, const void* vpool, int cache_dt,
+                                void* out, const int* token_seq, const int* positions, const int* seq_slot,
+                                const int* page_table, int max_pages, int page_size, int T, int nh, int nkv,
+                                int hd, int window, float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
+    if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
+    const long long warps = (long long)T * nh;
+    const long long blocks = (warps + AG_WARPS - 1) / AG_WARPS;
+    if (blocks > 2147483647LL) SP_FAIL("attention: too many (token, head) pairs for one launch");
+#define AG_LAUNCH(TQ, TC) \
+    attention_generic_kernel<TQ, TC><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale)
+    if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) AG_LAUNCH(float, __nv_bfloat16);
+    else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_F32) AG_LAUNCH(__nv_bfloat16, float);
+    else SP_FAIL("attention: unsupported dtype codes %d/%d", q_dt, cache_dt);
+#undef AG_LAUNCH
+    SP_CHECK_LAUNCH("attention_generic");
+    return 0;
+}
+
+// ============================================================== silu(gate) * up
+// gu row = [gate(0..I) | up(0..I)]; out row = silu(gate) ⊙ up, silu(z) = z / (1 + e^-z).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t rows, int I) {
+    const size_t n = rows * (size_t)I;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = e / I;
+        const int c = (int)(e % I);
+        const float g = sp_ld(gu, r * 2 * I + c);
+        const float u = sp_ld(gu, r * 2 * I + I + c);
+        sp_st(out, e, (g / (1.0f + expf(-g))) * u);
+    }
+}
+
+SP_API int sp_silu_mul(const void* gu, void* out, int dt, int rows, int I, cudaStream_t stream) {
+    if (rows <= 0 || I <= 0) return 0;
+    const size_t n = (size_t)rows * I;
+    const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    if (dt == SP_DT_F32) silu_mul_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, rows, I);
+    else if (dt == SP_DT_BF16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, rows, I);
+    else SP_FAIL("silu_mul: unsupported dtype code %d", dt);
+    SP_CHECK_LAUNCH("silu_mul");
+    return 0;
+}
+
+// ============================================================== residual add
+__global__ void add_inplace_kernel(float* __restrict__ dst, const void* __restrict__ src, int src_dt, size_t n) {
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x)
+        dst[e] += sp_ld_dt(src, src_dt, e);
+}
+
+SP_API int sp_add_inplace(float* dst, const void* src, int src_dt, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long want = (n + 255) / 256;
+    const int blocks = (int)(want > 148 * 16 ? 148 * 16 : want);
+    add_inplace_kernel<<<blocks, 256, 0, stream>>>(dst, src, src_dt, (size_t)n);
+    SP_CHECK_LAUNCH("add_inplace");
+    return 0;
+}
+
+// ============================================================== argmax
+// One block per row; the lowest index among equal maxima wins, as a serial scan with
+// a strict ``>`` would choose. NaNs never win.
+__global__ void argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int ld) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < V; c += blockDim.x) {
+        const float v = row[c];
+        if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+}
+
+SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0) SP_FAIL("argmax: empty rows");
+    argmax_rows_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, out, V, ld);
+    SP_CHECK_LAUNCH("argmax_rows");
+    return 0;
+}

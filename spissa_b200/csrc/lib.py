@@ -1,0 +1,193 @@
+"""ctypes bindings of the CUDA libraries: tensors in, a launch on the current stream.
+
+Every function here launches a hand-written kernel; there is no CPU or library
+fallback. A tensor that is not on a CUDA device, a library that cannot be built or a
+size that a kernel refuses raises ``KernelError`` with the kernel's own words.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_void_p, c_int, c_float, c_longlong
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dt_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"kernels take float32 and bfloat16 tensors, got {t.dtype}") from None
+
+
+_LIBS: dict = {}
+_LOADED_PATHS: dict = {}
+
+
+def load(module: str) -> ctypes.CDLL:
+    """Build (if needed) and load one kernel library; cached per process."""
+    lib = _LIBS.get(module)
+    if lib is None:
+        path = build.build_module(module)
+        try:
+            lib = ctypes.CDLL(str(path))
+        except OSError as e:
+            raise KernelError(f"cannot load kernel library {path}: {e}") from None
+        getattr(lib, f"sp_{module}_last_error").restype = ctypes.c_char_p
+        _LIBS[module] = lib
+        _LOADED_PATHS[module] = str(path)
+    return lib
+
+
+def loaded_libraries() -> dict:
+    return dict(_LOADED_PATHS)
+
+
+def _check(module: str, rc: int) -> None:
+    if rc != 0:
+        msg = getattr(_LIBS[module], f"sp_{module}_last_error")()
+        raise KernelError(msg.decode() if msg else f"kernel library {module} returned {rc}")
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise KernelError("kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_contig(*ts):
+    for t in ts:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernels take contiguous tensors")
+
+
+# ------------------------------------------------------------------ generic
+def embed_gather(table, ids, out, status=None):
+    """out[t,:] (float32) = table[ids[t],:]; an id outside the table zeroes the row and sets ``status``."""
+    lib = load("generic")
+    T, H = out.shape
+    _need_contig(table, ids, out)
+    _check("generic", lib.sp_embed_gather(
+        c_void_p(_ptr(table)), dt_code(table), c_void_p(_ptr(ids)), c_void_p(_ptr(out)),
+        T, H, table.shape[0], c_void_p(_ptr(status)), c_void_p(_stream())))
+
+
+def rmsnorm(x, weight, out, eps, rows=None):
+    """out[r,:] = x[rows[r] or r,:] / sqrt(mean(x²)+eps) · weight; ``x`` is float32."""
+    lib = load("generic")
+    if x.dtype != torch.float32:
+        raise KernelError("rmsnorm reads the 32-bit residual stream")
+    _need_contig(x, weight, out, rows)
+    n_rows, H = out.shape
+    _check("generic", lib.sp_rmsnorm(
+        c_void_p(_ptr(x)), c_void_p(_ptr(weight)), dt_code(weight), c_void_p(_ptr(out)), dt_code(out),
+        c_void_p(_ptr(rows)), n_rows, H, c_float(eps), c_void_p(_stream())))
+
+
+def gemm_generic(a, w, out, accumulate=False):
+    """out[M,N] (+)= a[M,K] · w[N,K]ᵀ with 32-bit FFMA accumulation, any sizes."""
+    lib = load("generic")
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2 or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"gemm shapes do not match: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm operands must have unit stride in their last dimension")
+    _check("generic", lib.sp_gemm_generic(
+        c_void_p(_ptr(a)), dt_code(a), c_void_p(_ptr(w)), dt_code(w), c_void_p(_ptr(out)), dt_code(out),
+        M, N, K, a.stride(0), w.stride(0), out.stride(0), int(bool(accumulate)), c_void_p(_stream())))
+
+
+def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, write_kv=True):
+    """Rotate q and k of ``qkv`` [T, (nh+2·nkv)·hd], store q to ``q_out`` and k, v into the paged cache.
+
+    ``meta`` carries ``token_seq``, ``positions``, ``seq_slot`` and the group's ``page_table``
+    and ``page_size``. ``rd`` = 0 writes without rotating.
+    """
+    lib = load("generic")
+    T = qkv.shape[0]
+    _need_contig(qkv, q_out)
+    pt = meta.page_table
+    _check("generic", lib.sp_rope_kv_write(
+        c_void_p(_ptr(qkv)), dt_code(qkv), c_void_p(_ptr(q_out)), dt_code(q_out),
+        c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool) if k_pool is not None else 0,
+        c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)),
+        c_void_p(_ptr(pt)), pt.shape[1] if pt is not None else 0, meta.page_size,
+        c_void_p(_ptr(inv_freq)), T, nh, nkv, hd, rd, int(bool(write_kv)), c_void_p(_stream())))
+
+
+def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
+    """Causal attention of every token of the step over its sequence's cached keys."""
+    lib = load("generic")
+    T = q.shape[0]
+    _need_contig(q, out)
+    pt = meta.page_table
+    _check("generic", lib.sp_attention_generic(
+        c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
+        c_void_p(_ptr(out)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
+        c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
+        T, nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_stream())))
+
+
+def silu_mul(gu, out):
+    """out[r,:] = silu(gu[r,:I]) ⊙ gu[r,I:]."""
+    lib = load("generic")
+    rows, I = out.shape
+    _need_contig(gu, out)
+    if gu.dtype != out.dtype or gu.shape[1] != 2 * I:
+        raise KernelError("silu_mul wants gu [rows, 2·I] and out [rows, I] of one dtype")
+    _check("generic", lib.sp_silu_mul(c_void_p(_ptr(gu)), c_void_p(_ptr(out)), dt_code(out), rows, I,
+                                      c_void_p(_stream())))
+
+
+def add_inplace(dst, src):
+    """dst (float32) += src."""
+    lib = load("generic")
+    _need_contig(dst, src)
+    if dst.dtype != torch.float32 or dst.numel() != src.numel():
+        raise KernelError("add_inplace wants a float32 destination and equal sizes")
+    _check("generic", lib.sp_add_inplace(c_void_p(_ptr(dst)), c_void_p(_ptr(src)), dt_code(src),
+                                         c_longlong(dst.numel()), c_void_p(_stream())))
+
+
+def argmax_rows(logits, out):
+    """out[r] = index of the first maximum of logits[r,:] (float32)."""
+    lib = load("generic")
+    rows, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax wants float32 logits with unit column stride")
+    _check("generic", lib.sp_argmax_rows(c_void_p(_ptr(logits)), c_void_p(_ptr(out)), rows, V,
+                                         logits.stride(0), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ sampling
+def sample_scratch_keys(rows: int, V: int) -> int:
+    lib = load("sampling")
+    lib.sp_sample_scratch_keys.restype = c_longlong
+    return int(lib.sp_sample_scratch_keys(rows, V))
+
+
+def sample_rows(logits, temperature, top_k, top_p, u, scratch, out):
+    """Temperature / top-k / top-p sampling of each row with the uniform numbers ``u``."""
+    lib = load("sampling")
+    rows, V = logits.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sampling wants float32 logits with unit column stride")
+    _check("sampling", lib.sp_sample_rows(
+        c_void_p(_ptr(logits)), logits.stride(0), rows, V, c_float(temperature), int(top_k), c_float(top_p),
+        c_void_p(_ptr(u)), c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(out)),
+        c_void_p(_stream())))

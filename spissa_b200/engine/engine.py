@@ -1,0 +1,157 @@
+"""The engine: a model with its weights on one GPU, its cache, and ONE step function.
+
+``Engine.step`` takes, for each sequence of a batch, the next tokens of that sequence
+and the places among them whose logits are wanted; it runs only those tokens, as one
+batch, against what earlier steps left in the cache, and returns the wanted logits.
+The reference's step is ``append_tokens`` for its single sequence
+(crates/spissa-runtime/src/models/llama/session/mod.rs:314-716: guard, embed, layers,
+final norm, last row, head; position offset = cached length, :326).
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass
+from pathlib import Path
+
+import torch
+
+from ..cache import CacheManager
+from ..config import load_config
+from ..parts.base import Runtime
+from ..weights import load_tensors, random_tensors
+from .batch import pack_step
+from .model import Model
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+class StepError(ValueError):
+    """A step was refused before anything ran; the cache is unchanged."""
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: list
+    want: list
+
+
+def _require_gpu(device) -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("spissa_b200 runs on a CUDA device (B200, sm_100a) only; none is visible. "
+                           "There is no CPU path.")
+    return torch.device(device)
+
+
+class Engine:
+    """``Engine.from_folder(dir, dtype=..., max_tokens=...)`` or ``Engine.from_config(cfg, seed=...)``."""
+
+    PAGE_SIZE = 64
+
+    def __init__(self, config, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
+                 device="cuda:0"):
+        self.device = _require_gpu(device)
+        self.config = config
+        self.dtype = _DTYPES[dtype]
+        self.rt = Runtime(self.device, self.dtype, self.PAGE_SIZE)
+        self.model = Model(config.to_spec())
+        with torch.cuda.device(self.device):
+            self.model.bind(tensors, self.rt)
+            n_pages = (max_tokens + self.PAGE_SIZE - 1) // self.PAGE_SIZE
+            if max_seqs is None:
+                max_seqs = max(1, min(n_pages, 256))
+            self.cache = CacheManager(self.model.cache_requests(), max_tokens, max_seqs, self.PAGE_SIZE,
+                                      self.dtype, self.device)
+        self.vocab_size = self.model.spec.vocab_size
+        self.max_position = self.model.spec.max_position
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
+                    device="cuda:0") -> "Engine":
+        dev = _require_gpu(device)
+        config = load_config(folder)
+        model = Model(config.to_spec())
+        tensors = load_tensors(folder, model.weight_specs(), dev, _DTYPES[dtype] == torch.float32)
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device)
+
+    @classmethod
+    def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int = 4096,
+                    max_seqs: int | None = None, device="cuda:0", std: float = 0.02,
+                    norm_std: float = 0.0) -> "Engine":
+        """Random weights drawn on the device (no file); the same generator rule as the folder writer."""
+        dev = _require_gpu(device)
+        model = Model(config.to_spec())
+        tensors = random_tensors(model.weight_specs(), seed, std, norm_std, torch.bfloat16, device=dev)
+        if _DTYPES[dtype] == torch.float32:
+            tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device)
+
+    # ------------------------------------------------------------------ slots
+    def acquire(self) -> int:
+        return self.cache.acquire()
+
+    def release(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    @property
+    def page_size(self) -> int:
+        return self.cache.page_size
+
+    @property
+    def max_seqs(self) -> int:
+        return self.cache.max_seqs
+
+    def free_tokens(self) -> int:
+        return self.cache.free_tokens()
+
+    # ------------------------------------------------------------------ generation
+    def generate(self, prompts, max_new_tokens: int, sampling=None, stop_ids=None, max_batch=None,
+                 on_token=None, return_logits: bool = False):
+        """Generate for a list of token-id prompts; see ``engine.generate.generate``."""
+        from ..sampling import Sampler, SamplingParams
+        from .generate import generate as run
+        if getattr(self, "_sampler", None) is None:
+            self._sampler = Sampler(self.device)
+        if stop_ids is None:
+            stop_ids = self.config.stop_token_ids() if hasattr(self.config, "stop_token_ids") else []
+        with torch.cuda.device(self.device):
+            return run(self, self._sampler, [list(p) for p in prompts], max_new_tokens,
+                       sampling or SamplingParams(), stop_ids, max_batch, on_token, return_logits)
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries) -> torch.Tensor:
+        """Run the given tokens; return logits [number of wanted places, vocab] as float32 on the device.
+
+        ``entries``: ``StepEntry`` objects or (slot, tokens, want) tuples. ``want`` holds indices into
+        that entry's ``tokens``. Rows come back in the order of the entries and of their ``want``.
+        Everything is checked before anything runs; a refused step leaves the cache as it was.
+        """
+        ents = [(e.slot, list(e.tokens), list(e.want)) if isinstance(e, StepEntry)
+                else (e[0], list(e[1]), list(e[2])) for e in entries]
+        if not ents:
+            raise StepError("a step needs at least one sequence")
+        lengths = []
+        for slot, toks, want in ents:
+            if not toks:
+                raise StepError(f"slot {slot}: a sequence of a step brings at least one token")
+            for t in toks:
+                if not (0 <= int(t) < self.vocab_size):
+                    raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {self.vocab_size}")
+            for w in want:
+                if not (0 <= int(w) < len(toks)):
+                    raise StepError(f"slot {slot}: wanted place {w} is outside the {len(toks)} tokens given")
+            lengths.append(self.cache.length(slot))
+        counts = [(slot, len(toks)) for slot, toks, _ in ents]
+        with torch.cuda.device(self.device):
+            tables = self.cache.reserve(counts)
+            batch = pack_step(ents, lengths, tables, self.device)
+            logits = self.model.forward(batch, self.cache)
+        self.cache.commit(counts)
+        self.steps_run += 1
+        return logits

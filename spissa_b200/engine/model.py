@@ -1,0 +1,68 @@
+"""A model put together from a ``ModelSpec``: embedding, layers in schedule order, norm, head.
+
+The model class is the same for every architecture; what differs is the spec that the
+architecture's configuration produces. Mirrors the reference's stateless forward
+(crates/spissa-runtime/src/models/llama/api.rs:292-346): embedding, the blocks, the
+final norm and the head — but only at the rows whose logits are wanted.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.spec import ModelSpec
+from ..parts import registry as part_registry
+from ..parts.base import Runtime
+from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
+
+
+class Model:
+    def __init__(self, spec: ModelSpec):
+        spec.validate()
+        self.spec = spec
+        self.embedding = part_registry.build_part("embedding", spec.embedding)
+        self.layers = []
+        for layer in spec.layers:
+            try:
+                cls = part_registry._REGISTRY["block"][layer.block]
+            except KeyError:
+                raise ValueError(f"no block arrangement registered as {layer.block!r}; "
+                                 f"known: {part_registry.known_parts('block')}") from None
+            self.layers.append(cls(mixer=layer.mixer, ffn=layer.ffn, norms=layer.norms))
+        self.final_norm = part_registry.build_part("norm", spec.final_norm)
+        self.head = part_registry.build_part("head", spec.head)
+        self.rt = None
+
+    # ------------------------------------------------------------------ weights
+    def parts(self) -> list:
+        return [self.embedding] + self.layers + [self.final_norm, self.head]
+
+    def weight_specs(self) -> list:
+        out = []
+        for p in self.parts():
+            out.extend(p.all_weight_specs())
+        return out
+
+    def bind(self, tensors: dict, rt: Runtime) -> None:
+        self.rt = rt
+        for p in self.parts():
+            p.bind_all(tensors, rt)
+
+    # ------------------------------------------------------------------ cache needs
+    def cache_requests(self) -> dict:
+        """cache id -> what the layer that writes it asks for."""
+        out = {}
+        for e in self.spec.schedule:
+            if e.writes_cache:
+                out[e.cache] = self.layers[e.layer].cache_request()
+        return out
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, step, cache) -> torch.Tensor:
+        """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer."""
+        h = self.embedding.forward(step.tokens)
+        for e in self.spec.schedule:
+            self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))
+        if step.n_want == 0:
+            return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=h.device)
+        x = self.final_norm.forward(h, rows=step.want_rows)
+        return self.head.forward(x)

@@ -1,0 +1,84 @@
+"""Causal grouped-query attention over the cache, as a mixer.
+
+q = x·Wqᵀ, k = x·Wkᵀ, v = x·Wvᵀ (no bias); positions are applied to q and k; k and v
+go to the cache at the token's position; each query head h attends, through kv head
+h // (heads / kv_heads), to the visible keys of its own sequence with scores scaled by
+1/√head_dim and a 32-bit softmax; the heads are projected back with Wo.
+crates/spissa-runtime/src/models/llama/generate.rs:274-450,
+crates/spissa-runtime/src/rotary.rs:335-415.
+
+The three projections run as one matrix product over the stacked weight
+[Wq; Wk; Wv]. With ``window`` = w a query at position p sees keys p−w+1 … p.
+A run that shares another run's cache (``cache.writes`` False) computes q only and
+reads the keys the other run stored.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..csrc import lib as K
+from .base import KVCacheRequest, Mixer, WeightSpec
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+@register_part("mixer", "attention")
+class GQAAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position=None, window=None, prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} kv heads")
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.num_kv_heads, self.head_dim = int(num_kv_heads), int(head_dim)
+        self.window = int(window) if window else None
+        self.scale = 1.0 / math.sqrt(self.head_dim)
+        n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.position = build_part("position", position) if position is not None else None
+        self.qkv = self.o = None
+
+    def children(self):
+        return [self.position] if self.position is not None else []
+
+    def weight_specs(self):
+        H, nh, nkv, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        return [WeightSpec(self.names["q"], (nh * hd, H)), WeightSpec(self.names["k"], (nkv * hd, H)),
+                WeightSpec(self.names["v"], (nkv * hd, H)), WeightSpec(self.names["o"], (H, nh * hd))]
+
+    def cache_request(self):
+        return KVCacheRequest(self.num_kv_heads, self.head_dim, self.window)
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        q, k, v = (tensors[self.names[x]] for x in "qkv")
+        if not (q.dtype == k.dtype == v.dtype):
+            raise ValueError(f"{self.prefix}: q, k and v projections must share a storage type")
+        self.qkv = Linear(torch.cat([q, k, v], dim=0))
+        self.q_only = Linear(q)
+        self.o = Linear(tensors[self.names["o"]])
+
+    def forward(self, x, step, cache, residual):
+        nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        T = x.shape[0]
+        writes = cache.writes
+        proj = self.qkv if writes else self.q_only
+        qkv = proj(x, out_dtype=torch.float32)                 # rotation reads unrounded products
+        if not writes:
+            pad = torch.empty(T, (nh + 2 * nkv) * hd, dtype=torch.float32, device=x.device)
+            pad[:, :nh * hd] = qkv
+            qkv = pad
+        rd, inv_freq = 0, None
+        if self.position is not None:
+            if hasattr(self.position, "rotary"):
+                inv_freq, rd = self.position.rotary()
+            else:
+                self.position.apply(qkv, step, nh, nkv, hd)
+        q = torch.empty(T, nh * hd, dtype=self.rt.act_dtype, device=x.device)
+        K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
+        ctx = torch.empty_like(q)
+        K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
+        self.o(ctx, out=residual, accumulate=True)

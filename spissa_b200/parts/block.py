@@ -1,0 +1,30 @@
+"""The pre-norm arrangement of a layer: h += mixer(norm(h)); h += ffn(norm(h)).
+
+crates/spissa-runtime/src/models/llama/generate.rs:190-199 (norm before attention),
+:459 (first residual sum), :465-471 (norm before the feed-forward), :773 (second sum).
+The residual stream ``h`` is 32-bit in every mode; mixer and feed-forward add into it.
+"""
+from __future__ import annotations
+
+from .base import Block
+from .registry import build_part, register_part
+
+
+@register_part("block", "prenorm")
+class PreNormBlock(Block):
+    def __init__(self, mixer, ffn, norms: dict, prefix: str = ""):
+        super().__init__(prefix)
+        self.mixer = build_part("mixer", mixer)
+        self.ffn = build_part("ffn", ffn)
+        self.mixer_norm = build_part("norm", norms["mixer"])
+        self.ffn_norm = build_part("norm", norms["ffn"])
+
+    def children(self):
+        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+
+    def cache_request(self):
+        return self.mixer.cache_request()
+
+    def forward(self, h, step, cache):
+        self.mixer.forward(self.mixer_norm.forward(h), step, cache, h)
+        self.ffn.forward(self.ffn_norm.forward(h), step, h)

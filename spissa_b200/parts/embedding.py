@@ -1,0 +1,58 @@
+"""Token embedding and output head.
+
+Embedding: h[t,:] = E[id_t,:], no scale (crates/spissa-runtime/src/ops.rs:6-30); the
+rows enter the 32-bit residual stream. Head: logits = x · Wᵀ with W either its own
+tensor or the embedding table when the model ties them
+(crates/spissa-runtime/src/models/llama/api.rs:176-181, :336-346); logits are 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import lib as K
+from .base import Part, WeightSpec
+from .linear import Linear
+from .registry import register_part
+
+
+@register_part("embedding", "embedding")
+class TokenEmbedding(Part):
+    def __init__(self, vocab_size: int, hidden_size: int, prefix: str = "", weight_name: str = "weight"):
+        super().__init__(prefix)
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.weight_name = prefix + weight_name
+        self.weight = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.weight_name, (self.vocab_size, self.hidden_size))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.weight = tensors[self.weight_name].contiguous()
+        self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        out = torch.empty(ids.shape[0], self.hidden_size, dtype=torch.float32, device=ids.device)
+        K.embed_gather(self.weight, ids, out, self.status)
+        return out
+
+
+@register_part("head", "lm_head")
+class LMHead(Part):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None = None, prefix: str = "",
+                 weight_name: str = "weight"):
+        super().__init__(prefix)
+        self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
+        self.tied_to = tied_to
+        self.weight_name = prefix + weight_name
+        self.proj = None
+
+    def weight_specs(self):
+        return [] if self.tied_to else [WeightSpec(self.weight_name, (self.vocab_size, self.hidden_size))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.proj = Linear(tensors[self.tied_to or self.weight_name])
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.proj(x, out_dtype=torch.float32)

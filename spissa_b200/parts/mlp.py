@@ -1,0 +1,44 @@
+"""SwiGLU feed-forward: down( silu(x·Wgᵀ) ⊙ (x·Wuᵀ) ), silu(z) = z / (1 + e^{-z}).
+
+crates/spissa-runtime/src/models/llama/generate.rs:590-637 (gate, up), :642-763 (down);
+crates/spissa-runtime/src/ops.rs:192-194 (silu). Gate and up run as one matrix product
+over the stacked weight [Wg; Wu]; the down projection adds into the residual stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..csrc import lib as K
+from .base import FeedForward, WeightSpec
+from .linear import Linear
+from .registry import register_part
+
+
+@register_part("ffn", "swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", names: dict | None = None):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        n = dict(gate="gate_proj.weight", up="up_proj.weight", down="down_proj.weight")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.gate_up = self.down = None
+
+    def weight_specs(self):
+        H, I = self.hidden_size, self.intermediate_size
+        return [WeightSpec(self.names["gate"], (I, H)), WeightSpec(self.names["up"], (I, H)),
+                WeightSpec(self.names["down"], (H, I))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
+        if g.dtype != u.dtype:
+            raise ValueError(f"{self.prefix}: gate and up projections must share a storage type")
+        self.gate_up = Linear(torch.cat([g, u], dim=0))
+        self.down = Linear(tensors[self.names["down"]])
+
+    def forward(self, x, step, residual):
+        gu = self.gate_up(x, out_dtype=self.rt.act_dtype)
+        act = torch.empty(x.shape[0], self.intermediate_size, dtype=self.rt.act_dtype, device=x.device)
+        K.silu_mul(gu, act)
+        self.down(act, out=residual, accumulate=True)

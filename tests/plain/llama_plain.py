@@ -152,6 +152,10 @@ def rope_inv_freq(theta: float, rotary_dim: int, scaling=None, dtype=torch.float
                     s = (n0 / wavelen[i] - lo) / (hi - lo)
                     out[i] = (1 - s) * inv[i] / f + s * inv[i]
             inv = out
+        elif kind == "linear":
+            # positions divided by the factor (crates/spissa-runtime/src/rotary.rs:127-193,
+            # the linear rule of the Gemma path); the same as dividing every frequency
+            inv = inv / scaling["factor"]
         elif kind in (None, "default"):
             pass
         else:

@@ -1,0 +1,297 @@
+"""Measures decoding and prefill of the Llama-3.2-1B shape with random bfloat16 weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
+about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
+events over exactly K decode steps after W warm-up steps; ``e2e`` is the same through the
+Python entry point (``Engine.generate``: host token lists in, host token lists out).
+``prefill`` is one 2,048-token prompt; ``points`` holds decoding at batch 1 and 64;
+``roofline`` compares the decode step with the bytes it has to read.
+Token ids are synthetic (seeded, uniform over the vocabulary), weights are N(0, 0.02).
+Every decode step reads all weights (2.47 GB), far more than the 126 MB L2, so no
+flush is needed between timed iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Llama 3.2 1B shape
+CONFIG_1B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=16, hidden_size=2048,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256,
+    rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072)
+CONTEXT = 4096
+PROMPT = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            d = json.load(fh)
+        out = dict(FALLBACK_PEAKS)
+        for k in out:
+            if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                out[k] = float(d[k])
+        out["source"] = "measured"
+        return out
+    except Exception:
+        return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=sorted(reasons), samples=len(sm))
+
+
+def model_numbers(cfg):
+    H, I, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
+    nh, nkv, hd, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.vocab_size
+    per_layer = H * nh * hd * 2 + H * nkv * hd * 2 + 3 * H * I
+    head = V * H
+    return dict(per_layer=per_layer, head=head, kv_bytes_per_token=2 * nkv * hd * 2 * L,
+                weight_bytes=(per_layer * L + head) * 2)
+
+
+def prefill_flops(cfg, T):
+    n = model_numbers(cfg)
+    gemm = 2.0 * T * n["per_layer"] * cfg.num_hidden_layers
+    attn = 4.0 * (T * (T + 1) / 2) * cfg.head_dim * cfg.num_attention_heads * cfg.num_hidden_layers
+    return gemm + attn + 2.0 * n["head"]
+
+
+def ragged_lengths(batch, seed):
+    rng = random.Random(seed)
+    if batch == 1:
+        return [PROMPT]
+    half = PROMPT // 8
+    lens = [PROMPT + rng.randrange(-half, half + 1) for _ in range(batch)]
+    lens[0] += PROMPT * batch - sum(lens)         # the mean is PROMPT exactly
+    return lens
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "Erik-cpu-create/spissa is a Rust CPU project with no Python package "
+                          "(pip: neither setup.py nor pyproject.toml) and no Rust toolchain is installed"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: this library runs on ONE GPU; --gpus %d is not supported" % args.gpus)
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from spissa_b200 import Engine, LlamaConfig, SamplingParams
+    from spissa_b200.csrc import lib
+
+    peaks = load_peaks()
+    cfg_dict = dict(CONFIG_1B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    if args.layers:
+        cfg_dict["num_hidden_layers"] = args.layers
+    cfg = LlamaConfig.from_dict(cfg_dict)
+    nums = model_numbers(cfg)
+    points = [int(x) for x in args.points.split(",") if x.strip()]
+    max_batch = max([args.batch] + points)
+    torch.cuda.set_device(0)
+    engine = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
+                                max_seqs=max_batch, device="cuda:0")
+    rng = random.Random(1234)
+    V = cfg.vocab_size
+
+    def prompts_for(batch):
+        return [[rng.randrange(V) for _ in range(n)] for n in ragged_lengths(batch, 99 + batch)]
+
+    from spissa_b200.sampling import Sampler
+    sampler = Sampler(engine.device)
+    greedy = SamplingParams()
+
+    def decode_run(batch, steps, warmup):
+        """Device-timed decode steps at ``batch`` after a ragged prefill; returns (ms per step, kv tokens, launches)."""
+        prompts = prompts_for(batch)
+        slots = [engine.acquire() for _ in range(batch)]
+        # prompts go in as chunks so that a step never carries more than 8k tokens
+        fed = [0] * batch
+        while any(f < len(p) for f, p in zip(fed, prompts)):
+            ents, room = [], 8192
+            for b in range(batch):
+                n = min(len(prompts[b]) - fed[b], room)
+                if n > 0:
+                    ents.append((slots[b], prompts[b][fed[b]:fed[b] + n], []))
+                    fed[b] += n
+                    room -= n
+                if room == 0:
+                    break
+            engine.step(ents)
+        toks = [rng.randrange(V) for _ in range(batch)]
+
+        def one():
+            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)])
+            return sampler.sample(logits, greedy, list(range(batch)), 0)
+
+        for _ in range(warmup):
+            one()
+        torch.cuda.synchronize()
+        kv_tokens = sum(engine.length(s) for s in slots) + batch * steps // 2
+        l0 = lib.launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        launches = lib.launches - l0
+        for s in slots:
+            engine.release(s)
+        return ms, kv_tokens, launches
+
+    # ---------------------------------------------------------------- decode, device timed
+    clocks = ClockSampler()
+    clocks.start()
+    ms_step, kv_tokens, launches = decode_run(args.batch, args.steps, args.warmup)
+    clock_info = clocks.stop()
+    value = args.batch * 1000.0 / ms_step
+    step_bytes = nums["weight_bytes"] + kv_tokens * nums["kv_bytes_per_token"]
+    achieved = step_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---------------------------------------------------------------- end to end through Engine.generate
+    e2e_prompts = prompts_for(args.batch)
+    e2e_new = max(8, min(args.steps, 64))
+    engine.generate([p[:64] for p in e2e_prompts], 4, greedy, stop_ids=[])          # warm the path
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    results, metrics = engine.generate(e2e_prompts, e2e_new, greedy, stop_ids=[])
+    torch.cuda.synchronize()
+    e2e = dict(value=round(metrics.decode_tok_s, 2), unit="tokens/s",
+               h2d_bytes_per_step=4 * args.batch * 8 + 4 * args.batch * (CONTEXT // engine.page_size),
+               d2h_bytes_per_step=4 * args.batch, new_tokens=e2e_new,
+               wall_s=round(time.perf_counter() - t0, 3))
+
+    # ---------------------------------------------------------------- prefill of 2,048 tokens
+    prompt = [rng.randrange(V) for _ in range(PROMPT)]
+
+    def prefill_once():
+        s = engine.acquire()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits = engine.step([(s, prompt, [PROMPT - 1])])
+        sampler.sample(logits, greedy, [0], 0)
+        e1.record()
+        torch.cuda.synchronize()
+        engine.release(s)
+        return e0.elapsed_time(e1)
+
+    for _ in range(3):
+        prefill_once()
+    pre_ms = sorted(prefill_once() for _ in range(5))[2]
+    flops = prefill_flops(cfg, PROMPT)
+    prefill = dict(value=round(PROMPT / (pre_ms * 1e-3), 1), tokens=PROMPT, ms=round(pre_ms, 3),
+                   frac=round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4))
+
+    # ---------------------------------------------------------------- other batch sizes
+    pts = {}
+    for b in points:
+        ms_b, _, _ = decode_run(b, max(8, args.steps // 2), 3)
+        pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
+
+    line = {
+        "metric": "decode tokens/s (Llama-3.2-1B shape, batch %d, ~%d-token prompts)" % (args.batch, PROMPT),
+        "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random N(0,0.02) weights", "impl": "ours",
+        "config": {
+            "model": "llama-3.2-1b-shape", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len_mean": PROMPT, "page_size": engine.page_size,
+            "parallelism": "single-gpu", "l2": "inputs larger than L2 (2.47 GB of weights per step)",
+            "peaks": peaks["source"],
+        },
+        "clocks": clock_info,
+        "e2e": e2e,
+        "gpu_launches": launches,
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": pts,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

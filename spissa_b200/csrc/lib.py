@@ -65,7 +65,12 @@ def _ptr(t):
     return t.data_ptr()
 
 
+launches = 0          # kernels launched through these bindings since import (bench.py reports the difference)
+
+
 def _stream() -> int:
+    global launches
+    launches += 1
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -62,4 +62,4 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor) -> float:
 # Allowed distance from the float64 plain implementation, as a fraction of the largest
 # logit. float32: products of a few hundred terms accumulate about 1e-6. bfloat16:
 # activations are rounded to 8 bits of mantissa (2^-9 relative) between kernels.
-TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+TOL = {"float32": 5e-6, "bfloat16": 1e-2}

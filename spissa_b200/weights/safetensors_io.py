@@ -123,5 +123,6 @@ def write_safetensors(path, tensors: dict, metadata: dict | None = None) -> None
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
             if t.numel():
-                fh.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool
-                         else t.to(torch.uint8).numpy().tobytes())
+                flat = t.reshape(-1)
+                flat = flat.to(torch.uint8) if t.dtype == torch.bool else flat.view(torch.uint8)
+                fh.write(flat.numpy().tobytes())

@@ -1,0 +1,199 @@
+"""Generation through the Python entry point, long decoding, first tokens, slot reuse, sampling in batches."""
+import json
+
+import pytest
+import torch
+
+import tiny
+import traces
+from plain import llama_plain as P
+from spissa_b200 import Engine, SamplingParams
+from spissa_b200.sampling import draw_seed
+from spissa_b200.weights import write_safetensors
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name, (cfg, init) in tiny.TINIES.items():
+        f = tmp_path_factory.mktemp(f"gen_{name}")
+        tiny.make_folder(cfg, init, f, std=0.06)           # wider weights: logits well apart
+        out[name] = (str(f),) + P.read_model_folder(f)
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_matches_plain_in_float32(folders, name):
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    lens = [5, 9, 13] if name == "A" else [1, 7, 40, 100]
+    prompts = [tiny.random_prompt(V, n, 7 * n) for n in lens]
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 8)
+    results, metrics = engine.generate(prompts, 8, SamplingParams(), stop_ids=[])
+    for p, r in zip(prompts, results):
+        assert r.tokens == P.generate_greedy(pcfg, w, p, 8), f"prompt of {len(p)}"
+        assert r.finish_reason == "length"
+    assert metrics.generated_tokens == 8 * len(prompts) and metrics.batches == 1
+    engine.cache.check()
+    assert engine.cache.slots.held_count == 0 and engine.free_tokens() == 64 * 8
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_in_bfloat16_stays_on_plain_near_maxima(folders, name):
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    prompts = [tiny.random_prompt(V, n, 3 * n + 1) for n in (4, 30, 66)]
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 6)
+    results, _ = engine.generate(prompts, 12, SamplingParams(), stop_ids=[])
+    for p, r in zip(prompts, results):
+        ids = list(p)
+        for tok in r.tokens:                               # teacher-forced along the engine's own tokens
+            row = P.model_logits(pcfg, w, ids, torch.float64)[-1]
+            assert float(row.max() - row[tok]) <= tiny.TOL["bfloat16"] * float(row.abs().max()) * 2
+            ids.append(tok)
+
+
+def test_stop_token_ends_a_request_and_frees_its_slot(folders):
+    folder, pcfg, w = folders["A"]
+    prompts = [tiny.random_prompt(256, n, n) for n in (6, 11)]
+    free_run = [P.generate_greedy(pcfg, w, p, 10) for p in prompts]
+    stop = free_run[0][3]
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 2)
+    results, _ = engine.generate(prompts, 10, SamplingParams(), stop_ids=[stop])
+    for r, free in zip(results, free_run):
+        want = free[:free.index(stop) + 1] if stop in free else free
+        assert r.tokens == want
+        assert r.finish_reason == ("stop" if stop in free else "length")
+    assert engine.cache.slots.held_count == 0
+    engine.cache.check()
+
+
+def test_more_requests_than_slots_run_as_batches_one_after_another(folders):
+    folder, pcfg, w = folders["B"]
+    prompts = [tiny.random_prompt(384, n, 11 * n) for n in (3, 70, 20, 1, 65, 9, 33)]
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 4, max_seqs=3)
+    results, metrics = engine.generate(prompts, 5, SamplingParams(), stop_ids=[])
+    assert metrics.batches >= 3
+    for p, r in zip(prompts, results):
+        assert r.tokens == P.generate_greedy(pcfg, w, p, 5)
+    engine.cache.check()
+
+
+def test_temperature_sampling_follows_plain_and_ignores_the_batch(folders):
+    """Tiny B, prompts of 1/7/40/100 tokens, 16 steps at temperature 0.8 with a fixed seed."""
+    folder, pcfg, w = folders["B"]
+    prompts = [tiny.random_prompt(384, n, 5 * n + 2) for n in (1, 7, 40, 100)]
+    params = SamplingParams(temperature=0.8, top_k=0, top_p=0.95, seed=4242)
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 8)
+    together, _ = engine.generate(prompts, 16, params, stop_ids=[])
+    for i, p in enumerate(prompts):
+        ids = list(p)
+        for step, tok in enumerate(together[i].tokens):
+            row = P.model_logits(pcfg, w, ids, torch.float32)[-1]
+            want = P.sample_top_k_top_p(row.tolist(), 0.8, 0, 0.95, draw_seed(4242, i, step))
+            if tok != want:                                  # only a draw on a boundary may differ, by one rank
+                probs = torch.softmax(row.double() / 0.8, 0)
+                order = sorted(range(384), key=lambda j: (-float(probs[j]), j))
+                assert abs(order.index(tok) - order.index(want)) <= 1
+            ids.append(tok)
+    # the same requests in other company draw the same tokens
+    pairs, _ = engine.generate(prompts, 16, params, stop_ids=[], max_batch=2)
+    assert [r.tokens for r in pairs] == [r.tokens for r in together]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_crosses_pages(folders, dtype, tmp_path):
+    folder, pcfg, w = folders["B"]
+    toks = tiny.random_prompt(384, 300, 1)
+    steps = traces.tail_one_by_one({"x": toks}, tail=297)
+    traces.run_in_process(folder, dtype, steps, str(tmp_path))
+    got = traces.collect(steps, str(tmp_path), 384)
+    ref = P.model_logits(pcfg, w, toks, torch.float64)
+    scale = float(ref.abs().max())
+    for (rid, pos), row in got.items():
+        err = float((row.double() - ref[pos]).abs().max()) / scale
+        assert err <= tiny.TOL[dtype], f"position {pos}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_first_tokens_one_by_one(folders, name, dtype, tmp_path):
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    reqs = {"a": tiny.random_prompt(V, 6, 1), "b": tiny.random_prompt(V, 1, 2), "c": tiny.random_prompt(V, 3, 3)}
+    steps = traces.ragged_batches(reqs, 3, {"a": 5, "b": 0, "c": 2})           # every request starts with ONE token
+    traces.run_in_process(folder, dtype, steps, str(tmp_path))
+    got = traces.collect(steps, str(tmp_path), V)
+    for rid, toks in reqs.items():
+        ref = P.model_logits(pcfg, w, toks, torch.float64)
+        for pos in range(len(toks)):
+            err = float((got[(rid, pos)].double() - ref[pos]).abs().max()) / float(ref.abs().max())
+            assert err <= tiny.TOL[dtype], f"{rid} position {pos}: {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_reused_pages_hold_nothing_of_their_last_owner(folders, dtype):
+    folder, pcfg, w = folders["A"]
+    engine = Engine.from_folder(folder, dtype=dtype, max_tokens=128, max_seqs=1)
+    first = tiny.random_prompt(256, 128, 9)
+    s = engine.acquire()
+    engine.step([(s, first, [])])
+    # poison what the first owner left behind: a reader of stale rows would see it
+    for g in engine.cache.kv_groups.values():
+        g.k.fill_(1e4)
+        g.v.fill_(-1e4)
+    engine.release(s)
+    second = tiny.random_prompt(256, 70, 10)
+    s2 = engine.acquire()
+    assert s2 == s
+    got = engine.step([(s2, second[:69], list(range(69)))])
+    got = torch.cat([got, engine.step([(s2, second[69:], [0])])], 0).cpu()
+    ref = P.model_logits(pcfg, w, second, torch.float64)
+    assert float((got.double() - ref).abs().max()) / float(ref.abs().max()) <= tiny.TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_peaky_attention_shows_misplaced_keys(tmp_path, dtype):
+    """Query and key projections scaled up: each query looks at few keys, so one wrong key shows."""
+    folder = tmp_path / "peaky"
+    tiny.make_folder(tiny.TINY_B, tiny.TINY_B_INIT, folder, std=0.05)
+    pcfg, w = P.read_model_folder(folder)
+    for k in list(w):
+        if "q_proj" in k or "k_proj" in k:
+            w[k] = (w[k].float() * 5).bfloat16()
+    write_safetensors(folder / "model.safetensors", w)
+    reqs = {f"r{i}": tiny.random_prompt(384, n, n) for i, n in enumerate([150, 40, 257])}
+    ref = {r: P.model_logits(pcfg, w, t, torch.float64) for r, t in reqs.items()}
+    scale = max(float(v.abs().max()) for v in ref.values())
+    # sharp softmaxes magnify rounding; the plain implementation in 32-bit shows by how much
+    noise = max(float((P.model_logits(pcfg, w, t, torch.float32).double() - ref[r]).abs().max())
+                for r, t in reqs.items()) / scale
+    # (5e-7 is that noise for the same model with ordinary weights); every budget grows with it
+    allowed = tiny.TOL[dtype] * max(1.0, noise / 5e-7)
+    for cut, steps in (("whole", traces.whole(reqs)), ("tail", traces.tail_one_by_one(reqs, 32)),
+                       ("ragged", traces.ragged_batches(reqs, 3, {"r0": 40, "r1": 3, "r2": 100}))):
+        out = tmp_path / cut
+        traces.run_in_process(str(folder), dtype, steps, str(out))
+        got = traces.collect(steps, str(out), 384)
+        worst = max(float((row.double() - ref[rid][pos]).abs().max()) for (rid, pos), row in got.items()) / scale
+        assert worst <= allowed, f"{cut}: {worst:.3e} (allowed {allowed:.3e}, 32-bit noise {noise:.3e})"
+
+
+def test_step_refusals_leave_the_cache_alone(folders):
+    from spissa_b200 import StepError
+    from spissa_b200.cache import CacheFull
+    folder, _, _ = folders["A"]
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=128, max_seqs=2)
+    s = engine.acquire()
+    engine.step([(s, [1, 2, 3], [2])])
+    for bad in ([(s, [], [])], [(s, [256], [0])], [(s, [-1], [0])], [(s, [1], [1])], []):
+        with pytest.raises(StepError):
+            engine.step(bad)
+    with pytest.raises(CacheFull):
+        engine.step([(s, [1] * 126, [])])
+    assert engine.length(s) == 3
+    engine.cache.check()
+    out = engine.step([(s, [4], [0])])
+    assert out.shape == (1, 256) and engine.length(s) == 4

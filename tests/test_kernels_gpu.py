@@ -1,0 +1,263 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's tiny models."""
+import math
+import random
+
+import pytest
+import torch
+
+import kernel_harness as KH
+from plain import llama_plain as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from spissa_b200.csrc import lib
+    return lib
+
+
+def close(got, ref, tol, what=""):
+    err = float((got.double().cpu() - ref.double().cpu()).abs().max())
+    scale = float(ref.double().abs().max()) or 1.0
+    assert err <= tol * scale, f"{what}: error {err:.3e} against scale {scale:.3e} (allowed {tol:.1e} of it)"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(K, dtype):
+    torch.manual_seed(0)
+    V, H = 333, 72
+    table = torch.randn(V, H).to(dtype)
+    ids = torch.tensor([0, 332, 17, 17, 200], dtype=torch.int32)
+    out = torch.empty(5, H, dtype=torch.float32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K.embed_gather(table.to(DEV), ids.to(DEV), out, status)
+    assert torch.equal(out.cpu(), P.embedding(table.float(), ids.tolist()))
+    assert int(status.item()) == 0
+    bad = torch.tensor([1, 333], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(2, H, dtype=torch.float32, device=DEV)
+    K.embed_gather(table.to(DEV), bad, out2, status)
+    assert int(status.item()) == 1 and float(out2[1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("H", [72, 2048, 4100])
+@pytest.mark.parametrize("wdt,odt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.float32, torch.bfloat16)])
+def test_rmsnorm(K, H, wdt, odt):
+    torch.manual_seed(1)
+    x = torch.randn(9, H) * 3
+    w = (1 + 0.1 * torch.randn(H)).to(wdt)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32)
+    ref = P.rms_norm(x.double(), w.double(), 1e-6)
+    out = torch.empty(9, H, dtype=odt, device=DEV)
+    K.rmsnorm(x.to(DEV), w.to(DEV), out, 1e-6)
+    close(out, ref, 2e-6 if odt == torch.float32 else 4e-3, "all rows")
+    out = torch.empty(4, H, dtype=odt, device=DEV)
+    K.rmsnorm(x.to(DEV), w.to(DEV), out, 1e-6, rows.to(DEV))
+    close(out, ref[rows.long()], 2e-6 if odt == torch.float32 else 4e-3, "gathered rows")
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (33, 130, 72), (100, 64, 200), (5, 333, 96), (64, 64, 16)])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)])
+def test_gemm_generic(K, M, N, K_, adt, wdt):
+    torch.manual_seed(2)
+    a = torch.randn(M, K_).to(adt)
+    w = torch.randn(N, K_).to(wdt)
+    ref = a.double() @ w.double().t()
+    out = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    K.gemm_generic(a.to(DEV), w.to(DEV), out)
+    close(out, ref, 2e-6, "float32 out")
+    base = torch.randn(M, N)
+    acc = base.clone().to(DEV)
+    K.gemm_generic(a.to(DEV), w.to(DEV), acc, accumulate=True)
+    close(acc, ref + base.double(), 2e-6, "accumulate")
+    outb = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    K.gemm_generic(a.to(DEV), w.to(DEV), outb)
+    close(outb, ref, 4e-3, "bfloat16 out")
+
+
+def test_gemm_row_does_not_depend_on_batch(K):
+    torch.manual_seed(3)
+    a = torch.randn(70, 200, device=DEV)
+    w = torch.randn(90, 200, device=DEV)
+    full = torch.empty(70, 90, device=DEV)
+    K.gemm_generic(a, w, full)
+    one = torch.empty(1, 90, device=DEV)
+    K.gemm_generic(a[37:38].contiguous(), w, one)
+    assert torch.equal(one[0], full[37])
+
+
+def rope_case(K, nh, nkv, hd, rd, theta, dtype, new_counts, before, seed):
+    torch.manual_seed(seed)
+    T = sum(new_counts)
+    meta = KH.paged_meta(new_counts, before, DEV, seed)
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd)
+    inv = P.rope_inv_freq(theta, rd) if rd else None
+    q_out = torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    k_pool = torch.zeros(meta.n_pages, nkv, KH.PAGE, hd, dtype=dtype, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    K.rope_kv_write(qkv.to(DEV), q_out, k_pool, v_pool, meta, inv.to(DEV) if rd else None, nh, nkv, hd, rd)
+    pos = meta.positions.cpu()
+    q = qkv[:, :nh * hd].reshape(T, nh, hd)
+    k = qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd)
+    v = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    if rd:
+        q, k = P.apply_rope(q, pos, inv), P.apply_rope(k, pos, inv)
+    tol = 2e-6 if dtype == torch.float32 else 4e-3
+    close(q_out, q.reshape(T, -1), tol, "q")
+    seq = meta.token_seq.cpu()
+    for t in range(T):
+        b, p = int(seq[t]), int(pos[t])
+        pg, off = meta.rows[b][p // KH.PAGE], p % KH.PAGE
+        close(k_pool[pg, :, off, :], k[t], tol, f"k of token {t}")
+        close(v_pool[pg, :, off, :], v[t], tol, f"v of token {t}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd,rd", [(4, 2, 16, 16), (3, 1, 32, 32), (3, 3, 48, 24), (8, 2, 128, 128),
+                                          (2, 2, 64, 0)])
+def test_rope_kv_write(K, dtype, nh, nkv, hd, rd):
+    rope_case(K, nh, nkv, hd, rd, 10000.0, dtype, [5, 1, 70], [0, 130, 60], seed=nh * 100 + hd)
+
+
+def attention_case(K, fn, nh, nkv, hd, dtype, new_counts, before, window, seed, tol):
+    torch.manual_seed(seed)
+    B = len(new_counts)
+    meta = KH.paged_meta(new_counts, before, DEV, seed)
+    qs = [torch.randn(t, nh, hd) for t in meta.total_len]
+    ks = [torch.randn(t, nkv, hd) for t in meta.total_len]
+    vs = [torch.randn(t, nkv, hd) for t in meta.total_len]
+    if dtype == torch.bfloat16:
+        qs, ks, vs = ([x.bfloat16().float() for x in xs] for xs in (qs, ks, vs))
+    k_pool, v_pool = KH.fill_cache(meta, ks, vs, nkv, hd, dtype, DEV)
+    q = torch.cat([qb[-n:] for qb, n in zip(qs, new_counts)], 0).reshape(-1, nh * hd).to(dtype).to(DEV)
+    out = torch.empty_like(q)
+    fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, 1.0 / math.sqrt(hd))
+    ref = KH.plain_attention_rows(qs, ks, vs, new_counts, window)
+    close(out, ref, tol, f"attention nh={nh} nkv={nkv} hd={hd} window={window}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("nh,nkv,hd", [(4, 2, 16), (3, 1, 32), (3, 3, 48), (8, 2, 64), (4, 1, 128), (2, 1, 256)])
+def test_attention_generic_prefill_and_decode(K, dtype, nh, nkv, hd):
+    tol = 3e-6 if dtype == torch.float32 else 6e-3
+    attention_case(K, K.attention_generic, nh, nkv, hd, dtype, [7, 1, 65, 33], [0, 199, 64, 31], None, hd, tol)
+    attention_case(K, K.attention_generic, nh, nkv, hd, dtype, [1, 1, 1], [0, 63, 300], None, hd + 1, tol)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_generic_window(K, window):
+    attention_case(K, K.attention_generic, 4, 2, 32, torch.float32, [40, 1, 130], [0, 250, 20], window, window, 3e-6)
+
+
+def needle_case(K, fn, dtype, length, needle, window=None, hd=64, nh=4, nkv=2):
+    """One key among ``length`` scores far above the rest: the output must be that key's value."""
+    torch.manual_seed(length + needle)
+    meta = KH.paged_meta([1], [length - 1], DEV, seed=needle)
+    k = torch.randn(length, nkv, hd) * 0.1
+    v = torch.randn(length, nkv, hd)
+    q = torch.randn(1, nh, hd) * 0.1
+    k[needle] = 0
+    k[needle, :, 0] = 40.0
+    q[0, :, 0] = 40.0
+    if dtype == torch.bfloat16:
+        q, k, v = q.bfloat16().float(), k.bfloat16().float(), v.bfloat16().float()
+    k_pool, v_pool = KH.fill_cache(meta, [k], [v], nkv, hd, dtype, DEV)
+    qd = q.reshape(1, nh * hd).to(dtype).to(DEV)
+    out = torch.empty_like(qd)
+    fn(qd, k_pool, v_pool, out, meta, nh, nkv, hd, window, 1.0 / math.sqrt(hd))
+    return out.float().cpu().reshape(nh, hd), v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("length,needle", [(700, 3), (700, 640), (129, 64), (64, 63), (1000, 0)])
+def test_attention_generic_finds_a_far_key(K, dtype, length, needle):
+    out, v = needle_case(K, K.attention_generic, dtype, length, needle)
+    for h in range(4):
+        assert torch.allclose(out[h], v[needle, h // 2], atol=2e-2), f"head {h} missed key {needle} of {length}"
+
+
+def test_attention_generic_window_edge(K):
+    # the key at p-window+1 is seen, the key at p-window is not
+    length, window = 300, 100
+    p = length - 1
+    out, v = needle_case(K, K.attention_generic, torch.float32, length, p - window + 1, window)
+    assert torch.allclose(out[0], v[p - window + 1, 0], atol=2e-2)
+    out, v = needle_case(K, K.attention_generic, torch.float32, length, p - window, window)
+    assert not torch.allclose(out[0], v[p - window, 0], atol=0.5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_silu_mul(K, dtype):
+    torch.manual_seed(4)
+    gu = (torch.randn(7, 2 * 136) * 3).to(dtype)
+    out = torch.empty(7, 136, dtype=dtype, device=DEV)
+    K.silu_mul(gu.to(DEV), out)
+    ref = P.silu(gu[:, :136].double()) * gu[:, 136:].double()
+    close(out, ref, 2e-6 if dtype == torch.float32 else 4e-3)
+
+
+def test_add_inplace(K):
+    torch.manual_seed(5)
+    a, b = torch.randn(1000), torch.randn(1000).bfloat16()
+    d = a.clone().to(DEV)
+    K.add_inplace(d, b.to(DEV))
+    assert torch.equal(d.cpu(), a + b.float())
+
+
+def test_argmax_first_maximum_wins(K):
+    torch.manual_seed(6)
+    logits = torch.randn(5, 128256)
+    logits[1, 777] = logits[1, 90000] = 50.0
+    logits[2, :] = 0.0
+    logits[3, 128255] = 60.0
+    logits[4, 5] = float("nan")
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    K.argmax_rows(logits.to(DEV), out)
+    want = [P.sample_argmax(logits[0].tolist()), 777, 0, 128255, P.sample_argmax(logits[4].tolist())]
+    assert out.tolist() == want
+
+
+def walk64(logits_row, temp, k, p, u):
+    """The reference's walk in float64: (ordering, running mass, kept count, target)."""
+    probs = torch.softmax(logits_row.double() / temp, 0)
+    order = sorted(range(len(probs)), key=lambda i: (-float(probs[i]), i))
+    kept = min(k, len(order)) if k > 0 else len(order)
+    cum = torch.cumsum(probs[order[:kept]], 0)
+    reach = (cum >= p).nonzero()
+    if len(reach):
+        kept = int(reach[0]) + 1
+    edge = float(probs[order[kept - 1]])            # the top-p cut compares a rounded sum: one token either way
+    return order, cum, kept, u * float(cum[kept - 1]), edge
+
+
+@pytest.mark.parametrize("V", [7, 333, 4096, 5000, 128256])
+def test_sampling_follows_the_reference_walk(K, V):
+    torch.manual_seed(V)
+    rows = 6
+    logits = torch.randn(rows, V) * 2.5
+    logits[0, :] = 0.0                                         # all equal: order by index
+    cases = [(0.8, 0, 0.95), (1.0, 1, 1.0), (1.3, 5, 0.5), (0.7, 0, 1.0), (1.0, 50, 0.9)]
+    scratch = torch.empty(K.sample_scratch_keys(rows, V), dtype=torch.int64, device=DEV)
+    for temp, k, p in cases:
+        for seed in ((1, 2, 3) if V <= 6000 else (1,)):
+            us = [P.seeded_unit_f32(seed * 100 + r) for r in range(rows)]
+            out = torch.empty(rows, dtype=torch.int32, device=DEV)
+            K.sample_rows(logits.to(DEV), temp, k, p, torch.tensor(us, device=DEV), scratch, out)
+            got = out.tolist()
+            for r in range(rows if V <= 6000 else 3):
+                # in float64 the chosen token's stretch of the running mass holds the draw, up to the
+                # rounding of 32-bit sums (1e-5 of the kept mass)
+                order, cum, kept, target, edge = walk64(logits[r], temp, k, p, us[r])
+                rank = order.index(got[r])
+                assert rank <= kept, (V, temp, k, p, r, "outside the kept set")
+                lo = float(cum[rank - 1]) if rank > 0 else 0.0
+                hi = float(cum[min(rank, kept - 1)])
+                slack = 1e-5 * float(cum[kept - 1]) + (edge if p < 1.0 else 0.0)
+                assert lo - slack <= target <= hi + slack, (V, temp, k, p, r, got[r], lo, target, hi)
+                if V <= 5000 and r > 0:
+                    # and it is the serial 32-bit walk's choice or its neighbour
+                    want = P.sample_top_k_top_p(logits[r].tolist(), temp, k, p, seed * 100 + r)
+                    assert abs(rank - order.index(want)) <= 1, (V, temp, k, p, r, got[r], want)

@@ -29,6 +29,7 @@ NVCC_FLAGS = [
 MODULES = {
     "generic": "generic_kernels.cu",
     "sampling": "sampling_kernels.cu",
+    "tc_gemm": "tc_gemm.cu",
 }
 
 

@@ -196,3 +196,64 @@ def sample_rows(logits, temperature, top_k, top_p, u, scratch, out):
         c_void_p(_ptr(logits)), logits.stride(0), rows, V, c_float(temperature), int(top_k), c_float(top_p),
         c_void_p(_ptr(u)), c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(out)),
         c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ tensor-core matrix product
+_STATUS: dict = {}
+
+STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
+               102: "the MMA issuer waited too long for a loaded pipeline stage",
+               103: "the epilogue waited too long for the accumulator"}
+
+
+def status_word(device) -> torch.Tensor:
+    """The int32 word in which kernels with bounded waits record that a wait ran out (0 = all well)."""
+    key = torch.device(device).index or 0
+    if key not in _STATUS:
+        _STATUS[key] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", key))
+    return _STATUS[key]
+
+
+def check_status(device) -> None:
+    """Synchronises and raises ``KernelError`` if a kernel gave up a wait since the last check."""
+    key = torch.device(device).index or 0
+    if key in _STATUS:
+        code = int(_STATUS[key].item())
+        if code:
+            _STATUS[key].zero_()
+            raise KernelError(f"a kernel gave up a bounded wait (code {code}: {STATUS_TEXT.get(code, 'unknown')})")
+
+
+def tc_gemm_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether ``tc_gemm`` takes these operands (bfloat16, K-major, rows a multiple of 16 bytes)."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+        return False
+    if a.stride(1) != 1 or w.stride(1) != 1 or a.shape[1] != w.shape[1]:
+        return False
+    K = a.shape[1]
+    return (K % 8 == 0 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+TC_STORE, TC_ACCUMULATE, TC_SILU_MUL = 0, 1, 2
+
+
+def tc_gemm(a, w, out, mode=TC_STORE, bn=128):
+    """out = a · wᵀ on the tcgen05 tensor cores (bfloat16 operands, float32 accumulation).
+
+    ``mode`` TC_STORE writes ``out`` (bfloat16 or float32), TC_ACCUMULATE adds into a float32 ``out``,
+    TC_SILU_MUL takes a weight whose rows interleave gate and up in blocks of ``bn``/2 and writes
+    silu(gate)·up into ``out`` [M, N/2].
+    """
+    lib = load("tc_gemm")
+    M, K = a.shape
+    N = w.shape[0]
+    want_cols = N // 2 if mode == TC_SILU_MUL else N
+    if out.shape[0] != M or out.shape[1] != want_cols or out.stride(1) != 1:
+        raise KernelError(f"tc_gemm: out {tuple(out.shape)} does not fit a {tuple(a.shape)}, w {tuple(w.shape)}")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("tc_gemm takes bfloat16 operands")
+    _check("tc_gemm", lib.sp_tc_gemm(
+        c_void_p(_ptr(a)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K,
+        a.stride(0), w.stride(0), out.stride(0), int(mode), int(bn), c_void_p(_ptr(status_word(a.device))),
+        c_void_p(_stream())))

@@ -1,0 +1,364 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: C[M,N] = A[M,K] · W[N,K]ᵀ.
+//
+// Both operands are K-major (a row of A or W is contiguous in K), as activations and the
+// checkpoint's [out, in] weights are (crates/spissa-runtime/src/ops.rs:62-105 states the
+// layout; the reference computes it with scalar/NEON dot products,
+// crates/spissa-runtime/src/streaming/kernels_raw16.rs:442-530).
+//
+// One CTA computes one 128 x BN tile of C:
+//   warp 0   one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
+//            128x64 tile of A and a BNx64 tile of W per pipeline stage;
+//   warp 1   allocates tensor memory and one thread issues tcgen05.mma (M=128, N=BN, K=16,
+//            four per stage) with the accumulator in tensor memory; tcgen05.commit hands
+//            each stage back to the loader and, at the end, the accumulator to
+//   warps 2-5 which read it with tcgen05.ld (each warp its own 32 lanes) and store it:
+//            plain, added into a float32 C, or as silu(gate)·up of an interleaved gate/up weight.
+// Every wait on an mbarrier is bounded by a wall-clock limit; when it runs out the kernel
+// records a code in ``status``, every role falls through to the common exit, and tensor
+// memory is freed. No load uses cluster multicast.
+#include "common.cuh"
+#include <cuda.h>
+
+SP_API const char* sp_tc_gemm_last_error() { return sp_error_text; }
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s
+
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: false (and a code in *status) when the phase did not complete in time.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (status) atomicCAS(status, 0, code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+
+// 32 lanes x 32 consecutive 32-bit columns: thread i of the warp gets lane (base lane + i)
+__device__ __forceinline__ void tc_ld_32x32(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (SBO), LBO 1 (unused by swizzled K-major), version 1.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// kind::f16 instruction descriptor: D float32, A and B bfloat16, both K-major, M x N
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;      // + slack to align to 1024
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ uint32_t tmem_slot;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101)) break;
+                const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
+                const uint32_t b_dst = a_dst + L::A_BYTES;
+                mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
+                tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
+                tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % STAGES;
+                const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
+                ok = mbar_wait(smem_u32(&bar_full[s]), phase, status, 102);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_src = smem_base + s * L::STAGE_BYTES;
+                const uint64_t da = umma_desc_sw128(a_src);
+                const uint64_t db = umma_desc_sw128(a_src + L::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    // 16 bf16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units
+                    tc_mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&bar_empty[s]));
+            }
+            tc_commit(smem_u32(&bar_acc));          // also after a failed wait: the epilogue must not hang
+        }
+    } else {
+        const int q = warp & 3;                      // this warp may touch tensor-memory lanes 32q .. 32q+31
+        const bool ok = mbar_wait(smem_u32(&bar_acc), 0, status, 103);
+        tc_fence_after();
+        const int row = m0 + q * 32 + lane;
+        const bool failed = !ok || (status && *(volatile int*)status != 0);
+        if (!failed) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (mode == MODE_SILU_MUL && c0 >= BN / 2) break;        // uniform over the warp
+                uint32_t r[32];
+                tc_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                if (mode == MODE_SILU_MUL) {
+                    // tile columns [0, BN/2) are gate rows, [BN/2, BN) the up rows of the same outputs
+                    uint32_t u[32];
+                    tc_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + BN / 2), u);
+                    tc_ld_wait();
+                    if (row >= M) continue;
+                    const int out_n = N / 2;
+                    const int col0 = (n0 / 2) + c0;
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int col = col0 + j;
+                        if (col < out_n) {
+                            const float g = __uint_as_float(r[j]);
+                            const float v = (g / (1.0f + expf(-g))) * __uint_as_float(u[j]);
+                            sp_st_dt(C, c_dt, (size_t)row * ldc + col, v);
+                        }
+                    }
+                    continue;
+                }
+                tc_ld_wait();
+                if (row >= M) continue;
+                const int col0 = n0 + c0;
+                const size_t base = (size_t)row * ldc + col0;
+                const bool full = col0 + 32 <= N;
+                if (c_dt == SP_DT_F32) {
+                    float* out = (float*)C + base;
+                    if (full && ((base & 3) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            if (mode == MODE_ACCUMULATE) {
+                                const float4 o = *(const float4*)(out + j);
+                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                            }
+                            *(float4*)(out + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) {
+                                float v = __uint_as_float(r[j]);
+                                if (mode == MODE_ACCUMULATE) v += out[j];
+                                out[j] = v;
+                            }
+                    }
+                } else {
+                    __nv_bfloat16* out = (__nv_bfloat16*)C + base;
+                    if (full && ((base & 7) == 0)) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 v;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                            v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
+                            *(uint4*)(out + j) = v;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with leading dimension ld, fetched in boxes of box_rows x 64
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) SP_FAIL("tc_gemm: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) SP_FAIL("tc_gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+template <int BN, int STAGES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc, int mode,
+           int* status, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status);
+    SP_CHECK_LAUNCH("tc_gemm");
+    return 0;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes these operands; the reason goes to the error text.
+SP_API int sp_tc_gemm_supported(const void* A, const void* W, int K, int lda, int ldw) {
+    if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8)) SP_FAIL("tc_gemm: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA)");
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) SP_FAIL("tc_gemm: operands must start on a 16-byte boundary");
+    return 0;
+}
+
+// mode 0: C = A·Wᵀ (C bfloat16 or float32); 1: C (float32) += A·Wᵀ;
+// mode 2: W holds gate and up rows interleaved in blocks of bn/2 and C [M, N/2] = silu(gate)·up.
+SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                      int mode, int bn, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (sp_tc_gemm_supported(A, W, K, lda, ldw)) return 1;
+    if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_gemm: accumulation needs a float32 C");
+    if (mode < 0 || mode > 2) SP_FAIL("tc_gemm: unknown mode %d", mode);
+    if (bn != 128 && bn != 256) SP_FAIL("tc_gemm: tile width %d is not built (128 or 256)", bn);
+    if (mode == MODE_SILU_MUL && (N % bn)) SP_FAIL("tc_gemm: the fused silu epilogue needs N (%d) to be a multiple of the tile width %d", N, bn);
+    if ((M + BM - 1) / BM > 65535) SP_FAIL("tc_gemm: M=%d is beyond this kernel's grid", M);
+    CUtensorMap ma, mw;
+    if (make_map(&ma, A, M, K, lda, BM)) return 1;
+    if (make_map(&mw, W, N, K, ldw, bn)) return 1;
+    if (bn == 128) return launch<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
+    return launch<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
+}

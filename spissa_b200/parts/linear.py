@@ -1,13 +1,23 @@
 """y = x · Wᵀ with W stored [out, in] (crates/spissa-runtime/src/ops.rs:62-105).
 
 ``Linear`` holds one weight matrix and picks the kernel for a call by the operands'
-storage types and sizes. The 32-bit path always uses the FFMA kernel.
+storage types and sizes: bfloat16 activations on a bfloat16 weight go to the tcgen05
+tensor-core kernel when the rows are multiples of 16 bytes; everything else, and the
+whole 32-bit path, goes to the FFMA kernel.
 """
 from __future__ import annotations
 
 import torch
 
 from ..csrc import lib as K
+
+SM_COUNT = 148
+
+
+def tile_width(M: int, N: int) -> int:
+    """256-wide tiles when they still fill the SMs, else 128-wide ones."""
+    tiles_256 = ((M + 127) // 128) * ((N + 255) // 256)
+    return 256 if tiles_256 >= SM_COUNT else 128
 
 
 class Linear:
@@ -24,5 +34,42 @@ class Linear:
             if accumulate:
                 raise ValueError("accumulation needs the tensor to add into")
             out = torch.empty(x.shape[0], self.out_features, dtype=out_dtype or x.dtype, device=x.device)
-        K.gemm_generic(x, self.weight, out, accumulate=accumulate)
+        if K.tc_gemm_supported(x, self.weight):
+            K.tc_gemm(x, self.weight, out, K.TC_ACCUMULATE if accumulate else K.TC_STORE,
+                      tile_width(x.shape[0], self.out_features))
+        else:
+            K.gemm_generic(x, self.weight, out, accumulate=accumulate)
+        return out
+
+
+class GatedLinear:
+    """silu(x·Wgᵀ) ⊙ (x·Wuᵀ) as one product over the stacked weight.
+
+    When the sizes allow, gate and up rows are interleaved in blocks (``block`` gate rows, then
+    the ``block`` up rows of the same outputs) so that one tile of the tensor-core kernel holds
+    both halves and applies silu·up in its epilogue.
+    """
+
+    def __init__(self, gate: torch.Tensor, up: torch.Tensor):
+        I = gate.shape[0]
+        self.intermediate = I
+        self.block = 128 if I % 128 == 0 else 64 if I % 64 == 0 else 0
+        fused = self.block and gate.dtype == torch.bfloat16 and gate.shape[1] % 8 == 0
+        if fused:
+            h = self.block
+            g = gate.reshape(I // h, h, -1)
+            u = up.reshape(I // h, h, -1)
+            self.weight = torch.stack([g, u], dim=1).reshape(2 * I, -1).contiguous()
+        else:
+            self.block = 0
+            self.weight = torch.cat([gate, up], dim=0).contiguous()
+        self.plain = Linear(self.weight)
+
+    def __call__(self, x: torch.Tensor, act_dtype) -> torch.Tensor:
+        out = torch.empty(x.shape[0], self.intermediate, dtype=act_dtype, device=x.device)
+        if self.block and K.tc_gemm_supported(x, self.weight):
+            K.tc_gemm(x, self.weight, out, K.TC_SILU_MUL, 2 * self.block)
+        else:
+            gu = self.plain(x, out_dtype=act_dtype)
+            K.silu_mul(gu, out)
         return out

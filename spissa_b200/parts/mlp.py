@@ -8,9 +8,8 @@ from __future__ import annotations
 
 import torch
 
-from ..csrc import lib as K
 from .base import FeedForward, WeightSpec
-from .linear import Linear
+from .linear import GatedLinear, Linear
 from .registry import register_part
 
 
@@ -34,11 +33,9 @@ class SwiGLU(FeedForward):
         g, u = tensors[self.names["gate"]], tensors[self.names["up"]]
         if g.dtype != u.dtype:
             raise ValueError(f"{self.prefix}: gate and up projections must share a storage type")
-        self.gate_up = Linear(torch.cat([g, u], dim=0))
+        self.gate_up = GatedLinear(g, u)
         self.down = Linear(tensors[self.names["down"]])
 
     def forward(self, x, step, residual):
-        gu = self.gate_up(x, out_dtype=self.rt.act_dtype)
-        act = torch.empty(x.shape[0], self.intermediate_size, dtype=self.rt.act_dtype, device=x.device)
-        K.silu_mul(gu, act)
+        act = self.gate_up(x, self.rt.act_dtype)
         self.down(act, out=residual, accumulate=True)

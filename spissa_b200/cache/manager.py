@@ -41,8 +41,9 @@ class KVGroup:
         self.page_size, self.n_pages = page_size, n_pages
         self.pages = IndexPool(n_pages, f"page of cache group {name}")
         shape = (len(self.cache_ids), n_pages, request.num_kv_heads, page_size, request.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device) if allocate else None
-        self.v = torch.empty(shape, dtype=dtype, device=device) if allocate else None
+        # zeros: a masked key's weight of zero must never meet a NaN left in fresh memory
+        self.k = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
+        self.v = torch.zeros(shape, dtype=dtype, device=device) if allocate else None
         self.index = {c: i for i, c in enumerate(self.cache_ids)}
 
     def pages_for(self, length: int) -> int:

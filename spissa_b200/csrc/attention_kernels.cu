@@ -1,0 +1,495 @@
+// Causal grouped-query attention over the paged cache for bfloat16 storage: a prefill kernel
+// (many query tokens per sequence) and a decode kernel (one query token per sequence, keys
+// split over CTAs, then combined).
+//
+// Meaning as in the reference (crates/spissa-runtime/src/rotary.rs:335-415, softmax :549-569):
+// score = q·k / sqrt(head_dim); keys after the query are not seen (nor keys before
+// pos-window+1 when a window is set); softmax in 32-bit with the maximum subtracted;
+// output = sum p·v; query head h reads kv head h / (heads / kv_heads).
+//
+// Both kernels walk the keys in tiles of 64 = one cache page ([page][kv head][64][head_dim],
+// so a tile is one contiguous block), staged in shared memory with cp.async, double
+// buffered. Products run on mma.sync m16n8k16 (bfloat16 in, float32 out); the running
+// maximum, sum and output stay in float32 registers (online softmax in the log2 domain).
+// Prefill: a CTA owns 64 consecutive query tokens of one head; each of its 4 warps owns 16.
+// Decode: a CTA owns the query heads of one kv head of one sequence (as the 16 rows of one
+// tile, unused rows zero) for one chunk of key tiles; each warp takes 16 keys of every tile.
+// Keys that no query may see are masked whatever the cache holds there; the cache is
+// zero-initialised so that a masked weight of zero never meets a NaN value.
+#include "common.cuh"
+
+SP_API const char* sp_attention_last_error() { return sp_error_text; }
+
+namespace {
+
+constexpr int KT = 64;                        // keys per tile = page size
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&p;
+}
+
+template <int HD>
+struct Tile {
+    static constexpr int ROW = HD * 2 + 16;           // bytes per shared-memory row; the pad spreads banks
+    static constexpr int BYTES = KT * ROW;
+    static constexpr int CHUNKS = HD / 8;             // 16-byte pieces per row
+};
+
+// Copy rows [0, n_rows) x HD of a bfloat16 matrix with row stride ``ld`` (elements) into a padded
+// shared tile; rows from n_rows to 64 are zeroed. All ``nthreads`` threads take part.
+template <int HD>
+__device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat16* src, size_t ld, int n_rows,
+                                                int tid, int nthreads) {
+    using T = Tile<HD>;
+    for (int c = tid; c < KT * T::CHUNKS; c += nthreads) {
+        const int r = c / T::CHUNKS, k = c % T::CHUNKS;
+        const uint32_t d = dst + r * T::ROW + k * 16;
+        if (r < n_rows) cp_async16(d, src + (size_t)r * ld + k * 8);
+        else asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(d), "r"(0u) : "memory");
+    }
+}
+
+// One warp, 16 query rows (fragments ``qf``), keys [key0, key0 + 8*NT) of the tile in shared memory.
+// Row ``g`` of the fragment sees keys lo[0]..hi[0], row g+8 keys lo[1]..hi[1] (absolute positions).
+template <int HD, int NT>
+__device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile,
+                                           int key0, int tile_pos0, const int (&lo)[2], const int (&hi)[2],
+                                           float scale_log2, float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
+                                           int lane) {
+    using T = Tile<HD>;
+    float s[NT][4];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    // S = Q · Kᵀ
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+            const int key = key0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
+            const int d = kk * 16 + (((lane >> 3) & 1) << 3);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4(k_tile + key * T::ROW + d * 2, b0, b1, b2, b3);
+            mma_bf16(s[2 * np], qf[kk], b0, b1);
+            mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+        }
+    }
+    // scale, mask, running maximum
+    const int t = lane & 3;
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = e >> 1;
+            const int key = tile_pos0 + key0 + nt * 8 + 2 * t + (e & 1);
+            const float v = (key > hi[r] || key < lo[r]) ? -INFINITY : s[nt][e] * scale_log2;
+            s[nt][e] = v;
+            mx[r] = fmaxf(mx[r], v);
+        }
+    }
+    float corr[2], msafe[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+        mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+        const float mnew = fmaxf(m[r], mx[r]);
+        msafe[r] = (mnew == -INFINITY) ? 0.0f : mnew;
+        corr[r] = exp2f(m[r] - msafe[r]);            // m = -inf gives 0
+        m[r] = mnew;
+    }
+    float sum[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float p = exp2f(s[nt][e] - msafe[e >> 1]);
+            s[nt][e] = p;
+            sum[e >> 1] += p;
+        }
+    }
+    l[0] = l[0] * corr[0] + sum[0];                   // per-lane partial; lanes are summed at the end
+    l[1] = l[1] * corr[1] + sum[1];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        o[i][0] *= corr[0]; o[i][1] *= corr[0];
+        o[i][2] *= corr[1]; o[i][3] *= corr[1];
+    }
+    // O += P · V
+#pragma unroll
+    for (int kk = 0; kk < NT / 2; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int dp = 0; dp < HD / 16; ++dp) {
+            const int key = key0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
+            const int d = dp * 16 + ((lane >> 4) << 3);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(v_tile + key * T::ROW + d * 2, b0, b1, b2, b3);
+            mma_bf16(o[2 * dp], a, b0, b1);
+            mma_bf16(o[2 * dp + 1], a, b2, b3);
+        }
+    }
+}
+
+template <int HD>
+__device__ __forceinline__ void load_q_frags(uint32_t q_tile, int row0, int lane, uint32_t (&qf)[HD / 16][4]) {
+    using T = Tile<HD>;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        const int row = row0 + (lane & 7) + (((lane >> 3) & 1) << 3);
+        const int d = kk * 16 + ((lane >> 4) << 3);
+        ldmatrix_x4(q_tile + row * T::ROW + d * 2, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
+}
+
+struct PagedKV {
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    const int* page_table;      // [rows][max_pages]
+    const int* seq_row;         // [B] row of each sequence in the table
+    int max_pages;
+    int nkv;
+};
+
+// ------------------------------------------------------------------ prefill
+template <int HD>
+__global__ void __launch_bounds__(128)
+flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, PagedKV kv,
+                     const int* __restrict__ seq_start, const int* __restrict__ positions, int n_seqs, int nh,
+                     int window, float scale_log2) {
+    using T = Tile<HD>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t q_tile = smem_u32(smem);
+    const uint32_t k_tiles = q_tile + T::BYTES;          // two stages of K, then two of V
+    const uint32_t v_tiles = k_tiles + 2 * T::BYTES;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // which sequence and which 64-token tile of it
+    int x = blockIdx.x, b = 0, first = 0, n_new = 0;
+    for (; b < n_seqs; ++b) {
+        first = seq_start[b];
+        n_new = seq_start[b + 1] - first;
+        const int nt = (n_new + KT - 1) / KT;
+        if (x < nt) break;
+        x -= nt;
+    }
+    if (b >= n_seqs) return;
+    const int t0 = first + x * KT;
+    const int n_rows = min(KT, n_new - x * KT);
+    const int pos0 = positions[t0];
+    const int h = blockIdx.y;
+    const int g = h / (nh / kv.nkv);
+    const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
+
+    const int last_pos = pos0 + n_rows - 1;
+    const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+    const int j_lo = first_key / KT, j_hi = last_pos / KT;
+
+    load_tile_async<HD>(q_tile, q + (size_t)t0 * nh * HD + (size_t)h * HD, (size_t)nh * HD, n_rows, tid, 128);
+    {
+        const size_t off = ((size_t)pt[j_lo] * kv.nkv + g) * KT * HD;
+        load_tile_async<HD>(k_tiles, kv.k + off, HD, KT, tid, 128);
+        load_tile_async<HD>(v_tiles, kv.v + off, HD, KT, tid, 128);
+    }
+    cp_async_commit();
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const int r0 = warp * 16 + (lane >> 2);
+    const int hi[2] = {pos0 + r0, pos0 + r0 + 8};
+    const int lo[2] = {window > 0 ? hi[0] - window + 1 : 0, window > 0 ? hi[1] - window + 1 : 0};
+    const int warp_hi = pos0 + warp * 16 + 15;                     // last key any row of this warp may see
+    const int warp_lo = window > 0 ? pos0 + warp * 16 - window + 1 : 0;
+    const bool warp_active = warp * 16 < n_rows;
+
+    for (int j = j_lo; j <= j_hi; ++j) {
+        const int stage = (j - j_lo) & 1;
+        if (j < j_hi) {
+            const size_t off = ((size_t)pt[j + 1] * kv.nkv + g) * KT * HD;
+            load_tile_async<HD>(k_tiles + (stage ^ 1) * T::BYTES, kv.k + off, HD, KT, tid, 128);
+            load_tile_async<HD>(v_tiles + (stage ^ 1) * T::BYTES, kv.v + off, HD, KT, tid, 128);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (j == j_lo) load_q_frags<HD>(q_tile, warp * 16, lane, qf);
+        const int tile_pos0 = j * KT;
+        if (warp_active && tile_pos0 <= warp_hi && tile_pos0 + KT - 1 >= warp_lo)
+            flash_step<HD, 8>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
+                              scale_log2, o, m, l, lane);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    const int t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = warp * 16 + (lane >> 2) + r * 8;
+        if (row >= n_rows) continue;
+        const float inv = 1.0f / l[r];
+        __nv_bfloat16* dst = out + (size_t)(t0 + row) * nh * HD + (size_t)h * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i)
+            *(uint32_t*)(dst + i * 8 + 2 * t) = pack_bf16(o[i][2 * r] * inv, o[i][2 * r + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------ decode
+// grid (chunks, kv heads, sequences). part_o [B][nh][chunks][HD], part_ml [B][nh][chunks][2] (m in log2 units).
+template <int HD>
+__global__ void __launch_bounds__(128)
+flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* __restrict__ seq_len, int nh,
+                    int window, float scale_log2, int chunk_tiles, float* __restrict__ part_o,
+                    float* __restrict__ part_ml) {
+    using T = Tile<HD>;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t q_tile = smem_u32(smem);                       // 16 rows used
+    const uint32_t k_tiles = q_tile + 16 * T::ROW;
+    const uint32_t v_tiles = k_tiles + 2 * T::BYTES;
+    float* merge = (float*)(smem + 16 * T::ROW + 4 * T::BYTES);    // [4 warps][16 rows][HD + 2]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int chunk = blockIdx.x, n_chunks = gridDim.x, g = blockIdx.y, b = blockIdx.z;
+    const int G = nh / kv.nkv;
+    const int p = seq_len[b] - 1;                                  // the query's position
+    const int first_key = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int j_first = first_key / KT + chunk * chunk_tiles;
+    const int j_last = min(p / KT, j_first + chunk_tiles - 1);
+    const size_t part_base = ((size_t)b * nh + (size_t)g * G) * n_chunks + chunk;   // + head_in_group * n_chunks
+
+    if (j_first > j_last) {                                        // nothing for this chunk
+        for (int i = tid; i < G; i += 128) {
+            part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
+            part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
+        }
+        return;
+    }
+    const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
+
+    // the G heads of this kv head as rows 0..G-1 of a 16-row tile
+    for (int c = tid; c < 16 * T::CHUNKS; c += 128) {
+        const int r = c / T::CHUNKS, k = c % T::CHUNKS;
+        const uint32_t d = q_tile + r * T::ROW + k * 16;
+        if (r < G) cp_async16(d, q + (size_t)b * nh * HD + (size_t)(g * G + r) * HD + k * 8);
+        else asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(d), "r"(0u) : "memory");
+    }
+    {
+        const size_t off = ((size_t)pt[j_first] * kv.nkv + g) * KT * HD;
+        load_tile_async<HD>(k_tiles, kv.k + off, HD, KT, tid, 128);
+        load_tile_async<HD>(v_tiles, kv.v + off, HD, KT, tid, 128);
+    }
+    cp_async_commit();
+
+    uint32_t qf[HD / 16][4];
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    const int hi[2] = {p, p};
+    const int lo[2] = {first_key, first_key};
+
+    for (int j = j_first; j <= j_last; ++j) {
+        const int stage = (j - j_first) & 1;
+        if (j < j_last) {
+            const size_t off = ((size_t)pt[j + 1] * kv.nkv + g) * KT * HD;
+            load_tile_async<HD>(k_tiles + (stage ^ 1) * T::BYTES, kv.k + off, HD, KT, tid, 128);
+            load_tile_async<HD>(v_tiles + (stage ^ 1) * T::BYTES, kv.v + off, HD, KT, tid, 128);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (j == j_first) load_q_frags<HD>(q_tile, 0, lane, qf);
+        flash_step<HD, 2>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo, hi,
+                          scale_log2, o, m, l, lane);
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    // merge the four warps' (m, l, o): each covered other keys of the same rows
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+    }
+    constexpr int MS = HD + 2;
+    const int t = lane & 3;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + r * 8;
+        float* dst = merge + ((size_t)warp * 16 + row) * MS;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            dst[i * 8 + 2 * t] = o[i][2 * r];
+            dst[i * 8 + 2 * t + 1] = o[i][2 * r + 1];
+        }
+        if (t == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
+    }
+    __syncthreads();
+    for (int e = tid; e < G * HD; e += 128) {
+        const int row = e / HD, d = e % HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, merge[((size_t)w * 16 + row) * MS + HD]);
+        const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+        float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float* src = merge + ((size_t)w * 16 + row) * MS;
+            const float f = exp2f(src[HD] - msafe);
+            acc += src[d] * f;
+            ll += src[HD + 1] * f;
+        }
+        const size_t pi = part_base + (size_t)row * n_chunks;
+        part_o[pi * HD + d] = acc;
+        if (d == 0) { part_ml[pi * 2] = mm; part_ml[pi * 2 + 1] = ll; }
+    }
+}
+
+// out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order
+template <typename TO>
+__global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      TO* __restrict__ out, int n_chunks, int HD) {
+    const size_t bh = blockIdx.x;
+    float mm = -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, part_ml[(bh * n_chunks + c) * 2]);
+    const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+    float ll = 0.0f;
+    for (int c = 0; c < n_chunks; ++c)
+        ll += part_ml[(bh * n_chunks + c) * 2 + 1] * exp2f(part_ml[(bh * n_chunks + c) * 2] - msafe);
+    const float inv = 1.0f / ll;
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float lc = part_ml[(bh * n_chunks + c) * 2 + 1];
+            if (lc > 0.0f) acc += part_o[(bh * n_chunks + c) * HD + d] * exp2f(part_ml[(bh * n_chunks + c) * 2] - msafe);
+        }
+        sp_st(out, bh * HD + d, acc * inv);
+    }
+}
+
+template <int HD>
+constexpr int prefill_smem() { return 5 * Tile<HD>::BYTES; }
+template <int HD>
+constexpr int decode_smem() { return 16 * Tile<HD>::ROW + 4 * Tile<HD>::BYTES + 4 * 16 * (HD + 2) * 4; }
+
+template <typename Kern>
+int opt_in_smem(Kern kern, int bytes, const char* name) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) SP_FAIL("%s: cannot reserve %d bytes of shared memory: %s", name, bytes, cudaGetErrorString(e));
+    return 0;
+}
+
+int check_common(int hd, int nh, int nkv, int page_size) {
+    if (hd != 64 && hd != 128) SP_FAIL("flash attention: head_dim %d is not built (64 and 128 are)", hd);
+    if (nkv <= 0 || nh % nkv) SP_FAIL("flash attention: %d heads are no multiple of %d kv heads", nh, nkv);
+    if (page_size != KT) SP_FAIL("flash attention: pages of %d tokens, this kernel walks pages of %d", page_size, KT);
+    return 0;
+}
+
+}  // namespace
+
+// Whether the flash kernels are built for this shape (1) or the generic kernel has to run (0).
+SP_API int sp_flash_supported(int hd, int nh, int nkv, int page_size) {
+    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && page_size == KT;
+}
+
+SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
+                            const int* positions, const int* seq_row, const int* page_table, int max_pages,
+                            int page_size, int n_seqs, int n_q_tiles, int nh, int nkv, int hd, int window,
+                            float scale, cudaStream_t stream) {
+    if (n_q_tiles <= 0) return 0;
+    if (check_common(hd, nh, nkv, page_size)) return 1;
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    dim3 grid(n_q_tiles, nh);
+    const float sl = scale * LOG2E;
+    if (hd == 64) {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_prefill_kernel<64>, prefill_smem<64>(), "flash_prefill")) return 1; ok = true; }
+        flash_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(
+            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
+    } else {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_prefill_kernel<128>, prefill_smem<128>(), "flash_prefill")) return 1; ok = true; }
+        flash_prefill_kernel<128><<<grid, 128, prefill_smem<128>(), stream>>>(
+            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
+    }
+    SP_CHECK_LAUNCH("flash_prefill");
+    return 0;
+}
+
+// Bytes of float32 scratch the decode pair needs: part_o then part_ml.
+SP_API long long sp_flash_decode_scratch_floats(int n_seqs, int nh, int hd, int n_chunks) {
+    return (long long)n_seqs * nh * n_chunks * (hd + 2);
+}
+
+SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+                           const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
+                           int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
+                           int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats,
+                           cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (check_common(hd, nh, nkv, page_size)) return 1;
+    if (nh / nkv > 16) SP_FAIL("flash decode: %d query heads per kv head, at most 16 fit one tile", nh / nkv);
+    if (chunk_tiles <= 0 || n_chunks <= 0 || n_chunks > 65535) SP_FAIL("flash decode: bad chunking %d x %d", n_chunks, chunk_tiles);
+    if (n_seqs > 65535) SP_FAIL("flash decode: %d sequences are beyond this kernel's grid", n_seqs);
+    const long long need = sp_flash_decode_scratch_floats(n_seqs, nh, hd, n_chunks);
+    if (scratch_floats < need) SP_FAIL("flash decode: scratch holds %lld floats, %lld are needed", scratch_floats, need);
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    float* part_o = scratch;
+    float* part_ml = scratch + (size_t)n_seqs * nh * n_chunks * hd;
+    dim3 grid(n_chunks, nkv, n_seqs);
+    const float sl = scale * LOG2E;
+    if (hd == 64) {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_decode_kernel<64>, decode_smem<64>(), "flash_decode")) return 1; ok = true; }
+        flash_decode_kernel<64><<<grid, 128, decode_smem<64>(), stream>>>(
+            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml);
+    } else {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_decode_kernel<128>, decode_smem<128>(), "flash_decode")) return 1; ok = true; }
+        flash_decode_kernel<128><<<grid, 128, decode_smem<128>(), stream>>>(
+            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml);
+    }
+    SP_CHECK_LAUNCH("flash_decode");
+    if (out_dt == SP_DT_BF16)
+        decode_combine_kernel<__nv_bfloat16><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_chunks, hd);
+    else
+        decode_combine_kernel<float><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (float*)out, n_chunks, hd);
+    SP_CHECK_LAUNCH("decode_combine");
+    return 0;
+}

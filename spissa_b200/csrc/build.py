@@ -30,6 +30,7 @@ MODULES = {
     "generic": "generic_kernels.cu",
     "sampling": "sampling_kernels.cu",
     "tc_gemm": "tc_gemm.cu",
+    "attention": "attention_kernels.cu",
 }
 
 

@@ -257,3 +257,59 @@ def tc_gemm(a, w, out, mode=TC_STORE, bn=128):
         c_void_p(_ptr(a)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K,
         a.stride(0), w.stride(0), out.stride(0), int(mode), int(bn), c_void_p(_ptr(status_word(a.device))),
         c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ flash attention (bfloat16)
+def flash_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int) -> bool:
+    """Whether the tensor-core attention kernels take this shape; else the generic kernel runs."""
+    if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
+        return False
+    return hd in (64, 128) and nkv > 0 and nh % nkv == 0 and nh // nkv <= 16 and page_size == 64
+
+
+def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
+    """Causal attention of a step's tokens (any number per sequence) over the paged cache.
+
+    ``seq_start`` [B+1] int32 on the device; ``n_q_tiles`` = sum over sequences of ceil(new tokens / 64).
+    """
+    lib = load("attention")
+    _need_contig(q, out)
+    pt = meta.page_table
+    _check("attention", lib.sp_flash_prefill(
+        c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
+        c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)),
+        c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles), nh, nkv, hd,
+        int(window or 0), c_float(scale), c_void_p(_stream())))
+
+
+def flash_decode_plan(n_seqs: int, nkv: int, max_len: int, page_size: int = 64) -> tuple:
+    """(tiles per chunk, chunks): enough CTAs to fill the GPU, at most one chunk per key tile."""
+    tiles = max(1, (max_len + page_size - 1) // page_size)
+    want = max(1, -(-296 // max(1, n_seqs * nkv)))
+    n_chunks = min(tiles, want)
+    chunk_tiles = -(-tiles // n_chunks)
+    n_chunks = -(-tiles // chunk_tiles)
+    return chunk_tiles, n_chunks
+
+
+def flash_decode_scratch_floats(n_seqs: int, nh: int, hd: int, n_chunks: int) -> int:
+    return n_seqs * nh * n_chunks * (hd + 2)
+
+
+def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks, scratch):
+    """One query token per sequence: keys split into chunks over CTAs, partial results combined in order.
+
+    ``seq_len`` [B] int32: each sequence's length including the query token. ``scratch``: float32,
+    at least ``flash_decode_scratch_floats`` elements.
+    """
+    global launches
+    lib = load("attention")
+    _need_contig(q, out)
+    pt = meta.page_table
+    n_seqs = q.shape[0]
+    _check("attention", lib.sp_flash_decode(
+        c_void_p(_ptr(q)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
+        c_void_p(_ptr(seq_len)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
+        n_seqs, nh, nkv, hd, int(window or 0), c_float(scale), int(chunk_tiles), int(n_chunks),
+        c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_stream())))
+    launches += 1            # two kernels: the chunks and the combine

@@ -80,5 +80,16 @@ class GQAAttention(Mixer):
         q = torch.empty(T, nh * hd, dtype=self.rt.act_dtype, device=x.device)
         K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
         ctx = torch.empty_like(q)
-        K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
+        if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
+            if step.all_single:
+                chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, step.max_len, cache.page_size)
+                need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
+                scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+                K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,
+                               self.scale, chunk_tiles, n_chunks, scratch)
+            else:
+                K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
+                                step.n_q_tiles, nh, nkv, hd, self.window, self.scale)
+        else:
+            K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
         self.o(ctx, out=residual, accumulate=True)

@@ -31,7 +31,7 @@ def paged_meta(new_counts, lengths_before, device, seed=0, page=PAGE, spare_page
         token_seq=torch.tensor(token_seq, dtype=torch.int32, device=device),
         positions=torch.tensor(positions, dtype=torch.int32, device=device),
         seq_slot=torch.arange(B, dtype=torch.int32, device=device),
-        page_table=table, page_size=page, n_pages=n_pages, rows=rows, total_len=total_len,
+        page_table=table, page_size=page, n_pages=n_pages, rows=rows, total_len=total_len, new_counts=list(new_counts),
         seq_len=torch.tensor(total_len, dtype=torch.int32, device=device),
         seq_start=torch.tensor([0] + list(torch.tensor(new_counts).cumsum(0)), dtype=torch.int32, device=device))
     return meta

@@ -261,3 +261,74 @@ def test_sampling_follows_the_reference_walk(K, V):
                     # and it is the serial 32-bit walk's choice or its neighbour
                     want = P.sample_top_k_top_p(logits[r].tolist(), temp, k, p, seed * 100 + r)
                     assert abs(rank - order.index(want)) <= 1, (V, temp, k, p, r, got[r], want)
+
+
+# ------------------------------------------------------------------ tensor-core attention (bfloat16)
+def flash_prefill_fn(K):
+    def fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
+        n_tiles = sum((c + 63) // 64 for c in meta.new_counts)
+        K.flash_prefill(q, k_pool, v_pool, out, meta, meta.seq_start, len(meta.new_counts), n_tiles, nh, nkv, hd,
+                        window, scale)
+    return fn
+
+
+def flash_decode_fn(K, chunk_tiles=None):
+    def fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
+        ct, nc = K.flash_decode_plan(q.shape[0], nkv, max(meta.total_len))
+        if chunk_tiles:
+            ct = chunk_tiles
+            nc = -(-((max(meta.total_len) + 63) // 64) // ct)
+        scratch = torch.full((K.flash_decode_scratch_floats(q.shape[0], nh, hd, nc),), float("nan"), device=DEV)
+        K.flash_decode(q, k_pool, v_pool, out, meta, meta.seq_len, nh, nkv, hd, window, scale, ct, nc, scratch)
+    return fn
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (6, 3, 128)])
+def test_flash_prefill(K, nh, nkv, hd):
+    fn = flash_prefill_fn(K)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [7, 1, 65, 33], [0, 199, 64, 31], None, hd, 6e-3)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [300, 64, 128], [0, 0, 100], None, hd + 2, 6e-3)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [1, 1, 1], [0, 63, 300], None, hd + 1, 6e-3)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100, 200])
+def test_flash_prefill_window(K, window):
+    attention_case(K, flash_prefill_fn(K), 4, 2, 64, torch.bfloat16, [40, 1, 230], [0, 250, 20], window, window, 6e-3)
+
+
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (32, 8, 64)])
+@pytest.mark.parametrize("chunk_tiles", [None, 1, 3])
+def test_flash_decode(K, nh, nkv, hd, chunk_tiles):
+    fn = flash_decode_fn(K, chunk_tiles)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [1, 1, 1, 1, 1], [0, 63, 64, 300, 700], None, hd + 3, 6e-3)
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100, 200])
+def test_flash_decode_window(K, window):
+    attention_case(K, flash_decode_fn(K, 2), 4, 2, 64, torch.bfloat16, [1, 1, 1], [0, 250, 20], window, window, 6e-3)
+
+
+@pytest.mark.parametrize("which", ["prefill", "decode"])
+@pytest.mark.parametrize("length,needle", [(700, 3), (700, 640), (129, 64), (64, 63), (1000, 0), (65, 64)])
+def test_flash_finds_a_far_key(K, which, length, needle):
+    fn = flash_prefill_fn(K) if which == "prefill" else flash_decode_fn(K)
+    out, v = needle_case(K, fn, torch.bfloat16, length, needle)
+    for h in range(4):
+        assert torch.allclose(out[h], v[needle, h // 2], atol=2e-2), f"head {h} missed key {needle} of {length}"
+
+
+@pytest.mark.parametrize("which", ["prefill", "decode"])
+def test_flash_window_edge(K, which):
+    fn = flash_prefill_fn(K) if which == "prefill" else flash_decode_fn(K)
+    length, window = 300, 100
+    p = length - 1
+    out, v = needle_case(K, fn, torch.bfloat16, length, p - window + 1, window)
+    assert torch.allclose(out[0], v[p - window + 1, 0], atol=2e-2)
+    out, v = needle_case(K, fn, torch.bfloat16, length, p - window, window)
+    assert not torch.allclose(out[0], v[p - window, 0], atol=0.5)
+
+
+def test_flash_ignores_junk_beyond_the_sequence(K):
+    """Rows of the last page beyond the sequence's end hold huge values; no query may see them."""
+    for fn, counts, before in ((flash_prefill_fn(K), [70], [0]), (flash_decode_fn(K), [1], [69])):
+        attention_case(K, fn, 4, 2, 64, torch.bfloat16, counts, before, None, 5, 6e-3)

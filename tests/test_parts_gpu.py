@@ -34,7 +34,9 @@ def bound(role, spec, tensors, dtype):
 def step_of(meta, T):
     return SimpleNamespace(n_tokens=T, token_seq=meta.token_seq, positions=meta.positions, seq_row=meta.seq_slot,
                            seq_slot=meta.seq_slot, seq_len=meta.seq_len, seq_start=meta.seq_start,
-                           n_seqs=len(meta.rows), all_single=False, max_new=T, max_len=max(meta.total_len))
+                           n_seqs=len(meta.rows), all_single=all(c == 1 for c in meta.new_counts),
+                           n_q_tiles=sum((c + 63) // 64 for c in meta.new_counts), max_new=T,
+                           max_len=max(meta.total_len))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

@@ -31,6 +31,7 @@ MODULES = {
     "sampling": "sampling_kernels.cu",
     "tc_gemm": "tc_gemm.cu",
     "attention": "attention_kernels.cu",
+    "gemv": "gemv_kernels.cu",
 }
 
 

@@ -1,0 +1,212 @@
+// Skinny bfloat16 products for decoding: out[M,N] = x[M,K] · W[N,K]ᵀ with M ≤ 64 tokens.
+//
+// The step is bound by streaming W from HBM once (the reference's batch-1 path streams rows
+// the same way, crates/spissa-runtime/src/streaming/kernels_raw16.rs:532-692, and fuses
+// silu(gate)·up at batch 1, crates/spissa-runtime/src/streaming/linear_multiply.rs:376-497).
+// A warp owns RT groups of 8 rows of W and a slice of K. Per 32 columns of K each lane loads
+// 16 contiguous bytes of "its" row of W straight from global memory, and 16 bytes of x per
+// 8-token group (x is small and stays in L1/L2); both feed mma.sync m16n8k16 with the tokens
+// as the 16 rows of A and 8 rows of W as the columns of B. The K positions inside a 32-block are
+// permuted the same way for both operands, which leaves the sum unchanged. The KS warps of a
+// CTA split K; their partial sums are added in warp order in shared memory, so the result does
+// not depend on timing. Epilogues: store, add into a float32 tensor, or silu(gate)·up when the
+// weight interleaves gate and up rows in blocks.
+#include "common.cuh"
+
+SP_API const char* sp_gemv_last_error() { return sp_error_text; }
+
+namespace {
+
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+constexpr int MAX_KS = 8;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {          // weights: read once, do not keep in L1
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_keep(const void* p) {            // activations: reused by every warp
+    uint4 v;
+    asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// MT: groups of 16 tokens; RT: groups of 8 rows of W per warp; UNROLL: 32-column blocks in flight.
+// For MODE_SILU_MUL RT must be 2: row group 0 is gate rows, group 1 the up rows ``pair`` rows further on.
+template <int MT, int RT, int UNROLL>
+__global__ void __launch_bounds__(MAX_KS * 32)
+gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+            int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int ks) {
+    __shared__ float red[MAX_KS][MT][RT][32][4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+
+    // rows of W this CTA owns
+    int row_base[RT];
+    if (mode == MODE_SILU_MUL) {
+        const int blk = (blockIdx.x * 8) / pair, within = (blockIdx.x * 8) % pair;
+        row_base[0] = blk * 2 * pair + within;
+        if (RT > 1) row_base[RT - 1] = row_base[0] + pair;
+    } else {
+#pragma unroll
+        for (int r = 0; r < RT; ++r) row_base[r] = (blockIdx.x * RT + r) * 8;
+    }
+
+    // this warp's slice of K, in blocks of 32 columns
+    const int kblocks = (K + 31) / 32;
+    const int per = (kblocks + ks - 1) / ks;
+    const int kb0 = warp * per, kb1 = min(kblocks, kb0 + per);
+
+    float acc[MT][RT][4];
+#pragma unroll
+    for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int r = 0; r < RT; ++r) acc[i][r][0] = acc[i][r][1] = acc[i][r][2] = acc[i][r][3] = 0.0f;
+
+    const __nv_bfloat16* wrow[RT];
+    bool wok[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        const int row = row_base[r] + g;
+        wok[r] = row < N;
+        wrow[r] = W + (size_t)(wok[r] ? row : 0) * ldw;
+    }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    for (int kb = kb0; kb < kb1; kb += UNROLL) {
+        uint4 wv[UNROLL][RT];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb + u) * 32 + 8 * t;
+            const bool kok = (kb + u) < kb1 && k < K;                 // K is a multiple of 8: whole 16 bytes or none
+#pragma unroll
+            for (int r = 0; r < RT; ++r) wv[u][r] = (kok && wok[r]) ? ld_stream(wrow[r] + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = (kb + u) * 32 + 8 * t;
+            const bool kok = (kb + u) < kb1 && k < K;
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+                const int m0 = i * 16 + g, m1 = m0 + 8;
+                const uint4 xa = (kok && m0 < M) ? ld_keep(x + (size_t)m0 * ldx + k) : zero;
+                const uint4 xb = (kok && m1 < M) ? ld_keep(x + (size_t)m1 * ldx + k) : zero;
+#pragma unroll
+                for (int r = 0; r < RT; ++r) {
+                    mma_bf16(acc[i][r], xa.x, xb.x, xa.y, xb.y, wv[u][r].x, wv[u][r].y);
+                    mma_bf16(acc[i][r], xa.z, xb.z, xa.w, xb.w, wv[u][r].z, wv[u][r].w);
+                }
+            }
+        }
+    }
+
+    // add the K slices in warp order
+    if (ks > 1) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int r = 0; r < RT; ++r)
+                *(float4*)red[warp][i][r][lane] = make_float4(acc[i][r][0], acc[i][r][1], acc[i][r][2], acc[i][r][3]);
+        __syncthreads();
+        if (warp != 0) return;
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                float4 s = *(float4*)red[0][i][r][lane];
+                for (int w = 1; w < ks; ++w) {
+                    const float4 v = *(float4*)red[w][i][r][lane];
+                    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                }
+                acc[i][r][0] = s.x; acc[i][r][1] = s.y; acc[i][r][2] = s.z; acc[i][r][3] = s.w;
+            }
+    }
+
+    // lane holds tokens (16i+g, 16i+g+8) x rows (2t, 2t+1) of every row group
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int m = i * 16 + g + (e >> 1) * 8;
+            if (m >= M) continue;
+            if (mode == MODE_SILU_MUL) {
+                const int blk = row_base[0] / (2 * pair), within = row_base[0] % (2 * pair);
+                const int col = blk * pair + within + 2 * t + (e & 1);
+                if (col < N / 2) {
+                    const float gate = acc[i][0][e], up = acc[i][RT - 1][e];
+                    sp_st_dt(out, out_dt, (size_t)m * ldo + col, (gate / (1.0f + expf(-gate))) * up);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RT; ++r) {
+                    const int col = row_base[r] + 2 * t + (e & 1);
+                    if (col >= N) continue;
+                    const size_t o = (size_t)m * ldo + col;
+                    float v = acc[i][r][e];
+                    if (mode == MODE_ACCUMULATE) v += ((float*)out)[o];
+                    sp_st_dt(out, out_dt, o, v);
+                }
+            }
+        }
+    }
+}
+
+int pick_ks(int K) {
+    const int kblocks = (K + 31) / 32;
+    int ks = kblocks / 8;                    // at least 8 blocks (256 columns) per warp
+    if (ks < 1) ks = 1;
+    if (ks > MAX_KS) ks = MAX_KS;
+    return ks;
+}
+
+}  // namespace
+
+SP_API int sp_gemv_supported(const void* x, const void* W, int M, int K, int ldx, int ldw) {
+    if (M <= 0 || M > 64) SP_FAIL("gemv: built for 1 to 64 tokens, got %d", M);
+    if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8)) SP_FAIL("gemv: K and the leading dimensions must be multiples of 8");
+    if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) SP_FAIL("gemv: operands must start on a 16-byte boundary");
+    return 0;
+}
+
+// mode 0: out = x·Wᵀ (bfloat16 or float32); 1: out (float32) += x·Wᵀ;
+// 2: W interleaves ``pair`` gate rows and ``pair`` up rows; out [M, N/2] = silu(gate)·up.
+SP_API int sp_gemv(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int ldx, int ldw,
+                   int ldo, int mode, int pair, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (sp_gemv_supported(x, W, M, K, ldx, ldw)) return 1;
+    if (mode == MODE_ACCUMULATE && out_dt != SP_DT_F32) SP_FAIL("gemv: accumulation needs a float32 output");
+    if (mode < 0 || mode > 2) SP_FAIL("gemv: unknown mode %d", mode);
+    if (mode == MODE_SILU_MUL && (pair <= 0 || (pair % 8) || N % (2 * pair)))
+        SP_FAIL("gemv: the fused silu epilogue needs blocks of a multiple of 8 rows that divide N/2 (N=%d, block %d)", N, pair);
+    const int ks = pick_ks(K);
+    const int threads = ks * 32;
+    const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
+    const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
+#define GV_LAUNCH(MT, RT, UN, blocks) \
+    gemv_kernel<MT, RT, UN><<<blocks, threads, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo, mode, pair, ks)
+    if (mode == MODE_SILU_MUL) {
+        const int blocks = (N / 2) / 8;
+        if (M <= 16) GV_LAUNCH(1, 2, 4, blocks);
+        else if (M <= 32) GV_LAUNCH(2, 2, 4, blocks);
+        else GV_LAUNCH(4, 2, 2, blocks);
+    } else if (M <= 16) {
+        GV_LAUNCH(1, 1, 8, (N + 7) / 8);
+    } else if (M <= 32) {
+        GV_LAUNCH(2, 2, 4, (N + 15) / 16);
+    } else {
+        GV_LAUNCH(4, 2, 2, (N + 15) / 16);
+    }
+#undef GV_LAUNCH
+    SP_CHECK_LAUNCH("gemv");
+    return 0;
+}

@@ -313,3 +313,31 @@ def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, sca
         n_seqs, nh, nkv, hd, int(window or 0), c_float(scale), int(chunk_tiles), int(n_chunks),
         c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_stream())))
     launches += 1            # two kernels: the chunks and the combine
+
+
+# ------------------------------------------------------------------ skinny products for decoding
+GEMV_MAX_TOKENS = 64
+
+
+def gemv_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
+        return False
+    if x.stride(1) != 1 or w.stride(1) != 1 or x.shape[1] != w.shape[1]:
+        return False
+    K = x.shape[1]
+    return (0 < x.shape[0] <= GEMV_MAX_TOKENS and K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def gemv(x, w, out, mode=TC_STORE, pair=0):
+    """out = x · wᵀ for up to 64 tokens, streaming ``w`` once. Modes as ``tc_gemm``; for TC_SILU_MUL
+    ``pair`` is the number of gate rows before the matching up rows in the interleaved weight."""
+    lib = load("gemv")
+    M, K = x.shape
+    N = w.shape[0]
+    want_cols = N // 2 if mode == TC_SILU_MUL else N
+    if out.shape[0] != M or out.shape[1] != want_cols or out.stride(1) != 1:
+        raise KernelError(f"gemv: out {tuple(out.shape)} does not fit x {tuple(x.shape)}, w {tuple(w.shape)}")
+    _check("gemv", lib.sp_gemv(
+        c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K,
+        x.stride(0), w.stride(0), out.stride(0), int(mode), int(pair), c_void_p(_stream())))

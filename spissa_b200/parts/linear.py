@@ -1,9 +1,9 @@
 """y = x · Wᵀ with W stored [out, in] (crates/spissa-runtime/src/ops.rs:62-105).
 
 ``Linear`` holds one weight matrix and picks the kernel for a call by the operands'
-storage types and sizes: bfloat16 activations on a bfloat16 weight go to the tcgen05
-tensor-core kernel when the rows are multiples of 16 bytes; everything else, and the
-whole 32-bit path, goes to the FFMA kernel.
+storage types and sizes: bfloat16 activations on a bfloat16 weight go to the weight-streaming
+kernel for a few tokens (decoding) and to the tcgen05 tensor-core kernel otherwise, when the
+rows are multiples of 16 bytes; everything else, and the whole 32-bit path, goes to the FFMA kernel.
 """
 from __future__ import annotations
 
@@ -12,6 +12,7 @@ import torch
 from ..csrc import lib as K
 
 SM_COUNT = 148
+GEMV_TOKENS = 16          # up to this many tokens the weight-streaming kernel runs instead of 128-row tiles
 
 
 def tile_width(M: int, N: int) -> int:
@@ -34,9 +35,11 @@ class Linear:
             if accumulate:
                 raise ValueError("accumulation needs the tensor to add into")
             out = torch.empty(x.shape[0], self.out_features, dtype=out_dtype or x.dtype, device=x.device)
-        if K.tc_gemm_supported(x, self.weight):
-            K.tc_gemm(x, self.weight, out, K.TC_ACCUMULATE if accumulate else K.TC_STORE,
-                      tile_width(x.shape[0], self.out_features))
+        mode = K.TC_ACCUMULATE if accumulate else K.TC_STORE
+        if x.shape[0] <= GEMV_TOKENS and K.gemv_supported(x, self.weight):
+            K.gemv(x, self.weight, out, mode)
+        elif K.tc_gemm_supported(x, self.weight):
+            K.tc_gemm(x, self.weight, out, mode, tile_width(x.shape[0], self.out_features))
         else:
             K.gemm_generic(x, self.weight, out, accumulate=accumulate)
         return out
@@ -67,7 +70,9 @@ class GatedLinear:
 
     def __call__(self, x: torch.Tensor, act_dtype) -> torch.Tensor:
         out = torch.empty(x.shape[0], self.intermediate, dtype=act_dtype, device=x.device)
-        if self.block and K.tc_gemm_supported(x, self.weight):
+        if self.block and x.shape[0] <= GEMV_TOKENS and K.gemv_supported(x, self.weight):
+            K.gemv(x, self.weight, out, K.TC_SILU_MUL, self.block)
+        elif self.block and K.tc_gemm_supported(x, self.weight):
             K.tc_gemm(x, self.weight, out, K.TC_SILU_MUL, 2 * self.block)
         else:
             gu = self.plain(x, out_dtype=act_dtype)

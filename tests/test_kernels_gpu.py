@@ -332,3 +332,92 @@ def test_flash_ignores_junk_beyond_the_sequence(K):
     """Rows of the last page beyond the sequence's end hold huge values; no query may see them."""
     for fn, counts, before in ((flash_prefill_fn(K), [70], [0]), (flash_decode_fn(K), [1], [69])):
         attention_case(K, fn, 4, 2, 64, torch.bfloat16, counts, before, None, 5, 6e-3)
+
+
+# ------------------------------------------------------------------ tensor-core products (bfloat16)
+def interleave(gate, up, h):
+    I = gate.shape[0]
+    return torch.stack([gate.reshape(I // h, h, -1), up.reshape(I // h, h, -1)], dim=1).reshape(2 * I, -1).contiguous()
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 8, 8), (1, 333, 72), (8, 3072, 2048), (3, 100, 200), (16, 2048, 8192),
+                                    (17, 72, 96), (32, 520, 264), (64, 2048, 2048), (33, 7, 40)])
+def test_gemv(K, M, N, K_):
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, K_).bfloat16()
+    w = torch.randn(N, K_).bfloat16()
+    ref = x.double() @ w.double().t()
+    for odt, tol in ((torch.float32, 3e-6), (torch.bfloat16, 4e-3)):
+        out = torch.full((M, N), 9.0, dtype=odt, device=DEV)
+        K.gemv(x.to(DEV), w.to(DEV), out)
+        close(out, ref, tol, f"store {odt}")
+    base = torch.randn(M, N)
+    acc = base.clone().to(DEV)
+    K.gemv(x.to(DEV), w.to(DEV), acc, mode=K.TC_ACCUMULATE)
+    close(acc, ref + base.double(), 3e-6, "accumulate")
+
+
+@pytest.mark.parametrize("M,I,K_,h", [(1, 64, 72, 64), (8, 8192, 2048, 128), (5, 192, 64, 64), (20, 256, 96, 128),
+                                      (64, 384, 200, 64)])
+def test_gemv_silu_mul(K, M, I, K_, h):
+    torch.manual_seed(I + M)
+    x = torch.randn(M, K_).bfloat16()
+    g, u = (torch.randn(I, K_) * 0.2).bfloat16(), (torch.randn(I, K_) * 0.2).bfloat16()
+    ref = P.silu(x.double() @ g.double().t()) * (x.double() @ u.double().t())
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    K.gemv(x.to(DEV), interleave(g, u, h).to(DEV), out, mode=K.TC_SILU_MUL, pair=h)
+    close(out, ref, 4e-3)
+
+
+def test_gemv_is_repeatable_and_row_independent(K):
+    torch.manual_seed(9)
+    x = torch.randn(8, 2048, device=DEV).bfloat16()
+    w = torch.randn(512, 2048, device=DEV).bfloat16()
+    a = torch.empty(8, 512, device=DEV)
+    b = torch.empty(8, 512, device=DEV)
+    K.gemv(x, w, a)
+    K.gemv(x, w, b)
+    assert torch.equal(a, b)
+    one = torch.empty(1, 512, device=DEV)
+    K.gemv(x[5:6].contiguous(), w, one)
+    assert torch.equal(one[0], a[5])
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(128, 128, 64, 128), (100, 72, 96, 128), (1, 333, 72, 128), (300, 200, 200, 128),
+                                       (257, 520, 136, 256), (2048, 3072, 2048, 256), (129, 256, 8, 256)])
+def test_tc_gemm(K, M, N, K_, bn):
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K_).bfloat16()
+    w = torch.randn(N, K_).bfloat16()
+    ref = a.double() @ w.double().t()
+    for odt, tol in ((torch.float32, 3e-6), (torch.bfloat16, 4e-3)):
+        out = torch.full((M, N), 9.0, dtype=odt, device=DEV)
+        K.tc_gemm(a.to(DEV), w.to(DEV), out, bn=bn)
+        close(out, ref, tol, f"store {odt}")
+    base = torch.randn(M, N)
+    acc = base.clone().to(DEV)
+    K.tc_gemm(a.to(DEV), w.to(DEV), acc, mode=K.TC_ACCUMULATE, bn=bn)
+    close(acc, ref + base.double(), 3e-6, "accumulate")
+    K.check_status(DEV)
+
+
+@pytest.mark.parametrize("M,I,K_,bn", [(200, 256, 96, 128), (130, 1024, 72, 256), (64, 192, 64, 128)])
+def test_tc_gemm_silu_mul(K, M, I, K_, bn):
+    torch.manual_seed(I)
+    a = torch.randn(M, K_).bfloat16()
+    g, u = (torch.randn(I, K_) * 0.2).bfloat16(), (torch.randn(I, K_) * 0.2).bfloat16()
+    ref = P.silu(a.double() @ g.double().t()) * (a.double() @ u.double().t())
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    K.tc_gemm(a.to(DEV), interleave(g, u, bn // 2).to(DEV), out, mode=K.TC_SILU_MUL, bn=bn)
+    close(out, ref, 4e-3)
+    K.check_status(DEV)
+
+
+def test_tc_gemm_refuses_rows_that_tma_cannot_fetch(K):
+    a = torch.randn(4, 12, device=DEV).bfloat16()
+    w = torch.randn(4, 12, device=DEV).bfloat16()
+    assert not K.tc_gemm_supported(a, w) and not K.gemv_supported(a, w)
+    with pytest.raises(K.KernelError, match="multiples of 8"):
+        K.tc_gemm(a, w, torch.empty(4, 4, device=DEV))
+    with pytest.raises(K.KernelError, match="multiples of 8"):
+        K.gemv(a, w, torch.empty(4, 4, device=DEV))

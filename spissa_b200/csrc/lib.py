@@ -285,7 +285,7 @@ def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh
 def flash_decode_plan(n_seqs: int, nkv: int, max_len: int, page_size: int = 64) -> tuple:
     """(tiles per chunk, chunks): enough CTAs to fill the GPU, at most one chunk per key tile."""
     tiles = max(1, (max_len + page_size - 1) // page_size)
-    want = max(1, -(-296 // max(1, n_seqs * nkv)))
+    want = max(1, -(-592 // max(1, n_seqs * nkv)))
     n_chunks = min(tiles, want)
     chunk_tiles = -(-tiles // n_chunks)
     n_chunks = -(-tiles // chunk_tiles)

@@ -50,7 +50,7 @@ class Engine:
     PAGE_SIZE = 64
 
     def __init__(self, config, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
-                 device="cuda:0"):
+                 device="cuda:0", use_graphs: bool = True):
         self.device = _require_gpu(device)
         self.config = config
         self.dtype = _DTYPES[dtype]
@@ -66,28 +66,33 @@ class Engine:
         self.vocab_size = self.model.spec.vocab_size
         self.max_position = self.model.spec.max_position
         self.steps_run = 0
+        # decode steps replay CUDA graphs once a (batch size, length bucket) has been seen before
+        self.use_graphs = use_graphs and self.model.graph_safe()
+        self._graphs: dict = {}
+        self._graph_seen: dict = {}
+        self.max_graphs = 24
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
-                    device="cuda:0") -> "Engine":
+                    device="cuda:0", use_graphs: bool = True) -> "Engine":
         dev = _require_gpu(device)
         config = load_config(folder)
         model = Model(config.to_spec())
         tensors = load_tensors(folder, model.weight_specs(), dev, _DTYPES[dtype] == torch.float32)
-        return cls(config, tensors, dtype, max_tokens, max_seqs, device)
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int = 4096,
                     max_seqs: int | None = None, device="cuda:0", std: float = 0.02,
-                    norm_std: float = 0.0) -> "Engine":
+                    norm_std: float = 0.0, use_graphs: bool = True) -> "Engine":
         """Random weights drawn on the device (no file); the same generator rule as the folder writer."""
         dev = _require_gpu(device)
         model = Model(config.to_spec())
         tensors = random_tensors(model.weight_specs(), seed, std, norm_std, torch.bfloat16, device=dev)
         if _DTYPES[dtype] == torch.float32:
             tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
-        return cls(config, tensors, dtype, max_tokens, max_seqs, device)
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs)
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:
@@ -150,8 +155,32 @@ class Engine:
         counts = [(slot, len(toks)) for slot, toks, _ in ents]
         with torch.cuda.device(self.device):
             tables = self.cache.reserve(counts)
-            batch = pack_step(ents, lengths, tables, self.device)
-            logits = self.model.forward(batch, self.cache)
+            graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+            if graph is not None:
+                full = graph.run([t[0] for _, t, _ in ents], lengths, [s for s, _, _ in ents], tables)
+                if all(len(w) == 1 for _, _, w in ents):
+                    logits = full.clone()        # the graph's own tensor is overwritten by the next replay
+                else:
+                    rows = [b for b, (_, _, w) in enumerate(ents) for _ in w]
+                    logits = full[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else full[:0]
+            else:
+                batch = pack_step(ents, lengths, tables, self.device)
+                logits = self.model.forward(batch, self.cache)
         self.cache.commit(counts)
         self.steps_run += 1
         return logits
+
+    def _decode_graph(self, ents, lengths):
+        """The graph for this decode step, or None when the step runs kernel by kernel."""
+        if any(len(t) != 1 for _, t, _ in ents):
+            return None
+        from .graph import DecodeGraph, length_bucket
+        key = (len(ents), length_bucket(max(lengths) + 1, self.page_size))
+        g = self._graphs.get(key)
+        if g is None:
+            seen = self._graph_seen.get(key, 0) + 1
+            self._graph_seen[key] = seen
+            if seen < 2 or len(self._graphs) >= self.max_graphs:
+                return None                      # the first step of a kind also warms every kernel up
+            g = self._graphs[key] = DecodeGraph(self, *key)
+        return g

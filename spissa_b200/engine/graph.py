@@ -1,0 +1,92 @@
+"""CUDA graphs for decode steps: one token per sequence, launch-bound when run kernel by kernel.
+
+A graph is captured per (batch size, length bucket): the bucket (a power of two of tokens)
+fixes the width of the page tables and the way the decode attention splits the keys, so that
+every launch in the graph has fixed arguments. The step's varying data (tokens, positions,
+slots, lengths, page tables) live in static device buffers that are refreshed with one small
+copy before each replay; page tables are copied only when they changed.
+"""
+from __future__ import annotations
+
+import torch
+
+from .batch import StepBatch
+
+
+def length_bucket(max_len: int, page_size: int) -> int:
+    b = 4 * page_size
+    while b < max_len:
+        b *= 2
+    return b
+
+
+class DecodeGraph:
+    RING = 4
+
+    def __init__(self, engine, n_seqs: int, bucket: int):
+        self.engine, self.B, self.bucket = engine, n_seqs, bucket
+        dev = engine.device
+        B = n_seqs
+        self.P = bucket // engine.page_size
+        self.groups = list(engine.cache.kv_groups)
+        self.n_dyn = 4 * B
+        self.n_tab = B * self.P
+        total = self.n_dyn + self.n_tab * len(self.groups)
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.pinned = [torch.zeros(total, dtype=torch.int32, pin_memory=True) for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        ar = torch.arange(B + 1, dtype=torch.int32, device=dev)
+        tables = {g: self.dev[self.n_dyn + i * self.n_tab:self.n_dyn + (i + 1) * self.n_tab].view(B, self.P)
+                  for i, g in enumerate(self.groups)}
+        self.batch = StepBatch(
+            n_tokens=B, n_seqs=B, tokens=self.dev[0:B], positions=self.dev[B:2 * B], token_seq=ar[:B],
+            seq_start=ar, seq_slot=self.dev[2 * B:3 * B], seq_row=ar[:B], seq_len=self.dev[3 * B:4 * B],
+            want_rows=ar[:B], n_want=B, max_new=1, max_len=bucket, all_single=True, n_q_tiles=B,
+            page_tables=tables, host={})
+        self.last_tables = None
+        self.graph = None
+        self.logits = None
+        self.kernels = 0
+
+    def _upload(self, tokens, positions, slots, tables: dict) -> None:
+        B = self.B
+        i = self.turn % self.RING
+        self.turn += 1
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        buf = self.pinned[i]
+        dyn = list(tokens) + list(positions) + list(slots) + [p + 1 for p in positions]
+        buf[:self.n_dyn] = torch.tensor(dyn, dtype=torch.int32)
+        flat_tables = [tables[g] for g in self.groups]
+        if flat_tables != self.last_tables:
+            rows = []
+            for t in flat_tables:
+                for r in t:
+                    rows.extend(r)
+                    rows.extend([0] * (self.P - len(r)))
+            buf[self.n_dyn:] = torch.tensor(rows, dtype=torch.int32)
+            self.dev.copy_(buf, non_blocking=True)
+            self.last_tables = [[list(r) for r in t] for t in flat_tables]
+        else:
+            self.dev[:self.n_dyn].copy_(buf[:self.n_dyn], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+    def run(self, tokens, positions, slots, tables: dict) -> torch.Tensor:
+        """Logits [B, vocab] of the step; the tensor is reused by the next replay."""
+        self._upload(tokens, positions, slots, tables)
+        from ..csrc import lib
+        if self.graph is None:
+            eng = self.engine
+            graph = torch.cuda.CUDAGraph()
+            before = lib.launches
+            with torch.cuda.graph(graph):
+                self.logits = eng.model.forward(self.batch, eng.cache)
+            self.kernels = lib.launches - before         # kernels the graph holds
+            lib.launches = before
+            self.graph = graph
+        self.graph.replay()
+        lib.launches += self.kernels
+        return self.logits

@@ -47,6 +47,12 @@ class Model:
         for p in self.parts():
             p.bind_all(tensors, rt)
 
+    def graph_safe(self) -> bool:
+        """True when every part only launches kernels with device-side arguments (can be captured)."""
+        def safe(p):
+            return getattr(p, "graph_safe", False) and all(safe(c) for c in p.children())
+        return all(safe(p) for p in self.parts())
+
     # ------------------------------------------------------------------ cache needs
     def cache_requests(self) -> dict:
         """cache id -> what the layer that writes it asks for."""

@@ -26,6 +26,8 @@ from .registry import build_part, register_part
 
 @register_part("mixer", "attention")
 class GQAAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position=None, window=None, prefix: str = "", names: dict | None = None):
         super().__init__(prefix)

@@ -70,7 +70,14 @@ class Runtime:
 
 
 class Part:
-    """Shared plumbing: the weight list, and taking bound tensors."""
+    """Shared plumbing: the weight list, and taking bound tensors.
+
+    ``graph_safe``: the part's ``forward`` only launches work whose arguments live on the
+    device (nothing is read from ``step.host``), so a decode step may be captured in a CUDA
+    graph. The built-in parts say True; a part that does not say so makes its model run
+    kernel by kernel.
+    """
+    graph_safe = False
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix

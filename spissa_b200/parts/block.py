@@ -12,6 +12,8 @@ from .registry import build_part, register_part
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):
+    graph_safe = True
+
     def __init__(self, mixer, ffn, norms: dict, prefix: str = ""):
         super().__init__(prefix)
         self.mixer = build_part("mixer", mixer)

@@ -17,6 +17,8 @@ from .registry import register_part
 
 @register_part("embedding", "embedding")
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, prefix: str = "", weight_name: str = "weight"):
         super().__init__(prefix)
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
@@ -39,6 +41,8 @@ class TokenEmbedding(Part):
 
 @register_part("head", "lm_head")
 class LMHead(Part):
+    graph_safe = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied_to: str | None = None, prefix: str = "",
                  weight_name: str = "weight"):
         super().__init__(prefix)

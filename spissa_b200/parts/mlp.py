@@ -15,6 +15,8 @@ from .registry import register_part
 
 @register_part("ffn", "swiglu")
 class SwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int, prefix: str = "", names: dict | None = None):
         super().__init__(prefix)
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)

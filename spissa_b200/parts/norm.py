@@ -14,6 +14,8 @@ from .registry import register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, prefix: str = "", weight_name: str = "weight"):
         super().__init__(prefix)
         self.size = int(size)

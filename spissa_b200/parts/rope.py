@@ -49,6 +49,8 @@ def rotary_inv_freq(theta: float, rotary_dim: int, scaling: dict | None) -> torc
 
 @register_part("position", "rotary")
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, theta: float, rotary_dim: int, scaling: dict | None = None, prefix: str = ""):
         super().__init__(prefix)
         self.theta = float(theta)

@@ -197,3 +197,35 @@ def test_step_refusals_leave_the_cache_alone(folders):
     engine.cache.check()
     out = engine.step([(s, [4], [0])])
     assert out.shape == (1, 256) and engine.length(s) == 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_graph_replay_equals_kernel_by_kernel(folders, name, dtype):
+    """Decode steps replayed from CUDA graphs give the logits of the same steps launched one by one,
+    while sequences leave the batch, lengths cross pages and the length bucket changes."""
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    lens = [250, 3, 61, 120]
+    seqs = [tiny.random_prompt(V, n + 40, 17 * n) for n in lens]
+    outs = []
+    for use_graphs in (False, True):
+        engine = Engine.from_folder(folder, dtype=dtype, max_tokens=64 * 12, use_graphs=use_graphs)
+        slots = [engine.acquire() for _ in seqs]
+        rows = [engine.step([(s, q[:n], [n - 1]) for s, q, n in zip(slots, seqs, lens)]).cpu()]
+        live = list(range(len(seqs)))
+        for i in range(40):
+            if i in (9, 20):                                  # a sequence ends earlier
+                engine.release(slots[live.pop(1)])
+            want = [[0] if (i + b) % 5 else [] for b in live]  # some steps want nothing of a sequence
+            rows.append(engine.step([(slots[b], [seqs[b][lens[b] + i]], wn) for b, wn in zip(live, want)]).cpu())
+        outs.append(torch.cat(rows))
+        if use_graphs:
+            assert len(engine._graphs) >= 3
+        engine.cache.check()
+    assert outs[0].shape == outs[1].shape
+    scale = float(outs[0].abs().max())
+    assert float((outs[0] - outs[1]).abs().max()) <= tiny.TOL[dtype] * scale
+    # and both are right
+    ref = P.model_logits(pcfg, w, seqs[0][:lens[0]], torch.float64)[-1]
+    assert float((outs[1][0].double() - ref).abs().max()) <= tiny.TOL[dtype] * float(ref.abs().max())

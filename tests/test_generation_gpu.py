@@ -229,3 +229,42 @@ def test_graph_replay_equals_kernel_by_kernel(folders, name, dtype):
     # and both are right
     ref = P.model_logits(pcfg, w, seqs[0][:lens[0]], torch.float64)[-1]
     assert float((outs[1][0].double() - ref).abs().max()) <= tiny.TOL[dtype] * float(ref.abs().max())
+
+
+def test_chat_session_keeps_its_cache_across_turns(folders):
+    """Two turns through one slot equal a whole recompute of the visible history
+    (the reference's check: crates/spissa-cli/src/commands/chat_session_token.rs:88-102)."""
+    from spissa_b200.engine.session import ChatSession
+    folder, pcfg, w = folders["A"]
+    engine = Engine.from_folder(folder, dtype="float32", max_tokens=256, max_seqs=1)
+    session = ChatSession(engine)
+    turn1, turn2 = tiny.random_prompt(256, 9, 1), tiny.random_prompt(256, 4, 2)
+    r1 = session.generate_turn(turn1, 5, stop_ids=[])
+    assert r1.tokens == P.generate_greedy(pcfg, w, turn1, 5)
+    assert engine.length(session.slot) == len(turn1) + 4          # the last token is not cached yet
+    r2 = session.generate_turn(turn2, 6, stop_ids=[])
+    assert r2.tokens == P.generate_greedy(pcfg, w, turn1 + r1.tokens + turn2, 6)
+    assert session.history == turn1 + r1.tokens + turn2 + r2.tokens
+    with pytest.raises(ValueError, match="limit"):
+        session.generate_turn([1], 10_000)
+    session.close()
+    assert engine.cache.slots.held_count == 0
+
+
+def test_command_line_generate(folders, tmp_path):
+    import os, subprocess, sys
+    folder, pcfg, w = folders["B"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    logits_out = tmp_path / "l.json"
+    proc = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "spissa-b200"), "generate", folder, "--token-ids", "5,6,7",
+         "--token-ids", "9", "--max-new-tokens", "4", "--dtype", "fp32", "--ctx", "64", "--stop-ids", "100000",
+         "--logits-out", str(logits_out)],
+        capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(l) for l in proc.stdout.strip().splitlines()]
+    assert lines[0]["tokens"] == P.generate_greedy(pcfg, w, [5, 6, 7], 4)
+    assert lines[1]["tokens"] == P.generate_greedy(pcfg, w, [9], 4)
+    first = torch.tensor(json.loads(logits_out.read_text())["first_step_logits"][0], dtype=torch.float64)
+    ref = P.model_logits(pcfg, w, [5, 6, 7], torch.float64)[-1]
+    assert float((first - ref).abs().max()) <= tiny.TOL["float32"] * float(ref.abs().max())

@@ -131,6 +131,103 @@ def ragged_lengths(batch, seed):
     return lens
 
 
+def kernel_case(name: str, reps: int) -> int:
+    """One kernel of the step alone, at the 1B shape, on rotating buffers larger than L2.
+
+    Prints one JSON line with its time and its fraction of the measured peak. This is what the
+    ncu summaries under profiles/ were captured from (``--kernel-case NAME --reps 3``).
+    """
+    import math
+    import torch
+    from types import SimpleNamespace
+    from spissa_b200.csrc import lib as K
+    peaks = load_peaks()
+    dev = torch.device("cuda:0")
+    torch.manual_seed(0)
+    H, I, V, nh, nkv, hd, T = 2048, 8192, 128256, 32, 8, 64, PROMPT
+    bf = torch.bfloat16
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device=dev) * 0.05).to(bf)
+
+    flops = bytes_ = 0.0
+    if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
+        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 128),
+                           "gemm_gate_up": (2 * I, H, K.TC_SILU_MUL, 256),
+                           "gemm_down": (H, I, K.TC_ACCUMULATE, 128)}[name]
+        n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [rnd(N, Kd) for _ in range(n_buf)]
+        a = rnd(T, Kd)
+        out = torch.zeros(T, N // 2 if mode == K.TC_SILU_MUL else N,
+                          dtype=torch.float32 if mode == K.TC_ACCUMULATE else bf, device=dev)
+        run = lambda i: K.tc_gemm(a, ws[i % n_buf], out, mode, bn)
+        flops = 2.0 * T * N * Kd
+    elif name in ("gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_head"):
+        N, Kd, mode = {"gemv_qkv": (3072, H, K.TC_STORE), "gemv_o": (H, H, K.TC_ACCUMULATE),
+                       "gemv_gate_up": (2 * I, H, K.TC_SILU_MUL), "gemv_down": (H, I, K.TC_ACCUMULATE),
+                       "gemv_head": (V, H, K.TC_STORE)}[name]
+        n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [rnd(N, Kd) for _ in range(n_buf)]
+        x = rnd(8, Kd)
+        out = torch.zeros(8, N // 2 if mode == K.TC_SILU_MUL else N,
+                          dtype=bf if mode == K.TC_SILU_MUL else torch.float32, device=dev)
+        run = lambda i: K.gemv(x, ws[i % n_buf], out, mode, 128)
+        bytes_ = N * Kd * 2.0
+    elif name in ("flash_prefill", "flash_decode"):
+        B = 1 if name == "flash_prefill" else 8
+        n_new = T if name == "flash_prefill" else 1
+        pages = B * (T // 64)
+        n_buf = 1 if name == "flash_prefill" else 40           # 40 x 8.4 MB of keys and values > L2
+        pools = [(rnd(pages, nkv, 64, hd), rnd(pages, nkv, 64, hd)) for _ in range(n_buf)]
+        table = torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64)
+        ar = torch.arange(B, dtype=torch.int32, device=dev)
+        meta = SimpleNamespace(page_table=table, page_size=64, seq_slot=ar,
+                               positions=(torch.arange(n_new, dtype=torch.int32, device=dev) + (T - n_new)).repeat(B),
+                               token_seq=ar.repeat_interleave(n_new))
+        q = rnd(B * n_new, nh * hd)
+        out = torch.empty_like(q)
+        scale = 1.0 / math.sqrt(hd)
+        if name == "flash_prefill":
+            seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+            run = lambda i: K.flash_prefill(q, pools[0][0], pools[0][1], out, meta, seq_start, 1, T // 64, nh, nkv,
+                                            hd, None, scale)
+            flops = 4.0 * (T * (T + 1) / 2) * hd * nh
+        else:
+            seq_len = torch.full((B,), T, dtype=torch.int32, device=dev)
+            ct, nc = K.flash_decode_plan(B, nkv, T)
+            scratch = torch.empty(K.flash_decode_scratch_floats(B, nh, hd, nc), device=dev)
+            run = lambda i: K.flash_decode(q, pools[i % n_buf][0], pools[i % n_buf][1], out, meta, seq_len, nh, nkv,
+                                           hd, None, scale, ct, nc, scratch)
+            bytes_ = B * T * nkv * hd * 2 * 2.0
+    else:
+        print("unknown kernel case", name)
+        return 2
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    # the launches are replayed from a CUDA graph so that the host's launch cost is not in the number
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for i in range(reps):
+            run(3 + i)
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    K.check_status(dev)
+    us = e0.elapsed_time(e1) * 1000.0 / reps
+    line = {"kernel_case": name, "us": round(us, 2), "reps": reps, "peaks": peaks["source"]}
+    if flops:
+        line.update(tflops=round(flops / us / 1e6, 1), frac=round(flops / us / 1e6 / peaks["bf16_tflops"], 4))
+    if bytes_:
+        line.update(gbs=round(bytes_ / us / 1e3, 1), frac=round(bytes_ / us / 1e3 / peaks["hbm_gbs"], 4))
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -140,7 +237,13 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
+    ap.add_argument("--kernel-case", default=None,
+                    help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
+                         "gemv_down|gemv_head|flash_prefill|flash_decode) instead of the step")
+    ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
+    if args.kernel_case:
+        return kernel_case(args.kernel_case, args.reps)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

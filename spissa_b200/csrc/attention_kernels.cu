@@ -270,13 +270,48 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     }
 }
 
+// The CTA that finishes last for a (sequence, kv head) combines all chunks of its G heads, in chunk
+// order whatever the order of arrival, and hands the counter back at zero for the next launch.
+template <int HD>
+__device__ __forceinline__ void combine_if_last(const float* part_o, const float* part_ml, int* counters, void* out,
+                                                int out_dt, int b, int g, int G, int nh, int nkv, int n_chunks,
+                                                int* is_last) {
+    __threadfence();                                    // this CTA's partials are visible before it is counted
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(&counters[b * nkv + g], 1);
+        *is_last = (prev == n_chunks - 1);
+        if (*is_last) counters[b * nkv + g] = 0;
+    }
+    __syncthreads();
+    if (!*is_last) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < G * HD; e += blockDim.x) {
+        const int row = e / HD, d = e % HD;
+        const size_t bh = (size_t)b * nh + (size_t)g * G + row;
+        float mm = -INFINITY;
+        for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, __ldcg(&part_ml[(bh * n_chunks + c) * 2]));
+        const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+        float ll = 0.0f, acc = 0.0f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const float lc = __ldcg(&part_ml[(bh * n_chunks + c) * 2 + 1]);
+            if (lc > 0.0f) {
+                const float f = exp2f(__ldcg(&part_ml[(bh * n_chunks + c) * 2]) - msafe);
+                ll += lc * f;
+                acc += __ldcg(&part_o[(bh * n_chunks + c) * HD + d]) * f;
+            }
+        }
+        sp_st_dt(out, out_dt, bh * HD + d, acc / ll);
+    }
+}
+
 // ------------------------------------------------------------------ decode
 // grid (chunks, kv heads, sequences). part_o [B][nh][chunks][HD], part_ml [B][nh][chunks][2] (m in log2 units).
 template <int HD>
 __global__ void __launch_bounds__(128)
 flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* __restrict__ seq_len, int nh,
                     int window, float scale_log2, int chunk_tiles, float* __restrict__ part_o,
-                    float* __restrict__ part_ml) {
+                    float* __restrict__ part_ml, int* __restrict__ counters, void* __restrict__ out, int out_dt) {
     using T = Tile<HD>;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t q_tile = smem_u32(smem);                       // 16 rows used
@@ -292,11 +327,13 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     const int j_last = min(p / KT, j_first + chunk_tiles - 1);
     const size_t part_base = ((size_t)b * nh + (size_t)g * G) * n_chunks + chunk;   // + head_in_group * n_chunks
 
+    __shared__ int is_last;
     if (j_first > j_last) {                                        // nothing for this chunk
         for (int i = tid; i < G; i += 128) {
             part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
             part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
         }
+        if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last);
         return;
     }
     const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
@@ -378,6 +415,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         part_o[pi * HD + d] = acc;
         if (d == 0) { part_ml[pi * 2] = mm; part_ml[pi * 2 + 1] = ll; }
     }
+    if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last);
 }
 
 // out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order
@@ -452,7 +490,9 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     return 0;
 }
 
-// Bytes of float32 scratch the decode pair needs: part_o then part_ml.
+// Floats of scratch the decode kernels need: part_o then part_ml. ``counters`` (optional, n_seqs·nkv ints,
+// zero before the first launch; the kernel returns them to zero) lets the last CTA combine the chunks;
+// without it a second kernel does.
 SP_API long long sp_flash_decode_scratch_floats(int n_seqs, int nh, int hd, int n_chunks) {
     return (long long)n_seqs * nh * n_chunks * (hd + 2);
 }
@@ -460,7 +500,7 @@ SP_API long long sp_flash_decode_scratch_floats(int n_seqs, int nh, int hd, int 
 SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
                            const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
                            int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
-                           int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats,
+                           int chunk_tiles, int n_chunks, float* scratch, long long scratch_floats, int* counters,
                            cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
@@ -477,15 +517,17 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     if (hd == 64) {
         static bool ok = false;
         if (!ok) { if (opt_in_smem(flash_decode_kernel<64>, decode_smem<64>(), "flash_decode")) return 1; ok = true; }
-        flash_decode_kernel<64><<<grid, 128, decode_smem<64>(), stream>>>(
-            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml);
+        SP_CHECK_CALL("flash_decode", sp_launch_cluster(flash_decode_kernel<64>, grid, dim3(128), decode_smem<64>(), stream, 1,
+                                                   (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles,
+                                                   part_o, part_ml, counters, out, out_dt));
     } else {
         static bool ok = false;
         if (!ok) { if (opt_in_smem(flash_decode_kernel<128>, decode_smem<128>(), "flash_decode")) return 1; ok = true; }
-        flash_decode_kernel<128><<<grid, 128, decode_smem<128>(), stream>>>(
-            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml);
+        SP_CHECK_CALL("flash_decode", sp_launch_cluster(flash_decode_kernel<128>, grid, dim3(128), decode_smem<128>(), stream,
+                                                   1, (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles,
+                                                   part_o, part_ml, counters, out, out_dt));
     }
-    SP_CHECK_LAUNCH("flash_decode");
+    if (counters) return 0;                  // the last CTA of every (sequence, kv head) has combined
     if (out_dt == SP_DT_BF16)
         decode_combine_kernel<__nv_bfloat16><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_chunks, hd);
     else

@@ -78,3 +78,33 @@ __device__ __forceinline__ float sp_block_max(float v, float* scratch) {
     r = sp_warp_max(r);
     return r;
 }
+
+// ---------------------------------------------------------------- launches with a cluster dimension
+// ``cluster_x`` CTAs that follow one another in x form a thread-block cluster (1 = none).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t sp_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t stream, int cluster_x, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    int n = 0;
+    if (cluster_x > 1) {
+        attrs[n].id = cudaLaunchAttributeClusterDimension;
+        attrs[n].val.clusterDim.x = (unsigned)cluster_x;
+        attrs[n].val.clusterDim.y = 1;
+        attrs[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
+#define SP_CHECK_CALL(name, call)                                                   \
+    do {                                                                           \
+        cudaError_t e_ = (call);                                                   \
+        if (e_ != cudaSuccess) SP_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
+    } while (0)

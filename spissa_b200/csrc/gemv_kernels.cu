@@ -3,14 +3,17 @@
 // The step is bound by streaming W from HBM once (the reference's batch-1 path streams rows
 // the same way, crates/spissa-runtime/src/streaming/kernels_raw16.rs:532-692, and fuses
 // silu(gate)·up at batch 1, crates/spissa-runtime/src/streaming/linear_multiply.rs:376-497).
-// A warp owns RT groups of 8 rows of W and a slice of K. Per 32 columns of K each lane loads
-// 16 contiguous bytes of "its" row of W straight from global memory, and 16 bytes of x per
-// 8-token group (x is small and stays in L1/L2); both feed mma.sync m16n8k16 with the tokens
-// as the 16 rows of A and 8 rows of W as the columns of B. The K positions inside a 32-block are
-// permuted the same way for both operands, which leaves the sum unchanged. The KS warps of a
-// CTA split K; their partial sums are added in warp order in shared memory, so the result does
-// not depend on timing. Epilogues: store, add into a float32 tensor, or silu(gate)·up when the
-// weight interleaves gate and up rows in blocks.
+//
+// A CTA owns RT groups of 8 rows of W and one slice of K; the CTAs of a thread-block cluster
+// (1, 2, 4 or 8) own the slices of the same rows, and the warps of a CTA split its slice again.
+// Per 32 columns of K each lane loads 16 contiguous bytes of "its" row of every row group straight
+// from global memory, and 16 bytes of x per 8-token group (x is small and stays in L1/L2); both
+// feed mma.sync m16n8k16 with the tokens as the 16 rows of A and 8 rows of W as the columns of B.
+// The K positions inside a 32-block are permuted the same way for both operands, which leaves the
+// sum unchanged. Partial sums are added in warp order in shared memory, then in cluster-rank order
+// by rank 0, which reads its peers' shared memory; the result does not depend on timing or on M.
+// Epilogues: store, add into a float32 tensor, or silu(gate)·up when the weight interleaves gate
+// and up rows in blocks of ``pair``.
 #include "common.cuh"
 
 SP_API const char* sp_gemv_last_error() { return sp_error_text; }
@@ -34,38 +37,65 @@ __device__ __forceinline__ uint4 ld_stream(const void* p) {          // weights:
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint4 ld_keep(const void* p) {            // activations: reused by every warp
+__device__ __forceinline__ uint4 ld_act(const void* p) {             // activations: reused by every CTA, keep in L1
     uint4 v;
     asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
-// MT: groups of 16 tokens; RT: groups of 8 rows of W per warp; UNROLL: 32-column blocks in flight.
-// For MODE_SILU_MUL RT must be 2: row group 0 is gate rows, group 1 the up rows ``pair`` rows further on.
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f4(const void* local, uint32_t rank) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(local);
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(ra) : "memory");
+    return v;
+}
+
+// MT: groups of 16 tokens; RT: groups of 8 rows of W per CTA; UNROLL: 32-column blocks requested at once.
+// MODE_SILU_MUL: the first RT/2 row groups are gate rows, the others the up rows ``pair`` rows further on.
 template <int MT, int RT, int UNROLL>
 __global__ void __launch_bounds__(MAX_KS * 32)
 gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-            int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int ks) {
-    __shared__ float red[MAX_KS][MT][RT][32][4];
+            int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int ks, int cs) {
+    __shared__ __align__(16) float red[MAX_KS][MT][RT][32][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int rank = cs > 1 ? (int)cluster_rank() : 0;
+    const int tile = blockIdx.x / cs;
 
     // rows of W this CTA owns
     int row_base[RT];
     if (mode == MODE_SILU_MUL) {
-        const int blk = (blockIdx.x * 8) / pair, within = (blockIdx.x * 8) % pair;
-        row_base[0] = blk * 2 * pair + within;
-        if (RT > 1) row_base[RT - 1] = row_base[0] + pair;
+        constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
+        const int o0 = tile * 8 * HALF;                   // first output of this CTA
+#pragma unroll
+        for (int r = 0; r < HALF; ++r) {
+            const int o = o0 + r * 8;
+            row_base[r] = (o / pair) * 2 * pair + (o % pair);
+            row_base[HALF + r < RT ? HALF + r : r] = row_base[r] + pair;
+        }
     } else {
 #pragma unroll
-        for (int r = 0; r < RT; ++r) row_base[r] = (blockIdx.x * RT + r) * 8;
+        for (int r = 0; r < RT; ++r) row_base[r] = (tile * RT + r) * 8;
     }
 
-    // this warp's slice of K, in blocks of 32 columns
+    // this warp's slice of K, in blocks of 32 columns: first by cluster rank, then by warp
     const int kblocks = (K + 31) / 32;
-    const int per = (kblocks + ks - 1) / ks;
-    const int kb0 = warp * per, kb1 = min(kblocks, kb0 + per);
+    const int per_cta = (kblocks + cs - 1) / cs;
+    const int cta0 = rank * per_cta, cta1 = min(kblocks, cta0 + per_cta);
+    const int per = (per_cta + ks - 1) / ks;
+    const int kb0 = min(cta1, cta0 + warp * per), kb1 = min(cta1, kb0 + per);
 
     float acc[MT][RT][4];
 #pragma unroll
@@ -99,8 +129,8 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
                 const int m0 = i * 16 + g, m1 = m0 + 8;
-                const uint4 xa = (kok && m0 < M) ? ld_keep(x + (size_t)m0 * ldx + k) : zero;
-                const uint4 xb = (kok && m1 < M) ? ld_keep(x + (size_t)m1 * ldx + k) : zero;
+                const uint4 xa = (kok && m0 < M) ? ld_act(x + (size_t)m0 * ldx + k) : zero;
+                const uint4 xb = (kok && m1 < M) ? ld_act(x + (size_t)m1 * ldx + k) : zero;
 #pragma unroll
                 for (int r = 0; r < RT; ++r) {
                     mma_bf16(acc[i][r], xa.x, xb.x, xa.y, xb.y, wv[u][r].x, wv[u][r].y);
@@ -110,27 +140,46 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
         }
     }
 
-    // add the K slices in warp order
-    if (ks > 1) {
+    // add the K slices of the warps in warp order ...
+    if (ks > 1 || cs > 1) {
 #pragma unroll
         for (int i = 0; i < MT; ++i)
 #pragma unroll
             for (int r = 0; r < RT; ++r)
                 *(float4*)red[warp][i][r][lane] = make_float4(acc[i][r][0], acc[i][r][1], acc[i][r][2], acc[i][r][3]);
         __syncthreads();
-        if (warp != 0) return;
+        if (warp == 0) {
 #pragma unroll
-        for (int i = 0; i < MT; ++i)
+            for (int i = 0; i < MT; ++i)
 #pragma unroll
-            for (int r = 0; r < RT; ++r) {
-                float4 s = *(float4*)red[0][i][r][lane];
-                for (int w = 1; w < ks; ++w) {
-                    const float4 v = *(float4*)red[w][i][r][lane];
-                    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                for (int r = 0; r < RT; ++r) {
+                    float4 s = *(float4*)red[0][i][r][lane];
+                    for (int w = 1; w < ks; ++w) {
+                        const float4 v = *(float4*)red[w][i][r][lane];
+                        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+                    }
+                    acc[i][r][0] = s.x; acc[i][r][1] = s.y; acc[i][r][2] = s.z; acc[i][r][3] = s.w;
+                    if (cs > 1) *(float4*)red[0][i][r][lane] = s;      // where the cluster's rank 0 looks
                 }
-                acc[i][r][0] = s.x; acc[i][r][1] = s.y; acc[i][r][2] = s.z; acc[i][r][3] = s.w;
-            }
+        }
     }
+    // ... then the K slices of the cluster in rank order
+    if (cs > 1) {
+        cluster_sync();                                    // every CTA's sum stands in its red[0]
+        if (rank == 0 && warp == 0) {
+#pragma unroll
+            for (int i = 0; i < MT; ++i)
+#pragma unroll
+                for (int r = 0; r < RT; ++r)
+                    for (int c = 1; c < cs; ++c) {
+                        const float4 v = ld_peer_f4(red[0][i][r][lane], (uint32_t)c);
+                        acc[i][r][0] += v.x; acc[i][r][1] += v.y; acc[i][r][2] += v.z; acc[i][r][3] += v.w;
+                    }
+        }
+        cluster_sync();                                    // peers keep their shared memory until rank 0 has read it
+        if (rank != 0) return;
+    }
+    if (warp != 0) return;
 
     // lane holds tokens (16i+g, 16i+g+8) x rows (2t, 2t+1) of every row group
 #pragma unroll
@@ -140,11 +189,14 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
             const int m = i * 16 + g + (e >> 1) * 8;
             if (m >= M) continue;
             if (mode == MODE_SILU_MUL) {
-                const int blk = row_base[0] / (2 * pair), within = row_base[0] % (2 * pair);
-                const int col = blk * pair + within + 2 * t + (e & 1);
-                if (col < N / 2) {
-                    const float gate = acc[i][0][e], up = acc[i][RT - 1][e];
-                    sp_st_dt(out, out_dt, (size_t)m * ldo + col, (gate / (1.0f + expf(-gate))) * up);
+                constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
+#pragma unroll
+                for (int r = 0; r < HALF; ++r) {
+                    const int col = tile * 8 * HALF + r * 8 + 2 * t + (e & 1);
+                    if (col < N / 2) {
+                        const float gate = acc[i][r][e], up = acc[i][HALF + r < RT ? HALF + r : r][e];
+                        sp_st_dt(out, out_dt, (size_t)m * ldo + col, (gate / (1.0f + expf(-gate))) * up);
+                    }
                 }
             } else {
 #pragma unroll
@@ -161,12 +213,25 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     }
 }
 
-int pick_ks(int K) {
+// How the work of one product is cut: row groups per CTA, CTAs per cluster along K, warps per CTA.
+struct Plan { int rt, cs, ks, tiles; };
+
+Plan make_plan(int M, int N, int K, int mode) {
+    Plan p;
+    const int outputs = mode == MODE_SILU_MUL ? N / 2 : N;
+    // few tokens: one row group per CTA (a gate/up pair for the fused epilogue) keeps the most CTAs in flight;
+    // more tokens: several row groups share the x fragments
+    const int wide = M <= 16 ? 1 : (M <= 32 ? 4 : 2);
+    p.rt = (mode == MODE_SILU_MUL) ? (wide < 2 ? 2 : wide) : wide;
+    const int per_tile = (mode == MODE_SILU_MUL) ? 8 * (p.rt / 2) : 8 * p.rt;
+    p.tiles = (outputs + per_tile - 1) / per_tile;
+    // a cluster splits K when one CTA's warps would need more than one round of loads for their slice
     const int kblocks = (K + 31) / 32;
-    int ks = kblocks / 8;                    // at least 8 blocks (256 columns) per warp
-    if (ks < 1) ks = 1;
-    if (ks > MAX_KS) ks = MAX_KS;
-    return ks;
+    p.cs = 1;
+    while (p.cs < 8 && kblocks > p.cs * MAX_KS * 8) p.cs *= 2;
+    const int per_cta = (kblocks + p.cs - 1) / p.cs;
+    p.ks = per_cta < MAX_KS ? (per_cta < 1 ? 1 : per_cta) : MAX_KS;
+    return p;
 }
 
 }  // namespace
@@ -188,25 +253,17 @@ SP_API int sp_gemv(const void* x, const void* W, void* out, int out_dt, int M, i
     if (mode < 0 || mode > 2) SP_FAIL("gemv: unknown mode %d", mode);
     if (mode == MODE_SILU_MUL && (pair <= 0 || (pair % 8) || N % (2 * pair)))
         SP_FAIL("gemv: the fused silu epilogue needs blocks of a multiple of 8 rows that divide N/2 (N=%d, block %d)", N, pair);
-    const int ks = pick_ks(K);
-    const int threads = ks * 32;
+    const Plan p = make_plan(M, N, K, mode);
+    const dim3 grid(p.tiles * p.cs), block(p.ks * 32);
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
-#define GV_LAUNCH(MT, RT, UN, blocks) \
-    gemv_kernel<MT, RT, UN><<<blocks, threads, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo, mode, pair, ks)
-    if (mode == MODE_SILU_MUL) {
-        const int blocks = (N / 2) / 8;
-        if (M <= 16) GV_LAUNCH(1, 2, 4, blocks);
-        else if (M <= 32) GV_LAUNCH(2, 2, 4, blocks);
-        else GV_LAUNCH(4, 2, 2, blocks);
-    } else if (M <= 16) {
-        GV_LAUNCH(1, 1, 8, (N + 7) / 8);
-    } else if (M <= 32) {
-        GV_LAUNCH(2, 2, 4, (N + 15) / 16);
-    } else {
-        GV_LAUNCH(4, 2, 2, (N + 15) / 16);
-    }
+#define GV_LAUNCH(MT, RT, UN)                                                                              \
+    SP_CHECK_CALL("gemv", sp_launch_cluster(gemv_kernel<MT, RT, UN>, grid, block, 0, stream, p.cs, xp, wp, out, out_dt, \
+                                       M, N, K, ldx, ldw, ldo, mode, pair, p.ks, p.cs))
+    if (p.rt == 4) GV_LAUNCH(2, 4, 2);
+    else if (p.rt == 2 && M <= 16) GV_LAUNCH(1, 2, 4);
+    else if (p.rt == 2) GV_LAUNCH(4, 2, 2);
+    else GV_LAUNCH(1, 1, 8);
 #undef GV_LAUNCH
-    SP_CHECK_LAUNCH("gemv");
     return 0;
 }

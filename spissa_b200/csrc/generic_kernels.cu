@@ -36,12 +36,13 @@ SP_API int sp_embed_gather(const void* table, int table_dt, const int* ids, floa
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dt == SP_DT_F32)
-        embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, T, H, V, status);
+        SP_CHECK_CALL("embed_gather", sp_launch_cluster(embed_gather_kernel<float>, dim3(T), dim3(threads), 0, stream, 1,
+                                                   (const float*)table, ids, out, T, H, V, status));
     else if (table_dt == SP_DT_BF16)
-        embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, T, H, V, status);
+        SP_CHECK_CALL("embed_gather", sp_launch_cluster(embed_gather_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream,
+                                                   1, (const __nv_bfloat16*)table, ids, out, T, H, V, status));
     else
         SP_FAIL("embed_gather: unsupported table dtype code %d", table_dt);
-    SP_CHECK_LAUNCH("embed_gather");
     return 0;
 }
 
@@ -69,13 +70,58 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const void* __restri
     }
 }
 
+// The same with each row held in registers: one read of x. For H a multiple of 4 up to 4096.
+__global__ void __launch_bounds__(256)
+rmsnorm_row_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt, void* __restrict__ out,
+                   int out_dt, const int* __restrict__ rows, int n_rows, int H, float eps) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    if (r >= n_rows) return;
+    const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
+    const int n4 = H >> 2;
+    float4 v[4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        v[i] = c < n4 ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = sp_block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + i * 256;
+        if (c >= n4) continue;
+        float wv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) wv[j] = sp_ld_dt(w, w_dt, (size_t)c * 4 + j);
+        const float o0 = v[i].x * inv * wv[0], o1 = v[i].y * inv * wv[1];
+        const float o2 = v[i].z * inv * wv[2], o3 = v[i].w * inv * wv[3];
+        const size_t o = (size_t)r * H + (size_t)c * 4;
+        if (out_dt == SP_DT_F32) {
+            *(float4*)((float*)out + o) = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
+            uint2 pk;
+            pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+            *(uint2*)((__nv_bfloat16*)out + o) = pk;
+        }
+    }
+}
+
 SP_API int sp_rmsnorm(const float* x, const void* w, int w_dt, void* out, int out_dt, const int* rows,
                       int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if ((w_dt | out_dt) & ~1) SP_FAIL("rmsnorm: unsupported dtype code");
-    // a fixed block size: the order of the row sum must not depend on the batch
-    rmsnorm_kernel<<<n_rows, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps);
-    SP_CHECK_LAUNCH("rmsnorm");
+    // fixed block sizes: the order of the row sum must not depend on the batch
+    if ((H & 3) == 0 && H <= 4096 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0)
+        SP_CHECK_CALL("rmsnorm", sp_launch_cluster(rmsnorm_row_kernel, dim3(n_rows), dim3(256), 0, stream, 1, x, w, w_dt, out,
+                                              out_dt, rows, n_rows, H, eps));
+    else
+        SP_CHECK_CALL("rmsnorm", sp_launch_cluster(rmsnorm_kernel, dim3(n_rows), dim3(256), 0, stream, 1, x, w, w_dt, out,
+                                              out_dt, rows, n_rows, H, eps));
     return 0;
 }
 
@@ -161,6 +207,9 @@ SP_API int sp_gemm_generic(const void* A, int a_dt, const void* W, int w_dt, voi
     return 0;
 }
 
+#define AG_WARPS 4
+#define AG_MAX_HD 256          // largest head size of the generic kernels
+
 // ============================================================== rope + cache write
 // qkv row t = [q heads | k heads | v heads]. Rotates q and k (rotate-half over the
 // first ``rd`` dims of each head, angle = position · inv_freq[i], all 32-bit), stores
@@ -193,14 +242,20 @@ __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict
         off = pos % pl.page_size;
     }
     const int n_rot_heads = nh + nkv;
-    // rotated heads: one thread per (head, pair) and per unrotated tail element
+    // the token's cosines and sines once, shared by every head
+    __shared__ float cs[2][AG_MAX_HD / 2];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[0][i] = cosf(ang);
+        cs[1][i] = sinf(ang);
+    }
+    __syncthreads();
     for (int e = threadIdx.x; e < n_rot_heads * hd; e += blockDim.x) {
         const int h = e / hd, d = e % hd;
         float v;
         if (d < rd) {
             const int i = d < half ? d : d - half;
-            const float ang = (float)pos * inv_freq[i];
-            const float c = cosf(ang), s = sinf(ang);
+            const float c = cs[0][i], s = cs[1][i];
             const float a = sp_ld(src, (size_t)h * hd + i);
             const float b = sp_ld(src, (size_t)h * hd + i + half);
             v = d < half ? a * c - b * s : b * c + a * s;
@@ -229,11 +284,14 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
                             int T, int nh, int nkv, int hd, int rd, int write_kv, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (rd < 0 || rd > hd || (rd & 1)) SP_FAIL("rope: rotary_dim %d must be even and at most head_dim %d", rd, hd);
+    if (rd > AG_MAX_HD) SP_FAIL("rope: rotary_dim %d is beyond this kernel's limit %d", rd, AG_MAX_HD);
     if (rd > 0 && !inv_freq) SP_FAIL("rope: a frequency table is needed when rotary_dim > 0");
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
     const int threads = 256;
-#define RK_LAUNCH(TIN, TQ, TC) \
-    rope_kv_write_kernel<TIN, TQ, TC><<<T, threads, 0, stream>>>((const TIN*)qkv, (TQ*)q_out, (TC*)kpool, (TC*)vpool, pl, inv_freq, T, nh, nkv, hd, rd, write_kv)
+#define RK_LAUNCH(TIN, TQ, TC)                                                                                  \
+    SP_CHECK_CALL("rope_kv_write", sp_launch_cluster(rope_kv_write_kernel<TIN, TQ, TC>, dim3(T), dim3(threads), 0, stream, 1, \
+                                                (const TIN*)qkv, (TQ*)q_out, (TC*)kpool, (TC*)vpool, pl, inv_freq, T, nh, \
+                                                nkv, hd, rd, write_kv))
     const int key = in_dt * 4 + q_dt * 2 + cache_dt;
     switch (key) {
         case 0: RK_LAUNCH(float, float, float); break;
@@ -247,7 +305,6 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
         default: SP_FAIL("rope: unsupported dtype codes");
     }
 #undef RK_LAUNCH
-    SP_CHECK_LAUNCH("rope_kv_write");
     return 0;
 }
 
@@ -257,8 +314,6 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
 // owns output dims d, d+32, ... . A token at position p sees keys lo..p with
 // lo = max(0, p-window+1) when window > 0, else 0. All keys, this step's included,
 // are read from the cache.
-#define AG_WARPS 4
-#define AG_MAX_HD 256
 
 template <typename TQ, typename TC>
 __global__ void __launch_bounds__(AG_WARPS * 32)
@@ -427,7 +482,7 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int* __rest
 SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (V <= 0) SP_FAIL("argmax: empty rows");
-    argmax_rows_kernel<<<rows, V >= 4096 ? 1024 : 256, 0, stream>>>(logits, out, V, ld);
-    SP_CHECK_LAUNCH("argmax_rows");
+    SP_CHECK_CALL("argmax_rows", sp_launch_cluster(argmax_rows_kernel, dim3(rows), dim3(V >= 4096 ? 1024 : 256), 0, stream, 1,
+                                              logits, out, V, ld));
     return 0;
 }

@@ -296,23 +296,28 @@ def flash_decode_scratch_floats(n_seqs: int, nh: int, hd: int, n_chunks: int) ->
     return n_seqs * nh * n_chunks * (hd + 2)
 
 
-def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks, scratch):
+def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks, scratch,
+                 counters=None):
     """One query token per sequence: keys split into chunks over CTAs, partial results combined in order.
 
     ``seq_len`` [B] int32: each sequence's length including the query token. ``scratch``: float32,
-    at least ``flash_decode_scratch_floats`` elements.
+    at least ``flash_decode_scratch_floats`` elements. ``counters``: int32, n_seqs·nkv zeros that the kernel
+    hands back as zeros; with them the last CTA of each (sequence, kv head) combines, else a second kernel.
     """
     global launches
     lib = load("attention")
     _need_contig(q, out)
     pt = meta.page_table
     n_seqs = q.shape[0]
+    if counters is not None and (counters.dtype != torch.int32 or counters.numel() < n_seqs * nkv):
+        raise KernelError("flash_decode: counters must be int32 with a word per (sequence, kv head)")
     _check("attention", lib.sp_flash_decode(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_len)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
         n_seqs, nh, nkv, hd, int(window or 0), c_float(scale), int(chunk_tiles), int(n_chunks),
-        c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_stream())))
-    launches += 1            # two kernels: the chunks and the combine
+        c_void_p(_ptr(scratch)), c_longlong(scratch.numel()), c_void_p(_ptr(counters)), c_void_p(_stream())))
+    if counters is None:
+        launches += 1        # two kernels: the chunks and the combine
 
 
 # ------------------------------------------------------------------ skinny products for decoding

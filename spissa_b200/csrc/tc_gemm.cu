@@ -220,14 +220,29 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (row >= M) continue;
                     const int out_n = N / 2;
                     const int col0 = (n0 / 2) + c0;
+                    float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int col = col0 + j;
-                        if (col < out_n) {
-                            const float g = __uint_as_float(r[j]);
-                            const float v = (g / (1.0f + expf(-g))) * __uint_as_float(u[j]);
-                            sp_st_dt(C, c_dt, (size_t)row * ldc + col, v);
+                        const float g = __uint_as_float(r[j]);
+                        v[j] = (g / (1.0f + expf(-g))) * __uint_as_float(u[j]);
+                    }
+                    const size_t base = (size_t)row * ldc + col0;
+                    if (c_dt == SP_DT_BF16 && col0 + 32 <= out_n && (base & 7) == 0) {
+                        __nv_bfloat16* out = (__nv_bfloat16*)C + base;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 w;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                            w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
+                            *(uint4*)(out + j) = w;
                         }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col0 + j < out_n) sp_st_dt(C, c_dt, base + j, v[j]);
                     }
                     continue;
                 }

@@ -62,6 +62,8 @@ class GQAAttention(Mixer):
         self.qkv = Linear(torch.cat([q, k, v], dim=0))
         self.q_only = Linear(q)
         self.o = Linear(tensors[self.names["o"]])
+        # arrival counters of the split-key decode attention; the kernel returns them to zero
+        self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
     def forward(self, x, step, cache, residual):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
@@ -88,7 +90,8 @@ class GQAAttention(Mixer):
                 need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
                 scratch = torch.empty(need, dtype=torch.float32, device=x.device)
                 K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,
-                               self.scale, chunk_tiles, n_chunks, scratch)
+                               self.scale, chunk_tiles, n_chunks, scratch,
+                               self.counters if T * nkv <= self.counters.numel() else None)
             else:
                 K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
                                 step.n_q_tiles, nh, nkv, hd, self.window, self.scale)

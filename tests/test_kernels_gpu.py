@@ -272,14 +272,19 @@ def flash_prefill_fn(K):
     return fn
 
 
-def flash_decode_fn(K, chunk_tiles=None):
+def flash_decode_fn(K, chunk_tiles=None, fused=True):
+    counters = torch.zeros(1024, dtype=torch.int32, device=DEV) if fused else None
+
     def fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
         ct, nc = K.flash_decode_plan(q.shape[0], nkv, max(meta.total_len))
         if chunk_tiles:
             ct = chunk_tiles
             nc = -(-((max(meta.total_len) + 63) // 64) // ct)
         scratch = torch.full((K.flash_decode_scratch_floats(q.shape[0], nh, hd, nc),), float("nan"), device=DEV)
-        K.flash_decode(q, k_pool, v_pool, out, meta, meta.seq_len, nh, nkv, hd, window, scale, ct, nc, scratch)
+        K.flash_decode(q, k_pool, v_pool, out, meta, meta.seq_len, nh, nkv, hd, window, scale, ct, nc, scratch,
+                       counters)
+        if fused:
+            assert int(counters.abs().sum()) == 0          # handed back at zero for the next launch
     return fn
 
 
@@ -298,8 +303,9 @@ def test_flash_prefill_window(K, window):
 
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (32, 8, 64)])
 @pytest.mark.parametrize("chunk_tiles", [None, 1, 3])
-def test_flash_decode(K, nh, nkv, hd, chunk_tiles):
-    fn = flash_decode_fn(K, chunk_tiles)
+@pytest.mark.parametrize("fused", [True, False])
+def test_flash_decode(K, nh, nkv, hd, chunk_tiles, fused):
+    fn = flash_decode_fn(K, chunk_tiles, fused)
     attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [1, 1, 1, 1, 1], [0, 63, 64, 300, 700], None, hd + 3, 6e-3)
 
 

@@ -151,6 +151,21 @@ def kernel_case(name: str, reps: int) -> int:
         return (torch.randn(*shape, device=dev) * 0.05).to(bf)
 
     flops = bytes_ = 0.0
+    if name == "step_b8":
+        # eight 2,048-token prompts one after another, then three decode steps at batch 8, kernel by kernel
+        # (no CUDA graph): the launch list of this run is what profiles/step_b8_launches.md summarises
+        from spissa_b200 import Engine, LlamaConfig
+        eng = Engine.from_config(LlamaConfig.from_dict(CONFIG_1B), seed=0, dtype="bfloat16", max_tokens=8 * CONTEXT,
+                                 max_seqs=8, use_graphs=False)
+        rng = random.Random(0)
+        slots = [eng.acquire() for _ in range(8)]
+        for sl in slots:
+            eng.step([(sl, [rng.randrange(V) for _ in range(T)], [T - 1])])
+        for i in range(3):
+            eng.step([(sl, [5 + i], [0]) for sl in slots])
+        torch.cuda.synchronize()
+        print(json.dumps({"kernel_case": name, "launches": K.launches}))
+        return 0
     if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
         N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 128),
                            "gemm_gate_up": (2 * I, H, K.TC_SILU_MUL, 256),
@@ -239,7 +254,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|flash_prefill|flash_decode) instead of the step")
+                         "gemv_down|gemv_head|flash_prefill|flash_decode|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     if args.kernel_case:

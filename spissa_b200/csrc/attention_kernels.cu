@@ -535,3 +535,74 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     SP_CHECK_LAUNCH("decode_combine");
     return 0;
 }
+
+// ------------------------------------------------------------------ decode without a caller's scratch
+// See attention_noalloc.h. The scratch of the split-key decode kernel lives here, in the library.
+#include "attention_noalloc.h"
+
+static __device__ __align__(256) float sp_static_partials[SP_FLASH_DECODE_STATIC_MAX_FLOATS];
+static __device__ __align__(256) int sp_static_counters[SP_FLASH_DECODE_STATIC_MAX_COUNTERS];
+
+namespace {
+constexpr int STATIC_MAX_DEVICES = 64;
+float* static_partials_ptr[STATIC_MAX_DEVICES];      // device addresses, looked up once per device
+int* static_counters_ptr[STATIC_MAX_DEVICES];
+}  // namespace
+
+SP_API int sp_flash_decode_static(const void* q, void* out, int out_dt, const void* kpool, const void* vpool,
+                                  const int* seq_len, const int* seq_row, const int* page_table, int max_pages,
+                                  int page_size, int n_seqs, int nh, int nkv, int hd, int window, float scale,
+                                  int chunk_tiles, int n_chunks, cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (check_common(hd, nh, nkv, page_size)) return 1;
+    if (nh / nkv > 16) SP_FAIL("flash decode: %d query heads per kv head, at most 16 fit one tile", nh / nkv);
+    if (chunk_tiles <= 0 || n_chunks <= 0 || n_chunks > 65535) SP_FAIL("flash decode: bad chunking %d x %d", n_chunks, chunk_tiles);
+    if (n_seqs > 65535) SP_FAIL("flash decode: %d sequences are beyond this kernel's grid", n_seqs);
+    if (out_dt != SP_DT_F32 && out_dt != SP_DT_BF16) SP_FAIL("flash decode: unsupported output dtype code %d", out_dt);
+    const long long need = sp_flash_decode_scratch_floats(n_seqs, nh, hd, n_chunks);
+    if (need > (long long)SP_FLASH_DECODE_STATIC_MAX_FLOATS)
+        SP_FAIL("flash decode (static scratch): %lld floats of partial results are needed, the built-in array holds %d; "
+                "use fewer chunks or the entry point that takes a scratch buffer", need, SP_FLASH_DECODE_STATIC_MAX_FLOATS);
+    if ((long long)n_seqs * nkv > (long long)SP_FLASH_DECODE_STATIC_MAX_COUNTERS)
+        SP_FAIL("flash decode (static scratch): %lld arrival counters are needed, the built-in array holds %d",
+                (long long)n_seqs * nkv, SP_FLASH_DECODE_STATIC_MAX_COUNTERS);
+
+    // the arrays' names are host-side handles; kernels need their device addresses, per device
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) SP_FAIL("flash decode (static scratch): cudaGetDevice failed: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) SP_FAIL("flash decode (static scratch): device %d is beyond the %d this build tracks", dev, STATIC_MAX_DEVICES);
+    if (!static_partials_ptr[dev]) {
+        float* pp = nullptr;
+        int* cp = nullptr;
+        e = cudaGetSymbolAddress((void**)&pp, sp_static_partials);
+        if (e != cudaSuccess || !pp) SP_FAIL("flash decode (static scratch): no address for the partial-result array: %s", cudaGetErrorString(e));
+        e = cudaGetSymbolAddress((void**)&cp, sp_static_counters);
+        if (e != cudaSuccess || !cp) SP_FAIL("flash decode (static scratch): no address for the counter array: %s", cudaGetErrorString(e));
+        static_counters_ptr[dev] = cp;
+        static_partials_ptr[dev] = pp;
+    }
+    float* part_o = static_partials_ptr[dev];
+    float* part_ml = part_o + (size_t)n_seqs * nh * n_chunks * hd;
+    int* counters = static_counters_ptr[dev];
+    // the counters must start at zero whatever an earlier, perhaps interrupted, call left there
+    e = cudaMemsetAsync(counters, 0, (size_t)n_seqs * nkv * sizeof(int), stream);
+    if (e != cudaSuccess) SP_FAIL("flash decode (static scratch): clearing the counters failed: %s", cudaGetErrorString(e));
+
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    dim3 grid(n_chunks, nkv, n_seqs);
+    const float sl = scale * LOG2E;
+    if (hd == 64) {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_decode_kernel<64>, decode_smem<64>(), "flash_decode")) return 1; ok = true; }
+        flash_decode_kernel<64><<<grid, 128, decode_smem<64>(), stream>>>(
+            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+    } else {
+        static bool ok = false;
+        if (!ok) { if (opt_in_smem(flash_decode_kernel<128>, decode_smem<128>(), "flash_decode")) return 1; ok = true; }
+        flash_decode_kernel<128><<<grid, 128, decode_smem<128>(), stream>>>(
+            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+    }
+    SP_CHECK_LAUNCH("flash_decode (static scratch)");
+    return 0;
+}

@@ -34,6 +34,12 @@ __device__ __forceinline__ float sp_ld(const __nv_bfloat16* p, size_t i) { retur
 __device__ __forceinline__ void sp_st(float* p, size_t i, float v) { p[i] = v; }
 __device__ __forceinline__ void sp_st(__nv_bfloat16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// two neighbouring elements at an even index (the arrays' rows have even length)
+__device__ __forceinline__ void sp_st2(float* p, size_t i, float a, float b) { *(float2*)(p + i) = make_float2(a, b); }
+__device__ __forceinline__ void sp_st2(__nv_bfloat16* p, size_t i, float a, float b) {
+    *(__nv_bfloat162*)(p + i) = __floats2bfloat162_rn(a, b);
+}
+
 __device__ __forceinline__ float sp_ld_dt(const void* p, int dt, size_t i) {
     return dt == SP_DT_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
 }

@@ -250,6 +250,44 @@ __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict
         cs[1][i] = sinf(ang);
     }
     __syncthreads();
+    const size_t qrow = (size_t)t * nh * hd;
+    if ((half & 1) == 0 && (hd & 1) == 0) {
+        // two neighbouring pairs per thread: 8-byte reads, one rounding and one store per two outputs
+        const int hp = half >> 1;                            // pairs of pairs per head
+        for (int e = threadIdx.x; e < n_rot_heads * hp; e += blockDim.x) {
+            const int h = e / hp, i = (e % hp) * 2;
+            const float a0 = sp_ld(src, (size_t)h * hd + i), a1 = sp_ld(src, (size_t)h * hd + i + 1);
+            const float b0 = sp_ld(src, (size_t)h * hd + half + i), b1 = sp_ld(src, (size_t)h * hd + half + i + 1);
+            const float c0 = cs[0][i], s0 = cs[1][i], c1 = cs[0][i + 1], s1 = cs[1][i + 1];
+            const float lo0 = a0 * c0 - b0 * s0, lo1 = a1 * c1 - b1 * s1;
+            const float hi0 = b0 * c0 + a0 * s0, hi1 = b1 * c1 + a1 * s1;
+            if (h < nh) {
+                sp_st2(q_out, qrow + (size_t)h * hd + i, lo0, lo1);
+                sp_st2(q_out, qrow + (size_t)h * hd + half + i, hi0, hi1);
+            } else if (write_kv) {
+                const size_t kb = (((size_t)page * nkv + (h - nh)) * pl.page_size + off) * hd;
+                sp_st2(kpool, kb + i, lo0, lo1);
+                sp_st2(kpool, kb + half + i, hi0, hi1);
+            }
+        }
+        // dims beyond the rotated ones pass through
+        const int tail = hd - rd;
+        for (int e = threadIdx.x; e < n_rot_heads * tail; e += blockDim.x) {
+            const int h = e / tail, d = rd + e % tail;
+            const float v = sp_ld(src, (size_t)h * hd + d);
+            if (h < nh) sp_st(q_out, qrow + (size_t)h * hd + d, v);
+            else if (write_kv) sp_st(kpool, (((size_t)page * nkv + (h - nh)) * pl.page_size + off) * hd + d, v);
+        }
+        if (write_kv) {
+            for (int e = threadIdx.x; e < nkv * (hd >> 1); e += blockDim.x) {
+                const int g = e / (hd >> 1), d = (e % (hd >> 1)) * 2;
+                const float v0 = sp_ld(src, (size_t)(nh + nkv) * hd + (size_t)g * hd + d);
+                const float v1 = sp_ld(src, (size_t)(nh + nkv) * hd + (size_t)g * hd + d + 1);
+                sp_st2(vpool, (((size_t)page * nkv + g) * pl.page_size + off) * hd + d, v0, v1);
+            }
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < n_rot_heads * hd; e += blockDim.x) {
         const int h = e / hd, d = e % hd;
         float v;
@@ -263,7 +301,7 @@ __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict
             v = sp_ld(src, (size_t)h * hd + d);
         }
         if (h < nh) {
-            sp_st(q_out, (size_t)t * nh * hd + (size_t)h * hd + d, v);
+            sp_st(q_out, qrow + (size_t)h * hd + d, v);
         } else if (write_kv) {
             const int g = h - nh;
             sp_st(kpool, (((size_t)page * nkv + g) * pl.page_size + off) * hd + d, v);

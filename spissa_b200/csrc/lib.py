@@ -203,7 +203,8 @@ _STATUS: dict = {}
 
 STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                102: "the MMA issuer waited too long for a loaded pipeline stage",
-               103: "the epilogue waited too long for the accumulator"}
+               103: "the epilogue waited too long for the accumulator",
+               104: "the MMA issuer waited too long for a free accumulator"}
 
 
 def status_word(device) -> torch.Tensor:

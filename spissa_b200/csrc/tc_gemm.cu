@@ -5,7 +5,7 @@
 // layout; the reference computes it with scalar/NEON dot products,
 // crates/spissa-runtime/src/streaming/kernels_raw16.rs:442-530).
 //
-// One CTA computes one 128 x BN tile of C:
+// A CTA computes 128 x BN tiles of C, one after another (a persistent grid of one CTA per SM):
 //   warp 0   one thread issues TMA loads (cp.async.bulk.tensor, 128-byte swizzle) of a
 //            128x64 tile of A and a BNx64 tile of W per pipeline stage;
 //   warp 1   allocates tensor memory and one thread issues tcgen05.mma (M=128, N=BN, K=16,
@@ -13,6 +13,7 @@
 //            each stage back to the loader and, at the end, the accumulator to
 //   warps 2-5 which read it with tcgen05.ld (each warp its own 32 lanes) and store it:
 //            plain, added into a float32 C, or as silu(gate)·up of an interleaved gate/up weight.
+// Tensor memory holds two accumulators: while warps 2-5 store tile i, warp 1 already issues tile i+1.
 // Every wait on an mbarrier is bounded by a wall-clock limit; when it runs out the kernel
 // records a code in ``status``, every role falls through to the common exit, and tensor
 // memory is freed. No load uses cluster multicast.
@@ -130,6 +131,55 @@ struct SmemLayout {
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;      // + slack to align to 1024
 };
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Stores 32 consecutive columns of one row, held as float32 in ``v``, the way ``mode`` asks.
+__device__ __forceinline__ void store_row32(void* C, int c_dt, size_t base, int col0, int n_cols, const float* v,
+                                            bool accumulate) {
+    const bool full = col0 + 32 <= n_cols;
+    if (c_dt == SP_DT_F32) {
+        float* out = (float*)C + base;
+        if (full && ((base & 3) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                float4 w = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (accumulate) {
+                    const float4 o = *(const float4*)(out + j);
+                    w.x += o.x; w.y += o.y; w.z += o.z; w.w += o.w;
+                }
+                *(float4*)(out + j) = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < n_cols) out[j] = accumulate ? v[j] + out[j] : v[j];
+        }
+    } else {
+        __nv_bfloat16* out = (__nv_bfloat16*)C + base;
+        if (full && ((base & 7) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                uint4 w;
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
+                *(uint4*)(out + j) = w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col0 + j < n_cols) out[j] = __float2bfloat16_rn(v[j]);
+        }
+    }
+}
+
+// Persistent: CTA b computes tiles b, b + gridDim.x, ... (M runs fastest over the tile index, so the
+// CTAs that run together share few tiles of W). Two accumulators in tensor memory let the epilogue
+// of one tile run while the next tile's products are issued.
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -138,26 +188,31 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
-    __shared__ __align__(8) uint64_t bar_acc;
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
     __shared__ uint32_t tmem_slot;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int num_kb = (K + BK - 1) / BK;
+    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    const int total_tiles = m_tiles * n_tiles;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&bar_full[s]), 1);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
-        mbar_init(smem_u32(&bar_acc), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);          // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)BN) : "memory");
+                     ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -167,130 +222,96 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
-                if (!mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101)) break;
-                const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
-                const uint32_t b_dst = a_dst + L::A_BYTES;
-                mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
-                tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+            uint32_t kbc = 0;                                   // pipeline slots used so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
+                    const int s = kbc % STAGES;
+                    const uint32_t phase = (kbc / STAGES) & 1u;
+                    ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101);
+                    if (!ok) break;
+                    const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
+                    const uint32_t b_dst = a_dst + L::A_BYTES;
+                    mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
+                    tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+            uint32_t kbc = 0, it = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % STAGES;
-                const uint32_t phase = (uint32_t)(kb / STAGES) & 1u;
-                ok = mbar_wait(smem_u32(&bar_full[s]), phase, status, 102);
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t buf = it & 1u, use = it >> 1;
+                ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), (use & 1u) ^ 1u, status, 104);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t a_src = smem_base + s * L::STAGE_BYTES;
-                const uint64_t da = umma_desc_sw128(a_src);
-                const uint64_t db = umma_desc_sw128(a_src + L::A_BYTES);
+                const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
+                    const int s = kbc % STAGES;
+                    const uint32_t phase = (kbc / STAGES) & 1u;
+                    ok = mbar_wait(smem_u32(&bar_full[s]), phase, status, 102);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_src = smem_base + s * L::STAGE_BYTES;
+                    const uint64_t da = umma_desc_sw128(a_src);
+                    const uint64_t db = umma_desc_sw128(a_src + L::A_BYTES);
 #pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    // 16 bf16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units
-                    tc_mma_bf16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // 16 bf16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units
+                        tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&bar_empty[s]));
                 }
-                tc_commit(smem_u32(&bar_empty[s]));
+                tc_commit(smem_u32(&bar_acc_full[buf]));        // also after a failed wait: the epilogue must not hang
             }
-            tc_commit(smem_u32(&bar_acc));          // also after a failed wait: the epilogue must not hang
         }
     } else {
         const int q = warp & 3;                      // this warp may touch tensor-memory lanes 32q .. 32q+31
-        const bool ok = mbar_wait(smem_u32(&bar_acc), 0, status, 103);
-        tc_fence_after();
-        const int row = m0 + q * 32 + lane;
-        const bool failed = !ok || (status && *(volatile int*)status != 0);
-        if (!failed) {
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            const uint32_t buf = it & 1u, use = it >> 1;
+            const bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), use & 1u, status, 103);
+            tc_fence_after();
+            if (!ok || (status && *(volatile int*)status != 0)) break;
+            const int row = m0 + q * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * (uint32_t)BN + ((uint32_t)(q * 32) << 16);
+            constexpr int SPAN = 32;
+            const int c_end = (mode == MODE_SILU_MUL) ? BN / 2 : BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (mode == MODE_SILU_MUL && c0 >= BN / 2) break;        // uniform over the warp
+            for (int c0 = 0; c0 < c_end; c0 += SPAN) {
                 uint32_t r[32];
-                tc_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+                float v[32];
+                tc_ld_32x32(taddr + (uint32_t)c0, r);
                 if (mode == MODE_SILU_MUL) {
                     // tile columns [0, BN/2) are gate rows, [BN/2, BN) the up rows of the same outputs
                     uint32_t u[32];
-                    tc_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c0 + BN / 2), u);
+                    tc_ld_32x32(taddr + (uint32_t)(c0 + BN / 2), u);
                     tc_ld_wait();
-                    if (row >= M) continue;
-                    const int out_n = N / 2;
-                    const int col0 = (n0 / 2) + c0;
-                    float v[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const float g = __uint_as_float(r[j]);
                         v[j] = (g / (1.0f + expf(-g))) * __uint_as_float(u[j]);
                     }
-                    const size_t base = (size_t)row * ldc + col0;
-                    if (c_dt == SP_DT_BF16 && col0 + 32 <= out_n && (base & 7) == 0) {
-                        __nv_bfloat16* out = (__nv_bfloat16*)C + base;
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 w;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]);
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]);
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                            w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
-                            *(uint4*)(out + j) = w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < out_n) sp_st_dt(C, c_dt, base + j, v[j]);
-                    }
-                    continue;
-                }
-                tc_ld_wait();
-                if (row >= M) continue;
-                const int col0 = n0 + c0;
-                const size_t base = (size_t)row * ldc + col0;
-                const bool full = col0 + 32 <= N;
-                if (c_dt == SP_DT_F32) {
-                    float* out = (float*)C + base;
-                    if (full && ((base & 3) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) {
-                            float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                   __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            if (mode == MODE_ACCUMULATE) {
-                                const float4 o = *(const float4*)(out + j);
-                                v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                            }
-                            *(float4*)(out + j) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) {
-                                float v = __uint_as_float(r[j]);
-                                if (mode == MODE_ACCUMULATE) v += out[j];
-                                out[j] = v;
-                            }
-                    }
                 } else {
-                    __nv_bfloat16* out = (__nv_bfloat16*)C + base;
-                    if (full && ((base & 7) == 0)) {
+                    tc_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 v;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
-                            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
-                            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
-                            v.x = *(uint32_t*)&p0; v.y = *(uint32_t*)&p1; v.z = *(uint32_t*)&p2; v.w = *(uint32_t*)&p3;
-                            *(uint4*)(out + j) = v;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) out[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-                    }
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                }
+                if (c0 + SPAN >= c_end) {            // all of this tile has left tensor memory: hand the buffer back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                }
+                if (row < M) {
+                    if (mode == MODE_SILU_MUL)
+                        store_row32(C, c_dt, (size_t)row * ldc + n0 / 2 + c0, n0 / 2 + c0, N / 2, v, false);
+                    else
+                        store_row32(C, c_dt, (size_t)row * ldc + n0 + c0, n0 + c0, N, v, mode == MODE_ACCUMULATE);
                 }
             }
         }
@@ -299,7 +320,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
     }
 }
 
@@ -345,7 +366,15 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
         if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    static int sm_count = 0;
+    if (!sm_count) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
+            sm_count = 148;
+    }
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status);
     SP_CHECK_LAUNCH("tc_gemm");
     return 0;
@@ -370,7 +399,6 @@ SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, in
     if (mode < 0 || mode > 2) SP_FAIL("tc_gemm: unknown mode %d", mode);
     if (bn != 128 && bn != 256) SP_FAIL("tc_gemm: tile width %d is not built (128 or 256)", bn);
     if (mode == MODE_SILU_MUL && (N % bn)) SP_FAIL("tc_gemm: the fused silu epilogue needs N (%d) to be a multiple of the tile width %d", N, bn);
-    if ((M + BM - 1) / BM > 65535) SP_FAIL("tc_gemm: M=%d is beyond this kernel's grid", M);
     CUtensorMap ma, mw;
     if (make_map(&ma, A, M, K, lda, BM)) return 1;
     if (make_map(&mw, W, N, K, ldw, bn)) return 1;

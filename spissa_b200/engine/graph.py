@@ -8,6 +8,9 @@ copy before each replay; page tables are copied only when they changed.
 """
 from __future__ import annotations
 
+import gc
+import weakref
+
 import torch
 
 from .batch import StepBatch
@@ -24,7 +27,7 @@ class DecodeGraph:
     RING = 4
 
     def __init__(self, engine, n_seqs: int, bucket: int):
-        self.engine, self.B, self.bucket = engine, n_seqs, bucket
+        self.engine, self.B, self.bucket = weakref.proxy(engine), n_seqs, bucket      # no cycle: engines free at once
         dev = engine.device
         B = n_seqs
         self.P = bucket // engine.page_size
@@ -82,8 +85,18 @@ class DecodeGraph:
             eng = self.engine
             graph = torch.cuda.CUDAGraph()
             before = lib.launches
-            with torch.cuda.graph(graph):
-                self.logits = eng.model.forward(self.batch, eng.cache)
+            # Nothing but kernel launches and pool allocations happens in the captured region. The relaxed
+            # mode keeps a stray runtime call of some finaliser (a pinned buffer of an old engine being
+            # returned, say) from invalidating the capture; the collector is held off meanwhile as well.
+            was_enabled = gc.isenabled()
+            gc.collect()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                    self.logits = eng.model.forward(self.batch, eng.cache)
+            finally:
+                if was_enabled:
+                    gc.enable()
             self.kernels = lib.launches - before         # kernels the graph holds
             lib.launches = before
             self.graph = graph

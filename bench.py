@@ -167,9 +167,9 @@ def kernel_case(name: str, reps: int) -> int:
         print(json.dumps({"kernel_case": name, "launches": K.launches}))
         return 0
     if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
-        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 128),
+        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 256),
                            "gemm_gate_up": (2 * I, H, K.TC_SILU_MUL, 256),
-                           "gemm_down": (H, I, K.TC_ACCUMULATE, 128)}[name]
+                           "gemm_down": (H, I, K.TC_ACCUMULATE, 256)}[name]
         n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
         ws = [rnd(N, Kd) for _ in range(n_buf)]
         a = rnd(T, Kd)

@@ -10,6 +10,7 @@ final norm, last row, head; position offset = cached length, :326).
 from __future__ import annotations
 
 import json
+import sys
 from dataclasses import dataclass
 from pathlib import Path
 
@@ -17,6 +18,7 @@ import torch
 
 from ..cache import CacheManager
 from ..config import load_config
+from ..csrc.lib import KernelError
 from ..parts.base import Runtime
 from ..weights import load_tensors, random_tensors
 from .batch import pack_step
@@ -125,9 +127,12 @@ class Engine:
             self._sampler = Sampler(self.device)
         if stop_ids is None:
             stop_ids = self.config.stop_token_ids() if hasattr(self.config, "stop_token_ids") else []
+        from ..csrc.lib import check_status
         with torch.cuda.device(self.device):
-            return run(self, self._sampler, [list(p) for p in prompts], max_new_tokens,
-                       sampling or SamplingParams(), stop_ids, max_batch, on_token, return_logits)
+            out = run(self, self._sampler, [list(p) for p in prompts], max_new_tokens,
+                      sampling or SamplingParams(), stop_ids, max_batch, on_token, return_logits)
+            check_status(self.device)
+            return out
 
     # ------------------------------------------------------------------ the step
     def step(self, entries) -> torch.Tensor:
@@ -156,8 +161,19 @@ class Engine:
         with torch.cuda.device(self.device):
             tables = self.cache.reserve(counts)
             graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+            full = None
             if graph is not None:
-                full = graph.run([t[0] for _, t, _ in ents], lengths, [s for s, _, _ in ents], tables)
+                try:
+                    full = graph.run([t[0] for _, t, _ in ents], lengths, [s for s, _, _ in ents], tables)
+                except (RuntimeError, KernelError) as e:
+                    if graph.graph is not None:
+                        raise                        # a replay failed: that is a real fault
+                    # the capture itself was refused: run this and all later steps kernel by kernel
+                    print(f"[spissa_b200] CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
+                          f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
+                    self.use_graphs = False
+                    self._graphs.clear()
+            if full is not None:
                 if all(len(w) == 1 for _, _, w in ents):
                     logits = full.clone()        # the graph's own tensor is overwritten by the next replay
                 else:

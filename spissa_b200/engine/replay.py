@@ -12,6 +12,7 @@ import os
 import numpy as np
 import torch
 
+from ..csrc.lib import check_status
 from .engine import Engine
 
 
@@ -42,6 +43,7 @@ def replay(model_dir, dtype: str, out_dir, max_tokens: int, lines, done_out, dev
                 os.replace(tmp, os.path.join(out_dir, f"{step_no}.f32"))
             else:
                 torch.cuda.synchronize(engine.device)
+            check_status(engine.device)          # a kernel that gave up a bounded wait must not pass silently
         for rid in rec.get("end", []):
             if rid in slots:
                 engine.release(slots.pop(rid))

@@ -48,6 +48,11 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ float fast_exp2(float x) {           // 2^x, flushes denormals, exp2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
     return *(uint32_t*)&p;
@@ -75,8 +80,10 @@ __device__ __forceinline__ void load_tile_async(uint32_t dst, const __nv_bfloat1
 }
 
 // One warp, 16 query rows (fragments ``qf``), keys [key0, key0 + 8*NT) of the tile in shared memory.
-// Row ``g`` of the fragment sees keys lo[0]..hi[0], row g+8 keys lo[1]..hi[1] (absolute positions).
-template <int HD, int NT>
+// Row ``g`` of the fragment sees keys lo[0]..hi[0], row g+8 keys lo[1]..hi[1] (absolute positions);
+// with MASKED false the caller vouches that every key of the tile is visible to every row.
+// m holds the running maximum of the raw scores times scale_log2 (the log2 domain).
+template <int HD, int NT, bool MASKED>
 __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uint32_t k_tile, uint32_t v_tile,
                                            int key0, int tile_pos0, const int (&lo)[2], const int (&hi)[2],
                                            float scale_log2, float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
@@ -98,7 +105,7 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
             mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
         }
     }
-    // scale, mask, running maximum
+    // mask, running maximum (of the raw scores; the scale is positive)
     const int t = lane & 3;
     float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -106,10 +113,11 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
-            const int key = tile_pos0 + key0 + nt * 8 + 2 * t + (e & 1);
-            const float v = (key > hi[r] || key < lo[r]) ? -INFINITY : s[nt][e] * scale_log2;
-            s[nt][e] = v;
-            mx[r] = fmaxf(mx[r], v);
+            if (MASKED) {
+                const int key = tile_pos0 + key0 + nt * 8 + 2 * t + (e & 1);
+                if (key > hi[r] || key < lo[r]) s[nt][e] = -INFINITY;
+            }
+            mx[r] = fmaxf(mx[r], s[nt][e]);
         }
     }
     float corr[2], msafe[2];
@@ -117,9 +125,9 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
     for (int r = 0; r < 2; ++r) {
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
         mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
-        const float mnew = fmaxf(m[r], mx[r]);
+        const float mnew = fmaxf(m[r], mx[r] * scale_log2);
         msafe[r] = (mnew == -INFINITY) ? 0.0f : mnew;
-        corr[r] = exp2f(m[r] - msafe[r]);            // m = -inf gives 0
+        corr[r] = fast_exp2(m[r] - msafe[r]);         // m = -inf gives 0
         m[r] = mnew;
     }
     float sum[2] = {0.0f, 0.0f};
@@ -127,7 +135,7 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
     for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float p = exp2f(s[nt][e] - msafe[e >> 1]);
+            const float p = fast_exp2(fmaf(s[nt][e], scale_log2, -msafe[e >> 1]));   // one FFMA, one MUFU
             s[nt][e] = p;
             sum[e >> 1] += p;
         }
@@ -245,9 +253,16 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
         __syncthreads();
         if (j == j_lo) load_q_frags<HD>(q_tile, warp * 16, lane, qf);
         const int tile_pos0 = j * KT;
-        if (warp_active && tile_pos0 <= warp_hi && tile_pos0 + KT - 1 >= warp_lo)
-            flash_step<HD, 8>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
-                              scale_log2, o, m, l, lane);
+        if (warp_active && tile_pos0 <= warp_hi && tile_pos0 + KT - 1 >= warp_lo) {
+            // every key of the tile is at or before the warp's first row and inside its last row's window
+            const bool all_seen = tile_pos0 + KT - 1 <= pos0 + warp * 16 && (window <= 0 || tile_pos0 >= warp_hi - window + 1);
+            if (all_seen)
+                flash_step<HD, 8, false>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
+                                         scale_log2, o, m, l, lane);
+            else
+                flash_step<HD, 8, true>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, 0, tile_pos0, lo, hi,
+                                        scale_log2, o, m, l, lane);
+        }
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -371,8 +386,12 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         cp_async_wait<1>();
         __syncthreads();
         if (j == j_first) load_q_frags<HD>(q_tile, 0, lane, qf);
-        flash_step<HD, 2>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo, hi,
-                          scale_log2, o, m, l, lane);
+        if (j * KT + KT - 1 <= p && j * KT >= first_key)
+            flash_step<HD, 2, false>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
+                                     hi, scale_log2, o, m, l, lane);
+        else
+            flash_step<HD, 2, true>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
+                                    hi, scale_log2, o, m, l, lane);
         __syncthreads();
     }
     cp_async_wait<0>();

@@ -352,10 +352,13 @@ def main() -> int:
     engine.generate([p[:64] for p in e2e_prompts], 4, greedy, stop_ids=[])          # warm the path
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    h2d0, steps0 = engine.h2d_bytes, engine.steps_run
     results, metrics = engine.generate(e2e_prompts, e2e_new, greedy, stop_ids=[])
     torch.cuda.synchronize()
+    # every step copies its token ids, positions, slots and (when they changed) page tables to the device
+    # and the chosen tokens (int32 per sequence) back to the host
     e2e = dict(value=round(metrics.decode_tok_s, 2), unit="tokens/s",
-               h2d_bytes_per_step=4 * args.batch * 8 + 4 * args.batch * (CONTEXT // engine.page_size),
+               h2d_bytes_per_step=round((engine.h2d_bytes - h2d0) / max(1, engine.steps_run - steps0)),
                d2h_bytes_per_step=4 * args.batch, new_tokens=e2e_new,
                wall_s=round(time.perf_counter() - t0, 3))
 

@@ -68,6 +68,7 @@ class Engine:
         self.vocab_size = self.model.spec.vocab_size
         self.max_position = self.model.spec.max_position
         self.steps_run = 0
+        self.h2d_bytes = 0            # bytes of step arrays copied to the device so far
         # decode steps replay CUDA graphs once a (batch size, length bucket) has been seen before
         self.use_graphs = use_graphs and self.model.graph_safe()
         self._graphs: dict = {}
@@ -181,6 +182,7 @@ class Engine:
                     logits = full[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else full[:0]
             else:
                 batch = pack_step(ents, lengths, tables, self.device)
+                self.h2d_bytes += batch.h2d_bytes
                 logits = self.model.forward(batch, self.cache)
         self.cache.commit(counts)
         self.steps_run += 1

@@ -70,9 +70,11 @@ class DecodeGraph:
                     rows.extend([0] * (self.P - len(r)))
             buf[self.n_dyn:] = torch.tensor(rows, dtype=torch.int32)
             self.dev.copy_(buf, non_blocking=True)
+            self.engine.h2d_bytes += buf.numel() * 4
             self.last_tables = [[list(r) for r in t] for t in flat_tables]
         else:
             self.dev[:self.n_dyn].copy_(buf[:self.n_dyn], non_blocking=True)
+            self.engine.h2d_bytes += self.n_dyn * 4
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev

@@ -10,7 +10,8 @@ crates/spissa-runtime/src/rotary.rs:335-415.
 The three projections run as one matrix product over the stacked weight
 [Wq; Wk; Wv]. With ``window`` = w a query at position p sees keys p−w+1 … p.
 A run that shares another run's cache (``cache.writes`` False) computes q only and
-reads the keys the other run stored.
+reads the keys the other run stored; a layer built with ``shares_kv`` has no k/v
+projections at all and can only run that way.
 """
 from __future__ import annotations
 
@@ -29,13 +30,14 @@ class GQAAttention(Mixer):
     graph_safe = True
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                 position=None, window=None, prefix: str = "", names: dict | None = None):
+                 position=None, window=None, shares_kv: bool = False, prefix: str = "", names: dict | None = None):
         super().__init__(prefix)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} kv heads")
         self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
         self.num_kv_heads, self.head_dim = int(num_kv_heads), int(head_dim)
         self.window = int(window) if window else None
+        self.shares_kv = bool(shares_kv)         # this layer has no k/v projections: it reads another run's cache
         self.scale = 1.0 / math.sqrt(self.head_dim)
         n = dict(q="q_proj.weight", k="k_proj.weight", v="v_proj.weight", o="o_proj.weight")
         n.update(names or {})
@@ -48,19 +50,23 @@ class GQAAttention(Mixer):
 
     def weight_specs(self):
         H, nh, nkv, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
-        return [WeightSpec(self.names["q"], (nh * hd, H)), WeightSpec(self.names["k"], (nkv * hd, H)),
-                WeightSpec(self.names["v"], (nkv * hd, H)), WeightSpec(self.names["o"], (H, nh * hd))]
+        own = [WeightSpec(self.names["q"], (nh * hd, H)), WeightSpec(self.names["o"], (H, nh * hd))]
+        if self.shares_kv:
+            return own
+        return own + [WeightSpec(self.names["k"], (nkv * hd, H)), WeightSpec(self.names["v"], (nkv * hd, H))]
 
     def cache_request(self):
         return KVCacheRequest(self.num_kv_heads, self.head_dim, self.window)
 
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
-        q, k, v = (tensors[self.names[x]] for x in "qkv")
-        if not (q.dtype == k.dtype == v.dtype):
-            raise ValueError(f"{self.prefix}: q, k and v projections must share a storage type")
-        self.qkv = Linear(torch.cat([q, k, v], dim=0))
+        q = tensors[self.names["q"]]
         self.q_only = Linear(q)
+        if not self.shares_kv:
+            k, v = tensors[self.names["k"]], tensors[self.names["v"]]
+            if not (q.dtype == k.dtype == v.dtype):
+                raise ValueError(f"{self.prefix}: q, k and v projections must share a storage type")
+            self.qkv = Linear(torch.cat([q, k, v], dim=0))
         self.o = Linear(tensors[self.names["o"]])
         # arrival counters of the split-key decode attention; the kernel returns them to zero
         self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
@@ -69,6 +75,8 @@ class GQAAttention(Mixer):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         T = x.shape[0]
         writes = cache.writes
+        if writes and self.shares_kv:
+            raise ValueError(f"{self.prefix}: a layer without k/v projections cannot be the writer of a cache")
         proj = self.qkv if writes else self.q_only
         qkv = proj(x, out_dtype=torch.float32)                 # rotation reads unrounded products
         if not writes:

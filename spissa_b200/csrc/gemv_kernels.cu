@@ -20,8 +20,23 @@ SP_API const char* sp_gemv_last_error() { return sp_error_text; }
 
 namespace {
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ROPE_KV = 3 };
 constexpr int MAX_KS = 8;
+
+// Where MODE_ROPE_KV sends its rows: W is [q heads | k heads | v heads] x head_dim rows; q and k are
+// rotated (rotate-half over the whole head, angle = position · inv_freq[i], float32), q goes to q_out,
+// k and v into the paged cache at the token's position ([page][kv head][page_size][head_dim]).
+struct RopeOut {
+    __nv_bfloat16* q_out;    // [M, nh * hd]
+    __nv_bfloat16* kpool;
+    __nv_bfloat16* vpool;
+    const int* positions;    // [M]
+    const int* token_seq;    // [M]
+    const int* seq_row;      // [sequences] row of the page table
+    const int* page_table;
+    const float* inv_freq;   // [hd / 2]
+    int max_pages, page_size, nh, nkv, hd;
+};
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -67,7 +82,8 @@ __device__ __forceinline__ float4 ld_peer_f4(const void* local, uint32_t rank) {
 template <int MT, int RT, int UNROLL>
 __global__ void __launch_bounds__(MAX_KS * 32)
 gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
-            int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int ks, int cs) {
+            int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int ks, int cs,
+            RopeOut rope) {
     __shared__ __align__(16) float red[MAX_KS][MT][RT][32][4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -76,7 +92,7 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
 
     // rows of W this CTA owns
     int row_base[RT];
-    if (mode == MODE_SILU_MUL) {
+    if (mode == MODE_SILU_MUL || mode == MODE_ROPE_KV) {
         constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
         const int o0 = tile * 8 * HALF;                   // first output of this CTA
 #pragma unroll
@@ -180,7 +196,6 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
         if (rank != 0) return;
     }
     if (warp != 0) return;
-
     // lane holds tokens (16i+g, 16i+g+8) x rows (2t, 2t+1) of every row group
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
@@ -196,6 +211,37 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
                     if (col < N / 2) {
                         const float gate = acc[i][r][e], up = acc[i][HALF + r < RT ? HALF + r : r][e];
                         sp_st_dt(out, out_dt, (size_t)m * ldo + col, (gate / (1.0f + expf(-gate))) * up);
+                    }
+                }
+            } else if (mode == MODE_ROPE_KV) {
+                constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
+                const int half = rope.hd >> 1;
+                const int pos = rope.positions[m];
+#pragma unroll
+                for (int r = 0; r < HALF; ++r) {
+                    const int row = row_base[r] + 2 * t + (e & 1);       // row of the first half; its partner is half on
+                    if (row >= N) continue;
+                    const int blk = row / rope.hd, d = row % rope.hd;    // head-sized block and dim < half
+                    const float a = acc[i][r][e], b = acc[i][HALF + r < RT ? HALF + r : r][e];
+                    float lo = a, hi = b;
+                    if (blk < rope.nh + rope.nkv) {
+                        const float ang = (float)pos * rope.inv_freq[d];
+                        const float c = cosf(ang), sn = sinf(ang);
+                        lo = a * c - b * sn;
+                        hi = b * c + a * sn;
+                    }
+                    if (blk < rope.nh) {
+                        __nv_bfloat16* q = rope.q_out + (size_t)m * rope.nh * rope.hd + (size_t)blk * rope.hd;
+                        q[d] = __float2bfloat16_rn(lo);
+                        q[d + half] = __float2bfloat16_rn(hi);
+                    } else {
+                        const bool is_k = blk < rope.nh + rope.nkv;
+                        const int kvh = is_k ? blk - rope.nh : blk - rope.nh - rope.nkv;
+                        const int page = rope.page_table[(size_t)rope.seq_row[rope.token_seq[m]] * rope.max_pages + pos / rope.page_size];
+                        __nv_bfloat16* dst = (is_k ? rope.kpool : rope.vpool) +
+                            (((size_t)page * rope.nkv + kvh) * rope.page_size + pos % rope.page_size) * rope.hd;
+                        dst[d] = __float2bfloat16_rn(lo);
+                        dst[d + half] = __float2bfloat16_rn(hi);
                     }
                 }
             } else {
@@ -218,12 +264,13 @@ struct Plan { int rt, cs, ks, tiles; };
 
 Plan make_plan(int M, int N, int K, int mode) {
     Plan p;
-    const int outputs = mode == MODE_SILU_MUL ? N / 2 : N;
+    const int outputs = (mode == MODE_SILU_MUL || mode == MODE_ROPE_KV) ? N / 2 : N;
     // few tokens: one row group per CTA (a gate/up pair for the fused epilogue) keeps the most CTAs in flight;
     // more tokens: several row groups share the x fragments
     const int wide = M <= 16 ? 1 : (M <= 32 ? 4 : 2);
-    p.rt = (mode == MODE_SILU_MUL) ? (wide < 2 ? 2 : wide) : wide;
-    const int per_tile = (mode == MODE_SILU_MUL) ? 8 * (p.rt / 2) : 8 * p.rt;
+    const bool paired = mode == MODE_SILU_MUL || mode == MODE_ROPE_KV;
+    p.rt = paired ? (wide < 2 ? 2 : wide) : wide;
+    const int per_tile = paired ? 8 * (p.rt / 2) : 8 * p.rt;
     p.tiles = (outputs + per_tile - 1) / per_tile;
     // a cluster splits K when one CTA's warps would need more than one round of loads for their slice
     const int kblocks = (K + 31) / 32;
@@ -243,27 +290,56 @@ SP_API int sp_gemv_supported(const void* x, const void* W, int M, int K, int ldx
     return 0;
 }
 
-// mode 0: out = x·Wᵀ (bfloat16 or float32); 1: out (float32) += x·Wᵀ;
-// 2: W interleaves ``pair`` gate rows and ``pair`` up rows; out [M, N/2] = silu(gate)·up.
-SP_API int sp_gemv(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int ldx, int ldw,
-                   int ldo, int mode, int pair, cudaStream_t stream) {
-    if (N <= 0) return 0;
-    if (sp_gemv_supported(x, W, M, K, ldx, ldw)) return 1;
-    if (mode == MODE_ACCUMULATE && out_dt != SP_DT_F32) SP_FAIL("gemv: accumulation needs a float32 output");
-    if (mode < 0 || mode > 2) SP_FAIL("gemv: unknown mode %d", mode);
-    if (mode == MODE_SILU_MUL && (pair <= 0 || (pair % 8) || N % (2 * pair)))
-        SP_FAIL("gemv: the fused silu epilogue needs blocks of a multiple of 8 rows that divide N/2 (N=%d, block %d)", N, pair);
+namespace {
+
+int launch_gemv(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int ldx, int ldw, int ldo,
+                int mode, int pair, const RopeOut& rope, cudaStream_t stream) {
     const Plan p = make_plan(M, N, K, mode);
     const dim3 grid(p.tiles * p.cs), block(p.ks * 32);
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
 #define GV_LAUNCH(MT, RT, UN)                                                                              \
-    SP_CHECK_CALL("gemv", sp_launch_cluster(gemv_kernel<MT, RT, UN>, grid, block, 0, stream, p.cs, xp, wp, out, out_dt, \
-                                       M, N, K, ldx, ldw, ldo, mode, pair, p.ks, p.cs))
+    SP_CHECK_CALL("gemv", sp_launch_cluster(gemv_kernel<MT, RT, UN>, grid, block, 0, stream, p.cs, xp, wp, out, out_dt,  \
+                                            M, N, K, ldx, ldw, ldo, mode, pair, p.ks, p.cs, rope))
     if (p.rt == 4) GV_LAUNCH(2, 4, 2);
     else if (p.rt == 2 && M <= 16) GV_LAUNCH(1, 2, 4);
     else if (p.rt == 2) GV_LAUNCH(4, 2, 2);
     else GV_LAUNCH(1, 1, 8);
 #undef GV_LAUNCH
     return 0;
+}
+
+int check_gemv(const void* x, const void* W, int M, int N, int K, int ldx, int ldw, int out_dt, int mode, int pair) {
+    if (sp_gemv_supported(x, W, M, K, ldx, ldw)) return 1;
+    if (mode == MODE_ACCUMULATE && out_dt != SP_DT_F32) SP_FAIL("gemv: accumulation needs a float32 output");
+    if (mode < 0 || mode > 3) SP_FAIL("gemv: unknown mode %d", mode);
+    if ((mode == MODE_SILU_MUL || mode == MODE_ROPE_KV) && (pair <= 0 || (pair % 8) || N % (2 * pair)))
+        SP_FAIL("gemv: paired rows need blocks of a multiple of 8 rows that divide N/2 (N=%d, block %d)", N, pair);
+    return 0;
+}
+
+}  // namespace
+
+// mode 0: out = x·Wᵀ (bfloat16 or float32); 1: out (float32) += x·Wᵀ;
+// 2: W interleaves ``pair`` gate rows and ``pair`` up rows; out [M, N/2] = silu(gate)·up.
+SP_API int sp_gemv(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int ldx, int ldw,
+                   int ldo, int mode, int pair, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (mode == MODE_ROPE_KV) SP_FAIL("gemv: the rotate-and-store epilogue has an entry point of its own");
+    if (check_gemv(x, W, M, N, K, ldx, ldw, out_dt, mode, pair)) return 1;
+    return launch_gemv(x, W, out, out_dt, M, N, K, ldx, ldw, ldo, mode, pair, RopeOut{}, stream);
+}
+
+// QKV for decoding in one kernel: W = [Wq; Wk; Wv], rotate-half on q and k in the epilogue, q to ``q_out``
+// (bfloat16), k and v into the paged bfloat16 cache at each token's position. x [M, K] bfloat16.
+SP_API int sp_gemv_qkv_rope(const void* x, int ldx, const void* W, int ldw, int M, int K, int nh, int nkv, int hd,
+                            void* q_out, void* kpool, void* vpool, const int* positions, const int* token_seq,
+                            const int* seq_row, const int* page_table, int max_pages, int page_size,
+                            const float* inv_freq, cudaStream_t stream) {
+    const int N = (nh + 2 * nkv) * hd;
+    if (hd % 16) SP_FAIL("gemv (qkv): head_dim %d must be a multiple of 16 for the fused rotation", hd);
+    if (check_gemv(x, W, M, N, K, ldx, ldw, SP_DT_BF16, MODE_ROPE_KV, hd / 2)) return 1;
+    RopeOut rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, positions, token_seq, seq_row,
+                 page_table, inv_freq, max_pages, page_size, nh, nkv, hd};
+    return launch_gemv(x, W, nullptr, SP_DT_BF16, M, N, K, ldx, ldw, 0, MODE_ROPE_KV, hd / 2, rope, stream);
 }

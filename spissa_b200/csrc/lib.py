@@ -347,3 +347,21 @@ def gemv(x, w, out, mode=TC_STORE, pair=0):
     _check("gemv", lib.sp_gemv(
         c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K,
         x.stride(0), w.stride(0), out.stride(0), int(mode), int(pair), c_void_p(_stream())))
+
+
+def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
+    """The QKV product of a few tokens with rotate-half and the cache write in its epilogue.
+
+    ``x`` bfloat16 [M, K]; ``w`` = [Wq; Wk; Wv]; q goes to ``q_out`` (bfloat16), k and v into the paged
+    bfloat16 cache at each token's position.
+    """
+    lib = load("gemv")
+    M, K = x.shape
+    pt = meta.page_table
+    if q_out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("gemv_qkv_rope works on bfloat16 weights, queries and cache")
+    _check("gemv", lib.sp_gemv_qkv_rope(
+        c_void_p(_ptr(x)), x.stride(0), c_void_p(_ptr(w)), w.stride(0), M, K, nh, nkv, hd, c_void_p(_ptr(q_out)),
+        c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.token_seq)),
+        c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, c_void_p(_ptr(inv_freq)),
+        c_void_p(_stream())))

@@ -21,7 +21,7 @@ import torch
 
 from ..csrc import lib as K
 from .base import KVCacheRequest, Mixer, WeightSpec
-from .linear import Linear
+from .linear import GEMV_TOKENS, Linear
 from .registry import build_part, register_part
 
 
@@ -77,20 +77,26 @@ class GQAAttention(Mixer):
         writes = cache.writes
         if writes and self.shares_kv:
             raise ValueError(f"{self.prefix}: a layer without k/v projections cannot be the writer of a cache")
-        proj = self.qkv if writes else self.q_only
-        qkv = proj(x, out_dtype=torch.float32)                 # rotation reads unrounded products
-        if not writes:
-            pad = torch.empty(T, (nh + 2 * nkv) * hd, dtype=torch.float32, device=x.device)
-            pad[:, :nh * hd] = qkv
-            qkv = pad
         rd, inv_freq = 0, None
-        if self.position is not None:
-            if hasattr(self.position, "rotary"):
-                inv_freq, rd = self.position.rotary()
-            else:
-                self.position.apply(qkv, step, nh, nkv, hd)
+        rotary = self.position is not None and hasattr(self.position, "rotary")
+        if rotary:
+            inv_freq, rd = self.position.rotary()
         q = torch.empty(T, nh * hd, dtype=self.rt.act_dtype, device=x.device)
-        K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
+        w = self.qkv.weight if writes else None
+        if (writes and rotary and rd == hd and hd % 16 == 0 and T <= GEMV_TOKENS and q.dtype == torch.bfloat16
+                and cache.k_pool.dtype == torch.bfloat16 and K.gemv_supported(x, w)):
+            # a few tokens: one kernel does the QKV product, the rotation and the cache write
+            K.gemv_qkv_rope(x, w, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd)
+        else:
+            proj = self.qkv if writes else self.q_only
+            qkv = proj(x, out_dtype=torch.float32)             # rotation reads unrounded products
+            if not writes:
+                pad = torch.empty(T, (nh + 2 * nkv) * hd, dtype=torch.float32, device=x.device)
+                pad[:, :nh * hd] = qkv
+                qkv = pad
+            if self.position is not None and not rotary:
+                self.position.apply(qkv, step, nh, nkv, hd)
+            K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
         ctx = torch.empty_like(q)
         if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
             if step.all_single:

@@ -427,3 +427,31 @@ def test_tc_gemm_refuses_rows_that_tma_cannot_fetch(K):
         K.tc_gemm(a, w, torch.empty(4, 4, device=DEV))
     with pytest.raises(K.KernelError, match="multiples of 8"):
         K.gemv(a, w, torch.empty(4, 4, device=DEV))
+
+
+# ------------------------------------------------------------------ the decode QKV product with rotation and cache write
+@pytest.mark.parametrize("nh,nkv,hd,H", [(4, 2, 16, 64), (3, 1, 32, 96), (8, 2, 64, 256), (4, 1, 128, 200), (3, 3, 48, 72)])
+def test_gemv_qkv_rope(K, nh, nkv, hd, H):
+    torch.manual_seed(nh * 10 + hd)
+    new_counts, before = [1, 3, 1, 2], [0, 130, 63, 64]
+    T = sum(new_counts)
+    meta = KH.paged_meta(new_counts, before, DEV, seed=hd)
+    x = torch.randn(T, H).bfloat16()
+    w = (torch.randn((nh + 2 * nkv) * hd, H) * 0.2).bfloat16()
+    inv = P.rope_inv_freq(10000.0, hd)
+    q_out = torch.zeros(T, nh * hd, dtype=torch.bfloat16, device=DEV)
+    k_pool = torch.zeros(meta.n_pages, nkv, KH.PAGE, hd, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.zeros_like(k_pool)
+    K.gemv_qkv_rope(x.to(DEV), w.to(DEV), q_out, k_pool, v_pool, meta, inv.to(DEV), nh, nkv, hd)
+    qkv = (x.double() @ w.double().t()).float()
+    pos = meta.positions.cpu()
+    q = P.apply_rope(qkv[:, :nh * hd].reshape(T, nh, hd), pos, inv)
+    k = P.apply_rope(qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd), pos, inv)
+    v = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd)
+    close(q_out, q.reshape(T, -1), 4e-3, "q")
+    seq = meta.token_seq.cpu()
+    for t in range(T):
+        b, p = int(seq[t]), int(pos[t])
+        pg, off = meta.rows[b][p // KH.PAGE], p % KH.PAGE
+        close(k_pool[pg, :, off, :], k[t], 4e-3, f"k of token {t}")
+        close(v_pool[pg, :, off, :], v[t], 4e-3, f"v of token {t}")

@@ -144,12 +144,14 @@ __device__ __forceinline__ void store_row32(void* C, int c_dt, size_t base, int 
         if (full && ((base & 3) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4) {
-                float4 w = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 if (accumulate) {
-                    const float4 o = *(const float4*)(out + j);
-                    w.x += o.x; w.y += o.y; w.z += o.z; w.w += o.w;
+                    // this CTA is the only one that adds to these elements, so the sum is the same as read-add-write;
+                    // the reduction needs no answer and hides the memory's latency
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                 ::"l"(out + j), "f"(v[j]), "f"(v[j + 1]), "f"(v[j + 2]), "f"(v[j + 3]) : "memory");
+                } else {
+                    *(float4*)(out + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                 }
-                *(float4*)(out + j) = w;
             }
         } else {
 #pragma unroll

@@ -259,6 +259,103 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
     }
 }
 
+// Many rows, few tokens (N ≥ 8192, M ≤ 16): no split of K. Every warp owns RT groups of 8 rows over all of
+// K and streams them through two register buffers, so that the next U blocks of W are always on their way
+// while the current ones are multiplied; there is no shared memory and no barrier. The sum over K runs in
+// order of K within a warp: it depends on neither timing nor M.
+template <int RT, int U>
+__global__ void __launch_bounds__(128)
+gemv_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W, void* __restrict__ out,
+                   int out_dt, int M, int N, int K, int ldx, int ldw, int ldo, int mode, int pair, int tiles) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int tile = blockIdx.x * 4 + warp;
+    if (tile >= tiles) return;
+    constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
+    int row_base[RT];
+    if (mode == MODE_SILU_MUL) {
+#pragma unroll
+        for (int r = 0; r < HALF; ++r) {
+            const int o = tile * 8 * HALF + r * 8;
+            row_base[r] = (o / pair) * 2 * pair + (o % pair);
+            row_base[HALF + r < RT ? HALF + r : r] = row_base[r] + pair;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < RT; ++r) row_base[r] = (tile * RT + r) * 8;
+    }
+    const __nv_bfloat16* wrow[RT];
+    bool wok[RT];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) {
+        const int row = row_base[r] + g;
+        wok[r] = row < N;
+        wrow[r] = W + (size_t)(wok[r] ? row : 0) * ldw;
+    }
+    const int kblocks = (K + 31) / 32;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    float acc[RT][4];
+#pragma unroll
+    for (int r = 0; r < RT; ++r) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.0f;
+
+    auto load = [&](uint4 (&b)[U][RT], int kb) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (kb + u) * 32 + 8 * t;
+            const bool kok = (kb + u) < kblocks && k < K;
+#pragma unroll
+            for (int r = 0; r < RT; ++r) b[u][r] = (kok && wok[r]) ? ld_stream(wrow[r] + k) : zero;
+        }
+    };
+    auto compute = [&](const uint4 (&b)[U][RT], int kb) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = (kb + u) * 32 + 8 * t;
+            const bool kok = (kb + u) < kblocks && k < K;
+            const uint4 xa = (kok && g < M) ? ld_act(x + (size_t)g * ldx + k) : zero;
+            const uint4 xb = (kok && g + 8 < M) ? ld_act(x + (size_t)(g + 8) * ldx + k) : zero;
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                mma_bf16(acc[r], xa.x, xb.x, xa.y, xb.y, b[u][r].x, b[u][r].y);
+                mma_bf16(acc[r], xa.z, xb.z, xa.w, xb.w, b[u][r].z, b[u][r].w);
+            }
+        }
+    };
+    uint4 buf0[U][RT], buf1[U][RT];
+    load(buf0, 0);
+    for (int kb = 0; kb < kblocks; kb += 2 * U) {
+        load(buf1, kb + U);
+        compute(buf0, kb);
+        load(buf0, kb + 2 * U);
+        compute(buf1, kb + U);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int m = g + (e >> 1) * 8;
+        if (m >= M) continue;
+        if (mode == MODE_SILU_MUL) {
+#pragma unroll
+            for (int r = 0; r < HALF; ++r) {
+                const int col = tile * 8 * HALF + r * 8 + 2 * t + (e & 1);
+                if (col < N / 2) {
+                    const float gate = acc[r][e], up = acc[HALF + r < RT ? HALF + r : r][e];
+                    sp_st_dt(out, out_dt, (size_t)m * ldo + col, (gate / (1.0f + expf(-gate))) * up);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < RT; ++r) {
+                const int col = row_base[r] + 2 * t + (e & 1);
+                if (col >= N) continue;
+                const size_t o = (size_t)m * ldo + col;
+                float v = acc[r][e];
+                if (mode == MODE_ACCUMULATE) v += ((float*)out)[o];
+                sp_st_dt(out, out_dt, o, v);
+            }
+        }
+    }
+}
+
 // How the work of one product is cut: row groups per CTA, CTAs per cluster along K, warps per CTA.
 struct Plan { int rt, cs, ks, tiles; };
 
@@ -294,10 +391,22 @@ namespace {
 
 int launch_gemv(const void* x, const void* W, void* out, int out_dt, int M, int N, int K, int ldx, int ldw, int ldo,
                 int mode, int pair, const RopeOut& rope, cudaStream_t stream) {
-    const Plan p = make_plan(M, N, K, mode);
-    const dim3 grid(p.tiles * p.cs), block(p.ks * 32);
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)W;
+    const int stream_tiles = mode == MODE_SILU_MUL ? (N / 2 + 7) / 8 : (N + 7) / 8;
+    if (M <= 16 && stream_tiles >= 148 * 16 && mode != MODE_ROPE_KV) {
+        // enough rows (the output head) to give every warp rows of its own and still fill every SM sixteen warps deep
+        if (mode == MODE_SILU_MUL)
+            gemv_stream_kernel<2, 4><<<(stream_tiles + 3) / 4, 128, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo,
+                                                                                mode, pair, stream_tiles);
+        else
+            gemv_stream_kernel<1, 8><<<(stream_tiles + 3) / 4, 128, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo,
+                                                                                mode, pair, stream_tiles);
+        SP_CHECK_LAUNCH("gemv_stream");
+        return 0;
+    }
+    const Plan p = make_plan(M, N, K, mode);
+    const dim3 grid(p.tiles * p.cs), block(p.ks * 32);
 #define GV_LAUNCH(MT, RT, UN)                                                                              \
     SP_CHECK_CALL("gemv", sp_launch_cluster(gemv_kernel<MT, RT, UN>, grid, block, 0, stream, p.cs, xp, wp, out, out_dt,  \
                                             M, N, K, ldx, ldw, ldo, mode, pair, p.ks, p.cs, rope))

@@ -455,3 +455,23 @@ def test_gemv_qkv_rope(K, nh, nkv, hd, H):
         pg, off = meta.rows[b][p // KH.PAGE], p % KH.PAGE
         close(k_pool[pg, :, off, :], k[t], 4e-3, f"k of token {t}")
         close(v_pool[pg, :, off, :], v[t], 4e-3, f"v of token {t}")
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 19000, 72), (8, 20008, 264), (16, 19004, 96)])
+def test_gemv_many_rows_streams_without_splitting_k(K, M, N, K_):
+    torch.manual_seed(N)
+    x = torch.randn(M, K_).bfloat16()
+    w = torch.randn(N, K_).bfloat16()
+    ref = x.double() @ w.double().t()
+    out = torch.full((M, N), 9.0, device=DEV)
+    K.gemv(x.to(DEV), w.to(DEV), out)
+    close(out, ref, 3e-6)
+    base = torch.randn(M, N)
+    acc = base.clone().to(DEV)
+    K.gemv(x.to(DEV), w.to(DEV), acc, mode=K.TC_ACCUMULATE)
+    close(acc, ref + base.double(), 3e-6)
+    I = 19008
+    g, u = (torch.randn(I, K_) * 0.2).bfloat16(), (torch.randn(I, K_) * 0.2).bfloat16()
+    outs = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    K.gemv(x.to(DEV), interleave(g, u, 64).to(DEV), outs, mode=K.TC_SILU_MUL, pair=64)
+    close(outs, P.silu(x.double() @ g.double().t()) * (x.double() @ u.double().t()), 4e-3)

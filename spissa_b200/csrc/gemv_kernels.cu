@@ -372,9 +372,10 @@ Plan make_plan(int M, int N, int K, int mode) {
     // a cluster splits K when one CTA's warps would need more than one round of loads for their slice
     const int kblocks = (K + 31) / 32;
     p.cs = 1;
-    while (p.cs < 8 && kblocks > p.cs * MAX_KS * 8) p.cs *= 2;
+    while (p.cs < 8 && kblocks > p.cs * MAX_KS * 16) p.cs *= 2;       // measured: two rounds per warp beat a wider cluster
     const int per_cta = (kblocks + p.cs - 1) / p.cs;
-    p.ks = per_cta < MAX_KS ? (per_cta < 1 ? 1 : per_cta) : MAX_KS;
+    const int max_ks = mode == MODE_SILU_MUL ? MAX_KS / 2 : MAX_KS;     // measured: the gate/up product runs best with four warps
+    p.ks = per_cta < max_ks ? (per_cta < 1 ? 1 : per_cta) : max_ks;
     return p;
 }
 

@@ -23,6 +23,7 @@ SP_API const char* sp_attention_last_error() { return sp_error_text; }
 namespace {
 
 constexpr int KT = 64;                        // keys per tile = page size
+constexpr int DEC_STAGES = 3;                 // tiles in flight per warp of the decode kernel
 constexpr float LOG2E = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -331,8 +332,8 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t q_tile = smem_u32(smem);                       // 16 rows used
     const uint32_t k_tiles = q_tile + 16 * T::ROW;
-    const uint32_t v_tiles = k_tiles + 2 * T::BYTES;
-    float* merge = (float*)(smem + 16 * T::ROW + 4 * T::BYTES);    // [4 warps][16 rows][HD + 2]
+    const uint32_t v_tiles = k_tiles + DEC_STAGES * T::BYTES;
+    float* merge = (float*)(smem + 16 * T::ROW + 2 * DEC_STAGES * T::BYTES);    // [4 warps][16 rows][HD + 2]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, n_chunks = gridDim.x, g = blockIdx.y, b = blockIdx.z;
     const int G = nh / kv.nkv;
@@ -360,12 +361,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         if (r < G) cp_async16(d, q + (size_t)b * nh * HD + (size_t)(g * G + r) * HD + k * 8);
         else asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(d), "r"(0u) : "memory");
     }
-    {
-        const size_t off = ((size_t)pt[j_first] * kv.nkv + g) * KT * HD;
-        load_tile_async<HD>(k_tiles, kv.k + off, HD, KT, tid, 128);
-        load_tile_async<HD>(v_tiles, kv.v + off, HD, KT, tid, 128);
-    }
-    cp_async_commit();
+    cp_async_commit();                                             // group 0: the queries
 
     uint32_t qf[HD / 16][4];
     float o[HD / 8][4];
@@ -375,24 +371,41 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     const int hi[2] = {p, p};
     const int lo[2] = {first_key, first_key};
 
-    for (int j = j_first; j <= j_last; ++j) {
-        const int stage = (j - j_first) & 1;
-        if (j < j_last) {
-            const size_t off = ((size_t)pt[j + 1] * kv.nkv + g) * KT * HD;
-            load_tile_async<HD>(k_tiles + (stage ^ 1) * T::BYTES, kv.k + off, HD, KT, tid, 128);
-            load_tile_async<HD>(v_tiles + (stage ^ 1) * T::BYTES, kv.v + off, HD, KT, tid, 128);
+    // Each warp fetches and uses only its own 16 keys of every tile, so inside the loop the warps
+    // need no barrier among themselves: a warp waits for its own copies and goes on.
+    auto fetch = [&](int j, int stage) {
+        const size_t off = ((size_t)pt[j] * kv.nkv + g) * KT * HD + (size_t)warp * 16 * HD;
+        const uint32_t kd = k_tiles + stage * T::BYTES + warp * 16 * T::ROW;
+        const uint32_t vd = v_tiles + stage * T::BYTES + warp * 16 * T::ROW;
+        for (int c = lane; c < 16 * T::CHUNKS; c += 32) {
+            const int r = c / T::CHUNKS, k = c % T::CHUNKS;
+            cp_async16(kd + r * T::ROW + k * 16, kv.k + off + (size_t)r * HD + k * 8);
+            cp_async16(vd + r * T::ROW + k * 16, kv.v + off + (size_t)r * HD + k * 8);
         }
+    };
+#pragma unroll
+    for (int s = 0; s < DEC_STAGES - 1; ++s) {
+        if (j_first + s <= j_last) fetch(j_first + s, s);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        if (j == j_first) load_q_frags<HD>(q_tile, 0, lane, qf);
+    }
+    cp_async_wait<DEC_STAGES - 1>();                               // the queries have landed (all later groups may fly)
+    __syncthreads();
+    load_q_frags<HD>(q_tile, 0, lane, qf);
+
+    for (int j = j_first; j <= j_last; ++j) {
+        const int it = j - j_first;
+        const int stage = it % DEC_STAGES;
+        if (j + DEC_STAGES - 1 <= j_last) fetch(j + DEC_STAGES - 1, (it + DEC_STAGES - 1) % DEC_STAGES);
+        cp_async_commit();
+        cp_async_wait<DEC_STAGES - 1>();
+        __syncwarp();
         if (j * KT + KT - 1 <= p && j * KT >= first_key)
             flash_step<HD, 2, false>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
                                      hi, scale_log2, o, m, l, lane);
         else
             flash_step<HD, 2, true>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
                                     hi, scale_log2, o, m, l, lane);
-        __syncthreads();
+        __syncwarp();                                              // the stage is free for this warp's next fetch
     }
     cp_async_wait<0>();
 
@@ -462,7 +475,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 template <int HD>
 constexpr int prefill_smem() { return 5 * Tile<HD>::BYTES; }
 template <int HD>
-constexpr int decode_smem() { return 16 * Tile<HD>::ROW + 4 * Tile<HD>::BYTES + 4 * 16 * (HD + 2) * 4; }
+constexpr int decode_smem() { return 16 * Tile<HD>::ROW + 2 * DEC_STAGES * Tile<HD>::BYTES + 4 * 16 * (HD + 2) * 4; }
 
 template <typename Kern>
 int opt_in_smem(Kern kern, int bytes, const char* name) {

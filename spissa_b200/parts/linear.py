@@ -13,6 +13,7 @@ from ..csrc import lib as K
 
 SM_COUNT = 148
 GEMV_TOKENS = 16          # up to this many tokens the weight-streaming kernel runs instead of 128-row tiles
+GATED_GEMV_TOKENS = 32    # the gate/up product streams faster than 64 wide tiles up to here (23.7 vs 40 us at 32 tokens)
 
 
 def tile_width(M: int, N: int) -> int:
@@ -70,7 +71,7 @@ class GatedLinear:
 
     def __call__(self, x: torch.Tensor, act_dtype) -> torch.Tensor:
         out = torch.empty(x.shape[0], self.intermediate, dtype=act_dtype, device=x.device)
-        if self.block and x.shape[0] <= GEMV_TOKENS and K.gemv_supported(x, self.weight):
+        if self.block and x.shape[0] <= GATED_GEMV_TOKENS and K.gemv_supported(x, self.weight):
             K.gemv(x, self.weight, out, K.TC_SILU_MUL, self.block)
         elif self.block and K.tc_gemm_supported(x, self.weight):
             K.tc_gemm(x, self.weight, out, K.TC_SILU_MUL, 2 * self.block)

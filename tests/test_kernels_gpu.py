@@ -390,7 +390,10 @@ def test_gemv_is_repeatable_and_row_independent(K):
 
 
 @pytest.mark.parametrize("M,N,K_,bn", [(128, 128, 64, 128), (100, 72, 96, 128), (1, 333, 72, 128), (300, 200, 200, 128),
-                                       (257, 520, 136, 256), (2048, 3072, 2048, 256), (129, 256, 8, 256)])
+                                       (257, 520, 136, 256), (2048, 3072, 2048, 256), (129, 256, 8, 256),
+                                       # one row of tiles and a long K: the cluster splits K
+                                       (64, 3072, 2048, 128), (17, 2048, 8192, 128), (128, 200, 1000, 128),
+                                       (100, 130, 520, 256), (33, 2048, 2048, 256)])
 def test_tc_gemm(K, M, N, K_, bn):
     torch.manual_seed(M + N)
     a = torch.randn(M, K_).bfloat16()
@@ -407,7 +410,8 @@ def test_tc_gemm(K, M, N, K_, bn):
     K.check_status(DEV)
 
 
-@pytest.mark.parametrize("M,I,K_,bn", [(200, 256, 96, 128), (130, 1024, 72, 256), (64, 192, 64, 128)])
+@pytest.mark.parametrize("M,I,K_,bn", [(200, 256, 96, 128), (130, 1024, 72, 256), (64, 192, 64, 128),
+                                       (64, 1024, 2048, 256), (20, 8192, 2048, 256), (128, 256, 1000, 128)])
 def test_tc_gemm_silu_mul(K, M, I, K_, bn):
     torch.manual_seed(I)
     a = torch.randn(M, K_).bfloat16()

@@ -19,8 +19,10 @@ from plain import llama_plain as P
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [5, 9, 13, 40, 70, 100], "B": [1, 7, 40, 100, 130, 200], "C": [3, 33, 64, 65, 128, 20]}
-DECODE = {"A": [2, 0, 9, 33, 5, 40], "B": [0, 6, 33, 1, 64, 70], "C": [2, 32, 1, 64, 3, 19]}
+LENGTHS = {"A": [5, 9, 13, 40, 70, 100], "B": [1, 7, 40, 100, 130, 200], "C": [3, 33, 64, 65, 128, 20],
+           "D": [150, 2, 64, 31, 90, 17]}
+DECODE = {"A": [2, 0, 9, 33, 5, 40], "B": [0, 6, 33, 1, 64, 70], "C": [2, 32, 1, 64, 3, 19],
+          "D": [40, 1, 0, 30, 33, 16]}
 
 
 @pytest.fixture(scope="module")
@@ -53,7 +55,7 @@ def check(got: dict, ref: dict, tol: float, what: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_agree_with_plain(models, name, dtype, tmp_path):
     m = models[name]
     V = m["cfg"]["vocab_size"]

@@ -35,7 +35,17 @@ TINY_C = dict(
     tie_word_embeddings=False, rms_norm_eps=1e-4, max_position_embeddings=256)
 TINY_C_INIT = dict(seed=5, norm_std=0.2)
 
-TINIES = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+# head size 80 (a step of 16 that is neither 64 nor 128), an intermediate size that no fused epilogue takes,
+# a hidden size that is no multiple of 64, more kv groups
+TINY_D = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama",
+    num_hidden_layers=2, hidden_size=200, num_attention_heads=6, num_key_value_heads=2, head_dim=80,
+    intermediate_size=120, vocab_size=1000, rope_theta=250000.0, rope_scaling=None,
+    tie_word_embeddings=True, rms_norm_eps=3e-6, max_position_embeddings=1024)
+TINY_D_INIT = dict(seed=77, norm_std=0.05)
+
+TINIES = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT),
+          "D": (TINY_D, TINY_D_INIT)}
 
 
 def make_folder(cfg_dict, init, folder, std=0.02):

@@ -19,7 +19,7 @@ import time
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
-HEADERS = ["common.cuh", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "tcgen05.cuh", "attention_noalloc.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--shared",
@@ -32,6 +32,7 @@ MODULES = {
     "tc_gemm": "tc_gemm.cu",
     "attention": "attention_kernels.cu",
     "gemv": "gemv_kernels.cu",
+    "flash_tc": "flash_tc.cu",
 }
 
 

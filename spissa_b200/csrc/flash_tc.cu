@@ -1,0 +1,327 @@
+// Causal prefill attention on the 5th-generation tensor cores, over the paged bfloat16 cache.
+//
+// Meaning as in the reference (crates/spissa-runtime/src/rotary.rs:335-415, softmax :549-569):
+// score = q·k / sqrt(head_dim), keys after the query are not seen, softmax in 32-bit with the maximum
+// subtracted, output = sum p·v, query head h reads kv head h / (heads / kv_heads).
+//
+// One CTA owns 128 consecutive query tokens of one head and walks the keys in blocks of 128 (two cache
+// pages of 64). Per block:
+//   warp 0   one thread fetches the two K pages and the two V pages with TMA (128-byte swizzle) into a
+//            two-stage ring; the query tile is fetched once;
+//   warp 1   one thread issues S = Q·Kᵀ (tcgen05.mma, M 128, N 128, A and B from shared memory, S in tensor
+//            memory) and, once the probabilities stand in tensor memory, O += P·V (A = P from tensor
+//            memory, B = V as an MN-major shared-memory operand, O in tensor memory);
+//   warps 2-5 one thread per query row: read the row of S (tcgen05.ld), running maximum and sum in the
+//            log2 domain, write P as bfloat16 pairs (tcgen05.st), rescale the row of O when the maximum
+//            moved, and at the end divide by the sum and store the row.
+// Tensor memory: S 128 columns, P 64, O head_dim. Every mbarrier wait is bounded; a wait that runs out
+// records a code in ``status`` and every role falls through to the common exit, where tensor memory is
+// freed. No load uses cluster multicast. Built for head size 64 without a window; the host refuses
+// anything else (the mma.sync kernel serves those).
+#include "tcgen05.cuh"
+
+SP_API const char* sp_flash_tc_last_error() { return sp_error_text; }
+
+namespace {
+
+constexpr int QT = 128;            // query rows per CTA
+constexpr int KB = 128;            // keys per block = two pages
+constexpr int PAGE = 64;
+constexpr int KV_STAGES = 2;
+constexpr float LOG2E = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD>
+struct Smem {
+    static constexpr int Q_BYTES = QT * HD * 2;
+    static constexpr int K_BYTES = KB * HD * 2;
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;              // K block then V block
+    static constexpr int TOTAL = Q_BYTES + KV_STAGES * STAGE_BYTES + 1024;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(192)
+flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
+                        const int* __restrict__ seq_start, const int* __restrict__ positions,
+                        const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
+                        int n_seqs, int nh, int nkv, float scale_log2, int* status) {
+    static_assert(HD == 64, "one 64-wide box per operand row");
+    using L = Smem<HD>;
+    constexpr uint32_t TMEM_COLS = 256;                           // S 128 | P 64 | O 64
+    constexpr uint32_t COL_S = 0, COL_P = 128, COL_O = 192;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s, bar_p, bar_o;
+    __shared__ uint32_t tmem_slot;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = smem_base;
+    const uint32_t kv_smem = smem_base + L::Q_BYTES;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // which sequence and which 128-token tile of it
+    int x = blockIdx.x, b = 0, first = 0, n_new = 0;
+    for (; b < n_seqs; ++b) {
+        first = seq_start[b];
+        n_new = seq_start[b + 1] - first;
+        const int nt = (n_new + QT - 1) / QT;
+        if (x < nt) break;
+        x -= nt;
+    }
+    const bool live = b < n_seqs;
+    const int t0 = live ? first + x * QT : 0;
+    const int n_rows = live ? min(QT, n_new - x * QT) : 0;
+    const int pos0 = live ? positions[t0] : 0;
+    const int h = blockIdx.y;
+    const int g = h / (nh / nkv);
+    const int n_blocks = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
+    const int* pt = page_table + (size_t)(live ? seq_row[b] : 0) * max_pages;
+    const int n_pages = live ? (pos0 + n_rows - 1) / PAGE + 1 : 0;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar_q), 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(smem_u32(&bar_kv_full[s]), 1);
+            mbar_init(smem_u32(&bar_kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_s), 1);
+        mbar_init(smem_u32(&bar_p), 4);                           // one arrival per softmax warp
+        mbar_init(smem_u32(&bar_o), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0 && live) {
+            mbar_expect_tx(smem_u32(&bar_q), L::Q_BYTES);
+            tma_load_2d(q_smem, &map_q, h * HD, t0, smem_u32(&bar_q));
+            for (int j = 0; j < n_blocks; ++j) {
+                const int s = j % KV_STAGES;
+                const uint32_t phase = (uint32_t)(j / KV_STAGES) & 1u;
+                if (!mbar_wait(smem_u32(&bar_kv_empty[s]), phase ^ 1u, status, 111)) break;
+                const uint32_t k_dst = kv_smem + s * L::STAGE_BYTES, v_dst = k_dst + L::K_BYTES;
+                mbar_expect_tx(smem_u32(&bar_kv_full[s]), L::STAGE_BYTES);
+                // the second page of the last block may lie beyond the sequence: any page of it will do, its keys are masked
+                const int p0 = pt[2 * j], p1 = pt[min(2 * j + 1, n_pages - 1)];
+                const int r0 = (p0 * nkv + g) * PAGE, r1 = (p1 * nkv + g) * PAGE;
+                tma_load_2d(k_dst, &map_k, 0, r0, smem_u32(&bar_kv_full[s]));
+                tma_load_2d(k_dst + PAGE * HD * 2, &map_k, 0, r1, smem_u32(&bar_kv_full[s]));
+                tma_load_2d(v_dst, &map_v, 0, r0, smem_u32(&bar_kv_full[s]));
+                tma_load_2d(v_dst + PAGE * HD * 2, &map_v, 0, r1, smem_u32(&bar_kv_full[s]));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && live) {
+            constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KB);            // S[128,128] = Q·Kᵀ, both K-major
+            constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(QT, HD);        // O[128,HD] += P·V, V MN-major
+            bool ok = mbar_wait(smem_u32(&bar_q), 0, status, 112);
+            auto issue_s = [&](int j) -> bool {
+                const int s = j % KV_STAGES;
+                if (!mbar_wait(smem_u32(&bar_kv_full[s]), (uint32_t)(j / KV_STAGES) & 1u, status, 113)) return false;
+                tc_fence_after();
+                const uint64_t dq = umma_desc_sw128(q_smem);
+                const uint64_t dk = umma_desc_sw128(kv_smem + s * L::STAGE_BYTES);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) tc_mma_bf16(tmem + COL_S, dq + 2 * k, dk + 2 * k, idesc_s, k != 0 ? 1u : 0u);
+                tc_commit(smem_u32(&bar_s));
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < n_blocks && ok; ++j) {
+                const int s = j % KV_STAGES;
+                ok = mbar_wait(smem_u32(&bar_p), (uint32_t)j & 1u, status, 114);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_src = kv_smem + s * L::STAGE_BYTES + L::K_BYTES;
+#pragma unroll
+                for (int k = 0; k < KB / 16; ++k) {
+                    // 16 keys further along K: two groups of 8 rows of 128 bytes = 2048 bytes; P: 8 columns
+                    tc_mma_bf16_ts(tmem + COL_O, tmem + COL_P + 8 * k, umma_desc_mn_sw128(v_src + k * 2048, 1024),
+                                   idesc_o, (j | k) != 0 ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&bar_kv_empty[s]));
+                tc_commit(smem_u32(&bar_o));
+                if (j + 1 < n_blocks) ok = issue_s(j + 1);
+            }
+        }
+    } else if (live) {
+        const int q = warp & 3;                                   // tensor-memory lanes 32q .. 32q+31
+        const int row = q * 32 + lane;
+        const int qpos = pos0 + row;
+        const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            ok = mbar_wait(smem_u32(&bar_s), (uint32_t)j & 1u, status, 115);
+            if (!ok) break;
+            tc_fence_after();
+            const int key0 = j * KB;
+            // pass 1: the row's maximum over the keys it may see
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KB; c0 += 32) {
+                uint32_t r[32];
+                tc_ld_32x32(lane_base + COL_S + c0, r);
+                tc_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (key0 + c0 + i <= qpos) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
+            const float m_new = fmaxf(m, mx * scale_log2);
+            const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float corr = ex2(m - m_safe);
+            // The previous block's O += P·V must be complete before its P is overwritten and before the row of O
+            // is rescaled to the new maximum.
+            if (j > 0) {
+                ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(j - 1) & 1u, status, 116);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t r[32];
+                        tc_ld_32x32(lane_base + COL_O + c0, r);
+                        tc_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+                        tc_st_32x32(lane_base + COL_O + c0, r);
+                    }
+                }
+            }
+            // pass 2: probabilities, their sum, and P as bfloat16 pairs into tensor memory
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < KB; c0 += 32) {
+                uint32_t r[32], pk[16];
+                tc_ld_32x32(lane_base + COL_S + c0, r);
+                tc_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const float p0 = key0 + c0 + i <= qpos ? ex2(fmaf(__uint_as_float(r[i]), scale_log2, -m_safe)) : 0.0f;
+                    const float p1 = key0 + c0 + i + 1 <= qpos ? ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_safe)) : 0.0f;
+                    sum += p0 + p1;
+                    __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+                    pk[i >> 1] = *(uint32_t*)&pr;
+                }
+                tc_st_32x16(lane_base + COL_P + (c0 >> 1), pk);
+            }
+            l = l * corr + sum;
+            m = m_new;
+            tc_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+        }
+        if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 1) & 1u, status, 117);
+        tc_fence_after();
+        if (ok && !(status && *(volatile int*)status != 0)) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = out + (size_t)(t0 + row) * nh * HD + (size_t)h * HD;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t r[32];
+                tc_ld_32x32(lane_base + COL_O + c0, r);
+                tc_ld_wait();
+                if (row < n_rows) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 w;
+                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
+                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv);
+                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv);
+                        w.x = *(uint32_t*)&a0; w.y = *(uint32_t*)&a1; w.z = *(uint32_t*)&a2; w.w = *(uint32_t*)&a3;
+                        *(uint4*)(dst + c0 + i) = w;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x cols bfloat16 with leading dimension ld, fetched in boxes of box_rows x 64 columns
+int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) SP_FAIL("flash_tc: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) SP_FAIL("flash_tc: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+}  // namespace
+
+// Whether this kernel takes the shape (1) or another attention kernel has to run (0).
+SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int window) {
+    return hd == 64 && nkv > 0 && nh % nkv == 0 && page_size == PAGE && window <= 0;
+}
+
+// q, out: [T, nh*hd] bfloat16; pools: [n_pages, nkv, 64, hd] bfloat16; n_q_tiles = sum over sequences of
+// ceil(new tokens / 128).
+SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, const void* vpool, long long n_pages,
+                               int T, const int* seq_start, const int* positions, const int* seq_row,
+                               const int* page_table, int max_pages, int page_size, int n_seqs, int n_q_tiles, int nh,
+                               int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
+    if (n_q_tiles <= 0) return 0;
+    if (!sp_flash_tc_supported(hd, nh, nkv, page_size, window))
+        SP_FAIL("flash_tc: built for head size 64, pages of 64 and no window (got head %d, page %d, window %d)", hd, page_size, window);
+    if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15) || ((uintptr_t)out & 15))
+        SP_FAIL("flash_tc: operands must start on a 16-byte boundary");
+    CUtensorMap mq, mk, mv;
+    if (make_map(&mq, q, T, nh * hd, (long long)nh * hd, QT)) return 1;
+    if (make_map(&mk, kpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
+    if (make_map(&mv, vpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(n_q_tiles, nh);
+    flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
+        mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
+        scale * LOG2E, status);
+    SP_CHECK_LAUNCH("flash_prefill_tc");
+    return 0;
+}

@@ -204,7 +204,14 @@ _STATUS: dict = {}
 STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                102: "the MMA issuer waited too long for a loaded pipeline stage",
                103: "the epilogue waited too long for the accumulator",
-               104: "the MMA issuer waited too long for a free accumulator"}
+               104: "the MMA issuer waited too long for a free accumulator",
+               111: "attention: the loader waited too long for a free key/value stage",
+               112: "attention: the MMA issuer waited too long for the queries",
+               113: "attention: the MMA issuer waited too long for keys and values",
+               114: "attention: the MMA issuer waited too long for the probabilities",
+               115: "attention: the softmax warps waited too long for the scores",
+               116: "attention: the softmax warps waited too long for the previous block's output",
+               117: "attention: the softmax warps waited too long for the last block's output"}
 
 
 def status_word(device) -> torch.Tensor:
@@ -373,3 +380,25 @@ def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
         c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.token_seq)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, c_void_p(_ptr(inv_freq)),
         c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ prefill attention on tcgen05
+def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int, window) -> bool:
+    """Whether the tcgen05 prefill attention takes this shape (head 64, pages of 64, no window, bfloat16)."""
+    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and hd == 64 and nkv > 0 and nh % nkv == 0
+            and page_size == 64 and not window and k_pool.is_contiguous())
+
+
+def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
+    """Causal attention of a step's tokens over the paged cache on the tcgen05 tensor cores.
+
+    ``n_q_tiles`` = sum over sequences of ceil(new tokens / 128). S, P and O live in tensor memory.
+    """
+    lib = load("flash_tc")
+    _need_contig(q, out, k_pool, v_pool)
+    pt = meta.page_table
+    _check("flash_tc", lib.sp_flash_prefill_tc(
+        c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
+        c_longlong(k_pool.shape[0]), q.shape[0], c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)),
+        c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles),
+        nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), c_void_p(_stream())))

@@ -479,3 +479,34 @@ def test_gemv_many_rows_streams_without_splitting_k(K, M, N, K_):
     outs = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
     K.gemv(x.to(DEV), interleave(g, u, 64).to(DEV), outs, mode=K.TC_SILU_MUL, pair=64)
     close(outs, P.silu(x.double() @ g.double().t()) * (x.double() @ u.double().t()), 4e-3)
+
+
+# ------------------------------------------------------------------ prefill attention on tcgen05 (head 64)
+def flash_tc_fn(K):
+    def fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
+        assert K.flash_tc_supported(q, k_pool, nh, nkv, hd, meta.page_size, window)
+        n_tiles = sum((c + 127) // 128 for c in meta.new_counts)
+        K.flash_prefill_tc(q, k_pool, v_pool, out, meta, meta.seq_start, len(meta.new_counts), n_tiles, nh, nkv, hd,
+                           window, scale)
+        K.check_status(DEV)
+    return fn
+
+
+@pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (3, 1), (32, 8)])
+def test_flash_prefill_tc(K, nh, nkv):
+    fn = flash_tc_fn(K)
+    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [7, 1, 65, 33], [0, 199, 64, 31], None, nh, 6e-3)
+    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [300, 64, 128, 129], [0, 0, 100, 27], None, nh + 2, 6e-3)
+    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [1, 1, 1], [0, 63, 300], None, nh + 1, 6e-3)
+
+
+@pytest.mark.parametrize("length,needle", [(700, 3), (700, 640), (129, 64), (64, 63), (1000, 0), (65, 64), (257, 128)])
+def test_flash_prefill_tc_finds_a_far_key(K, length, needle):
+    out, v = needle_case(K, flash_tc_fn(K), torch.bfloat16, length, needle)
+    for h in range(4):
+        assert torch.allclose(out[h], v[needle, h // 2], atol=2e-2), f"head {h} missed key {needle} of {length}"
+
+
+def test_flash_prefill_tc_ignores_junk_beyond_the_sequence(K):
+    attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [70], [0], None, 5, 6e-3)
+    attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [200, 3], [0, 190], None, 6, 6e-3)

@@ -188,11 +188,11 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=bf if mode == K.TC_SILU_MUL else torch.float32, device=dev)
         run = lambda i: K.gemv(x, ws[i % n_buf], out, mode, 128)
         bytes_ = N * Kd * 2.0
-    elif name in ("flash_prefill", "flash_decode"):
-        B = 1 if name == "flash_prefill" else 8
-        n_new = T if name == "flash_prefill" else 1
+    elif name in ("flash_prefill", "flash_prefill_tc", "flash_decode"):
+        B = 1 if name != "flash_decode" else 8
+        n_new = T if name != "flash_decode" else 1
         pages = B * (T // 64)
-        n_buf = 1 if name == "flash_prefill" else 40           # 40 x 8.4 MB of keys and values > L2
+        n_buf = 1 if name != "flash_decode" else 40           # 40 x 8.4 MB of keys and values > L2
         pools = [(rnd(pages, nkv, 64, hd), rnd(pages, nkv, 64, hd)) for _ in range(n_buf)]
         table = torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64)
         ar = torch.arange(B, dtype=torch.int32, device=dev)
@@ -206,6 +206,11 @@ def kernel_case(name: str, reps: int) -> int:
             seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
             run = lambda i: K.flash_prefill(q, pools[0][0], pools[0][1], out, meta, seq_start, 1, T // 64, nh, nkv,
                                             hd, None, scale)
+            flops = 4.0 * (T * (T + 1) / 2) * hd * nh
+        elif name == "flash_prefill_tc":
+            seq_start = torch.tensor([0, T], dtype=torch.int32, device=dev)
+            run = lambda i: K.flash_prefill_tc(q, pools[0][0], pools[0][1], out, meta, seq_start, 1, T // 128, nh, nkv,
+                                               hd, None, scale)
             flops = 4.0 * (T * (T + 1) / 2) * hd * nh
         else:
             seq_len = torch.full((B,), T, dtype=torch.int32, device=dev)
@@ -254,7 +259,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|flash_prefill|flash_decode|step_b8) instead of the step")
+                         "gemv_down|gemv_head|flash_prefill|flash_prefill_tc|flash_decode|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     args = ap.parse_args()
     if args.kernel_case:

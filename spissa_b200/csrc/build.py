@@ -19,7 +19,7 @@ import time
 from pathlib import Path
 
 CSRC = Path(__file__).resolve().parent
-HEADERS = ["common.cuh", "tcgen05.cuh", "attention_noalloc.h"]
+HEADERS = ["common.cuh", "async_copy.cuh", "tcgen05.cuh", "flash_common.cuh", "attention_noalloc.h"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo", "--shared",
@@ -33,6 +33,7 @@ MODULES = {
     "attention": "attention_kernels.cu",
     "gemv": "gemv_kernels.cu",
     "flash_tc": "flash_tc.cu",
+    "decode_layers": "decode_layers.cu",
 }
 
 

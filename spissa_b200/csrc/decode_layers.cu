@@ -1,0 +1,933 @@
+// All layers of a decode step (one new token per sequence, up to 16 sequences) in ONE persistent kernel.
+//
+// A layer here is the pre-norm block of the reference (crates/spissa-runtime/src/model.rs: norm → attention
+// → residual, norm → feed-forward → residual; kernels in rotary.rs): RMSNorm, stacked QKV projection,
+// rotate-half position encoding, grouped-query attention over the paged cache, output projection, RMSNorm,
+// gate/up projections with silu(gate)·up, down projection. Which tensors, sizes and constants a layer has
+// comes from a table of descriptors that the host builds from the parts of the model; the kernel knows no
+// model.
+//
+// Why one kernel: at a few tokens per step every product is a stream of weights through the SM, and as
+// separate kernels each stream starts from an empty pipe. Here one CTA per SM lives through the whole step:
+//   * a copy warp walks, for its CTA, the weight tiles of every product of every layer in the order the CTA
+//     will use them, and fetches them with bulk async copies into a ring of shared-memory stages. The ring
+//     does not care about phases: while the CTA waits at a grid barrier or works on attention, the weights
+//     of the products to come are already on their way, so HBM stays busy across phase boundaries;
+//   * eight consumer warps take the tiles (mma.sync m16n8k16, tokens as the 16 rows, 8+8 rows of W as the
+//     columns, each warp a 64-column slice of the tile's K), add their slices in warp order through shared
+//     memory and run the epilogue: rotate and store q / write k and v into the cache; add into the 32-bit
+//     residual; silu(gate)·up;
+//   * phases that need every CTA's result are separated by a grid barrier (cooperative launch; an atomic
+//     counter; bounded spin).
+// RMSNorm costs no phase of its own: whoever adds into the residual also sums the squares of what it wrote,
+// per CTA and token; the next product adds the CTAs' sums in CTA order and normalises the residual into shared
+// memory. Statistics, rotation angles, softmax and the residual are 32-bit. Every sum has a fixed order: a
+// token's result depends neither on timing nor on the other tokens of the step.
+//
+// Every wait (mbarrier, grid barrier) is bounded. A wait that runs out records a code in ``status`` and sets
+// an abort flag; from then on waits are skipped but the control flow stays the same, so that no warp is left
+// behind at a barrier: the kernel ends with a meaningless result and the host sees the code. No load uses
+// cluster multicast.
+#include "flash_common.cuh"
+#include <cuda.h>
+#include <stdlib.h>
+
+SP_API const char* sp_decode_layers_last_error() { return sp_error_text; }
+
+namespace {
+
+constexpr int CWARPS = 8;                       // consumer warps
+constexpr int CTHREADS = CWARPS * 32;
+constexpr int THREADS = CTHREADS + 32;          // and the copy warp
+constexpr int KC = 512;                         // columns of W per stage
+constexpr int BOXC = 256;                       // columns per TMA box (the most a box may have)
+constexpr int WSL = KC / CWARPS;                // columns of a tile per consumer warp
+constexpr int SS = WSL / 32;                    // steps of 32 columns per warp and tile
+constexpr int BOX_BYTES = 16 * BOXC * 2;        // one box: 2 halves x 8 rows x 256 columns
+constexpr int STAGE_BYTES = (KC / BOXC) * BOX_BYTES;
+constexpr int MAX_STAGES = 12;
+constexpr int MAXT = 16;                        // tokens per step
+constexpr int RED_FLOATS = CWARPS * 2 * 32 * 4; // one buffer of the K-slice sums
+constexpr int MAX_CHUNKS = 64;                  // key chunks per sequence
+constexpr int MAX_CHUNK_PAGES = 512;            // pages per chunk (their table entries wait in shared memory)
+constexpr int SMEM_LIMIT = 232448;              // per CTA on sm_100
+constexpr int STATIC_SMEM = 1536;               // barriers and small arrays below, rounded up
+
+struct LayerDesc {
+    const __nv_bfloat16* w_qkv;     // [(nh + 2 nkv) hd, H]  q heads, k heads, v heads
+    const __nv_bfloat16* w_o;       // [H, nh hd]
+    const __nv_bfloat16* w_gu;      // [2 I, H]  gu_pair gate rows, their gu_pair up rows, and so on
+    const __nv_bfloat16* w_down;    // [H, I]
+    const __nv_bfloat16* norm1;     // [H]
+    const __nv_bfloat16* norm2;     // [H]
+    __nv_bfloat16* k_pool;          // [pages, nkv, 64, hd]
+    __nv_bfloat16* v_pool;
+    const float* inv_freq;          // [hd / 2]
+    int nh, nkv, I, gu_pair;
+    float eps1, eps2, scale_log2;
+    int pad;
+};
+static_assert(sizeof(LayerDesc) == 104, "the host packs this layout");
+
+struct Params {
+    const LayerDesc* layers;
+    float* x;                       // [T, H] residual, in and out
+    __nv_bfloat16* q;               // [T, nh hd]
+    __nv_bfloat16* attn;            // [T, nh hd]
+    __nv_bfloat16* act;             // [T, I]
+    __nv_bfloat16* xw;              // [T, H] residual times the weight of the norm that reads it next
+    float* ssq;                     // [2][16][CTAs rounded up to 4] sums of squares of the residual, per token and CTA
+    float* part_o;                  // [T][nh][chunks][hd]
+    float* part_ml;                 // [T][nh][chunks][2]
+    const int* positions;           // [T] position of each new token = keys before it
+    const int* seq_row;             // [T] row of the page table
+    const int* page_table;
+    unsigned* sync;                 // [0] barrier arrivals (and the abort bit), [1] CTAs finished
+    int* status;
+    const CUtensorMap* maps;        // [layers][4]: QKV, output, gate/up, down; see sp_decode_layers_encode_map
+    unsigned long long* trace;      // optional: the global timer as CTA 0 leaves each grid barrier
+    int debug;
+    int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+// produced inside this kernel by other CTAs: read at L2, never from this SM's L1
+__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+// Predicated loads that leave zeros when ``pred`` is false. The zero is set BEFORE the load and nothing reads
+// the registers until their use: the warp goes on while the load is in flight.
+__device__ __forceinline__ void lds128_if(uint4& v, uint32_t a, bool pred) {
+    v = make_uint4(0, 0, 0, 0);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t@q ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n\t}"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "r"(a), "r"((int)pred));
+}
+__device__ __forceinline__ void ld_cg_u4_if(uint4& v, const void* p, bool pred) {
+    v = make_uint4(0, 0, 0, 0);
+    asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %5, 0;\n\t@q ld.global.cg.v4.b32 {%0,%1,%2,%3}, [%4];\n\t}"
+                 : "+r"(v.x), "+r"(v.y), "+r"(v.z), "+r"(v.w) : "l"(p), "r"((int)pred));
+}
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------- the products of a layer
+struct Job {
+    const __nv_bfloat16* W;
+    int N, K;          // rows and columns of W
+    int pair;          // > 0: rows come in pairs ``pair`` apart (rotation halves, gate and up); 0: plain rows
+    int n_blocks;      // blocks of 16 rows of W
+};
+
+template <int HD>
+__device__ __forceinline__ Job job_of(const LayerDesc& L, int which, int H) {
+    Job j;
+    if (which == 0) { j.W = L.w_qkv; j.N = (L.nh + 2 * L.nkv) * HD; j.K = H; j.pair = HD / 2; }
+    else if (which == 1) { j.W = L.w_o; j.N = H; j.K = L.nh * HD; j.pair = 0; }
+    else if (which == 2) { j.W = L.w_gu; j.N = 2 * L.I; j.K = H; j.pair = L.gu_pair; }
+    else { j.W = L.w_down; j.N = H; j.K = L.I; j.pair = 0; }
+    j.n_blocks = j.pair ? (j.N / 2 + 7) / 8 : (j.N + 15) / 16;
+    return j;
+}
+
+// rows of W in the two halves of block ``rb`` and how many of each half exist
+__device__ __forceinline__ void block_rows(const Job& j, int rb, int& rowA, int& rowB, int& nA, int& nB) {
+    if (j.pair) {
+        const int o0 = rb * 8;
+        rowA = (o0 / j.pair) * 2 * j.pair + (o0 % j.pair);
+        rowB = rowA + j.pair;
+        const int left = j.N / 2 - o0;
+        nA = nB = left >= 8 ? 8 : (left > 0 ? left : 0);
+    } else {
+        rowA = rb * 16;
+        rowB = rowA + 8;
+        const int la = j.N - rowA, lb = j.N - rowB;
+        nA = la >= 8 ? 8 : (la > 0 ? la : 0);
+        nB = lb >= 8 ? 8 : (lb > 0 ? lb : 0);
+    }
+}
+
+struct Shared {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    float rstd[MAXT];
+    float ssq[128];
+    float warp_sum[CWARPS];
+    int tok_pos[MAXT];     // position of each token, and the cache page that holds it
+    int tok_page[MAXT];
+    int aborted;
+};
+
+// Grid-barrier arrivals are counted in sync[0]; an abort sets ABORT_BIT there, which lets every waiter through.
+constexpr unsigned ABORT_BIT = 0x40000000u;
+
+__device__ __forceinline__ void raise_abort(const Params& p, Shared* sh, int code) {
+    if (p.status) atomicCAS(p.status, 0, code);
+    atomicOr(&p.sync[0], ABORT_BIT);
+    *(volatile int*)&sh->aborted = 1;
+}
+__device__ __forceinline__ bool is_aborted(Shared* sh) { return *(volatile int*)&sh->aborted != 0; }
+
+// ---------------------------------------------------------------- the copy warp
+template <int HD>
+__device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) {
+    const int G = gridDim.x, cta = blockIdx.x, S = p.n_stages;
+    uint32_t n = 0;
+    int cursor = 0;
+    for (int l = 0; l < p.n_layers; ++l) {
+        const LayerDesc L = p.layers[l];
+        for (int which = 0; which < 4; ++which) {
+            const Job j = job_of<HD>(L, which, p.H);
+            const int nkt = (j.K + KC - 1) / KC;
+            const CUtensorMap* map = p.maps + (size_t)l * 4 + which;
+            const int pr = j.pair ? j.pair : 8;
+            for (int rb = (cta - cursor + G) % G; rb < j.n_blocks; rb += G) {
+                const int o0 = rb * 8;                              // first of the block's 8 rows within each half
+                for (int kt = 0; kt < nkt; ++kt, ++n) {
+                    const int slot = n % S;
+                    const uint32_t full = smem_u32(&sh->full[slot]), empty = smem_u32(&sh->empty[slot]);
+                    if (!is_aborted(sh) && !mbar_wait(empty, ((n / S) & 1u) ^ 1u, nullptr, 0)) raise_abort(p, sh, 201);
+                    if (lane == 0) {
+                        // columns beyond K and rows beyond N arrive as zeros and count as bytes all the same
+                        mbar_expect_tx(full, (uint32_t)STAGE_BYTES);
+#pragma unroll
+                        for (int c = 0; c < KC / BOXC; ++c)
+                            tma_load_4d(ring + slot * STAGE_BYTES + c * BOX_BYTES, map, kt * KC + c * BOXC, o0 % pr, 0, o0 / pr, full);
+                    }
+                    __syncwarp();
+                }
+            }
+            cursor = (cursor + j.n_blocks) % G;
+        }
+    }
+    // after an abort tiles may still be in flight into this CTA's shared memory: let them land
+    if (is_aborted(sh)) {
+        for (uint32_t back = 1; back <= (uint32_t)S && back <= n; ++back) {
+            const uint32_t i = n - back;
+            mbar_wait(smem_u32(&sh->full[i % S]), (i / S) & 1u, nullptr, 0);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- consumers: one product
+// The 16 rows of a block are the M of the mma (rows 0-7 the first half, 8-15 the second), eight tokens its N;
+// tokens 8-15, when there are any, are a second N block. Lane (g, t) holds row g of both halves and token g,
+// eight consecutive columns each: K is permuted the same way in both operands, which a dot product allows.
+// ``aload(kt, a)``: starts the loads of the warp's activation fragments for tile kt: a[s][0] token g, a[s][1] token g + 8, eight
+// consecutive columns from kt·KC + warp·64 + s·32 + 8t. ``epi(rb, m, c, a, b, rowA, rowB, nA, nB, held)``: token m,
+// column c (0..7) of both halves of block rb; ``held`` is what ``pre(rb, m, c, rowA, rowB, nA, nB)`` returned when
+// the block began (loads that the epilogue needs, issued before the tiles so that they cost no waiting).
+struct Walk {
+    uint32_t n;        // tiles taken so far (the copy warp counts the same way)
+    int cursor;        // which CTA gets block 0 of the next product
+    int red_par;
+};
+
+template <bool WIDE, class ALoad, class Pre, class Epi>
+__device__ __forceinline__ void product(const Params& p, Shared* sh, const Job& j, Walk& w, uint32_t ring, float* red,
+                                        ALoad aload, Pre pre, Epi epi) {
+    constexpr int NF = WIDE ? 2 : 1;                              // token blocks of 8
+    constexpr int DEPTH = WIDE ? 2 : 4;                           // tiles whose activation fragments are in flight (as registers allow)
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = gridDim.x, S = p.n_stages;
+    const int nkt = (j.K + KC - 1) / KC;
+    const int first = ((int)blockIdx.x - w.cursor + G) % G;
+    if (first < j.n_blocks) {
+        // slot u of the ring holds the fragments of tile kt0 + u; after its use it is refilled for its next use
+        uint4 fr[DEPTH][SS][NF];
+#pragma unroll
+        for (int u = 0; u < DEPTH; ++u) aload(u < nkt ? u : 0, fr[u]);
+        for (int rb = first; rb < j.n_blocks; rb += G) {
+            int rowA, rowB, nA, nB;
+            block_rows(j, rb, rowA, rowB, nA, nB);
+            // what the epilogue will need from global memory is asked for now and arrives during the tiles
+            const int e_m = 8 * (tid >> 6) + 2 * ((tid >> 1) & 3) + (tid & 1), e_c = (tid >> 3) & 7;
+            float4 held = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (tid < 64 * NF) held = pre(rb, e_m, e_c, rowA, rowB, nA, nB);
+            float acc[NF][2][4];                                  // [token block][half of the lane's columns][c0..c3]
+#pragma unroll
+            for (int i = 0; i < NF; ++i)
+#pragma unroll
+                for (int h = 0; h < 2; ++h) acc[i][h][0] = acc[i][h][1] = acc[i][h][2] = acc[i][h][3] = 0.0f;
+            for (int kt0 = 0; kt0 < nkt; kt0 += DEPTH) {
+#pragma unroll
+                for (int u = 0; u < DEPTH; ++u) {
+                    const int kt = kt0 + u;
+                    if (kt >= nkt) break;
+                    const int slot = w.n % S;
+                    if (!(p.debug & 2) && !is_aborted(sh) && !mbar_wait(smem_u32(&sh->full[slot]), (w.n / S) & 1u, nullptr, 0)) raise_abort(p, sh, 202);
+                    const int kc = min(KC, j.K - kt * KC);
+                    const uint32_t base = ring + slot * STAGE_BYTES;
+                    if (warp * WSL < kc && !(p.debug & 1)) {
+                        uint4 wa[SS], wb[SS];
+#pragma unroll
+                        for (int s = 0; s < SS; ++s) {
+                            const int kl = warp * WSL + s * 32 + 8 * t;
+                            const uint32_t at = base + (kl / BOXC) * BOX_BYTES + (kl % BOXC) * 2;
+                            wa[s] = lds128(at + g * (BOXC * 2));                 // zeros where W ends
+                            wb[s] = lds128(at + (8 + g) * (BOXC * 2));
+                        }
+#pragma unroll
+                        for (int s = 0; s < SS; ++s)
+#pragma unroll
+                            for (int i = 0; i < NF; ++i) {
+                                mma16816(acc[i][0], wa[s].x, wb[s].x, wa[s].y, wb[s].y, fr[u][s][i].x, fr[u][s][i].y);
+                                mma16816(acc[i][1], wa[s].z, wb[s].z, wa[s].w, wb[s].w, fr[u][s][i].z, fr[u][s][i].w);
+                            }
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&sh->empty[slot]));
+                    ++w.n;
+                    aload(kt + DEPTH < nkt ? kt + DEPTH : (u < nkt ? u : 0), fr[u]);     // harmless after the last block
+                }
+            }
+            // the warps' K slices, added in warp order
+            float* buf = red + w.red_par * RED_FLOATS;
+#pragma unroll
+            for (int i = 0; i < NF; ++i)
+                *(float4*)(buf + ((warp * 2 + i) * 32 + lane) * 4) =
+                    make_float4(acc[i][0][0] + acc[i][1][0], acc[i][0][1] + acc[i][1][1], acc[i][0][2] + acc[i][1][2],
+                                acc[i][0][3] + acc[i][1][3]);
+            bar_sync(1, CTHREADS);
+            // thread (token block i, lane slot lp, v): token 8i + 2t + v, column g: c[v] is the first half, c[v + 2] the second
+            if (tid < 64 * NF) {
+                const int i = tid >> 6, lp = (tid >> 1) & 31, v = tid & 1;
+                float a = 0.0f, b = 0.0f;
+#pragma unroll
+                for (int ww = 0; ww < CWARPS; ++ww) {
+                    a += buf[((ww * 2 + i) * 32 + lp) * 4 + v];
+                    b += buf[((ww * 2 + i) * 32 + lp) * 4 + v + 2];
+                }
+                epi(rb, e_m, e_c, a, b, rowA, rowB, nA, nB, held);
+            }
+            w.red_par ^= 1;          // the other warps may run one block ahead of the epilogue: two buffers
+        }
+    }
+    w.cursor = (w.cursor + j.n_blocks) % G;
+}
+
+// ---------------------------------------------------------------- grid barrier
+__device__ __forceinline__ void grid_sync(const Params& p, Shared* sh, unsigned& epoch) {
+    bar_sync(1, CTHREADS);
+    ++epoch;
+    if (threadIdx.x == 0) {
+        const bool traced = p.trace && (blockIdx.x == 0 || blockIdx.x == 77) && epoch < 200u;
+        if (traced) p.trace[(blockIdx.x ? 400 : 0) + 2 * epoch] = global_ns();
+        // release: what this CTA wrote (seen by this thread through the CTA barrier) is visible before the count
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync) : "memory");
+        const unsigned target = epoch * gridDim.x;
+        if (!is_aborted(sh)) {
+            unsigned long long t0 = 0;
+            unsigned spins = 0, seen;
+            while ((seen = ld_acquire_u32(p.sync)) < target) {
+                if ((++spins & 255u) == 0u) {
+                    const unsigned long long now = global_ns();
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > WAIT_LIMIT_NS) { raise_abort(p, sh, 203); break; }
+                }
+            }
+            if (seen & ABORT_BIT) *(volatile int*)&sh->aborted = 1;
+        }
+        if (traced) p.trace[(blockIdx.x ? 400 : 0) + 2 * epoch + 1] = global_ns();
+    }
+    bar_sync(1, CTHREADS);
+}
+
+// ---------------------------------------------------------------- the product's input and its statistics
+// The residual reaches a product already multiplied by the norm's weight and rounded (``xw``, written by whoever
+// last added into the residual); 1/rms, which needs every CTA's sum of squares, multiplies the product's result
+// in the epilogue instead: y = rstd · (x ⊙ w)·Wᵀ. Here: xw into shared memory (one asynchronous copy) and
+// rstd[m] from the CTAs' sums, added in CTA order. A warp issues in order and a load from L2 takes a
+// microsecond or two under load, so all loads are issued before the first use.
+__device__ __noinline__ void stage_xw(const Params& p, Shared* sh, const float* ssq_src, float eps, uint32_t xn) {
+    constexpr int SSQ = 3;                       // float4 of CTA sums per thread: up to 16 x 3 x 4 = 192 CTAs in one batch
+    const int tid = threadIdx.x;
+    const int n8 = p.H >> 3;
+    for (int c = tid; c < p.T * n8; c += CTHREADS) {
+        const int m = c / n8, k8 = c - m * n8;
+        cp_async16(xn + m * p.xn_row + k8 * 16, p.xw + (size_t)m * p.H + (size_t)k8 * 8);
+    }
+    cp_async_commit();
+    {
+        // token m's sums lie side by side: 16 threads fetch them four at a time (every CTA reads all of them, so
+        // few, wide requests matter here)
+        const int m = tid >> 4, jj = tid & 15;
+        const int gp4 = ((int)gridDim.x + 3) >> 2;
+        const float4* row = (const float4*)(ssq_src + (size_t)m * gp4 * 4);
+        float4 part[SSQ];
+#pragma unroll
+        for (int u = 0; u < SSQ; ++u) {
+            const int c = jj + 16 * u;
+            part[u] = (m < p.T && c < gp4) ? __ldcg(row + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float s = 0.0f;
+#pragma unroll
+        for (int u = 0; u < SSQ; ++u) s += (part[u].x + part[u].y) + (part[u].z + part[u].w);
+        if (m < p.T)
+            for (int c = jj + 16 * SSQ; c < gp4; c += 16) { const float4 v = __ldcg(row + c); s += (v.x + v.y) + (v.z + v.w); }
+        s += __shfl_xor_sync(0xffffffffu, s, 8);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        if (jj == 0) sh->rstd[m] = 1.0f / sqrtf(s / (float)p.H + eps);
+    }
+    cp_async_wait<0>();
+    bar_sync(1, CTHREADS);
+}
+
+// the sums of squares that the epilogue threads (tid < 128) gathered while adding into the residual, per token,
+// in a fixed order: token m sits in threads 64·(m / 8) + 8g + 2·((m % 8) / 2) + m % 2, g = 0..7
+__device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, int stride) {
+    const int tid = threadIdx.x;
+    sh->ssq[tid] = mine;
+    bar_sync(2, 128);
+    if (tid < MAXT) {
+        const int m = tid;
+        float s = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < 8; ++gg) s += sh->ssq[64 * (m >> 3) + 8 * gg + 2 * ((m & 7) >> 1) + (m & 1)];
+        __stcg(dst + (size_t)m * stride, s);
+    }
+}
+
+// ---------------------------------------------------------------- attention: chunks of keys, then their combination
+template <int HD, int ST>
+__device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& L, uint8_t* scratch) {
+    using TL = Tile<HD>;
+    const uint32_t q_tile = smem_u32(scratch);                     // 16 rows
+    const uint32_t k_tiles = q_tile + 16 * TL::ROW;
+    const uint32_t v_tiles = k_tiles + ST * TL::BYTES;
+    float* merge = (float*)(scratch + 16 * TL::ROW + 2 * ST * TL::BYTES);    // [4 warps][16 rows][HD + 2]
+    int* pt_s = (int*)(merge + 4 * 16 * (HD + 2));                            // the chunk's page-table entries
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int Gq = L.nh / L.nkv;
+    const int n_items = p.T * L.nkv * p.n_chunks;
+    for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
+        const int b = it / (L.nkv * p.n_chunks), g = (it / p.n_chunks) % L.nkv, chunk = it % p.n_chunks;
+        const int pos = p.positions[b];
+        const int j_first = chunk * p.chunk_pages;
+        const int j_last = min(pos / KT, j_first + p.chunk_pages - 1);
+        const size_t part_base = ((size_t)b * L.nh + (size_t)g * Gq) * p.n_chunks + chunk;
+        if (j_first > j_last) {                                    // no keys in this chunk (the same for all 128 threads)
+            for (int i = tid; i < Gq; i += 128) {
+                p.part_ml[(part_base + (size_t)i * p.n_chunks) * 2] = -INFINITY;
+                p.part_ml[(part_base + (size_t)i * p.n_chunks) * 2 + 1] = 0.0f;
+            }
+            continue;
+        }
+        // the table entries first, all at once: a load inside the loop would stall the warp for its whole way to L2
+        const int* pt = p.page_table + (size_t)p.seq_row[b] * p.max_pages + j_first;
+        for (int i = tid; i <= j_last - j_first; i += 128) pt_s[i] = pt[i];
+        for (int c = tid; c < 16 * TL::CHUNKS; c += 128) {
+            const int r = c / TL::CHUNKS, k = c % TL::CHUNKS;
+            const uint32_t d = q_tile + r * TL::ROW + k * 16;
+            if (r < Gq) cp_async16(d, p.q + (size_t)b * L.nh * HD + (size_t)(g * Gq + r) * HD + k * 8);
+            else asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};" ::"r"(d), "r"(0u) : "memory");
+        }
+        cp_async_commit();
+
+        uint32_t qf[HD / 16][4];
+        float o[HD / 8][4];
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+        const int hi[2] = {pos, pos};
+        const int lo[2] = {0, 0};
+        // each warp fetches and uses its own 16 keys of every page: no barrier among the warps inside the loop
+        auto fetch = [&](int j, int stage) {
+            const size_t off = ((size_t)pt_s[j - j_first] * L.nkv + g) * KT * HD + (size_t)warp * 16 * HD;
+            const uint32_t kd = k_tiles + stage * TL::BYTES + warp * 16 * TL::ROW;
+            const uint32_t vd = v_tiles + stage * TL::BYTES + warp * 16 * TL::ROW;
+            for (int c = lane; c < 16 * TL::CHUNKS; c += 32) {
+                const int r = c / TL::CHUNKS, k = c % TL::CHUNKS;
+                cp_async16(kd + r * TL::ROW + k * 16, L.k_pool + off + (size_t)r * HD + k * 8);
+                cp_async16(vd + r * TL::ROW + k * 16, L.v_pool + off + (size_t)r * HD + k * 8);
+            }
+        };
+        bar_sync(2, 128);                                          // the table entries are in place
+#pragma unroll
+        for (int s = 0; s < ST - 1; ++s) {
+            if (j_first + s <= j_last) fetch(j_first + s, s);
+            cp_async_commit();
+        }
+        cp_async_wait<ST - 1>();
+        bar_sync(2, 128);
+        load_q_frags<HD>(q_tile, 0, lane, qf);
+        for (int j = j_first; j <= j_last; ++j) {
+            const int i = j - j_first, stage = i % ST;
+            if (j + ST - 1 <= j_last) fetch(j + ST - 1, (i + ST - 1) % ST);
+            cp_async_commit();
+            cp_async_wait<ST - 1>();
+            __syncwarp();
+            if (j * KT + KT - 1 <= pos)
+                flash_step<HD, 2, false>(qf, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, lo,
+                                         hi, L.scale_log2, o, m, l, lane);
+            else
+                flash_step<HD, 2, true>(qf, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, lo,
+                                        hi, L.scale_log2, o, m, l, lane);
+            __syncwarp();
+        }
+        cp_async_wait<0>();
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        }
+        constexpr int MS = HD + 2;
+        const int t = lane & 3;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float* dst = merge + ((size_t)warp * 16 + (lane >> 2) + r * 8) * MS;
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                dst[i * 8 + 2 * t] = o[i][2 * r];
+                dst[i * 8 + 2 * t + 1] = o[i][2 * r + 1];
+            }
+            if (t == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
+        }
+        bar_sync(2, 128);
+        for (int e = tid; e < Gq * HD; e += 128) {
+            const int row = e / HD, d = e % HD;
+            float mm = -INFINITY;
+#pragma unroll
+            for (int ww = 0; ww < 4; ++ww) mm = fmaxf(mm, merge[((size_t)ww * 16 + row) * MS + HD]);
+            const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+            float acc = 0.0f, ll = 0.0f;
+#pragma unroll
+            for (int ww = 0; ww < 4; ++ww) {
+                const float* src = merge + ((size_t)ww * 16 + row) * MS;
+                const float f = exp2f(src[HD] - msafe);
+                acc += src[d] * f;
+                ll += src[HD + 1] * f;
+            }
+            const size_t pi = part_base + (size_t)row * p.n_chunks;
+            p.part_o[pi * HD + d] = acc;
+            if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+        }
+        bar_sync(2, 128);                                          // the tiles are free for the next item
+    }
+}
+
+// out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order; one warp per (token, head)
+template <int HD>
+__device__ __noinline__ void attention_combine(const Params& p, const LayerDesc& L) {
+    constexpr int CB = 8;                                          // chunks whose loads are issued together
+    constexpr int DPL = HD / 32;                                   // output dims per lane
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nc = p.n_chunks;
+    for (int r = blockIdx.x * CWARPS + warp; r < p.T * L.nh; r += gridDim.x * CWARPS) {
+        const size_t bh = (size_t)r;
+        // lane c holds (m, l) of chunk c, c + 32, ...: the maximum over all chunks first
+        float mm = -INFINITY;
+        for (int c = lane; c < nc; c += 32) mm = fmaxf(mm, __ldcg(&p.part_ml[(bh * nc + c) * 2]));
+        mm = sp_warp_max(mm);
+        const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+        float ll = 0.0f, acc[DPL];
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
+        for (int c0 = 0; c0 < nc; c0 += CB) {
+            float mc[CB], lc[CB], oc[CB][DPL];
+#pragma unroll
+            for (int u = 0; u < CB; ++u) {
+                const int c = c0 + u;
+                if (c < nc) {
+                    const float2 ml = __ldcg((const float2*)&p.part_ml[(bh * nc + c) * 2]);
+                    mc[u] = ml.x; lc[u] = ml.y;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) oc[u][i] = __ldcg(&p.part_o[(bh * nc + c) * HD + lane + 32 * i]);
+                } else {
+                    mc[u] = -INFINITY; lc[u] = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) oc[u][i] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < CB; ++u) {
+                if (lc[u] > 0.0f) {                                 // chunks in order
+                    const float f = exp2f(mc[u] - msafe);
+                    ll += lc[u] * f;
+#pragma unroll
+                    for (int i = 0; i < DPL; ++i) acc[i] += oc[u][i] * f;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) p.attn[bh * HD + lane + 32 * i] = __float2bfloat16_rn(acc[i] / ll);
+    }
+}
+
+// ---------------------------------------------------------------- the consumer warps' walk through the layers
+template <int HD, int ST, bool WIDE>
+__device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red, uint8_t* uni) {
+    constexpr int NF = WIDE ? 2 : 1;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int G = gridDim.x, cta = blockIdx.x, T = p.T, H = p.H;
+    unsigned epoch = 0;
+    Walk w{0u, 0, 0};
+    const int gp = ((G + 3) >> 2) << 2;                        // floats per token in the table of sums
+    float* ssq_a = p.ssq;                                      // written by the output projection
+    float* ssq_b = p.ssq + (size_t)gp * 16;                    // written by the down projection (and here, first)
+
+    if (tid < T) {
+        const int pos = p.positions[tid];
+        sh->tok_pos[tid] = pos;
+        sh->tok_page[tid] = p.page_table[(size_t)p.seq_row[tid] * p.max_pages + pos / KT];
+    }
+    // sums of squares of the incoming residual and its product with the first norm's weight: CTA m does token m
+    {
+        float s = 0.0f;
+        if (cta < T) {
+            const __nv_bfloat16* w0 = p.layers[0].norm1;
+            for (int k = tid; k < H; k += CTHREADS) {
+                const float v = __ldcg(p.x + (size_t)cta * H + k);
+                s = fmaf(v, v, s);
+                p.xw[(size_t)cta * H + k] = __float2bfloat16_rn(v * __bfloat162float(w0[k]));
+            }
+        }
+        s = sp_warp_sum(s);
+        if (lane == 0) sh->warp_sum[warp] = s;
+        bar_sync(1, CTHREADS);
+        if (tid < MAXT) {
+            float tot = 0.0f;
+            for (int ww = 0; ww < CWARPS; ++ww) tot += sh->warp_sum[ww];
+            __stcg(ssq_b + (size_t)tid * gp + cta, (tid == cta) ? tot : 0.0f);
+        }
+        grid_sync(p, sh, epoch);
+    }
+
+    const uint32_t xn = smem_u32(uni);
+    // activation fragments from the normalised residual in shared memory
+    auto aload_xn = [&](int kt, uint4 (&a)[SS][NF]) {
+#pragma unroll
+        for (int s = 0; s < SS; ++s) {
+            const int k = kt * KC + warp * WSL + s * 32 + 8 * t;
+#pragma unroll
+            for (int i = 0; i < NF; ++i) lds128_if(a[s][i], xn + (g + 8 * i) * p.xn_row + k * 2, k < H && g + 8 * i < T);
+        }
+    };
+    // the same from a bfloat16 matrix [T, K] that other CTAs wrote in the phase before
+    auto aload_global = [&](const __nv_bfloat16* src, int K, int kt, uint4 (&a)[SS][NF]) {
+#pragma unroll
+        for (int s = 0; s < SS; ++s) {
+            const int k = kt * KC + warp * WSL + s * 32 + 8 * t;
+#pragma unroll
+            for (int i = 0; i < NF; ++i) ld_cg_u4_if(a[s][i], src + (size_t)(g + 8 * i) * K + k, k < K && g + 8 * i < T);
+        }
+    };
+
+    auto no_pre = [](int, int, int, int, int, int, int) { return make_float4(0.f, 0.f, 0.f, 0.f); };
+
+    for (int l = 0; l < p.n_layers; ++l) {
+        const LayerDesc L = p.layers[l];
+        const int nqk = L.nh + L.nkv;
+
+        // ---- QKV, rotation, cache write
+        stage_xw(p, sh, ssq_b, L.eps1, xn);
+        if (p.trace && cta == 0 && tid == 0) p.trace[600 + 4 * l] = global_ns();
+        product<WIDE>(p, sh, job_of<HD>(L, 0, H), w, ring, red, aload_xn, no_pre,
+                [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4&) {
+                    if (m >= T || c >= nA) return;
+                    const int row = rowA + c, blk = row / HD, d = row % HD;     // d < HD / 2; its partner is HD / 2 on
+                    const int pos = sh->tok_pos[m];
+                    a *= sh->rstd[m];
+                    b *= sh->rstd[m];
+                    float lo = a, hi = b;
+                    if (blk < nqk) {
+                        const float ang = (float)pos * L.inv_freq[d];
+                        const float cs = cosf(ang), sn = sinf(ang);
+                        lo = a * cs - b * sn;
+                        hi = b * cs + a * sn;
+                    }
+                    __nv_bfloat16* dst;
+                    if (blk < L.nh) {
+                        dst = p.q + (size_t)m * L.nh * HD + (size_t)blk * HD;
+                    } else {
+                        const bool is_k = blk < nqk;
+                        const int kvh = is_k ? blk - L.nh : blk - nqk;
+                        const int page = sh->tok_page[m];
+                        dst = (is_k ? L.k_pool : L.v_pool) + (((size_t)page * L.nkv + kvh) * KT + pos % KT) * HD;
+                    }
+                    dst[d] = __float2bfloat16_rn(lo);
+                    dst[d + HD / 2] = __float2bfloat16_rn(hi);
+                });
+        if (p.trace && cta == 0 && tid == 0) p.trace[601 + 4 * l] = global_ns();
+        grid_sync(p, sh, epoch);
+
+        // ---- attention
+        if (warp < 4) attention_chunks<HD, ST>(p, L, uni);
+        grid_sync(p, sh, epoch);
+        attention_combine<HD>(p, L);
+        grid_sync(p, sh, epoch);
+
+        // ---- output projection into the residual
+        // residual += product; its square for the next norm's statistics; residual times the next norm's weight
+        float ssq = 0.0f;
+        const __nv_bfloat16* next_w = L.norm2;
+        auto x_pre = [&](int rb, int m, int c, int rowA, int rowB, int nA, int nB) {
+            float4 h = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < T && c < nA) { h.x = __ldcg(p.x + (size_t)m * H + rowA + c); h.z = next_w ? __bfloat162float(next_w[rowA + c]) : 0.0f; }
+            if (m < T && c < nB) { h.y = __ldcg(p.x + (size_t)m * H + rowB + c); h.w = next_w ? __bfloat162float(next_w[rowB + c]) : 0.0f; }
+            return h;
+        };
+        auto add_into_x = [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4& h) {
+            if (m >= T) return;
+            if (c < nA) {
+                const float v = h.x + a;
+                __stcg(p.x + (size_t)m * H + rowA + c, v);
+                p.xw[(size_t)m * H + rowA + c] = __float2bfloat16_rn(v * h.z);
+                ssq = fmaf(v, v, ssq);
+            }
+            if (c < nB) {
+                const float v = h.y + b;
+                __stcg(p.x + (size_t)m * H + rowB + c, v);
+                p.xw[(size_t)m * H + rowB + c] = __float2bfloat16_rn(v * h.w);
+                ssq = fmaf(v, v, ssq);
+            }
+        };
+        {
+            const int Ko = L.nh * HD;
+            product<WIDE>(p, sh, job_of<HD>(L, 1, H), w, ring, red,
+                    [&](int kt, uint4 (&a)[SS][NF]) { aload_global(p.attn, Ko, kt, a); },
+                    x_pre, add_into_x);
+        }
+        if (warp < 4) publish_ssq(sh, ssq, ssq_a + cta, gp);
+        grid_sync(p, sh, epoch);
+
+        // ---- gate and up with silu(gate)·up
+        stage_xw(p, sh, ssq_a, L.eps2, xn);
+        if (p.trace && cta == 0 && tid == 0) p.trace[602 + 4 * l] = global_ns();
+        product<WIDE>(p, sh, job_of<HD>(L, 2, H), w, ring, red, aload_xn, no_pre,
+                [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4&) {
+                    if (m >= T || c >= nA) return;
+                    a *= sh->rstd[m];
+                    b *= sh->rstd[m];
+                    p.act[(size_t)m * L.I + rb * 8 + c] = __float2bfloat16_rn((a / (1.0f + expf(-a))) * b);
+                });
+        if (p.trace && cta == 0 && tid == 0) p.trace[603 + 4 * l] = global_ns();
+        grid_sync(p, sh, epoch);
+
+        // ---- down projection into the residual
+        ssq = 0.0f;
+        next_w = l + 1 < p.n_layers ? p.layers[l + 1].norm1 : nullptr;
+        {
+            const int Kd = L.I;
+            product<WIDE>(p, sh, job_of<HD>(L, 3, H), w, ring, red,
+                    [&](int kt, uint4 (&a)[SS][NF]) { aload_global(p.act, Kd, kt, a); },
+                    x_pre, add_into_x);
+        }
+        if (warp < 4) publish_ssq(sh, ssq, ssq_b + cta, gp);
+        if (l + 1 < p.n_layers) grid_sync(p, sh, epoch);
+    }
+}
+
+// ---------------------------------------------------------------- the kernel
+template <int HD, int ST>
+__global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_constant__ Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ Shared sh_;
+    Shared* sh = &sh_;
+    const uint32_t ring = smem_u32(smem);
+    float* red = (float*)(smem + (size_t)p.n_stages * STAGE_BYTES);
+    uint8_t* uni = (uint8_t*)(red + 2 * RED_FLOATS);               // normalised residual, or attention tiles
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = gridDim.x, cta = blockIdx.x;
+
+    if (tid == 0) {
+        for (int s = 0; s < p.n_stages; ++s) {
+            mbar_init(smem_u32(&sh->full[s]), 1);
+            mbar_init(smem_u32(&sh->empty[s]), CWARPS);
+        }
+        sh->aborted = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (p.trace && (cta == 0 || cta == 77) && tid == 0) p.trace[cta ? 401 : 1] = global_ns();
+    if (warp == CWARPS) {
+        copy_warp<HD>(p, sh, ring, lane);
+    } else if (p.T > 8) {
+        consumers<HD, ST, true>(p, sh, ring, red, uni);
+    } else {
+        consumers<HD, ST, false>(p, sh, ring, red, uni);
+    }
+    __syncthreads();
+    // the last CTA to finish hands the counters back at zero for the next launch
+    if (tid == 0) {
+        if (p.trace && cta == 0) p.trace[1023] = global_ns();
+        __threadfence();
+        const unsigned prev = atomicAdd(&p.sync[1], 1u);
+        if (prev == (unsigned)G - 1u) {
+            p.sync[0] = 0u;
+            p.sync[1] = 0u;
+            __threadfence();
+        }
+    }
+}
+
+template <int HD>
+constexpr int attention_bytes(int st) {
+    return 16 * Tile<HD>::ROW + 2 * st * Tile<HD>::BYTES + 4 * 16 * (HD + 2) * 4 + MAX_CHUNK_PAGES * 4;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
+    }
+    return n;
+}
+
+unsigned long long* trace_buffer = nullptr;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+}  // namespace
+
+// Optional: 1024 64-bit words on the device into which CTA 0 writes the global timer at the start ([0]), as it
+// leaves each grid barrier ([1], [2], ...) and at its end ([1023]). Null (the default) switches it off.
+SP_API void sp_decode_layers_set_trace(void* buffer) { trace_buffer = (unsigned long long*)buffer; }
+
+// The TMA view of one weight matrix W [N, K] (bfloat16, rows contiguous) as the kernel walks it: row
+// blk·2·pair + h·pair + r is element (r, h, blk) of a 4-dimensional tensor [N / (2 pair)][2][pair][K], from which
+// one box takes 8 rows of both halves x 256 columns. ``pair`` 0 means plain rows (8 and 8). Writes the 128 bytes of
+// the map to ``out`` (host memory); the host copies the maps of all layers to the device, 64-byte aligned.
+SP_API int sp_decode_layers_encode_map(void* out, const void* W, int N, int K, int pair) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) SP_FAIL("decode_layers: the driver does not offer cuTensorMapEncodeTiled");
+    const int pr = pair > 0 ? pair : 8;
+    if ((pr % 8) || (N % (2 * pr)) || (K % 8) || ((uintptr_t)W & 15))
+        SP_FAIL("decode_layers: a matrix of %d x %d in row pairs %d apart does not fit the tile walk", N, K, pr);
+    cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)pr, 2u, (cuuint64_t)(N / (2 * pr))};
+    cuuint64_t strides[3] = {(cuuint64_t)K * 2, (cuuint64_t)pr * K * 2, (cuuint64_t)2 * pr * K * 2};
+    cuuint32_t box[4] = {(cuuint32_t)BOXC, 8u, 2u, 1u};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUtensorMap map;
+    CUresult r = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(W), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) SP_FAIL("decode_layers: cuTensorMapEncodeTiled failed with code %d (N %d, K %d, pair %d)", (int)r, N, K, pr);
+    memcpy(out, &map, sizeof(map));
+    return 0;
+}
+SP_API int sp_decode_layers_map_bytes() { return (int)sizeof(CUtensorMap); }
+
+// CTAs of the kernel = SMs of the device: the host sizes ``ssq`` ([2][CTAs][16] floats) with it.
+SP_API int sp_decode_layers_ctas() { return sm_count(); }
+SP_API int sp_decode_layers_max_chunks() { return MAX_CHUNKS; }
+SP_API int sp_decode_layers_desc_bytes() { return (int)sizeof(LayerDesc); }
+
+// Whether the kernel takes these sizes (1) or the layers have to run part by part (0, with the reason as the
+// library's last error). ``max_i``, ``max_qdim`` are the largest feed-forward width and heads·head_dim of any layer.
+SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int max_heads_per_kv) {
+    if (T <= 0 || T > MAXT) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: 1 to %d tokens, got %d", MAXT, T); return 0; }
+    if (hd != 64 && hd != 128) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: head_dim %d is not built (64 and 128 are)", hd); return 0; }
+    if (page_size != KT) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: pages of %d tokens, built for %d", page_size, KT); return 0; }
+    if (H % 8) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: width %d is no multiple of 8", H); return 0; }
+    if (max_heads_per_kv > 16) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: %d query heads per kv head, at most 16 fit one tile", max_heads_per_kv); return 0; }
+    const int xn = T * (((H * 2 + 127) / 128) * 128 + 64);
+    const int att = hd == 64 ? attention_bytes<64>(3) : attention_bytes<128>(2);
+    const int uni = xn > att ? xn : att;
+    if ((SMEM_LIMIT - STATIC_SMEM - 2 * RED_FLOATS * 4 - uni) / STAGE_BYTES < 2) {
+        snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: width %d with %d tokens leaves no room for the weight ring", H, T);
+        return 0;
+    }
+    return 1;
+}
+
+// ``layers``: n_layers descriptors on the device. ``len_pages``: pages that the longest sequence of the step
+// may hold (it only shapes the split of the keys; any actual length is handled). ``max_nkv``: most kv heads of
+// any layer. part_o / part_ml hold T·max(nh)·MAX_CHUNKS·(hd + 2) floats together; sync: 3 zeroed words.
+SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, int T, int H, int hd, float* x, void* q, void* attn,
+                            void* act, void* xw, float* ssq, float* part_o, float* part_ml, const int* positions,
+                            const int* seq_row, const int* page_table, int max_pages, int page_size, int len_pages,
+                            int max_nkv, int max_heads_per_kv, unsigned* sync, int* status, cudaStream_t stream) {
+    if (n_layers <= 0) return 0;
+    if (!sp_decode_layers_supported(T, H, hd, page_size, max_heads_per_kv)) return 1;
+    const int G = sm_count();
+    if (G <= 0) SP_FAIL("decode_layers: cannot read the number of SMs");
+    if (((uintptr_t)x & 15) || ((uintptr_t)q & 15) || ((uintptr_t)attn & 15) || ((uintptr_t)act & 15))
+        SP_FAIL("decode_layers: buffers must start on a 16-byte boundary");
+    Params p;
+    if ((uintptr_t)maps & 63) SP_FAIL("decode_layers: the tensor maps must start on a 64-byte boundary");
+    p.layers = (const LayerDesc*)layers;
+    p.maps = (const CUtensorMap*)maps;
+    p.x = x; p.q = (__nv_bfloat16*)q; p.attn = (__nv_bfloat16*)attn; p.act = (__nv_bfloat16*)act; p.xw = (__nv_bfloat16*)xw;
+    p.ssq = ssq; p.part_o = part_o; p.part_ml = part_ml;
+    p.positions = positions; p.seq_row = seq_row; p.page_table = page_table;
+    p.sync = sync; p.status = status; p.trace = trace_buffer;
+    p.debug = getenv("SPDBG") ? atoi(getenv("SPDBG")) : 0;
+    p.n_layers = n_layers; p.T = T; p.H = H; p.max_pages = max_pages;
+    p.xn_row = ((H * 2 + 127) / 128) * 128 + 64;
+    const int xn = T * p.xn_row;
+    const int att = hd == 64 ? attention_bytes<64>(3) : attention_bytes<128>(2);
+    const int uni = xn > att ? xn : att;
+    int stages = (SMEM_LIMIT - STATIC_SMEM - 2 * RED_FLOATS * 4 - uni) / STAGE_BYTES;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    p.n_stages = stages;
+    // split of the keys: about one (sequence, kv head, chunk) item per CTA
+    if (len_pages < 1) len_pages = 1;
+    int want = G / (T * (max_nkv > 0 ? max_nkv : 1));
+    if (want < 1) want = 1;
+    if (want > MAX_CHUNKS) want = MAX_CHUNKS;
+    if (want > len_pages) want = len_pages;
+    if (want * MAX_CHUNK_PAGES < len_pages) want = (len_pages + MAX_CHUNK_PAGES - 1) / MAX_CHUNK_PAGES;
+    if (want > MAX_CHUNKS) SP_FAIL("decode_layers: %d pages per sequence are more than %d chunks of %d hold", len_pages, MAX_CHUNKS, MAX_CHUNK_PAGES);
+    p.chunk_pages = (len_pages + want - 1) / want;
+    p.n_chunks = (len_pages + p.chunk_pages - 1) / p.chunk_pages;
+    const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;
+
+    void* args[] = {(void*)&p};
+    const void* fn = hd == 64 ? (const void*)decode_layers_kernel<64, 3> : (const void*)decode_layers_kernel<128, 2>;
+    static bool configured[2] = {false, false};
+    const int which = hd == 64 ? 0 : 1;
+    if (!configured[which]) {
+        cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - STATIC_SMEM);
+        if (e != cudaSuccess) SP_FAIL("decode_layers: cannot reserve shared memory: %s", cudaGetErrorString(e));
+        int per_sm = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, THREADS, smem);
+        if (e != cudaSuccess || per_sm < 1) SP_FAIL("decode_layers: one CTA of %d bytes does not fit an SM", smem);
+        configured[which] = true;
+    }
+    SP_CHECK_CALL("decode_layers", cudaLaunchCooperativeKernel(fn, dim3(G), dim3(THREADS), args, (size_t)smem, stream));
+    return 0;
+}

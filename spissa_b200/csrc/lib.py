@@ -169,6 +169,14 @@ def add_inplace(dst, src):
                                          c_longlong(dst.numel()), c_void_p(_stream())))
 
 
+def prefetch_l2(t: torch.Tensor):
+    """Hint: start bringing the contiguous tensor ``t`` into L2; returns without waiting. No result depends on it."""
+    lib = load("generic")
+    _need_contig(t)
+    _check("generic", lib.sp_prefetch_l2(c_void_p(_ptr(t)), c_longlong(t.numel() * t.element_size()),
+                                         c_void_p(_stream())))
+
+
 def argmax_rows(logits, out):
     """out[r] = index of the first maximum of logits[r,:] (float32)."""
     lib = load("generic")
@@ -205,6 +213,9 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                102: "the MMA issuer waited too long for a loaded pipeline stage",
                103: "the epilogue waited too long for the accumulator",
                104: "the MMA issuer waited too long for a free accumulator",
+               201: "decode layers: the copy warp waited too long for a free stage of the weight ring",
+               202: "decode layers: a consumer warp waited too long for a weight tile",
+               203: "decode layers: a CTA waited too long at the grid barrier",
                111: "attention: the loader waited too long for a free key/value stage",
                112: "attention: the MMA issuer waited too long for the queries",
                113: "attention: the MMA issuer waited too long for keys and values",
@@ -402,3 +413,50 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
         c_longlong(k_pool.shape[0]), q.shape[0], c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)),
         c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, int(n_seqs), int(n_q_tiles),
         nh, nkv, hd, int(window or 0), c_float(scale), c_void_p(_ptr(status_word(q.device))), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ all layers of a decode step in one kernel
+def decode_layers_ctas() -> int:
+    return int(load("decode_layers").sp_decode_layers_ctas())
+
+
+def decode_layers_max_chunks() -> int:
+    return int(load("decode_layers").sp_decode_layers_max_chunks())
+
+
+def decode_layers_desc_bytes() -> int:
+    return int(load("decode_layers").sp_decode_layers_desc_bytes())
+
+
+def decode_layers_supported(T: int, H: int, hd: int, page_size: int, max_heads_per_kv: int) -> bool:
+    return bool(load("decode_layers").sp_decode_layers_supported(int(T), int(H), int(hd), int(page_size),
+                                                                 int(max_heads_per_kv)))
+
+
+def decode_layers_encode_map(w: torch.Tensor, pair: int) -> bytes:
+    """The TMA view of weight ``w`` [N, K] for the decode kernel's tile walk (rows in pairs ``pair`` apart; 0: plain)."""
+    lib = load("decode_layers")
+    _need_contig(w)
+    n = int(lib.sp_decode_layers_map_bytes())
+    buf = ctypes.create_string_buffer(n)
+    _check("decode_layers", lib.sp_decode_layers_encode_map(buf, c_void_p(_ptr(w)), w.shape[0], w.shape[1], int(pair)))
+    return buf.raw
+
+
+def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, part_o, part_ml, positions, seq_row, page_table,
+                  page_size, len_pages, max_nkv, max_heads_per_kv, sync):
+    """Every layer of a decode step (one token per sequence, T ≤ 16) on the residual ``x`` [T, H] float32, in place.
+
+    ``table``: the layers' descriptors on the device (``decode_layers_desc_bytes()`` each). One cooperative launch;
+    counts as one kernel.
+    """
+    lib = load("decode_layers")
+    _need_contig(x, q, attn, act, page_table)
+    if x.dtype != torch.float32 or x.shape[0] != T or x.shape[1] != H:
+        raise KernelError(f"decode_layers: the residual must be float32 [{T}, {H}], got {x.dtype} {tuple(x.shape)}")
+    _check("decode_layers", lib.sp_decode_layers(
+        c_void_p(_ptr(table)), c_void_p(_ptr(maps)), int(n_layers), int(T), int(H), int(hd), c_void_p(_ptr(x)), c_void_p(_ptr(q)),
+        c_void_p(_ptr(attn)), c_void_p(_ptr(act)), c_void_p(_ptr(xw)), c_void_p(_ptr(ssq)), c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)),
+        c_void_p(_ptr(positions)), c_void_p(_ptr(seq_row)), c_void_p(_ptr(page_table)), page_table.shape[1],
+        int(page_size), int(len_pages), int(max_nkv), int(max_heads_per_kv), c_void_p(_ptr(sync)),
+        c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))

@@ -2,51 +2,10 @@
 // waits, TMA tile loads (never with cluster multicast), tcgen05 fences / commit / mma / ld / st, the
 // shared-memory matrix descriptors and the kind::f16 instruction descriptor.
 #pragma once
-#include "common.cuh"
+#include "async_copy.cuh"
 #include <cuda.h>
 
 namespace {
-
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;   // 2 s: a wait that takes longer is given up
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-
-// Bounded wait: false (and a code in *status) when the phase did not complete in time.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
-    while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (global_ns() - t0 > WAIT_LIMIT_NS) {
-            if (status) atomicCAS(status, 0, code);
-            return false;
-        }
-    }
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
@@ -125,10 +84,6 @@ __device__ __forceinline__ void tc_st_32x32(uint32_t taddr, const uint32_t* r) {
     tc_st_32x16(taddr + 16, r + 16);
 }
 __device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
 
 // Shared-memory descriptor of an MN-major tile with 128-byte swizzle (rows of 64 bfloat16 along M or N,
 // one row per K index): 8 K rows form a 1024-byte group (SBO); ``lbo_bytes`` leads to the next 64 of M/N.

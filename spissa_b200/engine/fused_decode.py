@@ -1,0 +1,130 @@
+"""A decode step's layers in one persistent kernel, when every layer's parts allow it.
+
+The parts stay what decides: each may describe itself through ``fused_fields()`` (tensors, sizes and
+constants, see ``parts.base.Part``). If every entry of the schedule is a pre-norm block of an RMS norm, a
+rotary grouped-query attention that writes its own cache and a SwiGLU feed-forward, in bfloat16, the layers of
+a step that brings one token per sequence (up to 16 sequences) run as ``csrc/decode_layers.cu``; any other
+model, step or size runs part by part as before. Both ways give the same result up to rounding and are
+compared with each other and with the plain implementation in the tests.
+"""
+from __future__ import annotations
+
+import struct
+
+import torch
+
+from ..csrc import lib as K
+
+MAX_TOKENS = 16
+
+
+class FusedDecode:
+    """The descriptor table and scratch buffers of one model on one cache."""
+
+    def __init__(self, model, fields: list):
+        self.model = model
+        self.fields = fields                   # per schedule entry
+        first = fields[0]["mixer"]
+        self.H = first["hidden_size"]
+        self.hd = first["head_dim"]
+        self.max_nkv = max(f["mixer"]["num_kv_heads"] for f in fields)
+        self.max_nh = max(f["mixer"]["num_heads"] for f in fields)
+        self.max_group = max(f["mixer"]["num_heads"] // f["mixer"]["num_kv_heads"] for f in fields)
+        self.max_I = max(f["ffn"]["intermediate_size"] for f in fields)
+        self.table = None
+        self.cache_id = None
+        self.group = None
+
+    # ------------------------------------------------------------------ planning
+    @classmethod
+    def plan(cls, model):
+        """A runner for ``model`` or None when some layer has to run part by part."""
+        if model.rt is None or model.rt.act_dtype != torch.bfloat16 or not model.spec.schedule:
+            return None
+        fields = []
+        for e in model.spec.schedule:
+            blk = model.layers[e.layer]
+            f = blk.fused_fields() if e.writes_cache else None
+            if not f or f.get("kind") != "prenorm" or f["mixer"].get("kind") != "gqa_rotary" \
+                    or f["ffn"].get("kind") != "swiglu" or f["mixer_norm"].get("kind") != "rmsnorm" \
+                    or f["ffn_norm"].get("kind") != "rmsnorm":
+                return None
+            fields.append(f)
+        H, hd = fields[0]["mixer"]["hidden_size"], fields[0]["mixer"]["head_dim"]
+        for f in fields:
+            m, ff = f["mixer"], f["ffn"]
+            if m["hidden_size"] != H or m["head_dim"] != hd or ff["hidden_size"] != H:
+                return None
+            if f["mixer_norm"]["size"] != H or f["ffn_norm"]["size"] != H:
+                return None
+            if ff["pair"] % 8 or ff["intermediate_size"] % 8 or (m["num_heads"] * hd) % 8 or H % 16:
+                return None
+            for w in (m["qkv"], m["o"], ff["gate_up"], ff["down"]):
+                if not w.is_contiguous() or w.data_ptr() % 16:
+                    return None
+        plan = cls(model, fields)
+        if not K.decode_layers_supported(1, H, hd, model.rt.page_size, plan.max_group):
+            return None
+        return plan
+
+    def takes(self, step, cache) -> bool:
+        if not step.all_single or step.n_tokens > MAX_TOKENS:
+            return False
+        if not K.decode_layers_supported(step.n_tokens, self.H, self.hd, cache.page_size, self.max_group):
+            return False
+        if self.cache_id != id(cache):
+            self._bind_cache(cache)
+        return self.table is not None
+
+    def _bind_cache(self, cache) -> None:
+        """The descriptor table for this cache: every entry's pools must lie in one group of full keys."""
+        self.cache_id, self.table = id(cache), None
+        groups = {cache.cache_group.get(e.cache) for e in self.model.spec.schedule}
+        if len(groups) != 1:
+            return
+        gname = groups.pop()
+        g = cache.kv_groups.get(gname)
+        if g is None or g.request.window or g.k.dtype != torch.bfloat16:
+            return
+        dev = self.model.rt.device
+        rows, maps = [], []
+        keep = []
+        for e, f in zip(self.model.spec.schedule, self.fields):
+            m, ff = f["mixer"], f["ffn"]
+            i = g.index[e.cache]
+            k_pool, v_pool = g.k[i], g.v[i]
+            inv = m["inv_freq"].to(device=dev, dtype=torch.float32).contiguous()
+            keep += [inv, k_pool, v_pool]
+            rows.append(struct.pack(
+                "<9Q4i3fi", m["qkv"].data_ptr(), m["o"].data_ptr(), ff["gate_up"].data_ptr(), ff["down"].data_ptr(),
+                f["mixer_norm"]["weight"].data_ptr(), f["ffn_norm"]["weight"].data_ptr(), k_pool.data_ptr(),
+                v_pool.data_ptr(), inv.data_ptr(), m["num_heads"], m["num_kv_heads"], ff["intermediate_size"],
+                ff["pair"], float(f["mixer_norm"]["eps"]), float(f["ffn_norm"]["eps"]),
+                float(m["scale"]) * 1.4426950408889634, 0))
+            maps += [K.decode_layers_encode_map(m["qkv"], self.hd // 2), K.decode_layers_encode_map(m["o"], 0),
+                     K.decode_layers_encode_map(ff["gate_up"], ff["pair"]), K.decode_layers_encode_map(ff["down"], 0)]
+        blob = b"".join(rows)
+        assert len(blob) == len(rows) * K.decode_layers_desc_bytes()
+        self.keep = keep
+        self.group = gname
+        self.maps = torch.frombuffer(bytearray(b"".join(maps)), dtype=torch.uint8).to(dev)
+        self.table = torch.frombuffer(bytearray(blob), dtype=torch.uint8).to(dev)
+        ctas, chunks = K.decode_layers_ctas(), K.decode_layers_max_chunks()
+        bf = torch.bfloat16
+        self.q = torch.empty(MAX_TOKENS, self.max_nh * self.hd, dtype=bf, device=dev)
+        self.attn = torch.empty_like(self.q)
+        self.act = torch.empty(MAX_TOKENS, self.max_I, dtype=bf, device=dev)
+        self.xw = torch.empty(MAX_TOKENS, self.H, dtype=bf, device=dev)
+        self.ssq = torch.zeros(2 * 16 * ((ctas + 3) // 4 * 4), dtype=torch.float32, device=dev)
+        self.part_o = torch.empty(MAX_TOKENS * self.max_nh * chunks * self.hd, dtype=torch.float32, device=dev)
+        self.part_ml = torch.empty(MAX_TOKENS * self.max_nh * chunks * 2, dtype=torch.float32, device=dev)
+        self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    # ------------------------------------------------------------------ running
+    def run(self, h: torch.Tensor, step, cache) -> None:
+        """All layers on the residual stream ``h`` [T, H] (float32), in place."""
+        pt = step.page_tables[self.group]
+        len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
+        K.decode_layers(self.table, self.maps, len(self.fields), step.n_tokens, self.H, self.hd, h, self.q, self.attn, self.act,
+                        self.xw, self.ssq, self.part_o, self.part_ml, step.positions, step.seq_row, pt, cache.page_size,
+                        len_pages, self.max_nkv, self.max_group, self.sync)

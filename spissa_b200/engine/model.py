@@ -31,6 +31,8 @@ class Model:
         self.final_norm = part_registry.build_part("norm", spec.final_norm)
         self.head = part_registry.build_part("head", spec.head)
         self.rt = None
+        self.fuse_decode = True        # run a decode step's layers as one kernel when every layer's parts allow it
+        self._fused = False            # False: not planned yet; None: the parts do not allow it
 
     # ------------------------------------------------------------------ weights
     def parts(self) -> list:
@@ -66,8 +68,14 @@ class Model:
     def forward(self, step, cache) -> torch.Tensor:
         """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer."""
         h = self.embedding.forward(step.tokens)
-        for e in self.spec.schedule:
-            self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))
+        if self.fuse_decode and self._fused is False:
+            from .fused_decode import FusedDecode
+            self._fused = FusedDecode.plan(self)
+        if self.fuse_decode and self._fused is not None and self._fused.takes(step, cache):
+            self._fused.run(h, step, cache)
+        else:
+            for e in self.spec.schedule:
+                self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))
         if step.n_want == 0:
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=h.device)
         x = self.final_norm.forward(h, rows=step.want_rows)

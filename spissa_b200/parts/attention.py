@@ -71,6 +71,17 @@ class GQAAttention(Mixer):
         # arrival counters of the split-key decode attention; the kernel returns them to zero
         self.counters = torch.zeros(4096, dtype=torch.int32, device=rt.device)
 
+    def fused_fields(self):
+        rotary = self.position is not None and hasattr(self.position, "rotary")
+        if self.shares_kv or self.window or not rotary or self.qkv is None:
+            return None
+        inv_freq, rd = self.position.rotary()
+        if rd != self.head_dim or self.qkv.weight.dtype != torch.bfloat16 or self.o.weight.dtype != torch.bfloat16:
+            return None
+        return dict(kind="gqa_rotary", qkv=self.qkv.weight, o=self.o.weight, inv_freq=inv_freq, scale=self.scale,
+                    hidden_size=self.hidden_size, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                    head_dim=self.head_dim)
+
     def forward(self, x, step, cache, residual):
         nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
         T = x.shape[0]

@@ -79,6 +79,12 @@ class Part:
     """
     graph_safe = False
 
+    def fused_fields(self):
+        """What a kernel that runs several parts at once needs of this part (tensors, sizes, constants), as a
+        dict with a ``kind`` entry, or None when this part must run by its own ``forward`` (the default).
+        Called after ``bind``. A part never has to offer this; offering it changes no result."""
+        return None
+
     def __init__(self, prefix: str = ""):
         self.prefix = prefix
         self.rt: Optional[Runtime] = None

@@ -27,6 +27,11 @@ class PreNormBlock(Block):
     def cache_request(self):
         return self.mixer.cache_request()
 
+    def fused_fields(self):
+        f = dict(kind="prenorm", mixer_norm=self.mixer_norm.fused_fields(), mixer=self.mixer.fused_fields(),
+                 ffn_norm=self.ffn_norm.fused_fields(), ffn=self.ffn.fused_fields())
+        return None if any(v is None for v in f.values()) else f
+
     def forward(self, h, step, cache):
         self.mixer.forward(self.mixer_norm.forward(h), step, cache, h)
         self.ffn.forward(self.ffn_norm.forward(h), step, h)

@@ -38,6 +38,13 @@ class SwiGLU(FeedForward):
         self.gate_up = GatedLinear(g, u)
         self.down = Linear(tensors[self.names["down"]])
 
+    def fused_fields(self):
+        gu = self.gate_up
+        if gu is None or not gu.block or gu.weight.dtype != torch.bfloat16 or self.down.weight.dtype != torch.bfloat16:
+            return None
+        return dict(kind="swiglu", gate_up=gu.weight, pair=gu.block, down=self.down.weight,
+                    hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
+
     def forward(self, x, step, residual):
         act = self.gate_up(x, self.rt.act_dtype)
         self.down(act, out=residual, accumulate=True)

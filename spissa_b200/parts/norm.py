@@ -30,6 +30,11 @@ class RMSNorm(Norm):
         super().bind(tensors, rt)
         self.weight = tensors[self.weight_name].contiguous()
 
+    def fused_fields(self):
+        if self.weight is None or self.weight.dtype != torch.bfloat16:
+            return None
+        return dict(kind="rmsnorm", weight=self.weight, eps=self.eps, size=self.size)
+
     def forward(self, h: torch.Tensor, rows: torch.Tensor | None = None) -> torch.Tensor:
         n = h.shape[0] if rows is None else rows.shape[0]
         out = torch.empty(n, self.size, dtype=self.rt.act_dtype, device=h.device)

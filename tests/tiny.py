@@ -44,8 +44,27 @@ TINY_D = dict(
     tie_word_embeddings=True, rms_norm_eps=3e-6, max_position_embeddings=1024)
 TINY_D_INIT = dict(seed=77, norm_std=0.05)
 
+# head size 64 with an odd head count and one kv head, a width that no tile divides: every layer of a decode
+# step of this one (and of F) runs inside the one-kernel decode path
+TINY_E = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama",
+    num_hidden_layers=3, hidden_size=208, num_attention_heads=3, num_key_value_heads=1, head_dim=64,
+    intermediate_size=320, vocab_size=777, rope_theta=50000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=128),
+    tie_word_embeddings=True, rms_norm_eps=2e-5, max_position_embeddings=1024)
+TINY_E_INIT = dict(seed=31, norm_std=0.1)
+
+# head size 128, two kv groups, a width above one weight tile's 512 columns plus a ragged rest
+TINY_F = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama",
+    num_hidden_layers=2, hidden_size=592, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+    intermediate_size=1152, vocab_size=515, rope_theta=10000.0, rope_scaling=None,
+    tie_word_embeddings=False, rms_norm_eps=1e-5, max_position_embeddings=1024)
+TINY_F_INIT = dict(seed=41, norm_std=0.05)
+
 TINIES = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT),
-          "D": (TINY_D, TINY_D_INIT)}
+          "D": (TINY_D, TINY_D_INIT), "E": (TINY_E, TINY_E_INIT), "F": (TINY_F, TINY_F_INIT)}
 
 
 def make_folder(cfg_dict, init, folder, std=0.02):

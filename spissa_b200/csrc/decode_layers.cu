@@ -30,7 +30,6 @@
 // cluster multicast.
 #include "flash_common.cuh"
 #include <cuda.h>
-#include <stdlib.h>
 
 SP_API const char* sp_decode_layers_last_error() { return sp_error_text; }
 
@@ -39,7 +38,7 @@ namespace {
 constexpr int CWARPS = 8;                       // consumer warps
 constexpr int CTHREADS = CWARPS * 32;
 constexpr int THREADS = CTHREADS + 32;          // and the copy warp
-constexpr int KC = 512;                         // columns of W per stage
+constexpr int KC = 1024;                        // columns of W per stage
 constexpr int BOXC = 256;                       // columns per TMA box (the most a box may have)
 constexpr int WSL = KC / CWARPS;                // columns of a tile per consumer warp
 constexpr int SS = WSL / 32;                    // steps of 32 columns per warp and tile
@@ -48,7 +47,7 @@ constexpr int STAGE_BYTES = (KC / BOXC) * BOX_BYTES;
 constexpr int MAX_STAGES = 12;
 constexpr int MAXT = 16;                        // tokens per step
 constexpr int RED_FLOATS = CWARPS * 2 * 32 * 4; // one buffer of the K-slice sums
-constexpr int MAX_CHUNKS = 64;                  // key chunks per sequence
+constexpr int MAX_CHUNKS = 16;                  // key chunks per sequence (their partial results are combined in one batch of loads)
 constexpr int MAX_CHUNK_PAGES = 512;            // pages per chunk (their table entries wait in shared memory)
 constexpr int SMEM_LIMIT = 232448;              // per CTA on sm_100
 constexpr int STATIC_SMEM = 1536;               // barriers and small arrays below, rounded up
@@ -86,7 +85,6 @@ struct Params {
     int* status;
     const CUtensorMap* maps;        // [layers][4]: QKV, output, gate/up, down; see sp_decode_layers_encode_map
     unsigned long long* trace;      // optional: the global timer as CTA 0 leaves each grid barrier
-    int debug;
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
 };
 
@@ -195,8 +193,8 @@ __device__ __forceinline__ bool is_aborted(Shared* sh) { return *(volatile int*)
 template <int HD>
 __device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) {
     const int G = gridDim.x, cta = blockIdx.x, S = p.n_stages;
-    uint32_t n = 0;
-    int cursor = 0;
+    uint32_t n = 0, phase = 0;
+    int cursor = 0, slot = 0;
     for (int l = 0; l < p.n_layers; ++l) {
         const LayerDesc L = p.layers[l];
         for (int which = 0; which < 4; ++which) {
@@ -207,9 +205,8 @@ __device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) 
             for (int rb = (cta - cursor + G) % G; rb < j.n_blocks; rb += G) {
                 const int o0 = rb * 8;                              // first of the block's 8 rows within each half
                 for (int kt = 0; kt < nkt; ++kt, ++n) {
-                    const int slot = n % S;
                     const uint32_t full = smem_u32(&sh->full[slot]), empty = smem_u32(&sh->empty[slot]);
-                    if (!is_aborted(sh) && !mbar_wait(empty, ((n / S) & 1u) ^ 1u, nullptr, 0)) raise_abort(p, sh, 201);
+                    if (!is_aborted(sh) && !mbar_wait(empty, phase ^ 1u, nullptr, 0)) raise_abort(p, sh, 201);
                     if (lane == 0) {
                         // columns beyond K and rows beyond N arrive as zeros and count as bytes all the same
                         mbar_expect_tx(full, (uint32_t)STAGE_BYTES);
@@ -218,6 +215,7 @@ __device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) 
                             tma_load_4d(ring + slot * STAGE_BYTES + c * BOX_BYTES, map, kt * KC + c * BOXC, o0 % pr, 0, o0 / pr, full);
                     }
                     __syncwarp();
+                    if (++slot == S) { slot = 0; phase ^= 1u; }
                 }
             }
             cursor = (cursor + j.n_blocks) % G;
@@ -241,7 +239,8 @@ __device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) 
 // column c (0..7) of both halves of block rb; ``held`` is what ``pre(rb, m, c, rowA, rowB, nA, nB)`` returned when
 // the block began (loads that the epilogue needs, issued before the tiles so that they cost no waiting).
 struct Walk {
-    uint32_t n;        // tiles taken so far (the copy warp counts the same way)
+    int slot;          // stage of the next tile (the copy warp walks the ring the same way)
+    uint32_t phase;    // how often the ring has been walked, mod 2
     int cursor;        // which CTA gets block 0 of the next product
     int red_par;
 };
@@ -250,7 +249,7 @@ template <bool WIDE, class ALoad, class Pre, class Epi>
 __device__ __forceinline__ void product(const Params& p, Shared* sh, const Job& j, Walk& w, uint32_t ring, float* red,
                                         ALoad aload, Pre pre, Epi epi) {
     constexpr int NF = WIDE ? 2 : 1;                              // token blocks of 8
-    constexpr int DEPTH = WIDE ? 2 : 4;                           // tiles whose activation fragments are in flight (as registers allow)
+    constexpr int DEPTH = WIDE ? 1 : 2;                           // tiles whose activation fragments are in flight (as registers allow)
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = gridDim.x, S = p.n_stages;
     const int nkt = (j.K + KC - 1) / KC;
@@ -277,11 +276,11 @@ __device__ __forceinline__ void product(const Params& p, Shared* sh, const Job& 
                 for (int u = 0; u < DEPTH; ++u) {
                     const int kt = kt0 + u;
                     if (kt >= nkt) break;
-                    const int slot = w.n % S;
-                    if (!(p.debug & 2) && !is_aborted(sh) && !mbar_wait(smem_u32(&sh->full[slot]), (w.n / S) & 1u, nullptr, 0)) raise_abort(p, sh, 202);
+                    const int slot = w.slot;
+                    if (!is_aborted(sh) && !mbar_wait(smem_u32(&sh->full[slot]), w.phase, nullptr, 0)) raise_abort(p, sh, 202);
                     const int kc = min(KC, j.K - kt * KC);
                     const uint32_t base = ring + slot * STAGE_BYTES;
-                    if (warp * WSL < kc && !(p.debug & 1)) {
+                    if (warp * WSL < kc) {
                         uint4 wa[SS], wb[SS];
 #pragma unroll
                         for (int s = 0; s < SS; ++s) {
@@ -300,7 +299,7 @@ __device__ __forceinline__ void product(const Params& p, Shared* sh, const Job& 
                     }
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&sh->empty[slot]));
-                    ++w.n;
+                    if (++w.slot == S) { w.slot = 0; w.phase ^= 1u; }
                     aload(kt + DEPTH < nkt ? kt + DEPTH : (u < nkt ? u : 0), fr[u]);     // harmless after the last block
                 }
             }
@@ -414,18 +413,25 @@ __device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, 
 }
 
 // ---------------------------------------------------------------- attention: chunks of keys, then their combination
-template <int HD, int ST>
-__device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& L, uint8_t* scratch) {
+// GROUPS groups of four warps, each with tiles of its own, work on different (sequence, kv head, chunk) items.
+template <int HD, int ST, int GROUPS>
+__device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& L, uint8_t* scratch_all) {
     using TL = Tile<HD>;
+    constexpr int GROUP_BYTES = 16 * TL::ROW + 2 * ST * TL::BYTES + MAX_CHUNK_PAGES * 4;
+    constexpr int MS = HD + 2;
+    static_assert(4 * 16 * MS * 4 <= ST * TL::BYTES, "the merge buffer reuses the key tiles");
+    const int wg = (threadIdx.x >> 5) >> 2;                        // warp group
+    const int tid = threadIdx.x & 127, warp = tid >> 5, lane = tid & 31;
+    const int bar = 2 + wg;
+    uint8_t* scratch = scratch_all + (size_t)wg * GROUP_BYTES;
     const uint32_t q_tile = smem_u32(scratch);                     // 16 rows
     const uint32_t k_tiles = q_tile + 16 * TL::ROW;
     const uint32_t v_tiles = k_tiles + ST * TL::BYTES;
-    float* merge = (float*)(scratch + 16 * TL::ROW + 2 * ST * TL::BYTES);    // [4 warps][16 rows][HD + 2]
-    int* pt_s = (int*)(merge + 4 * 16 * (HD + 2));                            // the chunk's page-table entries
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    float* merge = (float*)(scratch + 16 * TL::ROW);               // [4 warps][16 rows][HD + 2], over the key tiles once they are used up
+    int* pt_s = (int*)(scratch + 16 * TL::ROW + 2 * ST * TL::BYTES);         // the chunk's page-table entries
     const int Gq = L.nh / L.nkv;
     const int n_items = p.T * L.nkv * p.n_chunks;
-    for (int it = blockIdx.x; it < n_items; it += gridDim.x) {
+    for (int it = blockIdx.x * GROUPS + wg; it < n_items; it += gridDim.x * GROUPS) {
         const int b = it / (L.nkv * p.n_chunks), g = (it / p.n_chunks) % L.nkv, chunk = it % p.n_chunks;
         const int pos = p.positions[b];
         const int j_first = chunk * p.chunk_pages;
@@ -467,14 +473,14 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
                 cp_async16(vd + r * TL::ROW + k * 16, L.v_pool + off + (size_t)r * HD + k * 8);
             }
         };
-        bar_sync(2, 128);                                          // the table entries are in place
+        bar_sync(bar, 128);                                        // the table entries are in place
 #pragma unroll
         for (int s = 0; s < ST - 1; ++s) {
             if (j_first + s <= j_last) fetch(j_first + s, s);
             cp_async_commit();
         }
         cp_async_wait<ST - 1>();
-        bar_sync(2, 128);
+        bar_sync(bar, 128);
         load_q_frags<HD>(q_tile, 0, lane, qf);
         for (int j = j_first; j <= j_last; ++j) {
             const int i = j - j_first, stage = i % ST;
@@ -496,7 +502,7 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
             l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
         }
-        constexpr int MS = HD + 2;
+        bar_sync(bar, 128);                                        // every warp is done with the key tiles: they become the merge buffer
         const int t = lane & 3;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -508,7 +514,7 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
             }
             if (t == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
         }
-        bar_sync(2, 128);
+        bar_sync(bar, 128);
         for (int e = tid; e < Gq * HD; e += 128) {
             const int row = e / HD, d = e % HD;
             float mm = -INFINITY;
@@ -527,14 +533,14 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
             p.part_o[pi * HD + d] = acc;
             if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
         }
-        bar_sync(2, 128);                                          // the tiles are free for the next item
+        bar_sync(bar, 128);                                        // the tiles are free for the next item
     }
 }
 
 // out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order; one warp per (token, head)
 template <int HD>
 __device__ __noinline__ void attention_combine(const Params& p, const LayerDesc& L) {
-    constexpr int CB = 8;                                          // chunks whose loads are issued together
+    constexpr int CB = MAX_CHUNKS;                                 // chunks whose loads are issued together: all of them
     constexpr int DPL = HD / 32;                                   // output dims per lane
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nc = p.n_chunks;
@@ -580,13 +586,13 @@ __device__ __noinline__ void attention_combine(const Params& p, const LayerDesc&
 }
 
 // ---------------------------------------------------------------- the consumer warps' walk through the layers
-template <int HD, int ST, bool WIDE>
+template <int HD, int ST, int AG, bool WIDE>
 __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red, uint8_t* uni) {
     constexpr int NF = WIDE ? 2 : 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int G = gridDim.x, cta = blockIdx.x, T = p.T, H = p.H;
     unsigned epoch = 0;
-    Walk w{0u, 0, 0};
+    Walk w{0, 0u, 0, 0};
     const int gp = ((G + 3) >> 2) << 2;                        // floats per token in the table of sums
     float* ssq_a = p.ssq;                                      // written by the output projection
     float* ssq_b = p.ssq + (size_t)gp * 16;                    // written by the down projection (and here, first)
@@ -646,7 +652,6 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 
         // ---- QKV, rotation, cache write
         stage_xw(p, sh, ssq_b, L.eps1, xn);
-        if (p.trace && cta == 0 && tid == 0) p.trace[600 + 4 * l] = global_ns();
         product<WIDE>(p, sh, job_of<HD>(L, 0, H), w, ring, red, aload_xn, no_pre,
                 [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4&) {
                     if (m >= T || c >= nA) return;
@@ -673,11 +678,10 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
                     dst[d] = __float2bfloat16_rn(lo);
                     dst[d + HD / 2] = __float2bfloat16_rn(hi);
                 });
-        if (p.trace && cta == 0 && tid == 0) p.trace[601 + 4 * l] = global_ns();
         grid_sync(p, sh, epoch);
 
         // ---- attention
-        if (warp < 4) attention_chunks<HD, ST>(p, L, uni);
+        if (warp < 4 * AG) attention_chunks<HD, ST, AG>(p, L, uni);
         grid_sync(p, sh, epoch);
         attention_combine<HD>(p, L);
         grid_sync(p, sh, epoch);
@@ -718,7 +722,6 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 
         // ---- gate and up with silu(gate)·up
         stage_xw(p, sh, ssq_a, L.eps2, xn);
-        if (p.trace && cta == 0 && tid == 0) p.trace[602 + 4 * l] = global_ns();
         product<WIDE>(p, sh, job_of<HD>(L, 2, H), w, ring, red, aload_xn, no_pre,
                 [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4&) {
                     if (m >= T || c >= nA) return;
@@ -726,7 +729,6 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
                     b *= sh->rstd[m];
                     p.act[(size_t)m * L.I + rb * 8 + c] = __float2bfloat16_rn((a / (1.0f + expf(-a))) * b);
                 });
-        if (p.trace && cta == 0 && tid == 0) p.trace[603 + 4 * l] = global_ns();
         grid_sync(p, sh, epoch);
 
         // ---- down projection into the residual
@@ -744,7 +746,8 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 }
 
 // ---------------------------------------------------------------- the kernel
-template <int HD, int ST>
+// HD: head size; ST: stages of the attention's key/value tiles; AG: warp groups that work on attention
+template <int HD, int ST, int AG>
 __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Shared sh_;
@@ -770,9 +773,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
     if (warp == CWARPS) {
         copy_warp<HD>(p, sh, ring, lane);
     } else if (p.T > 8) {
-        consumers<HD, ST, true>(p, sh, ring, red, uni);
+        consumers<HD, ST, AG, true>(p, sh, ring, red, uni);
     } else {
-        consumers<HD, ST, false>(p, sh, ring, red, uni);
+        consumers<HD, ST, AG, false>(p, sh, ring, red, uni);
     }
     __syncthreads();
     // the last CTA to finish hands the counters back at zero for the next launch
@@ -789,9 +792,10 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
 }
 
 template <int HD>
-constexpr int attention_bytes(int st) {
-    return 16 * Tile<HD>::ROW + 2 * st * Tile<HD>::BYTES + 4 * 16 * (HD + 2) * 4 + MAX_CHUNK_PAGES * 4;
+constexpr int attention_bytes(int st, int groups) {
+    return groups * (16 * Tile<HD>::ROW + 2 * st * Tile<HD>::BYTES + MAX_CHUNK_PAGES * 4);
 }
+constexpr int ATT_BYTES_64 = attention_bytes<64>(2, 2), ATT_BYTES_128 = attention_bytes<128>(2, 1);
 
 int sm_count() {
     static int n = 0;
@@ -854,6 +858,7 @@ SP_API int sp_decode_layers_map_bytes() { return (int)sizeof(CUtensorMap); }
 // CTAs of the kernel = SMs of the device: the host sizes ``ssq`` ([2][CTAs][16] floats) with it.
 SP_API int sp_decode_layers_ctas() { return sm_count(); }
 SP_API int sp_decode_layers_max_chunks() { return MAX_CHUNKS; }
+SP_API int sp_decode_layers_max_pages() { return MAX_CHUNKS * MAX_CHUNK_PAGES; }
 SP_API int sp_decode_layers_desc_bytes() { return (int)sizeof(LayerDesc); }
 
 // Whether the kernel takes these sizes (1) or the layers have to run part by part (0, with the reason as the
@@ -865,7 +870,7 @@ SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int m
     if (H % 8) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: width %d is no multiple of 8", H); return 0; }
     if (max_heads_per_kv > 16) { snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: %d query heads per kv head, at most 16 fit one tile", max_heads_per_kv); return 0; }
     const int xn = T * (((H * 2 + 127) / 128) * 128 + 64);
-    const int att = hd == 64 ? attention_bytes<64>(3) : attention_bytes<128>(2);
+    const int att = hd == 64 ? ATT_BYTES_64 : ATT_BYTES_128;
     const int uni = xn > att ? xn : att;
     if ((SMEM_LIMIT - STATIC_SMEM - 2 * RED_FLOATS * 4 - uni) / STAGE_BYTES < 2) {
         snprintf(sp_error_text, sizeof(sp_error_text), "decode_layers: width %d with %d tokens leaves no room for the weight ring", H, T);
@@ -895,18 +900,17 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     p.ssq = ssq; p.part_o = part_o; p.part_ml = part_ml;
     p.positions = positions; p.seq_row = seq_row; p.page_table = page_table;
     p.sync = sync; p.status = status; p.trace = trace_buffer;
-    p.debug = getenv("SPDBG") ? atoi(getenv("SPDBG")) : 0;
     p.n_layers = n_layers; p.T = T; p.H = H; p.max_pages = max_pages;
     p.xn_row = ((H * 2 + 127) / 128) * 128 + 64;
     const int xn = T * p.xn_row;
-    const int att = hd == 64 ? attention_bytes<64>(3) : attention_bytes<128>(2);
+    const int att = hd == 64 ? ATT_BYTES_64 : ATT_BYTES_128;
     const int uni = xn > att ? xn : att;
     int stages = (SMEM_LIMIT - STATIC_SMEM - 2 * RED_FLOATS * 4 - uni) / STAGE_BYTES;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.n_stages = stages;
     // split of the keys: about one (sequence, kv head, chunk) item per CTA
     if (len_pages < 1) len_pages = 1;
-    int want = G / (T * (max_nkv > 0 ? max_nkv : 1));
+    int want = G * (hd == 64 ? 2 : 1) / (T * (max_nkv > 0 ? max_nkv : 1));
     if (want < 1) want = 1;
     if (want > MAX_CHUNKS) want = MAX_CHUNKS;
     if (want > len_pages) want = len_pages;
@@ -917,7 +921,7 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;
 
     void* args[] = {(void*)&p};
-    const void* fn = hd == 64 ? (const void*)decode_layers_kernel<64, 3> : (const void*)decode_layers_kernel<128, 2>;
+    const void* fn = hd == 64 ? (const void*)decode_layers_kernel<64, 2, 2> : (const void*)decode_layers_kernel<128, 2, 1>;
     static bool configured[2] = {false, false};
     const int which = hd == 64 ? 0 : 1;
     if (!configured[which]) {

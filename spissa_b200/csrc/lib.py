@@ -424,6 +424,11 @@ def decode_layers_max_chunks() -> int:
     return int(load("decode_layers").sp_decode_layers_max_chunks())
 
 
+def decode_layers_max_pages() -> int:
+    """Pages of the longest sequence that the kernel's split of the keys can hold."""
+    return int(load("decode_layers").sp_decode_layers_max_pages())
+
+
 def decode_layers_desc_bytes() -> int:
     return int(load("decode_layers").sp_decode_layers_desc_bytes())
 

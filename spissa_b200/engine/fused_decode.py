@@ -32,6 +32,7 @@ class FusedDecode:
         self.max_group = max(f["mixer"]["num_heads"] // f["mixer"]["num_kv_heads"] for f in fields)
         self.max_I = max(f["ffn"]["intermediate_size"] for f in fields)
         self.table = None
+        self.runs = 0                          # steps run through the kernel so far
         self.cache_id = None
         self.group = None
 
@@ -69,6 +70,8 @@ class FusedDecode:
 
     def takes(self, step, cache) -> bool:
         if not step.all_single or step.n_tokens > MAX_TOKENS:
+            return False
+        if (step.max_len + cache.page_size - 1) // cache.page_size > K.decode_layers_max_pages():
             return False
         if not K.decode_layers_supported(step.n_tokens, self.H, self.hd, cache.page_size, self.max_group):
             return False
@@ -123,6 +126,7 @@ class FusedDecode:
     # ------------------------------------------------------------------ running
     def run(self, h: torch.Tensor, step, cache) -> None:
         """All layers on the residual stream ``h`` [T, H] (float32), in place."""
+        self.runs += 1
         pt = step.page_tables[self.group]
         len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
         K.decode_layers(self.table, self.maps, len(self.fields), step.n_tokens, self.H, self.hd, h, self.q, self.attn, self.act,

@@ -10,7 +10,7 @@ from spissa_b200.config import (ConfigError, LlamaConfig, ModelSpec, PartSpec, S
 from spissa_b200.engine.model import Model
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_tiny_configs_parse_and_round_trip(name):
     d = tiny.TINIES[name][0]
     cfg = config_from_dict(d)

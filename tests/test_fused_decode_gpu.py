@@ -1,0 +1,141 @@
+"""The one-kernel decode path against the plain implementation and against the same engine run part by part.
+
+Configurations E (head 64) and F (head 128) are built so that every layer qualifies; the tests check that the
+kernel really ran (its run counter), that 16 sequences use the two-token-block form and 17 fall back, that
+sequences of very different lengths, page crossings and a far key come out right, and that what cannot be
+fused (32-bit, a head size the kernel is not built for) quietly runs part by part.
+"""
+import pytest
+import torch
+
+import tiny
+from plain import llama_plain as P
+from spissa_b200 import Engine
+
+pytestmark = pytest.mark.gpu
+
+TOL = tiny.TOL["bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name in ("A", "E", "F"):
+        cfg, init = tiny.TINIES[name]
+        f = tmp_path_factory.mktemp(f"fused_{name}")
+        tiny.make_folder(cfg, init, f)                     # the weights' usual width: the bfloat16 budget is set for it
+        out[name] = (str(f),) + P.read_model_folder(f)
+    return out
+
+
+def decode_rows(engine, seqs, prompt_lens, n_steps):
+    """Prompts in one step, then one token each per step; returns the logits rows of the decode steps."""
+    slots = [engine.acquire() for _ in seqs]
+    engine.step([(s, q[:n], []) for s, q, n in zip(slots, seqs, prompt_lens)])
+    rows = []
+    for i in range(n_steps):
+        rows.append(engine.step([(s, [q[n + i]], [0]) for s, q, n in zip(slots, seqs, prompt_lens)]).float().cpu())
+    for s in slots:
+        engine.release(s)
+    engine.cache.check()
+    return torch.stack(rows)                    # [steps, sequences, vocab]
+
+
+@pytest.mark.parametrize("name", ["E", "F"])
+def test_kernel_runs_and_agrees_with_plain_and_with_the_parts(folders, name):
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    lens = [130, 1, 63]                                    # a page boundary is crossed while decoding
+    steps = 70
+    seqs = [tiny.random_prompt(V, n + steps, 31 * n + 1) for n in lens]
+    got = {}
+    for fuse in (True, False):
+        engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 16, use_graphs=False, fuse_decode=fuse)
+        got[fuse] = decode_rows(engine, seqs, lens, steps)
+        fused = engine.model._fused
+        if fuse:
+            assert fused is not None and fused.runs == steps, "the decode steps did not go through the kernel"
+        else:
+            assert not fused
+    # both ways are within the bfloat16 budget of the plain implementation, at every step (so at most two budgets apart)
+    for b, (q, n) in enumerate(zip(seqs, lens)):
+        ref = P.model_logits(pcfg, w, q, torch.float64)
+        scale = float(ref.abs().max())
+        for fuse in (True, False):
+            err = float((got[fuse][:, b].double() - ref[n:n + steps]).abs().max()) / scale
+            assert err <= TOL, f"{name}: sequence {b}, {'one kernel' if fuse else 'part by part'}: {err:.3e}"
+
+
+def test_sixteen_sequences_in_one_step_and_seventeen_part_by_part(folders):
+    folder, pcfg, w = folders["E"]
+    V = pcfg["vocab_size"]
+    for B, expect_runs in ((16, 5), (17, 0), (9, 5)):
+        lens = [3 + 11 * b for b in range(B)]
+        seqs = [tiny.random_prompt(V, n + 5, 7 * n + B) for n in lens]
+        engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 4 * B, max_seqs=B, use_graphs=False)
+        rows = decode_rows(engine, seqs, lens, 5)
+        assert engine.model._fused.runs == expect_runs
+        for b in (0, B // 2, B - 1):
+            ref = P.model_logits(pcfg, w, seqs[b], torch.float64)
+            err = float((rows[4, b].double() - ref[lens[b] + 4]).abs().max()) / float(ref.abs().max())
+            assert err <= TOL, f"{B} sequences, sequence {b}: {err:.3e}"
+
+
+def test_a_token_does_not_depend_on_its_company(folders):
+    """The same sequence decoded alone and among others gives the same logits bit for bit: every sum in the
+    kernel has an order that depends on neither timing nor the other tokens."""
+    folder, pcfg, w = folders["E"]
+    V = pcfg["vocab_size"]
+    lens = [40, 100, 7, 64, 129]
+    seqs = [tiny.random_prompt(V, n + 6, n) for n in lens]
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 24, use_graphs=False)
+    together = decode_rows(engine, seqs, lens, 6)
+    again = decode_rows(engine, seqs, lens, 6)                                  # other slots and pages
+    assert torch.equal(together, again)
+    alone = decode_rows(engine, seqs[1:2], lens[1:2], 6)
+    scale = float(together.abs().max())
+    # the prompt ran in other company (another tile shape may round differently), the decode steps must agree closely
+    assert float((alone[:, 0] - together[:, 1]).abs().max()) <= TOL * scale
+
+
+def test_what_cannot_be_fused_runs_part_by_part(folders):
+    folder, pcfg, w = folders["E"]
+    e32 = Engine.from_folder(folder, dtype="float32", max_tokens=256, use_graphs=False)
+    s = e32.acquire()
+    e32.step([(s, [1, 2, 3], [])])
+    e32.step([(s, [4], [0])])
+    assert e32.model._fused is None                                              # 32-bit: planned and refused
+    folder_a = folders["A"][0]
+    ea = Engine.from_folder(folder_a, dtype="bfloat16", max_tokens=256, use_graphs=False)
+    s = ea.acquire()
+    ea.step([(s, [1, 2, 3], [])])
+    ea.step([(s, [4], [0])])
+    assert ea.model._fused is None                                               # head size 16: the kernel is not built for it
+
+
+def test_long_context_far_key(folders, tmp_path):
+    """One key far back, made to stand out by scaling the query and key projections: the chunked attention inside
+    the kernel has to find it in whichever chunk it lies."""
+    cfg, init = tiny.TINIES["E"]
+    folder = tmp_path / "peaky_e"
+    tiny.make_folder(cfg, init, folder, std=0.05)
+    pcfg, w = P.read_model_folder(folder)
+    from spissa_b200.weights import write_safetensors
+    for k in list(w):
+        if "q_proj" in k or "k_proj" in k:
+            w[k] = (w[k].float() * 4).bfloat16()
+    write_safetensors(folder / "model.safetensors", w)
+    V = cfg["vocab_size"]
+    lens = [900, 515]
+    steps = 8
+    seqs = [tiny.random_prompt(V, n + steps, n) for n in lens]
+    engine = Engine.from_folder(str(folder), dtype="bfloat16", max_tokens=64 * 32, use_graphs=False)
+    rows = decode_rows(engine, seqs, lens, steps)
+    assert engine.model._fused.runs == steps
+    for b, (q, n) in enumerate(zip(seqs, lens)):
+        ref = P.model_logits(pcfg, w, q, torch.float64)
+        noise = float((P.model_logits(pcfg, w, q, torch.float32).double() - ref).abs().max()) / float(ref.abs().max())
+        allowed = TOL * max(1.0, noise / 5e-7)
+        for i in range(steps):
+            err = float((rows[i, b].double() - ref[n + i]).abs().max()) / float(ref.abs().max())
+            assert err <= allowed, f"sequence {b} step {i}: {err:.3e} (allowed {allowed:.3e})"

@@ -155,16 +155,20 @@ def test_reused_pages_hold_nothing_of_their_last_owner(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_peaky_attention_shows_misplaced_keys(tmp_path, dtype):
-    """Query and key projections scaled up: each query looks at few keys, so one wrong key shows."""
+@pytest.mark.parametrize("name", ["B", "E"])
+def test_peaky_attention_shows_misplaced_keys(tmp_path, dtype, name):
+    """Query and key projections scaled up: each query looks at few keys, so one wrong key shows.
+    (E decodes through the one-kernel path in bfloat16.)"""
     folder = tmp_path / "peaky"
-    tiny.make_folder(tiny.TINY_B, tiny.TINY_B_INIT, folder, std=0.05)
+    cfg, init = tiny.TINIES[name]
+    tiny.make_folder(cfg, init, folder, std=0.05)
     pcfg, w = P.read_model_folder(folder)
     for k in list(w):
         if "q_proj" in k or "k_proj" in k:
             w[k] = (w[k].float() * 5).bfloat16()
     write_safetensors(folder / "model.safetensors", w)
-    reqs = {f"r{i}": tiny.random_prompt(384, n, n) for i, n in enumerate([150, 40, 257])}
+    V = cfg["vocab_size"]
+    reqs = {f"r{i}": tiny.random_prompt(V, n, n) for i, n in enumerate([150, 40, 257])}
     ref = {r: P.model_logits(pcfg, w, t, torch.float64) for r, t in reqs.items()}
     scale = max(float(v.abs().max()) for v in ref.values())
     # sharp softmaxes magnify rounding; the plain implementation in 32-bit shows by how much
@@ -176,7 +180,7 @@ def test_peaky_attention_shows_misplaced_keys(tmp_path, dtype):
                        ("ragged", traces.ragged_batches(reqs, 3, {"r0": 40, "r1": 3, "r2": 100}))):
         out = tmp_path / cut
         traces.run_in_process(str(folder), dtype, steps, str(out))
-        got = traces.collect(steps, str(out), 384)
+        got = traces.collect(steps, str(out), V)
         worst = max(float((row.double() - ref[rid][pos]).abs().max()) for (rid, pos), row in got.items()) / scale
         assert worst <= allowed, f"{cut}: {worst:.3e} (allowed {allowed:.3e}, 32-bit noise {noise:.3e})"
 
@@ -200,7 +204,7 @@ def test_step_refusals_leave_the_cache_alone(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "E"])
 def test_graph_replay_equals_kernel_by_kernel(folders, name, dtype):
     """Decode steps replayed from CUDA graphs give the logits of the same steps launched one by one,
     while sequences leave the batch, lengths cross pages and the length bucket changes."""

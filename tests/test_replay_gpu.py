@@ -3,7 +3,7 @@
 The same requests are replayed (a) each alone and whole, (b) with the last 32 tokens one
 by one, (c) in batches of unequal lengths whose shorter requests end earlier, one batch
 after another with a cache that holds just one batch, so that slots and pages are used
-again — in 32-bit and in bfloat16, for three tiny configurations.
+again — in 32-bit and in bfloat16, for six tiny configurations (E and F decode through the one-kernel path in bfloat16).
 """
 import json
 import os
@@ -20,9 +20,9 @@ from plain import llama_plain as P
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [5, 9, 13, 40, 70, 100], "B": [1, 7, 40, 100, 130, 200], "C": [3, 33, 64, 65, 128, 20],
-           "D": [150, 2, 64, 31, 90, 17]}
+           "D": [150, 2, 64, 31, 90, 17], "E": [70, 129, 3, 200, 64, 33], "F": [40, 1, 130, 65, 7, 90]}
 DECODE = {"A": [2, 0, 9, 33, 5, 40], "B": [0, 6, 33, 1, 64, 70], "C": [2, 32, 1, 64, 3, 19],
-          "D": [40, 1, 0, 30, 33, 16]}
+          "D": [40, 1, 0, 30, 33, 16], "E": [33, 70, 2, 64, 0, 32], "F": [39, 0, 66, 1, 6, 30]}
 
 
 @pytest.fixture(scope="module")
@@ -55,7 +55,7 @@ def check(got: dict, ref: dict, tol: float, what: str):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_cuts_agree_with_plain(models, name, dtype, tmp_path):
     m = models[name]
     V = m["cfg"]["vocab_size"]

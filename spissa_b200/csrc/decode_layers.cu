@@ -176,6 +176,8 @@ struct Shared {
     float warp_sum[CWARPS];
     int tok_pos[MAXT];     // position of each token, and the cache page that holds it
     int tok_page[MAXT];
+    int ptc[2][64];        // per attention group: page-table entries of its last item (the table is the same in every layer)
+    int ptc_key[2][3];     // whose they are: sequence, first and last page
     int aborted;
 };
 
@@ -415,7 +417,7 @@ __device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, 
 // ---------------------------------------------------------------- attention: chunks of keys, then their combination
 // GROUPS groups of four warps, each with tiles of its own, work on different (sequence, kv head, chunk) items.
 template <int HD, int ST, int GROUPS>
-__device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& L, uint8_t* scratch_all) {
+__device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const LayerDesc& L, uint8_t* scratch_all) {
     using TL = Tile<HD>;
     constexpr int GROUP_BYTES = 16 * TL::ROW + 2 * ST * TL::BYTES + MAX_CHUNK_PAGES * 4;
     constexpr int MS = HD + 2;
@@ -444,9 +446,18 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
             }
             continue;
         }
-        // the table entries first, all at once: a load inside the loop would stall the warp for its whole way to L2
-        const int* pt = p.page_table + (size_t)p.seq_row[b] * p.max_pages + j_first;
-        for (int i = tid; i <= j_last - j_first; i += 128) pt_s[i] = pt[i];
+        // The table entries first, all at once: a load inside the loop would stall the warp for its whole way to
+        // L2. A short list stays in shared memory for the layers to come, which ask for the same entries.
+        const int cnt = j_last - j_first + 1;
+        int* key = sh->ptc_key[wg];
+        const bool small = cnt <= 64;
+        const bool hit = small && key[0] == b && key[1] == j_first && key[2] == j_last;
+        const int* pts = small ? sh->ptc[wg] : pt_s;
+        if (!hit) {
+            const int* pt = p.page_table + (size_t)p.seq_row[b] * p.max_pages + j_first;
+            int* dst = small ? sh->ptc[wg] : pt_s;
+            for (int i = tid; i < cnt; i += 128) dst[i] = pt[i];
+        }
         for (int c = tid; c < 16 * TL::CHUNKS; c += 128) {
             const int r = c / TL::CHUNKS, k = c % TL::CHUNKS;
             const uint32_t d = q_tile + r * TL::ROW + k * 16;
@@ -463,17 +474,21 @@ __device__ __noinline__ void attention_chunks(const Params& p, const LayerDesc& 
         const int hi[2] = {pos, pos};
         const int lo[2] = {0, 0};
         // each warp fetches and uses its own 16 keys of every page: no barrier among the warps inside the loop
+        // the warp's 16 keys of a page are 16·HD consecutive elements: lane takes 16-byte pieces lane, lane + 32, ...
+        constexpr int PIECES = 16 * TL::CHUNKS / 32;
+        const uint32_t lane_dst = warp * 16 * TL::ROW + (lane / TL::CHUNKS) * TL::ROW + (lane % TL::CHUNKS) * 16;
+        const size_t lane_src = ((size_t)g * KT + (size_t)warp * 16) * HD + (size_t)lane * 8;
         auto fetch = [&](int j, int stage) {
-            const size_t off = ((size_t)pt_s[j - j_first] * L.nkv + g) * KT * HD + (size_t)warp * 16 * HD;
-            const uint32_t kd = k_tiles + stage * TL::BYTES + warp * 16 * TL::ROW;
-            const uint32_t vd = v_tiles + stage * TL::BYTES + warp * 16 * TL::ROW;
-            for (int c = lane; c < 16 * TL::CHUNKS; c += 32) {
-                const int r = c / TL::CHUNKS, k = c % TL::CHUNKS;
-                cp_async16(kd + r * TL::ROW + k * 16, L.k_pool + off + (size_t)r * HD + k * 8);
-                cp_async16(vd + r * TL::ROW + k * 16, L.v_pool + off + (size_t)r * HD + k * 8);
+            const size_t off = (size_t)pts[j - j_first] * L.nkv * KT * HD + lane_src;
+            const uint32_t kd = k_tiles + stage * TL::BYTES + lane_dst, vd = v_tiles + stage * TL::BYTES + lane_dst;
+#pragma unroll
+            for (int u = 0; u < PIECES; ++u) {
+                cp_async16(kd + u * (32 / TL::CHUNKS) * TL::ROW, L.k_pool + off + (size_t)u * 256);
+                cp_async16(vd + u * (32 / TL::CHUNKS) * TL::ROW, L.v_pool + off + (size_t)u * 256);
             }
         };
         bar_sync(bar, 128);                                        // the table entries are in place
+        if (tid == 0 && !hit) { key[0] = small ? b : -1; key[1] = j_first; key[2] = j_last; }
 #pragma unroll
         for (int s = 0; s < ST - 1; ++s) {
             if (j_first + s <= j_last) fetch(j_first + s, s);
@@ -597,6 +612,7 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
     float* ssq_a = p.ssq;                                      // written by the output projection
     float* ssq_b = p.ssq + (size_t)gp * 16;                    // written by the down projection (and here, first)
 
+    if (tid < 2) sh->ptc_key[tid][0] = -1;
     if (tid < T) {
         const int pos = p.positions[tid];
         sh->tok_pos[tid] = pos;
@@ -681,7 +697,7 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
         grid_sync(p, sh, epoch);
 
         // ---- attention
-        if (warp < 4 * AG) attention_chunks<HD, ST, AG>(p, L, uni);
+        if (warp < 4 * AG) attention_chunks<HD, ST, AG>(p, sh, L, uni);
         grid_sync(p, sh, epoch);
         attention_combine<HD>(p, L);
         grid_sync(p, sh, epoch);

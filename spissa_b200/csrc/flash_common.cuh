@@ -73,7 +73,14 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
     float s[NT][4];
 #pragma unroll
     for (int i = 0; i < NT; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-    // S = Q · Kᵀ
+    // S = Q · Kᵀ. With few key blocks per warp the products of even and odd steps along head_dim go to
+    // accumulators of their own, so that an mma does not have to wait for the one before it.
+    constexpr bool SPLIT = NT <= 2 && (HD / 16) % 2 == 0;
+    float s2[SPLIT ? NT : 1][4];
+    if (SPLIT) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) s2[i][0] = s2[i][1] = s2[i][2] = s2[i][3] = 0.0f;
+    }
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
@@ -82,9 +89,20 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
             const int d = kk * 16 + (((lane >> 3) & 1) << 3);
             uint32_t b0, b1, b2, b3;
             ldmatrix_x4(k_tile + key * T::ROW + d * 2, b0, b1, b2, b3);
-            mma_bf16(s[2 * np], qf[kk], b0, b1);
-            mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+            if (SPLIT && (kk & 1)) {
+                mma_bf16(s2[2 * np], qf[kk], b0, b1);
+                mma_bf16(s2[2 * np + 1], qf[kk], b2, b3);
+            } else {
+                mma_bf16(s[2 * np], qf[kk], b0, b1);
+                mma_bf16(s[2 * np + 1], qf[kk], b2, b3);
+            }
         }
+    }
+    if (SPLIT) {
+#pragma unroll
+        for (int i = 0; i < NT; ++i)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[i][e] += s2[i][e];
     }
     // mask, running maximum (of the raw scores; the scale is positive)
     const int t = lane & 3;

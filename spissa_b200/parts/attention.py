@@ -117,6 +117,11 @@ class GQAAttention(Mixer):
                 K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,
                                self.scale, chunk_tiles, n_chunks, scratch,
                                self.counters if T * nkv <= self.counters.numel() else None)
+            elif T >= 256 and K.flash_tc_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size, self.window):
+                # long prompts: 128-token tiles on the tcgen05 tensor cores (S, P and O in tensor memory)
+                tiles = sum((n + 127) // 128 for n in step.host["new_counts"])
+                K.flash_prefill_tc(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles,
+                                   nh, nkv, hd, self.window, self.scale)
             else:
                 K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
                                 step.n_q_tiles, nh, nkv, hd, self.window, self.scale)

@@ -131,6 +131,9 @@ def ragged_lengths(batch, seed):
     return lens
 
 
+KERNEL_CASE_LAYERS = 0
+
+
 def kernel_case(name: str, reps: int) -> int:
     """One kernel of the step alone, at the 1B shape, on rotating buffers larger than L2.
 
@@ -152,11 +155,12 @@ def kernel_case(name: str, reps: int) -> int:
 
     flops = bytes_ = 0.0
     if name == "step_b8":
-        # eight 2,048-token prompts one after another, then three decode steps at batch 8, kernel by kernel
-        # (no CUDA graph): the launch list of this run is what profiles/step_b8_launches.md summarises
+        # eight 2,048-token prompts one after another, then three decode steps at batch 8, kernel by kernel and
+        # part by part (no CUDA graph, no one-kernel decode): the launch list of this run is what
+        # profiles/step_b8_launches.md summarises
         from spissa_b200 import Engine, LlamaConfig
         eng = Engine.from_config(LlamaConfig.from_dict(CONFIG_1B), seed=0, dtype="bfloat16", max_tokens=8 * CONTEXT,
-                                 max_seqs=8, use_graphs=False)
+                                 max_seqs=8, use_graphs=False, fuse_decode=False)
         rng = random.Random(0)
         slots = [eng.acquire() for _ in range(8)]
         for sl in slots:
@@ -165,6 +169,46 @@ def kernel_case(name: str, reps: int) -> int:
             eng.step([(sl, [5 + i], [0]) for sl in slots])
         torch.cuda.synchronize()
         print(json.dumps({"kernel_case": name, "launches": K.launches}))
+        return 0
+    if name == "decode_layers":
+        # the one-kernel decode path alone: eight 2,048-token prompts, then decode steps launched one by one; the
+        # last one records the global timer as CTA 0 enters and leaves each grid barrier (phase times per layer)
+        import ctypes
+        from spissa_b200 import Engine, LlamaConfig
+        cfg = dict(CONFIG_1B)
+        if KERNEL_CASE_LAYERS:
+            cfg["num_hidden_layers"] = KERNEL_CASE_LAYERS
+        nl = cfg["num_hidden_layers"]
+        eng = Engine.from_config(LlamaConfig.from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=8 * CONTEXT,
+                                 max_seqs=8, use_graphs=False)
+        rng = random.Random(0)
+        slots = [eng.acquire() for _ in range(8)]
+        for sl in slots:
+            eng.step([(sl, [rng.randrange(V) for _ in range(T)], [T - 1])])
+        for i in range(max(1, reps - 1)):
+            eng.step([(sl, [5 + i], [0]) for sl in slots])
+        trace = torch.zeros(1024, dtype=torch.int64, device=dev)
+        lib = K.load("decode_layers")
+        lib.sp_decode_layers_set_trace(ctypes.c_void_p(trace.data_ptr()))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.step([(sl, [9], [0]) for sl in slots])
+        e1.record()
+        torch.cuda.synchronize()
+        lib.sp_decode_layers_set_trace(ctypes.c_void_p(0))
+        K.check_status(dev)
+        t = trace.cpu().tolist()
+        names = ["input statistics"] + ["qkv", "attention", "combine", "output projection", "gate/up", "down"] * nl
+        work, wait = {}, {}
+        for e in range(1, 6 * nl + 1):              # barrier e: entered at t[2e], left at t[2e + 1]
+            work.setdefault(names[e - 1], []).append(t[2 * e] - t[2 * e - 1])
+            wait.setdefault(names[e - 1], []).append(t[2 * e + 1] - t[2 * e])
+        med = lambda v: sorted(v)[len(v) // 2] / 1e3
+        print(json.dumps({"kernel_case": name, "layers": nl, "kernel_us": round((t[1023] - t[1]) / 1e3, 1),
+                          "step_ms_with_host": round(e0.elapsed_time(e1), 3),
+                          "phase_us_median": {k: round(med(v), 2) for k, v in work.items()},
+                          "barrier_us_median": {k: round(med(v), 2) for k, v in wait.items()},
+                          "fused_steps": eng.model._fused.runs if eng.model._fused else 0}))
         return 0
     if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
         N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 256),
@@ -259,10 +303,13 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|flash_prefill|flash_prefill_tc|flash_decode|step_b8) instead of the step")
+                         "gemv_down|gemv_head|flash_prefill|flash_prefill_tc|flash_decode|decode_layers|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
+    ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()
     if args.kernel_case:
+        global KERNEL_CASE_LAYERS
+        KERNEL_CASE_LAYERS = args.case_layers
         return kernel_case(args.kernel_case, args.reps)
 
     if args.impl == "reference":

@@ -84,7 +84,7 @@ struct Params {
     unsigned* sync;                 // [0] barrier arrivals (and the abort bit), [1] CTAs finished
     int* status;
     const CUtensorMap* maps;        // [layers][4]: QKV, output, gate/up, down; see sp_decode_layers_encode_map
-    unsigned long long* trace;      // optional: the global timer as CTA 0 leaves each grid barrier
+    unsigned long long* trace;      // optional: the global timer at each grid barrier, see sp_decode_layers_set_trace
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
 };
 
@@ -843,8 +843,9 @@ EncodeTiledFn encode_fn() {
 
 }  // namespace
 
-// Optional: 1024 64-bit words on the device into which CTA 0 writes the global timer at the start ([0]), as it
-// leaves each grid barrier ([1], [2], ...) and at its end ([1023]). Null (the default) switches it off.
+// Optional: 1024 64-bit words on the device into which CTA 0 writes the global timer: [1] at its start, [2e] as it
+// enters grid barrier e (e = 1, 2, ...), [2e + 1] as it leaves it, [1023] at its end; CTA 77 does the same from
+// word 400 on. Null (the default) switches it off.
 SP_API void sp_decode_layers_set_trace(void* buffer) { trace_buffer = (unsigned long long*)buffer; }
 
 // The TMA view of one weight matrix W [N, K] (bfloat16, rows contiguous) as the kernel walks it: row

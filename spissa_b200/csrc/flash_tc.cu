@@ -4,20 +4,24 @@
 // score = q·k / sqrt(head_dim), keys after the query are not seen, softmax in 32-bit with the maximum
 // subtracted, output = sum p·v, query head h reads kv head h / (heads / kv_heads).
 //
-// One CTA owns 128 consecutive query tokens of one head and walks the keys in blocks of 128 (two cache
-// pages of 64). Per block:
-//   warp 0   one thread fetches the two K pages and the two V pages with TMA (128-byte swizzle) into a
-//            two-stage ring; the query tile is fetched once;
-//   warp 1   one thread issues S = Q·Kᵀ (tcgen05.mma, M 128, N 128, A and B from shared memory, S in tensor
-//            memory) and, once the probabilities stand in tensor memory, O += P·V (A = P from tensor
-//            memory, B = V as an MN-major shared-memory operand, O in tensor memory);
-//   warps 2-5 one thread per query row: read the row of S (tcgen05.ld), running maximum and sum in the
-//            log2 domain, write P as bfloat16 pairs (tcgen05.st), rescale the row of O when the maximum
-//            moved, and at the end divide by the sum and store the row.
-// Tensor memory: S 128 columns, P 64, O head_dim. Every mbarrier wait is bounded; a wait that runs out
-// records a code in ``status`` and every role falls through to the common exit, where tensor memory is
-// freed. No load uses cluster multicast. Built for head size 64 without a window; the host refuses
-// anything else (the mma.sync kernel serves those).
+// One CTA owns 128 consecutive query tokens of one head and walks the keys page by page (64 keys):
+//   warp 0   one thread fetches the query tile once and a K page and a V page per block with TMA (128-byte
+//            swizzle) into a four-stage ring;
+//   warp 1   one thread issues S = Q·Kᵀ (tcgen05.mma, M 128, N 64, A and B from shared memory) into one of TWO
+//            score buffers in tensor memory, one block ahead of the softmax, and, once a block's probabilities
+//            stand in tensor memory, O += P·V (A = P from tensor memory, B = V as an MN-major operand);
+//   warps 2-5 one thread per query row: the row's 64 scores into registers (tcgen05.ld), maximum and sum in the
+//            log2 domain, P as bfloat16 pairs over the first half of the score buffer it came from
+//            (tcgen05.st). The reference maximum of a row only moves when the block's maximum exceeds it by
+//            more than 2^8 (then O's row and the sum are rescaled, after the product before it has finished);
+//            until then probabilities may be as large as 256, which bfloat16 and the 32-bit sum hold, and the
+//            final division by the sum is exact about it. Keys are masked only in blocks that reach beyond
+//            the tile's first query.
+// Tensor memory: S0 64 columns, S1 64, O 64 of 256 allocated: two CTAs per SM, so that one CTA's softmax runs
+// under the other's products. Heavy tiles (late queries, many keys) are launched first. Every mbarrier wait is
+// bounded; a wait that runs out records a code in ``status`` and every role falls through to the common exit,
+// where tensor memory is freed. No load uses cluster multicast. Built for head size 64 without a window; the
+// host refuses anything else (the mma.sync kernel serves those).
 #include "tcgen05.cuh"
 
 SP_API const char* sp_flash_tc_last_error() { return sp_error_text; }
@@ -25,10 +29,11 @@ SP_API const char* sp_flash_tc_last_error() { return sp_error_text; }
 namespace {
 
 constexpr int QT = 128;            // query rows per CTA
-constexpr int KB = 128;            // keys per block = two pages
+constexpr int KB = 64;             // keys per block = one page
 constexpr int PAGE = 64;
-constexpr int KV_STAGES = 2;
+constexpr int KV_STAGES = 4;         // with the query tile 81 KB per CTA: two CTAs per SM, as tensor memory allows
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_STEP = 8.0f;   // the reference maximum follows the true one in steps of at least this (log2 units)
 
 __device__ __forceinline__ float ex2(float x) {
     float y;
@@ -40,7 +45,7 @@ template <int HD>
 struct Smem {
     static constexpr int Q_BYTES = QT * HD * 2;
     static constexpr int K_BYTES = KB * HD * 2;
-    static constexpr int STAGE_BYTES = 2 * K_BYTES;              // K block then V block
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;              // K page then V page
     static constexpr int TOTAL = Q_BYTES + KV_STAGES * STAGE_BYTES + 1024;
 };
 
@@ -53,10 +58,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         int n_seqs, int nh, int nkv, float scale_log2, int* status) {
     static_assert(HD == 64, "one 64-wide box per operand row");
     using L = Smem<HD>;
-    constexpr uint32_t TMEM_COLS = 256;                           // S 128 | P 64 | O 64
-    constexpr uint32_t COL_S = 0, COL_P = 128, COL_O = 192;
+    constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O 64 | unused
+    constexpr uint32_t COL_S = 0, COL_O = 128;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s, bar_p, bar_o;
+    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p, bar_o;
     __shared__ uint32_t tmem_slot;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -64,8 +69,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t kv_smem = smem_base + L::Q_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // which sequence and which 128-token tile of it
-    int x = blockIdx.x, b = 0, first = 0, n_new = 0;
+    // which sequence and which 128-token tile of it; the launch order runs from the last tile to the first
+    int x = (int)gridDim.x - 1 - (int)blockIdx.x, b = 0, first = 0, n_new = 0;
     for (; b < n_seqs; ++b) {
         first = seq_start[b];
         n_new = seq_start[b + 1] - first;
@@ -81,7 +86,6 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int g = h / (nh / nkv);
     const int n_blocks = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
     const int* pt = page_table + (size_t)(live ? seq_row[b] : 0) * max_pages;
-    const int n_pages = live ? (pos0 + n_rows - 1) / PAGE + 1 : 0;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar_q), 1);
@@ -89,7 +93,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             mbar_init(smem_u32(&bar_kv_full[s]), 1);
             mbar_init(smem_u32(&bar_kv_empty[s]), 1);
         }
-        mbar_init(smem_u32(&bar_s), 1);
+        mbar_init(smem_u32(&bar_s[0]), 1);
+        mbar_init(smem_u32(&bar_s[1]), 1);
         mbar_init(smem_u32(&bar_p), 4);                           // one arrival per softmax warp
         mbar_init(smem_u32(&bar_o), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -115,18 +120,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!mbar_wait(smem_u32(&bar_kv_empty[s]), phase ^ 1u, status, 111)) break;
                 const uint32_t k_dst = kv_smem + s * L::STAGE_BYTES, v_dst = k_dst + L::K_BYTES;
                 mbar_expect_tx(smem_u32(&bar_kv_full[s]), L::STAGE_BYTES);
-                // the second page of the last block may lie beyond the sequence: any page of it will do, its keys are masked
-                const int p0 = pt[2 * j], p1 = pt[min(2 * j + 1, n_pages - 1)];
-                const int r0 = (p0 * nkv + g) * PAGE, r1 = (p1 * nkv + g) * PAGE;
+                const int r0 = (pt[j] * nkv + g) * PAGE;
                 tma_load_2d(k_dst, &map_k, 0, r0, smem_u32(&bar_kv_full[s]));
-                tma_load_2d(k_dst + PAGE * HD * 2, &map_k, 0, r1, smem_u32(&bar_kv_full[s]));
                 tma_load_2d(v_dst, &map_v, 0, r0, smem_u32(&bar_kv_full[s]));
-                tma_load_2d(v_dst + PAGE * HD * 2, &map_v, 0, r1, smem_u32(&bar_kv_full[s]));
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && live) {
-            constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KB);            // S[128,128] = Q·Kᵀ, both K-major
+            constexpr uint32_t idesc_s = umma_idesc_bf16(QT, KB);            // S[128,64] = Q·Kᵀ, both K-major
             constexpr uint32_t idesc_o = umma_idesc_bf16_bmn(QT, HD);        // O[128,HD] += P·V, V MN-major
             bool ok = mbar_wait(smem_u32(&bar_q), 0, status, 112);
             auto issue_s = [&](int j) -> bool {
@@ -135,27 +136,32 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 tc_fence_after();
                 const uint64_t dq = umma_desc_sw128(q_smem);
                 const uint64_t dk = umma_desc_sw128(kv_smem + s * L::STAGE_BYTES);
+                const uint32_t d = tmem + COL_S + (uint32_t)(j & 1) * KB;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) tc_mma_bf16(tmem + COL_S, dq + 2 * k, dk + 2 * k, idesc_s, k != 0 ? 1u : 0u);
-                tc_commit(smem_u32(&bar_s));
+                for (int k = 0; k < HD / 16; ++k) tc_mma_bf16(d, dq + 2 * k, dk + 2 * k, idesc_s, k != 0 ? 1u : 0u);
+                tc_commit(smem_u32(&bar_s[j & 1]));
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int j = 0; j < n_blocks && ok; ++j) {
-                const int s = j % KV_STAGES;
+                // The next block's scores go to the other buffer while the softmax works on this one. That buffer
+                // still holds the probabilities of block j-1 for the product issued before: the pipe runs in order.
+                if (j + 1 < n_blocks) ok = issue_s(j + 1);
+                if (!ok) break;
                 ok = mbar_wait(smem_u32(&bar_p), (uint32_t)j & 1u, status, 114);
                 if (!ok) break;
                 tc_fence_after();
+                const int s = j % KV_STAGES;
                 const uint32_t v_src = kv_smem + s * L::STAGE_BYTES + L::K_BYTES;
+                const uint32_t p_src = tmem + COL_S + (uint32_t)(j & 1) * KB;
 #pragma unroll
                 for (int k = 0; k < KB / 16; ++k) {
                     // 16 keys further along K: two groups of 8 rows of 128 bytes = 2048 bytes; P: 8 columns
-                    tc_mma_bf16_ts(tmem + COL_O, tmem + COL_P + 8 * k, umma_desc_mn_sw128(v_src + k * 2048, 1024),
+                    tc_mma_bf16_ts(tmem + COL_O, p_src + 8 * k, umma_desc_mn_sw128(v_src + k * 2048, 1024),
                                    idesc_o, (j | k) != 0 ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&bar_kv_empty[s]));
                 tc_commit(smem_u32(&bar_o));
-                if (j + 1 < n_blocks) ok = issue_s(j + 1);
             }
         }
     } else if (live) {
@@ -163,64 +169,70 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const int row = q * 32 + lane;
         const int qpos = pos0 + row;
         const uint32_t lane_base = tmem + ((uint32_t)(q * 32) << 16);
-        float m = -INFINITY, l = 0.0f;
+        float m = -INFINITY, l = 0.0f;                            // reference maximum (log2 units) and sum
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
-            ok = mbar_wait(smem_u32(&bar_s), (uint32_t)j & 1u, status, 115);
+            ok = mbar_wait(smem_u32(&bar_s[j & 1]), (uint32_t)(j >> 1) & 1u, status, 115);
             if (!ok) break;
             tc_fence_after();
+            const uint32_t s_addr = lane_base + COL_S + (uint32_t)(j & 1) * KB;
+            uint32_t r[KB];
+            tc_ld_32x32(s_addr, r);
+            tc_ld_32x32(s_addr + 32, r + 32);
+            tc_ld_wait();
             const int key0 = j * KB;
-            // pass 1: the row's maximum over the keys it may see
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KB; c0 += 32) {
-                uint32_t r[32];
-                tc_ld_32x32(lane_base + COL_S + c0, r);
-                tc_ld_wait();
+            if (key0 + KB - 1 > pos0) {                           // some row of the tile cannot see some key of the block
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (key0 + c0 + i <= qpos) mx = fmaxf(mx, __uint_as_float(r[i]));
+                for (int i = 0; i < KB; ++i)
+                    if (key0 + i > qpos) r[i] = 0xff800000u;      // -inf
             }
-            const float m_new = fmaxf(m, mx * scale_log2);
-            const float m_safe = (m_new == -INFINITY) ? 0.0f : m_new;
-            const float corr = ex2(m - m_safe);
-            // The previous block's O += P·V must be complete before its P is overwritten and before the row of O
-            // is rescaled to the new maximum.
-            if (j > 0) {
-                ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(j - 1) & 1u, status, 116);
-                if (!ok) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
+            // four chains each for the maximum and the sum: one chain of 64 dependent operations would cost more
+            // than the exponentials
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int i = 0; i < KB; i += 4) {
+                mx4[0] = fmaxf(mx4[0], __uint_as_float(r[i]));
+                mx4[1] = fmaxf(mx4[1], __uint_as_float(r[i + 1]));
+                mx4[2] = fmaxf(mx4[2], __uint_as_float(r[i + 2]));
+                mx4[3] = fmaxf(mx4[3], __uint_as_float(r[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            // move the reference only when it is far behind (or not set yet)
+            const bool move = mx > m + RESCALE_STEP || (m == -INFINITY && mx > -INFINITY);
+            if (__any_sync(0xffffffffu, move)) {
+                const float m_new = move ? mx : m;
+                const float corr = (m == -INFINITY) ? 0.0f : ex2(m - m_new);      // 1 for rows that stay
+                if (j > 0) {
+                    // O's row may only be touched once the product before has finished with it
+                    ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(j - 1) & 1u, status, 116);
+                    if (!ok) break;
+                    tc_fence_after();
 #pragma unroll 1
                     for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t r[32];
-                        tc_ld_32x32(lane_base + COL_O + c0, r);
+                        uint32_t o[32];
+                        tc_ld_32x32(lane_base + COL_O + c0, o);
                         tc_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-                        tc_st_32x32(lane_base + COL_O + c0, r);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                        tc_st_32x32(lane_base + COL_O + c0, o);
                     }
                 }
+                l *= corr;
+                m = m_new;
             }
-            // pass 2: probabilities, their sum, and P as bfloat16 pairs into tensor memory
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c0 = 0; c0 < KB; c0 += 32) {
-                uint32_t r[32], pk[16];
-                tc_ld_32x32(lane_base + COL_S + c0, r);
-                tc_ld_wait();
+            const float m_safe = (m == -INFINITY) ? 0.0f : m;
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            uint32_t pk[KB / 2];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const float p0 = key0 + c0 + i <= qpos ? ex2(fmaf(__uint_as_float(r[i]), scale_log2, -m_safe)) : 0.0f;
-                    const float p1 = key0 + c0 + i + 1 <= qpos ? ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_safe)) : 0.0f;
-                    sum += p0 + p1;
-                    __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
-                    pk[i >> 1] = *(uint32_t*)&pr;
-                }
-                tc_st_32x16(lane_base + COL_P + (c0 >> 1), pk);
+            for (int i = 0; i < KB; i += 2) {
+                const float p0 = ex2(fmaf(__uint_as_float(r[i]), scale_log2, -m_safe));
+                const float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), scale_log2, -m_safe));
+                sum4[(i >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 pr = __floats2bfloat162_rn(p0, p1);
+                pk[i >> 1] = *(uint32_t*)&pr;
             }
-            l = l * corr + sum;
-            m = m_new;
+            l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+            tc_st_32x32(s_addr, pk);                              // P over the first half of the scores it came from
             tc_st_wait();
             tc_fence_before();
             __syncwarp();

@@ -401,7 +401,7 @@ def main() -> int:
     # ---------------------------------------------------------------- end to end through Engine.generate
     e2e_prompts = prompts_for(args.batch)
     e2e_new = max(8, min(args.steps, 64))
-    engine.generate([p[:64] for p in e2e_prompts], 4, greedy, stop_ids=[])          # warm the path
+    engine.generate(e2e_prompts, 4, greedy, stop_ids=[])          # warm the path: the same shapes, so their graphs exist
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     h2d0, steps0 = engine.h2d_bytes, engine.steps_run

@@ -505,6 +505,23 @@ SP_API int sp_prefetch_l2(const void* p, long long bytes, cudaStream_t stream) {
     return 0;
 }
 
+// ============================================================== gather of int32
+// dst[i] = src[idx[i]]: the tokens a step takes from the sampler's output of the step before, on the device
+__global__ void gather_i32_kernel(const int* __restrict__ src, const int* __restrict__ idx, int* __restrict__ dst, int n,
+                                  int n_src) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int j = idx[i];
+    dst[i] = (j >= 0 && j < n_src) ? src[j] : 0;
+}
+
+SP_API int sp_gather_i32(const int* src, const int* idx, int* dst, int n, int n_src, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    gather_i32_kernel<<<(n + 127) / 128, 128, 0, stream>>>(src, idx, dst, n, n_src);
+    SP_CHECK_LAUNCH("gather_i32");
+    return 0;
+}
+
 // ============================================================== argmax
 // One block per row; the lowest index among equal maxima wins, as a serial scan with
 // a strict ``>`` would choose. NaNs never win.

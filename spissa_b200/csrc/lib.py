@@ -177,6 +177,16 @@ def prefetch_l2(t: torch.Tensor):
                                          c_void_p(_stream())))
 
 
+def gather_i32(src, idx, dst):
+    """dst[i] = src[idx[i]] for int32 tensors on the device (indices outside ``src`` give 0)."""
+    lib = load("generic")
+    _need_contig(src, idx, dst)
+    if src.dtype != torch.int32 or idx.dtype != torch.int32 or dst.dtype != torch.int32 or idx.numel() < dst.numel():
+        raise KernelError("gather_i32 takes int32 tensors and one index per output")
+    _check("generic", lib.sp_gather_i32(c_void_p(_ptr(src)), c_void_p(_ptr(idx)), c_void_p(_ptr(dst)), dst.numel(),
+                                        src.numel(), c_void_p(_stream())))
+
+
 def argmax_rows(logits, out):
     """out[r] = index of the first maximum of logits[r,:] (float32)."""
     lib = load("generic")

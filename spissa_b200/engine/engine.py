@@ -18,6 +18,7 @@ import torch
 
 from ..cache import CacheManager
 from ..config import load_config
+from ..csrc import lib as K
 from ..csrc.lib import KernelError
 from ..parts.base import Runtime
 from ..weights import load_tensors, random_tensors
@@ -184,6 +185,49 @@ class Engine:
             else:
                 batch = pack_step(ents, lengths, tables, self.device)
                 self.h2d_bytes += batch.h2d_bytes
+                logits = self.model.forward(batch, self.cache)
+        self.cache.commit(counts)
+        self.steps_run += 1
+        return logits
+
+    def step_device(self, slots, token_source: torch.Tensor, rows) -> torch.Tensor:
+        """A decode step whose tokens are already on the device: sequence i takes ``token_source[rows[i]]``
+        (int32, for instance the sampler's output of the step before), so the host never waits for them.
+
+        Returns logits [len(slots), vocab] (float32); the tensor may be the step's own buffer and holds only
+        until the next step. Token ids are not checked on the host: they come from this library's sampler.
+        """
+        slots = [int(s) for s in slots]
+        rows = [int(r) for r in rows]
+        if not slots or len(rows) != len(slots):
+            raise StepError("a step needs at least one sequence and one token row for each")
+        if token_source.dtype != torch.int32 or token_source.dim() != 1 or not token_source.is_cuda:
+            raise StepError("the token source is a one-dimensional int32 tensor on the device")
+        if any(not (0 <= r < token_source.numel()) for r in rows):
+            raise StepError("a token row lies outside the token source")
+        lengths = [self.cache.length(s) for s in slots]
+        counts = [(s, 1) for s in slots]
+        ents = [(s, [0], [0]) for s in slots]
+        with torch.cuda.device(self.device):
+            tables = self.cache.reserve(counts)
+            graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+            logits = None
+            if graph is not None:
+                try:
+                    logits = graph.run(None, lengths, slots, tables, token_source, rows)
+                except (RuntimeError, KernelError) as e:
+                    if graph.graph is not None:
+                        raise                        # a replay failed: that is a real fault
+                    print(f"[spissa_b200] CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
+                          f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
+                    self.use_graphs = False
+                    self._graphs.clear()
+            if logits is None:
+                # kernel by kernel: the packed arrays, with the tokens filled in on the device
+                batch = pack_step(ents, lengths, tables, self.device)
+                self.h2d_bytes += batch.h2d_bytes
+                idx = torch.tensor(rows, dtype=torch.int32).to(self.device)
+                K.gather_i32(token_source, idx, batch.tokens)
                 logits = self.model.forward(batch, self.cache)
         self.cache.commit(counts)
         self.steps_run += 1

@@ -12,6 +12,12 @@ stop test lives in the caller's callback, crates/spissa-cli/src/commands/chat.rs
 The loop needs from its engine only ``acquire()``, ``release(slot)``, ``step(entries)``
 and the numbers ``free_tokens()`` / ``page_size`` for planning, and from its sampler
 ``sample(logits, params, requests, step)``; tests drive it with scripted fakes.
+
+When the engine also offers ``step_device`` (tokens taken from a device tensor) and nobody
+listens token by token, decoding runs one step ahead of the host: the sampler's output feeds
+the next step on the device, and the host reads a step's tokens while the next step runs. A
+stop token is then seen one step late; the sequence's extra token is dropped and its slot is
+returned as before, so results are the same as in the step-by-step loop.
 """
 from __future__ import annotations
 
@@ -77,6 +83,64 @@ def plan_batches(prompt_lens: list, max_new_tokens: int, token_budget: int, max_
     return batches
 
 
+def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics) -> int:
+    """Decode ``live`` = [(request, slot)] to the end, one step ahead of the host. Returns the steps run.
+
+    Every live request has its last token in ``results`` and on the host. A launch takes its tokens from the
+    device tensor that the launch before sampled into; the host reads that tensor, through pinned memory, only
+    after the next launch is queued. Limits by length are known when a step is launched; a stop token shows one
+    step late, so a request that stopped may have run one step too many: that step's token is dropped.
+    """
+    import torch
+    device = engine.device
+    done = set()                                   # requests that ended (their slots are released)
+    emitted = {req: len(results[req].tokens) for req, _ in live}       # tokens out, counting those still in flight
+    token_source = torch.tensor([results[req].tokens[-1] for req, _ in live], dtype=torch.int32).to(device)
+    order = list(live)                             # row i of token_source belongs to order[i]
+    in_flight = []                                 # [(order, pinned tokens, event)] oldest first
+    steps = 0
+
+    def settle(entry):
+        rows, pinned, event = entry
+        event.synchronize()
+        for (req, slot), tok in zip(rows, pinned.tolist()):
+            if req in done:
+                continue                           # it stopped a step earlier: this token was never asked for
+            res = results[req]
+            res.tokens.append(int(tok))
+            metrics.generated_tokens += 1
+            if int(tok) in stop:
+                res.finish_reason = "stop"
+            elif len(res.tokens) >= max_new_tokens:
+                res.finish_reason = "length"
+            if res.finish_reason:
+                done.add(req)
+                engine.release(slot)
+
+    while True:
+        nxt = [(i, rs) for i, rs in enumerate(order) if rs[0] not in done and emitted[rs[0]] < max_new_tokens]
+        if not nxt:
+            break
+        rows = [i for i, _ in nxt]
+        order = [rs for _, rs in nxt]
+        logits = engine.step_device([slot for _, slot in order], token_source, rows)
+        step_no = emitted[order[0][0]]             # every request of a batch has the same count: they started together
+        token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
+        pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=True)
+        pinned.copy_(token_source, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        for req, _ in order:
+            emitted[req] += 1
+        in_flight.append((order, pinned, event))
+        steps += 1
+        if len(in_flight) > 1:
+            settle(in_flight.pop(0))               # the step before the one just queued
+    while in_flight:
+        settle(in_flight.pop(0))
+    return steps
+
+
 def generate(engine, sampler, prompts: list, max_new_tokens: int, params: SamplingParams = SamplingParams(),
              stop_ids=(), max_batch: Optional[int] = None, on_token: Optional[Callable] = None,
              return_logits: bool = False, token_budget: Optional[int] = None):
@@ -139,6 +203,11 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
                 metrics.ttft_ms = (t1 - t_start) * 1000.0
             live = take(live, tokens, logits)
             step_no = 1
+            if live and on_token is None and not return_logits and hasattr(engine, "step_device"):
+                t0 = time.perf_counter()
+                metrics.steps += _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics)
+                metrics.decode_ms += (time.perf_counter() - t0) * 1000.0
+                live = []
             while live:
                 t0 = time.perf_counter()
                 logits = engine.step([(slot, [results[req].tokens[-1]], [0]) for req, slot in live])

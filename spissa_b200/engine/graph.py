@@ -35,7 +35,7 @@ class DecodeGraph:
         B = n_seqs
         self.P = bucket // engine.page_size
         self.groups = list(engine.cache.kv_groups)
-        self.n_dyn = 4 * B
+        self.n_dyn = 5 * B            # tokens, positions, slots, lengths, and where a step's tokens lie in a device tensor
         self.n_tab = B * self.P
         total = self.n_dyn + self.n_tab * len(self.groups)
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -55,37 +55,47 @@ class DecodeGraph:
         self.logits = None
         self.kernels = 0
 
-    def _upload(self, tokens, positions, slots, tables: dict) -> None:
+    def _upload(self, tokens, positions, slots, tables: dict, rows=None) -> None:
+        """``tokens`` None: the tokens are on the device already; ``rows`` says where (see ``run``)."""
         B = self.B
         i = self.turn % self.RING
         self.turn += 1
         if self.events[i] is not None:
             self.events[i].synchronize()
         buf = self.pinned[i]
-        dyn = list(tokens) + list(positions) + list(slots) + [p + 1 for p in positions]
+        dyn = (list(tokens) if tokens is not None else [0] * B) + list(positions) + list(slots) + \
+            [p + 1 for p in positions] + (list(rows) if rows is not None else [0] * B)
         buf[:self.n_dyn] = torch.tensor(dyn, dtype=torch.int32)
+        first = 0 if tokens is not None else B      # leave the token block alone when the device fills it
         flat_tables = [tables[g] for g in self.groups]
         if flat_tables != self.last_tables:
-            rows = []
+            flat = []
             for t in flat_tables:
                 for r in t:
-                    rows.extend(r)
-                    rows.extend([0] * (self.P - len(r)))
-            buf[self.n_dyn:] = torch.tensor(rows, dtype=torch.int32)
-            self.dev.copy_(buf, non_blocking=True)
-            self.engine.h2d_bytes += buf.numel() * 4
+                    flat.extend(r)
+                    flat.extend([0] * (self.P - len(r)))
+            buf[self.n_dyn:] = torch.tensor(flat, dtype=torch.int32)
+            self.dev[first:].copy_(buf[first:], non_blocking=True)
+            self.engine.h2d_bytes += (buf.numel() - first) * 4
             self.last_tables = [[list(r) for r in t] for t in flat_tables]
         else:
-            self.dev[:self.n_dyn].copy_(buf[:self.n_dyn], non_blocking=True)
-            self.engine.h2d_bytes += self.n_dyn * 4
+            self.dev[first:self.n_dyn].copy_(buf[first:self.n_dyn], non_blocking=True)
+            self.engine.h2d_bytes += (self.n_dyn - first) * 4
         ev = torch.cuda.Event()
         ev.record()
         self.events[i] = ev
 
-    def run(self, tokens, positions, slots, tables: dict) -> torch.Tensor:
-        """Logits [B, vocab] of the step; the tensor is reused by the next replay."""
-        self._upload(tokens, positions, slots, tables)
+    def run(self, tokens, positions, slots, tables: dict, token_source=None, rows=None) -> torch.Tensor:
+        """Logits [B, vocab] of the step; the tensor is reused by the next replay.
+
+        With ``token_source`` (int32 on the device) the step's tokens are ``token_source[rows]`` and never
+        visit the host: the sampler's output of one step feeds the next."""
         from ..csrc import lib
+        if token_source is None:
+            self._upload(tokens, positions, slots, tables)
+        else:
+            self._upload(None, positions, slots, tables, rows)
+            lib.gather_i32(token_source, self.dev[4 * self.B:5 * self.B], self.dev[0:self.B])
         if self.graph is None:
             eng = self.engine
             graph = torch.cuda.CUDAGraph()

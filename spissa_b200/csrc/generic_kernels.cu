@@ -481,30 +481,6 @@ SP_API int sp_add_inplace(float* dst, const void* src, int src_dt, long long n, 
     return 0;
 }
 
-// ============================================================== L2 prefetch
-// Asks the memory system to bring ``bytes`` at ``p`` into L2 and returns at once: each thread issues
-// bulk prefetches of 4 KiB and the kernel ends without waiting for them, so the bytes stream in
-// behind the kernels that follow in the stream. A hint only: it changes no result.
-__global__ void prefetch_l2_kernel(const char* __restrict__ p, size_t bytes) {
-    constexpr size_t CHUNK = 4096;
-    for (size_t off = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * CHUNK; off < bytes;
-         off += (size_t)gridDim.x * blockDim.x * CHUNK) {
-        const size_t left = bytes - off;
-        const uint32_t n = (uint32_t)(left < CHUNK ? (left & ~(size_t)15) : CHUNK);
-        if (n) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p + off), "r"(n) : "memory");
-    }
-}
-
-SP_API int sp_prefetch_l2(const void* p, long long bytes, cudaStream_t stream) {
-    if (bytes <= 0) return 0;
-    if ((uintptr_t)p & 15) SP_FAIL("prefetch_l2: the range must start on a 16-byte boundary");
-    const long long chunks = (bytes + 4095) / 4096;
-    const int blocks = (int)((chunks + 127) / 128 > 148 ? 148 : (chunks + 127) / 128);
-    prefetch_l2_kernel<<<blocks, 128, 0, stream>>>((const char*)p, (size_t)bytes);
-    SP_CHECK_LAUNCH("prefetch_l2");
-    return 0;
-}
-
 // ============================================================== gather of int32
 // dst[i] = src[idx[i]]: the tokens a step takes from the sampler's output of the step before, on the device
 __global__ void gather_i32_kernel(const int* __restrict__ src, const int* __restrict__ idx, int* __restrict__ dst, int n,

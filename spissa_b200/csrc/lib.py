@@ -169,14 +169,6 @@ def add_inplace(dst, src):
                                          c_longlong(dst.numel()), c_void_p(_stream())))
 
 
-def prefetch_l2(t: torch.Tensor):
-    """Hint: start bringing the contiguous tensor ``t`` into L2; returns without waiting. No result depends on it."""
-    lib = load("generic")
-    _need_contig(t)
-    _check("generic", lib.sp_prefetch_l2(c_void_p(_ptr(t)), c_longlong(t.numel() * t.element_size()),
-                                         c_void_p(_stream())))
-
-
 def gather_i32(src, idx, dst):
     """dst[i] = src[idx[i]] for int32 tensors on the device (indices outside ``src`` give 0)."""
     lib = load("generic")

@@ -510,3 +510,11 @@ def test_flash_prefill_tc_finds_a_far_key(K, length, needle):
 def test_flash_prefill_tc_ignores_junk_beyond_the_sequence(K):
     attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [70], [0], None, 5, 6e-3)
     attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [200, 3], [0, 190], None, 6, 6e-3)
+
+
+def test_gather_i32(K):
+    src = torch.arange(100, 140, dtype=torch.int32, device=DEV)
+    idx = torch.tensor([3, 0, 39, 7, 7, -1, 40], dtype=torch.int32, device=DEV)
+    dst = torch.full((7,), -5, dtype=torch.int32, device=DEV)
+    K.gather_i32(src, idx, dst)
+    assert dst.tolist() == [103, 100, 139, 107, 107, 0, 0]          # rows outside the source give 0

@@ -139,3 +139,5 @@ def test_toy_mixer_with_state_runs_through_the_engine(toy, tmp_path, dtype):
     for s in slots:
         engine.release(s)
     engine.cache.check()
+    # a layer that offers no description of itself keeps the whole model out of the one-kernel decode path
+    assert engine.model._fused is None

@@ -43,6 +43,24 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
     }
 }
 
+// The same for waits inside a CTA whose threads meet at barriers afterwards: ``flag`` (shared memory) is raised by
+// the first wait that runs out and ends every other wait of the CTA at once. The caller goes on with the same
+// control flow (its results are meaningless then), so that no thread is left behind at a barrier.
+__device__ __forceinline__ bool mbar_wait_flag(uint32_t bar, uint32_t parity, int* status, int code, volatile int* flag) {
+    if (*flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*flag) return false;
+        if (global_ns() - t0 > WAIT_LIMIT_NS) {
+            if (status) atomicCAS(status, 0, code);
+            *flag = 1;
+            return false;
+        }
+    }
+}
+
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }

@@ -37,8 +37,9 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     const uint32_t v_tiles = k_tiles + 2 * T::BYTES;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    // which sequence and which 64-token tile of it
-    int x = blockIdx.x, b = 0, first = 0, n_new = 0;
+    // which sequence and which 64-token tile of it. Heads run fastest over the grid and tiles from the last to the
+    // first: the tiles with the most keys start first in every head, the short ones fill the end.
+    int x = (int)gridDim.y - 1 - (int)blockIdx.y, b = 0, first = 0, n_new = 0;
     for (; b < n_seqs; ++b) {
         first = seq_start[b];
         n_new = seq_start[b + 1] - first;
@@ -50,7 +51,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     const int t0 = first + x * KT;
     const int n_rows = min(KT, n_new - x * KT);
     const int pos0 = positions[t0];
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int g = h / (nh / kv.nkv);
     const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
 
@@ -341,7 +342,8 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     if (n_q_tiles <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
     PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
-    dim3 grid(n_q_tiles, nh);
+    if (n_q_tiles > 65535) SP_FAIL("flash_prefill: %d query tiles are beyond this kernel's grid", n_q_tiles);
+    dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
     if (hd == 64) {
         static bool ok = false;

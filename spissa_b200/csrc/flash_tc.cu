@@ -69,8 +69,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t kv_smem = smem_base + L::Q_BYTES;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // which sequence and which 128-token tile of it; the launch order runs from the last tile to the first
-    int x = (int)gridDim.x - 1 - (int)blockIdx.x, b = 0, first = 0, n_new = 0;
+    // which sequence and which 128-token tile of it. Heads run fastest over the grid and tiles from the last to the
+    // first, so that the tiles with the most keys start first in every head and the short ones fill the end.
+    int x = (int)gridDim.y - 1 - (int)blockIdx.y, b = 0, first = 0, n_new = 0;
     for (; b < n_seqs; ++b) {
         first = seq_start[b];
         n_new = seq_start[b + 1] - first;
@@ -82,7 +83,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int t0 = live ? first + x * QT : 0;
     const int n_rows = live ? min(QT, n_new - x * QT) : 0;
     const int pos0 = live ? positions[t0] : 0;
-    const int h = blockIdx.y;
+    const int h = blockIdx.x;
     const int g = h / (nh / nkv);
     const int n_blocks = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
     const int* pt = page_table + (size_t)(live ? seq_row[b] : 0) * max_pages;
@@ -330,7 +331,8 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
         if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(n_q_tiles, nh);
+    if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
+    dim3 grid(nh, n_q_tiles);
     flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
         mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
         scale * LOG2E, status);

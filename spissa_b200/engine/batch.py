@@ -43,33 +43,33 @@ def pack_step(entries, lengths_before, kv_tables: dict, device, pinned: bool = T
     ``kv_tables``: kv group name -> list (per entry) of page lists covering the new length.
     """
     B = len(entries)
-    tokens, positions, token_seq, seq_start, want_rows = [], [], [], [0], []
-    seq_slot, seq_len = [], []
+    # long token lists are handled as tensors, not element by element: a prompt of thousands of tokens is packed in
+    # tens of microseconds instead of a millisecond of interpreter time in front of the first kernel
+    seq_start, want_rows, seq_slot, seq_len = [0], [], [], []
+    tok_parts, pos_parts, seq_parts = [], [], []
     for b, ((slot, toks, want), before) in enumerate(zip(entries, lengths_before)):
-        base = len(tokens)
-        tokens.extend(int(t) for t in toks)
-        positions.extend(range(before, before + len(toks)))
-        token_seq.extend([b] * len(toks))
-        seq_start.append(len(tokens))
+        n = len(toks)
+        base = seq_start[-1]
+        tok_parts.append(toks if isinstance(toks, torch.Tensor) else torch.tensor(toks, dtype=torch.int32))
+        pos_parts.append(torch.arange(before, before + n, dtype=torch.int32))
+        seq_parts.append(torch.full((n,), b, dtype=torch.int32))
+        seq_start.append(base + n)
         seq_slot.append(int(slot))
-        seq_len.append(before + len(toks))
+        seq_len.append(before + n)
         for w in want:
             want_rows.append(base + int(w))
-    T, W = len(tokens), len(want_rows)
+    T, W = seq_start[-1], len(want_rows)
     widths = {g: max(1, max(len(p) for p in rows)) for g, rows in kv_tables.items()}
     sizes = [T, T, T, B + 1, B, B, B, W] + [B * widths[g] for g in kv_tables]
     total = sum(sizes)
     flat = torch.empty(total, dtype=torch.int32, pin_memory=pinned and torch.cuda.is_available())
-    parts = [tokens, positions, token_seq, seq_start, seq_slot, list(range(B)), seq_len, want_rows]
+    small = seq_start + seq_slot + list(range(B)) + seq_len + want_rows
     for g, rows in kv_tables.items():
         w = widths[g]
-        tab = []
         for r in rows:
-            tab.extend(r)
-            tab.extend([0] * (w - len(r)))
-        parts.append(tab)
-    flat_list = [x for p in parts for x in p]
-    flat.copy_(torch.tensor(flat_list, dtype=torch.int32))
+            small.extend(r)
+            small.extend([0] * (w - len(r)))
+    torch.cat(tok_parts + pos_parts + seq_parts + [torch.tensor(small, dtype=torch.int32)], out=flat)
     dev = flat.to(device, non_blocking=True)
     views, off = [], 0
     for s in sizes:

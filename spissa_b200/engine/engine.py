@@ -150,12 +150,25 @@ class Engine:
         if not ents:
             raise StepError("a step needs at least one sequence")
         lengths = []
+        packed = {}                                  # entry index -> its tokens as an int32 tensor
         for slot, toks, want in ents:
             if not toks:
                 raise StepError(f"slot {slot}: a sequence of a step brings at least one token")
-            for t in toks:
-                if not (0 <= int(t) < self.vocab_size):
+            if len(toks) > 32:
+                # a prompt: checked as a tensor (which the packing below takes as it is)
+                try:
+                    as_tensor = torch.tensor(toks, dtype=torch.int64)
+                except (TypeError, ValueError, RuntimeError, OverflowError):
+                    raise StepError(f"slot {slot}: token ids must be integers") from None
+                bad = (as_tensor < 0) | (as_tensor >= self.vocab_size)
+                if bool(bad.any()):
+                    t = int(as_tensor[bad][0])
                     raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {self.vocab_size}")
+                packed[len(lengths)] = as_tensor.to(torch.int32)
+            else:
+                for t in toks:
+                    if not (0 <= int(t) < self.vocab_size):
+                        raise StepError(f"slot {slot}: token id {t} is outside the vocabulary of {self.vocab_size}")
             for w in want:
                 if not (0 <= int(w) < len(toks)):
                     raise StepError(f"slot {slot}: wanted place {w} is outside the {len(toks)} tokens given")
@@ -183,7 +196,8 @@ class Engine:
                     rows = [b for b, (_, _, w) in enumerate(ents) for _ in w]
                     logits = full[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else full[:0]
             else:
-                batch = pack_step(ents, lengths, tables, self.device)
+                batch = pack_step([(sl, packed.get(i, tk), w) for i, (sl, tk, w) in enumerate(ents)], lengths, tables,
+                                  self.device)
                 self.h2d_bytes += batch.h2d_bytes
                 logits = self.model.forward(batch, self.cache)
         self.cache.commit(counts)

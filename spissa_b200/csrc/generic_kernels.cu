@@ -111,11 +111,67 @@ rmsnorm_row_kernel(const float* __restrict__ x, const void* __restrict__ w, int 
     }
 }
 
+// One warp per row, the row in registers (NV float4 per lane), eight rows per block: every lane has all its loads
+// in flight at once and the row sum needs no shared memory. For H = 128·NV.
+template <int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_warp_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt, void* __restrict__ out,
+                    int out_dt, const int* __restrict__ rows, int n_rows, int H, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + warp;
+    if (r >= n_rows) return;
+    const float4* src = (const float4*)(x + (size_t)(rows ? rows[r] : r) * H);
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) v[i] = src[lane + 32 * i];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        ss = fmaf(v[i].x, v[i].x, ss); ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss); ss = fmaf(v[i].w, v[i].w, ss);
+    }
+    ss = sp_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        float wv[4];
+        if (w_dt == SP_DT_BF16) {
+            const uint2 wb = ((const uint2*)w)[c];
+            const __nv_bfloat162 w01 = *(const __nv_bfloat162*)&wb.x, w23 = *(const __nv_bfloat162*)&wb.y;
+            wv[0] = __low2float(w01); wv[1] = __high2float(w01); wv[2] = __low2float(w23); wv[3] = __high2float(w23);
+        } else {
+            const float4 wf = ((const float4*)w)[c];
+            wv[0] = wf.x; wv[1] = wf.y; wv[2] = wf.z; wv[3] = wf.w;
+        }
+        const float o0 = v[i].x * inv * wv[0], o1 = v[i].y * inv * wv[1];
+        const float o2 = v[i].z * inv * wv[2], o3 = v[i].w * inv * wv[3];
+        const size_t o = (size_t)r * H + (size_t)c * 4;
+        if (out_dt == SP_DT_F32) {
+            *(float4*)((float*)out + o) = make_float4(o0, o1, o2, o3);
+        } else {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(o0, o1), p1 = __floats2bfloat162_rn(o2, o3);
+            uint2 pk;
+            pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+            *(uint2*)((__nv_bfloat16*)out + o) = pk;
+        }
+    }
+}
+
 SP_API int sp_rmsnorm(const float* x, const void* w, int w_dt, void* out, int out_dt, const int* rows,
                       int n_rows, int H, float eps, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if ((w_dt | out_dt) & ~1) SP_FAIL("rmsnorm: unsupported dtype code");
     // fixed block sizes: the order of the row sum must not depend on the batch
+    const bool aligned = ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0);
+#define SP_NORM_WARP(NV)                                                                                        \
+    if (aligned && H == 128 * NV) {                                                                             \
+        rmsnorm_warp_kernel<NV><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
+        SP_CHECK_LAUNCH("rmsnorm");                                                                             \
+        return 0;                                                                                               \
+    }
+    SP_NORM_WARP(4) SP_NORM_WARP(8) SP_NORM_WARP(16) SP_NORM_WARP(24) SP_NORM_WARP(32)
+#undef SP_NORM_WARP
     if ((H & 3) == 0 && H <= 4096 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0)
         SP_CHECK_CALL("rmsnorm", sp_launch_cluster(rmsnorm_row_kernel, dim3(n_rows), dim3(256), 0, stream, 1, x, w, w_dt, out,
                                               out_dt, rows, n_rows, H, eps));
@@ -316,6 +372,61 @@ __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict
     }
 }
 
+// The common case in one pass of 16-byte reads: float32 products in, bfloat16 q and cache out, the whole head
+// rotated (rd == hd), hd a multiple of 8. One block of 128 threads per token; a thread takes four neighbouring
+// pairs (a[i..i+3], b[i..i+3]) of one head, or four values of v.
+__global__ void __launch_bounds__(128)
+rope_kv_write_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+                          __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, KvPlace pl,
+                          const float* __restrict__ inv_freq, int T, int nh, int nkv, int hd, int write_kv) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int pos = pl.positions[t];
+    const int half = hd >> 1;
+    const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd;
+    int page = 0, off = 0;
+    if (write_kv) {
+        const int slot = pl.seq_slot[pl.token_seq[t]];
+        page = pl.page_table[(size_t)slot * pl.max_pages + pos / pl.page_size];
+        off = pos % pl.page_size;
+    }
+    __shared__ float cs[2][AG_MAX_HD / 2];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[0][i] = cosf(ang);
+        cs[1][i] = sinf(ang);
+    }
+    __syncthreads();
+    auto pack4 = [](float a, float b, float c, float d) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(a, b), p1 = __floats2bfloat162_rn(c, d);
+        uint2 pk;
+        pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+        return pk;
+    };
+    const int per_head = half >> 2;                          // groups of four pairs
+    const int n_rot = (nh + (write_kv ? nkv : 0)) * per_head;
+    for (int e = threadIdx.x; e < n_rot; e += blockDim.x) {
+        const int h = e / per_head, i = (e - h * per_head) * 4;
+        const float4 a = *(const float4*)(src + (size_t)h * hd + i);
+        const float4 b = *(const float4*)(src + (size_t)h * hd + half + i);
+        const float4 c = *(const float4*)&cs[0][i], sn = *(const float4*)&cs[1][i];
+        const uint2 lo = pack4(a.x * c.x - b.x * sn.x, a.y * c.y - b.y * sn.y, a.z * c.z - b.z * sn.z, a.w * c.w - b.w * sn.w);
+        const uint2 hi = pack4(b.x * c.x + a.x * sn.x, b.y * c.y + a.y * sn.y, b.z * c.z + a.z * sn.z, b.w * c.w + a.w * sn.w);
+        __nv_bfloat16* dst = h < nh ? q_out + (size_t)t * nh * hd + (size_t)h * hd
+                                    : kpool + (((size_t)page * nkv + (h - nh)) * pl.page_size + off) * hd;
+        *(uint2*)(dst + i) = lo;
+        *(uint2*)(dst + half + i) = hi;
+    }
+    if (write_kv) {
+        const int per_v = hd >> 2;
+        for (int e = threadIdx.x; e < nkv * per_v; e += blockDim.x) {
+            const int g = e / per_v, d = (e - g * per_v) * 4;
+            const float4 v = *(const float4*)(src + (size_t)(nh + nkv) * hd + (size_t)g * hd + d);
+            *(uint2*)(vpool + (((size_t)page * nkv + g) * pl.page_size + off) * hd + d) = pack4(v.x, v.y, v.z, v.w);
+        }
+    }
+}
+
 SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, void* kpool, void* vpool,
                             int cache_dt, const int* token_seq, const int* positions, const int* seq_slot,
                             const int* page_table, int max_pages, int page_size, const float* inv_freq,
@@ -325,6 +436,13 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
     if (rd > AG_MAX_HD) SP_FAIL("rope: rotary_dim %d is beyond this kernel's limit %d", rd, AG_MAX_HD);
     if (rd > 0 && !inv_freq) SP_FAIL("rope: a frequency table is needed when rotary_dim > 0");
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
+    if (in_dt == SP_DT_F32 && q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16 && rd == hd && (hd % 8) == 0 &&
+        ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0)) {
+        rope_kv_write_bf16_kernel<<<T, 128, 0, stream>>>((const float*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool,
+                                                         (__nv_bfloat16*)vpool, pl, inv_freq, T, nh, nkv, hd, write_kv);
+        SP_CHECK_LAUNCH("rope_kv_write");
+        return 0;
+    }
     const int threads = 256;
 #define RK_LAUNCH(TIN, TQ, TC)                                                                                  \
     SP_CHECK_CALL("rope_kv_write", sp_launch_cluster(rope_kv_write_kernel<TIN, TQ, TC>, dim3(T), dim3(threads), 0, stream, 1, \

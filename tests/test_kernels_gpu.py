@@ -41,7 +41,7 @@ def test_embed_gather(K, dtype):
     assert int(status.item()) == 1 and float(out2[1].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("H", [72, 2048, 4100])
+@pytest.mark.parametrize("H", [72, 512, 1000, 2048, 3072, 4096, 4100])
 @pytest.mark.parametrize("wdt,odt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.float32, torch.bfloat16)])
 def test_rmsnorm(K, H, wdt, odt):

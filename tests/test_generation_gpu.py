@@ -118,7 +118,7 @@ def test_long_decoding_crosses_pages(folders, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "E"])
 def test_first_tokens_one_by_one(folders, name, dtype, tmp_path):
     folder, pcfg, w = folders[name]
     V = pcfg["vocab_size"]

@@ -10,19 +10,29 @@
 // Why one kernel: at a few tokens per step every product is a stream of weights through the SM, and as
 // separate kernels each stream starts from an empty pipe. Here one CTA per SM lives through the whole step:
 //   * a copy warp walks, for its CTA, the weight tiles of every product of every layer in the order the CTA
-//     will use them, and fetches them with bulk async copies into a ring of shared-memory stages. The ring
-//     does not care about phases: while the CTA waits at a grid barrier or works on attention, the weights
-//     of the products to come are already on their way, so HBM stays busy across phase boundaries;
-//   * eight consumer warps take the tiles (mma.sync m16n8k16, tokens as the 16 rows, 8+8 rows of W as the
-//     columns, each warp a 64-column slice of the tile's K), add their slices in warp order through shared
-//     memory and run the epilogue: rotate and store q / write k and v into the cache; add into the 32-bit
-//     residual; silu(gate)·up;
+//     will use them (blocks of 16 rows of W are dealt to the CTAs round robin, the deal going on from product
+//     to product) and fetches them as TMA boxes (8 + 8 rows x 256 columns, 8 KB a request) into a ring of
+//     shared-memory stages. The ring does not care about phases: while the CTA waits at a grid barrier or
+//     works on attention, the weights of the products to come are already on their way, so HBM stays busy
+//     across phase boundaries;
+//   * eight consumer warps take the tiles (mma.sync m16n8k16: the block's 16 rows of W are M, eight tokens N,
+//     each warp a slice of the tile's columns, K permuted alike in both operands so that fragments are plain
+//     16-byte loads), add their slices in warp order through shared memory and run the epilogue: rotate and
+//     store q / write k and v into the cache; add into the 32-bit residual; silu(gate)·up;
+//   * attention runs inside: the keys of every (sequence, kv head) in chunks over the CTAs, two groups of four
+//     warps per CTA with cp.async double buffering, then one warp per (token, head) combines the chunks;
 //   * phases that need every CTA's result are separated by a grid barrier (cooperative launch; an atomic
 //     counter; bounded spin).
-// RMSNorm costs no phase of its own: whoever adds into the residual also sums the squares of what it wrote,
-// per CTA and token; the next product adds the CTAs' sums in CTA order and normalises the residual into shared
-// memory. Statistics, rotation angles, softmax and the residual are 32-bit. Every sum has a fixed order: a
-// token's result depends neither on timing nor on the other tokens of the step.
+// RMSNorm costs no pass of its own: whoever adds into the residual also stores it multiplied by the next norm's
+// weight (bfloat16, the next product's input) and sums the squares of what it wrote, per CTA and token; the
+// next product adds the CTAs' sums in CTA order and multiplies its RESULT by 1/rms: y = rstd·(x ⊙ w)·Wᵀ.
+// Statistics, rotation angles, softmax and the residual are 32-bit. Every sum has a fixed order: a token's
+// result depends neither on timing nor on the other tokens of the step.
+//
+// A warp issues in order and a load from L2 takes a microsecond or two while the weights stream, so wherever
+// a phase needs data from global memory all loads are issued before the first use, the token positions and
+// page-table entries stay in shared memory across layers, and an epilogue's reads are asked for before its
+// tiles.
 //
 // Every wait (mbarrier, grid barrier) is bounded. A wait that runs out records a code in ``status`` and sets
 // an abort flag; from then on waits are skipped but the control flow stays the same, so that no warp is left

@@ -232,7 +232,9 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=bf if mode == K.TC_SILU_MUL else torch.float32, device=dev)
         run = lambda i: K.gemv(x, ws[i % n_buf], out, mode, 128)
         bytes_ = N * Kd * 2.0
-    elif name in ("flash_prefill", "flash_prefill_tc", "flash_decode"):
+    elif name in ("flash_prefill", "flash_prefill_tc", "flash_decode", "flash_prefill_128", "flash_prefill_tc_128"):
+        if name.endswith("_128"):          # the 8B shape's attention: 32 heads of 128, 8 kv heads
+            hd, name = 128, name[:-4]
         B = 1 if name != "flash_decode" else 8
         n_new = T if name != "flash_decode" else 1
         pages = B * (T // 64)
@@ -303,7 +305,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|flash_prefill|flash_prefill_tc|flash_decode|decode_layers|step_b8) instead of the step")
+                         "gemv_down|gemv_head|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode|decode_layers|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()

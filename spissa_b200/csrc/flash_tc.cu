@@ -31,7 +31,8 @@ namespace {
 constexpr int QT = 128;            // query rows per CTA
 constexpr int KB = 64;             // keys per block = one page
 constexpr int PAGE = 64;
-constexpr int KV_STAGES = 4;         // with the query tile 81 KB per CTA: two CTAs per SM, as tensor memory allows
+// key/value stages: with the query tile 81 KB (head 64) or 97 KB (head 128) per CTA, so that two CTAs share an SM
+template <int HD> __host__ __device__ constexpr int kv_stages() { return HD == 64 ? 4 : 2; }
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float RESCALE_STEP = 8.0f;   // the reference maximum follows the true one in steps of at least this (log2 units)
 
@@ -41,12 +42,16 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+// Operands lie in shared memory as boxes of 64 columns (one 128-byte swizzle span): a query tile is HD / 64 boxes of
+// 128 rows, a K or V page HD / 64 boxes of 64 rows.
 template <int HD>
 struct Smem {
-    static constexpr int Q_BYTES = QT * HD * 2;
-    static constexpr int K_BYTES = KB * HD * 2;
+    static constexpr int BOXES = HD / 64;
+    static constexpr int Q_BOX = QT * 128, KV_BOX = KB * 128;    // bytes
+    static constexpr int Q_BYTES = BOXES * Q_BOX;
+    static constexpr int K_BYTES = BOXES * KV_BOX;
     static constexpr int STAGE_BYTES = 2 * K_BYTES;              // K page then V page
-    static constexpr int TOTAL = Q_BYTES + KV_STAGES * STAGE_BYTES + 1024;
+    static constexpr int TOTAL = Q_BYTES + kv_stages<HD>() * STAGE_BYTES + 1024;
 };
 
 template <int HD>
@@ -56,9 +61,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ seq_start, const int* __restrict__ positions,
                         const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
                         int n_seqs, int nh, int nkv, float scale_log2, int* status) {
-    static_assert(HD == 64, "one 64-wide box per operand row");
+    static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
     using L = Smem<HD>;
-    constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O 64 | unused
+    constexpr int KV_STAGES = kv_stages<HD>();
+    constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O HD
     constexpr uint32_t COL_S = 0, COL_O = 128;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p, bar_o;
@@ -114,7 +120,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     if (warp == 0) {
         if (lane == 0 && live) {
             mbar_expect_tx(smem_u32(&bar_q), L::Q_BYTES);
-            tma_load_2d(q_smem, &map_q, h * HD, t0, smem_u32(&bar_q));
+#pragma unroll
+            for (int c = 0; c < L::BOXES; ++c) tma_load_2d(q_smem + c * L::Q_BOX, &map_q, h * HD + c * 64, t0, smem_u32(&bar_q));
             for (int j = 0; j < n_blocks; ++j) {
                 const int s = j % KV_STAGES;
                 const uint32_t phase = (uint32_t)(j / KV_STAGES) & 1u;
@@ -122,8 +129,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const uint32_t k_dst = kv_smem + s * L::STAGE_BYTES, v_dst = k_dst + L::K_BYTES;
                 mbar_expect_tx(smem_u32(&bar_kv_full[s]), L::STAGE_BYTES);
                 const int r0 = (pt[j] * nkv + g) * PAGE;
-                tma_load_2d(k_dst, &map_k, 0, r0, smem_u32(&bar_kv_full[s]));
-                tma_load_2d(v_dst, &map_v, 0, r0, smem_u32(&bar_kv_full[s]));
+#pragma unroll
+                for (int c = 0; c < L::BOXES; ++c) {
+                    tma_load_2d(k_dst + c * L::KV_BOX, &map_k, c * 64, r0, smem_u32(&bar_kv_full[s]));
+                    tma_load_2d(v_dst + c * L::KV_BOX, &map_v, c * 64, r0, smem_u32(&bar_kv_full[s]));
+                }
             }
         }
     } else if (warp == 1) {
@@ -135,11 +145,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const int s = j % KV_STAGES;
                 if (!mbar_wait(smem_u32(&bar_kv_full[s]), (uint32_t)(j / KV_STAGES) & 1u, status, 113)) return false;
                 tc_fence_after();
-                const uint64_t dq = umma_desc_sw128(q_smem);
-                const uint64_t dk = umma_desc_sw128(kv_smem + s * L::STAGE_BYTES);
                 const uint32_t d = tmem + COL_S + (uint32_t)(j & 1) * KB;
 #pragma unroll
-                for (int k = 0; k < HD / 16; ++k) tc_mma_bf16(d, dq + 2 * k, dk + 2 * k, idesc_s, k != 0 ? 1u : 0u);
+                for (int k = 0; k < HD / 16; ++k) {
+                    // 16 of head_dim further: +2 (16-byte units) inside a box, the next box after four steps
+                    const uint64_t dq = umma_desc_sw128(q_smem + (k / 4) * L::Q_BOX) + 2 * (k % 4);
+                    const uint64_t dk = umma_desc_sw128(kv_smem + s * L::STAGE_BYTES + (k / 4) * L::KV_BOX) + 2 * (k % 4);
+                    tc_mma_bf16(d, dq, dk, idesc_s, k != 0 ? 1u : 0u);
+                }
                 tc_commit(smem_u32(&bar_s[j & 1]));
                 return true;
             };
@@ -157,8 +170,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 const uint32_t p_src = tmem + COL_S + (uint32_t)(j & 1) * KB;
 #pragma unroll
                 for (int k = 0; k < KB / 16; ++k) {
-                    // 16 keys further along K: two groups of 8 rows of 128 bytes = 2048 bytes; P: 8 columns
-                    tc_mma_bf16_ts(tmem + COL_O, p_src + 8 * k, umma_desc_mn_sw128(v_src + k * 2048, 1024),
+                    // 16 keys further along K: two groups of 8 rows of 128 bytes = 2048 bytes; P: 8 columns; the next 64
+                    // of head_dim lie one box further
+                    tc_mma_bf16_ts(tmem + COL_O, p_src + 8 * k, umma_desc_mn_sw128(v_src + k * 2048, L::KV_BOX),
                                    idesc_o, (j | k) != 0 ? 1u : 0u);
                 }
                 tc_commit(smem_u32(&bar_kv_empty[s]));
@@ -307,7 +321,7 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
 
 // Whether this kernel takes the shape (1) or another attention kernel has to run (0).
 SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int window) {
-    return hd == 64 && nkv > 0 && nh % nkv == 0 && page_size == PAGE && window <= 0;
+    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && page_size == PAGE && window <= 0;
 }
 
 // q, out: [T, nh*hd] bfloat16; pools: [n_pages, nkv, 64, hd] bfloat16; n_q_tiles = sum over sequences of
@@ -318,24 +332,35 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
                                int nkv, int hd, int window, float scale, int* status, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (!sp_flash_tc_supported(hd, nh, nkv, page_size, window))
-        SP_FAIL("flash_tc: built for head size 64, pages of 64 and no window (got head %d, page %d, window %d)", hd, page_size, window);
+        SP_FAIL("flash_tc: built for head sizes 64 and 128, pages of 64 and no window (got head %d, page %d, window %d)", hd, page_size, window);
     if (((uintptr_t)q & 15) || ((uintptr_t)kpool & 15) || ((uintptr_t)vpool & 15) || ((uintptr_t)out & 15))
         SP_FAIL("flash_tc: operands must start on a 16-byte boundary");
     CUtensorMap mq, mk, mv;
     if (make_map(&mq, q, T, nh * hd, (long long)nh * hd, QT)) return 1;
     if (make_map(&mk, kpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
     if (make_map(&mv, vpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
-        if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
-        configured = true;
-    }
     if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
-    flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
-        mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-        scale * LOG2E, status);
+    static bool configured[2] = {false, false};
+    if (hd == 64) {
+        if (!configured[0]) {
+            cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
+            if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
+            configured[0] = true;
+        }
+        flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
+            mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
+            scale * LOG2E, status);
+    } else {
+        if (!configured[1]) {
+            cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
+            if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<128>::TOTAL, cudaGetErrorString(e));
+            configured[1] = true;
+        }
+        flash_prefill_tc_kernel<128><<<grid, 192, Smem<128>::TOTAL, stream>>>(
+            mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
+            scale * LOG2E, status);
+    }
     SP_CHECK_LAUNCH("flash_prefill_tc");
     return 0;
 }

@@ -397,8 +397,8 @@ def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
 
 # ------------------------------------------------------------------ prefill attention on tcgen05
 def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int, window) -> bool:
-    """Whether the tcgen05 prefill attention takes this shape (head 64, pages of 64, no window, bfloat16)."""
-    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and hd == 64 and nkv > 0 and nh % nkv == 0
+    """Whether the tcgen05 prefill attention takes this shape (head 64 or 128, pages of 64, no window, bfloat16)."""
+    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and hd in (64, 128) and nkv > 0 and nh % nkv == 0
             and page_size == 64 and not window and k_pool.is_contiguous())
 
 

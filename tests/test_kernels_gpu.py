@@ -492,12 +492,13 @@ def flash_tc_fn(K):
     return fn
 
 
+@pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("nh,nkv", [(8, 2), (4, 4), (3, 1), (32, 8)])
-def test_flash_prefill_tc(K, nh, nkv):
+def test_flash_prefill_tc(K, nh, nkv, hd):
     fn = flash_tc_fn(K)
-    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [7, 1, 65, 33], [0, 199, 64, 31], None, nh, 6e-3)
-    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [300, 64, 128, 129], [0, 0, 100, 27], None, nh + 2, 6e-3)
-    attention_case(K, fn, nh, nkv, 64, torch.bfloat16, [1, 1, 1], [0, 63, 300], None, nh + 1, 6e-3)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [7, 1, 65, 33], [0, 199, 64, 31], None, nh, 6e-3)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [300, 64, 128, 129], [0, 0, 100, 27], None, nh + 2, 6e-3)
+    attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [1, 1, 1], [0, 63, 300], None, nh + 1, 6e-3)
 
 
 @pytest.mark.parametrize("length,needle", [(700, 3), (700, 640), (129, 64), (64, 63), (1000, 0), (65, 64), (257, 128)])
@@ -507,9 +508,33 @@ def test_flash_prefill_tc_finds_a_far_key(K, length, needle):
         assert torch.allclose(out[h], v[needle, h // 2], atol=2e-2), f"head {h} missed key {needle} of {length}"
 
 
-def test_flash_prefill_tc_ignores_junk_beyond_the_sequence(K):
-    attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [70], [0], None, 5, 6e-3)
-    attention_case(K, flash_tc_fn(K), 4, 2, 64, torch.bfloat16, [200, 3], [0, 190], None, 6, 6e-3)
+@pytest.mark.parametrize("hd", [64, 128])
+def test_flash_prefill_tc_ignores_junk_beyond_the_sequence(K, hd):
+    attention_case(K, flash_tc_fn(K), 4, 2, hd, torch.bfloat16, [70], [0], None, 5, 6e-3)
+    attention_case(K, flash_tc_fn(K), 4, 2, hd, torch.bfloat16, [200, 3], [0, 190], None, 6, 6e-3)
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+def test_flash_prefill_tc_reference_maximum_moves_late(K, hd):
+    """Scores that keep growing along the keys: the row's reference maximum has to move (and the output so far be
+    rescaled) in every block, also late ones; random inputs alone would move it once."""
+    torch.manual_seed(11)
+    nh = nkv = 2
+    L = 640
+    q = torch.randn(L, nh, hd) * 0.1
+    k = torch.randn(L, nkv, hd) * 0.1
+    v = torch.randn(L, nkv, hd)
+    s = math.sqrt(hd)
+    q[:, :, 0] = s                                    # score of key j = 0.6 j: 38 more per block of 64 keys
+    k[:, :, 0] = 0.6 * torch.arange(L).float()[:, None]
+    q, k, v = (x.bfloat16().float() for x in (q, k, v))
+    meta = KH.paged_meta([L], [0], DEV, 3)
+    k_pool, v_pool = KH.fill_cache(meta, [k], [v], nkv, hd, torch.bfloat16, DEV)
+    qd = q.reshape(L, nh * hd).bfloat16().to(DEV)
+    out = torch.empty_like(qd)
+    flash_tc_fn(K)(qd, k_pool, v_pool, out, meta, nh, nkv, hd, None, 1.0 / s)
+    ref = KH.plain_attention_rows([q], [k], [v], [L])
+    close(out, ref, 2e-2, "growing scores")
 
 
 def test_gather_i32(K):

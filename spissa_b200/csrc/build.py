@@ -34,6 +34,7 @@ MODULES = {
     "gemv": "gemv_kernels.cu",
     "flash_tc": "flash_tc.cu",
     "decode_layers": "decode_layers.cu",
+    "tc_stream": "tc_stream.cu",
 }
 
 

@@ -215,6 +215,9 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                102: "the MMA issuer waited too long for a loaded pipeline stage",
                103: "the epilogue waited too long for the accumulator",
                104: "the MMA issuer waited too long for a free accumulator",
+               121: "tc_stream: the TMA loader waited too long for a free pipeline stage",
+               122: "tc_stream: the MMA issuer waited too long for operands",
+               123: "tc_stream: the epilogue warps waited too long for the accumulator",
                201: "decode layers: the copy warp waited too long for a free stage of the weight ring",
                202: "decode layers: a consumer warp waited too long for a weight tile",
                203: "decode layers: a CTA waited too long at the grid barrier",
@@ -467,3 +470,29 @@ def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, par
         c_void_p(_ptr(positions)), c_void_p(_ptr(seq_row)), c_void_p(_ptr(page_table)), page_table.shape[1],
         int(page_size), int(len_pages), int(max_nkv), int(max_heads_per_kv), c_void_p(_ptr(sync)),
         c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))
+
+
+# ------------------------------------------------------------------ weight-streaming tensor-core product (17..128 tokens)
+def tc_stream_supported(x: torch.Tensor, w: torch.Tensor, mode=TC_STORE, pair: int = 0) -> bool:
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
+        return False
+    if x.stride(1) != 1 or w.stride(1) != 1 or x.shape[1] != w.shape[1]:
+        return False
+    return load("tc_stream").sp_tc_stream_supported(
+        c_void_p(_ptr(x)), c_void_p(_ptr(w)), x.shape[0], w.shape[0], x.shape[1], x.stride(0), w.stride(0),
+        int(mode), int(pair)) == 0
+
+
+def tc_stream(x, w, out, mode=TC_STORE, pair=0):
+    """out = x · wᵀ for up to 128 tokens on the tensor cores with the rows of ``w`` as the instruction's M: every SM
+    streams its share of ``w``; K is cut over the CTAs of a cluster, whose pieces are added in a fixed order. Modes as ``tc_gemm``; for
+    TC_SILU_MUL ``pair`` is the number of gate rows before the matching up rows in the interleaved weight."""
+    lib = load("tc_stream")
+    M, K = x.shape
+    N = w.shape[0]
+    want_cols = N // 2 if mode == TC_SILU_MUL else N
+    if out.shape[0] != M or out.shape[1] != want_cols or out.stride(1) != 1:
+        raise KernelError(f"tc_stream: out {tuple(out.shape)} does not fit x {tuple(x.shape)}, w {tuple(w.shape)}")
+    _check("tc_stream", lib.sp_tc_stream(
+        c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(out)), dt_code(out), M, N, K, x.stride(0), w.stride(0),
+        out.stride(0), int(mode), int(pair), c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))

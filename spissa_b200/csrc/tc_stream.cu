@@ -1,0 +1,314 @@
+// bfloat16 product for a few dozen tokens on the 5th-generation tensor cores: C[M,N] = A[M,K] · W[N,K]ᵀ with
+// M ≤ 128, built to stream W (crates/spissa-runtime/src/ops.rs:62-105 states the layout and the product).
+//
+// With so few tokens the product is a stream of weights; what matters is that every SM pulls its share of W all
+// the time. The tile kernel of tc_gemm.cu has one row of 128-token tiles here, so only N / 256 CTAs exist, each
+// computing on 128 rows of which most are padding. This kernel turns the product round: 128 rows of W are the
+// M of the tensor-core instruction and the tokens its N (16 to 128 columns), so an instruction does no more
+// work than there are tokens, and K is cut into pieces so that about two CTAs per SM exist:
+//   grid (W tiles of 128 rows, pieces of K); a CTA computes its piece of Wtile · Aᵀ into tensor memory:
+//   warp 0   one thread fetches, per stage, a 128 x 64 box of W and a tokens x 64 box of A with TMA (128-byte swizzle);
+//   warp 1   one thread issues tcgen05.mma (M 128 = rows of W, N = tokens, K 16, four per stage);
+//   warps 2-5 read the accumulator (one row of W per thread, the tokens along its columns).
+// The CTAs of one W tile form a thread-block cluster. Each leaves its piece of the sum in its own shared memory;
+// then every CTA takes a share of the tokens, adds the pieces of all CTAs for them through distributed shared
+// memory, in order of K, and runs the epilogue for them: store / add into a float32 C / silu(gate)·up (the CTA
+// then computes the gate tile and the up tile of the same outputs into two accumulators). A row of W is a column of C: the 32 lanes of a warp write 32 neighbouring elements of one
+// token's row. Every mbarrier wait is bounded and records a code in ``status``; no load uses cluster multicast.
+#include "tcgen05.cuh"
+
+SP_API const char* sp_tc_stream_last_error() { return sp_error_text; }
+
+namespace {
+
+constexpr int BW = 128;                     // rows of W per CTA
+constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle span
+constexpr int UMMA_K = 16;
+constexpr int MAX_SPLITS = 8;
+
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+
+// NT: tokens padded to a multiple of 16 (the N of the instruction); GATED: two W tiles per CTA
+template <int NT, bool GATED>
+struct Layout {
+    static constexpr int W_BYTES = BW * BK * 2;
+    static constexpr int A_BYTES = NT * BK * 2;
+    static constexpr int STAGE_BYTES = (GATED ? 2 : 1) * W_BYTES + A_BYTES;
+    static constexpr int STAGES = GATED ? 2 : 4;                 // two CTAs per SM either way: one computes while the other adds up
+    // after the products the same memory holds this CTA's piece of the sum: [part][token][128 rows] float32
+    static constexpr int PIECE_BYTES = (GATED ? 2 : 1) * NT * BW * 4;
+    static constexpr int TOTAL = (STAGES * STAGE_BYTES > PIECE_BYTES ? STAGES * STAGE_BYTES : PIECE_BYTES) + 1024;
+    static constexpr uint32_t TMEM_COLS = (GATED ? 2 : 1) * NT <= 32 ? 32 : (GATED ? 2 : 1) * NT <= 64 ? 64
+                                          : (GATED ? 2 : 1) * NT <= 128 ? 128 : 256;
+};
+
+struct Args {
+    void* C;                // [M, ldc]: float32 or bfloat16
+    int* status;
+    int c_dt, M, N, K, ldc, mode, pair, pieces;
+};
+
+template <int NT, bool GATED>
+__global__ void __launch_bounds__(192)
+tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a, const Args a) {
+    using L = Layout<NT, GATED>;
+    constexpr int STAGES = L::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc;
+    __shared__ uint32_t tmem_slot;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / a.pieces, piece = blockIdx.x % a.pieces;     // the cluster's rank is the piece of K
+    const int num_kb = (a.K + BK - 1) / BK;
+    const int per = (num_kb + a.pieces - 1) / a.pieces;
+    const int kb0 = piece * per, kb1 = min(num_kb, kb0 + per);        // the host makes every piece non-empty
+    // rows of W: plain tiles, or the gate rows of block ``tile`` and the up rows ``pair`` further on
+    const int row_g = GATED ? tile * 2 * a.pair : tile * BW;
+    const int row_u = row_g + a.pair;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_acc), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(&tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+
+    constexpr int PARTS = GATED ? 2 : 1;
+    const int q = warp & 3;                                       // epilogue warps: tensor-memory lanes 32q .. 32q+31
+    const int row = q * 32 + lane;                                 // row of the W tile = column of C within the tile
+    // where this thread's row of the tile goes in C
+    const int col = GATED ? tile * a.pair + row : tile * BW + row;
+    const bool col_ok = GATED ? (row < a.pair && col < a.N / 2) : col < a.N;
+    auto emit = [&](int j, float g, float u) {                     // token j of this column
+        if (j >= a.M || !col_ok) return;
+        const size_t o = (size_t)j * a.ldc + col;
+        if (GATED) sp_st_dt(a.C, a.c_dt, o, (g / (1.0f + expf(-g))) * u);
+        else if (a.mode == MODE_ACCUMULATE) ((float*)a.C)[o] += g;
+        else sp_st_dt(a.C, a.c_dt, o, g);
+    };
+    bool healthy = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = kb0, i = 0; kb < kb1; ++kb, ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(smem_u32(&bar_empty[s]), (((uint32_t)i / STAGES) & 1u) ^ 1u, a.status, 121)) break;
+                const uint32_t w_dst = smem_base + s * L::STAGE_BYTES;
+                mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
+                tma_load_2d(w_dst, &map_w, kb * BK, row_g, smem_u32(&bar_full[s]));
+                if (GATED) tma_load_2d(w_dst + L::W_BYTES, &map_w, kb * BK, row_u, smem_u32(&bar_full[s]));
+                tma_load_2d(w_dst + (GATED ? 2 : 1) * L::W_BYTES, &map_a, kb * BK, 0, smem_u32(&bar_full[s]));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(BW, NT);
+            for (int kb = kb0, i = 0; kb < kb1; ++kb, ++i) {
+                const int s = i % STAGES;
+                if (!mbar_wait(smem_u32(&bar_full[s]), ((uint32_t)i / STAGES) & 1u, a.status, 122)) break;
+                tc_fence_after();
+                const uint32_t w_src = smem_base + s * L::STAGE_BYTES;
+                const uint64_t dw = umma_desc_sw128(w_src);
+                const uint64_t du = umma_desc_sw128(w_src + L::W_BYTES);
+                const uint64_t da = umma_desc_sw128(w_src + (GATED ? 2 : 1) * L::W_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    tc_mma_bf16(tmem_base, dw + 2 * k, da + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+                    if (GATED) tc_mma_bf16(tmem_base + NT, du + 2 * k, da + 2 * k, idesc, (i | k) != 0 ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&bar_empty[s]));
+            }
+            tc_commit(smem_u32(&bar_acc));                         // also after a failed wait: the epilogue must not hang
+        }
+    } else {
+        const bool ok = mbar_wait(smem_u32(&bar_acc), 0, a.status, 123);
+        tc_fence_after();
+        healthy = ok && !(a.status && *(volatile int*)a.status != 0);
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (a.pieces == 1) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < NT; c0 += 32) {
+                uint32_t rg[32], ru[32];
+                tc_ld_32x32(lane_base + (uint32_t)c0, rg);
+                if (GATED) tc_ld_32x32(lane_base + (uint32_t)(NT + c0), ru);
+                tc_ld_wait();
+                if (healthy) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) emit(c0 + j, __uint_as_float(rg[j]), GATED ? __uint_as_float(ru[j]) : 0.0f);
+                }
+            }
+        } else {
+            // this piece into this CTA's shared memory (the pipeline's stages are free by now), [part][token][row]
+#pragma unroll 1
+            for (int c0 = 0; c0 < PARTS * NT; c0 += 32) {
+                uint32_t r[32];
+                tc_ld_32x32(lane_base + (uint32_t)c0, r);
+                tc_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    asm volatile("st.shared.b32 [%0], %1;" ::"r"(smem_base + (uint32_t)(((c0 + j) * BW + row) * 4)), "r"(r[j]) : "memory");
+            }
+        }
+    }
+    if (a.pieces > 1) {
+        // every CTA of the cluster has left its piece in its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (warp >= 2 && healthy) {
+            // this CTA's share of the tokens: the pieces in order of K through distributed shared memory
+            const int per_t = (a.M + a.pieces - 1) / a.pieces;
+            const int j0 = piece * per_t, j1 = min(a.M, j0 + per_t);
+            uint32_t peer[MAX_SPLITS];
+#pragma unroll
+            for (int sp = 0; sp < MAX_SPLITS; ++sp)
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer[sp]) : "r"(smem_base), "r"(sp < a.pieces ? sp : 0));
+            // four tokens at a time: a load from another CTA's shared memory takes long, so many are asked for at once
+            for (int jb = j0; jb < j1; jb += 4) {
+                float pg[4][MAX_SPLITS], pu[4][MAX_SPLITS];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int sp = 0; sp < MAX_SPLITS; ++sp) {
+                        pg[t][sp] = pu[t][sp] = 0.0f;
+                        if (sp < a.pieces && jb + t < j1) {
+                            const uint32_t at = peer[sp] + (uint32_t)(((jb + t) * BW + row) * 4);
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pg[t][sp]) : "r"(at));
+                            if (GATED) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pu[t][sp]) : "r"(at + (uint32_t)(NT * BW * 4)));
+                        }
+                    }
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    float g = pg[t][0], u = pu[t][0];
+#pragma unroll
+                    for (int sp = 1; sp < MAX_SPLITS; ++sp) { g += pg[t][sp]; u += pu[t][sp]; }
+                    if (jb + t < j1) emit(jb + t, g, u);
+                }
+            }
+        }
+        // nobody leaves (and frees its shared memory) before every CTA has read what it needs
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with leading dimension ld, fetched in boxes of box_rows x 64
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) SP_FAIL("tc_stream: the driver does not offer cuTensorMapEncodeTiled");
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) SP_FAIL("tc_stream: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int NT, bool GATED>
+int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Args& args, int tiles, cudaStream_t stream) {
+    using L = Layout<NT, GATED>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<NT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("tc_stream: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+        configured = true;
+    }
+    SP_CHECK_CALL("tc_stream", sp_launch_cluster(tc_stream_kernel<NT, GATED>, dim3(tiles * args.pieces), dim3(192),
+                                                 (size_t)L::TOTAL, stream, args.pieces, mw, ma, args));
+    return 0;
+}
+
+int tiles_of(int N, int mode, int pair) { return mode == MODE_SILU_MUL ? N / (2 * pair) : (N + BW - 1) / BW; }
+
+int pieces_of(int tiles, int K) {
+    const int num_kb = (K + BK - 1) / BK;
+    int want = (2 * sm_count() + tiles - 1) / tiles;               // about two CTAs per SM
+    if (want > MAX_SPLITS) want = MAX_SPLITS;
+    if (want > num_kb) want = num_kb;
+    if (want < 1) want = 1;
+    const int per = (num_kb + want - 1) / want;
+    return (num_kb + per - 1) / per;                               // every piece holds at least one block of K
+}
+
+}  // namespace
+
+SP_API int sp_tc_stream_max_tokens() { return 128; }
+
+// Whether this kernel takes the product (0) or another has to (1, the reason as the last error).
+SP_API int sp_tc_stream_supported(const void* A, const void* W, int M, int N, int K, int lda, int ldw, int mode, int pair) {
+    if (M <= 0 || M > 128) SP_FAIL("tc_stream: built for 1 to 128 tokens, got %d", M);
+    if (K <= 0 || (K % 8) || (lda % 8) || (ldw % 8)) SP_FAIL("tc_stream: K and the leading dimensions must be multiples of 8 (16-byte rows for TMA)");
+    if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) SP_FAIL("tc_stream: operands must start on a 16-byte boundary");
+    if (mode == MODE_SILU_MUL && (pair <= 0 || pair > BW || (pair % 8) || (N % (2 * pair))))
+        SP_FAIL("tc_stream: gate and up rows in blocks of %d do not fit tiles of %d rows", pair, BW);
+    return 0;
+}
+
+// mode 0: C = A·Wᵀ (bfloat16 or float32); 1: C (float32) += A·Wᵀ; 2: W interleaves ``pair`` gate rows and ``pair``
+// up rows, C [M, N/2] = silu(gate)·up.
+SP_API int sp_tc_stream(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                        int mode, int pair, int* status, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (mode < 0 || mode > 2) SP_FAIL("tc_stream: unknown mode %d", mode);
+    if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_stream: accumulation needs a float32 C");
+    if (sp_tc_stream_supported(A, W, M, N, K, lda, ldw, mode, pair)) return 1;
+    const int tiles = tiles_of(N, mode, pair);
+    Args args;
+    args.C = C; args.status = status;
+    args.c_dt = c_dt; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.mode = mode; args.pair = pair;
+    args.pieces = pieces_of(tiles, K);
+    const int nt = M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    CUtensorMap mw, ma;
+    // gate/up tiles are ``pair`` rows each (the box still has 128 rows: those beyond belong to the next block and are ignored)
+    if (make_map(&mw, W, N, K, ldw, BW)) return 1;
+    if (make_map(&ma, A, M, K, lda, nt)) return 1;
+    const bool gated = mode == MODE_SILU_MUL;
+    if (nt == 32) return gated ? launch<32, true>(mw, ma, args, tiles, stream) : launch<32, false>(mw, ma, args, tiles, stream);
+    if (nt == 64) return gated ? launch<64, true>(mw, ma, args, tiles, stream) : launch<64, false>(mw, ma, args, tiles, stream);
+    return gated ? launch<128, true>(mw, ma, args, tiles, stream) : launch<128, false>(mw, ma, args, tiles, stream);
+}

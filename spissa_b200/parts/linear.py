@@ -2,8 +2,9 @@
 
 ``Linear`` holds one weight matrix and picks the kernel for a call by the operands'
 storage types and sizes: bfloat16 activations on a bfloat16 weight go to the weight-streaming
-kernel for a few tokens (decoding) and to the tcgen05 tensor-core kernel otherwise, when the
-rows are multiples of 16 bytes; everything else, and the whole 32-bit path, goes to the FFMA kernel.
+kernel for a few tokens (decoding), to the tcgen05 kernel that streams the weight with its rows as the
+instruction's M for a few dozen tokens, and to the tcgen05 tile kernel otherwise, when the rows are
+multiples of 16 bytes; everything else, and the whole 32-bit path, goes to the FFMA kernel.
 """
 from __future__ import annotations
 
@@ -13,7 +14,9 @@ from ..csrc import lib as K
 
 SM_COUNT = 148
 GEMV_TOKENS = 16          # up to this many tokens the weight-streaming kernel runs instead of 128-row tiles
-GATED_GEMV_TOKENS = 32    # the gate/up product streams faster than 64 wide tiles up to here (23.7 vs 40 us at 32 tokens)
+GATED_GEMV_TOKENS = 16    # the same for the gate/up product
+STREAM_TOKENS = 64        # from there up to this many tokens the weight streams through tcgen05 with the tokens as the
+#                           instruction's N (at 64 tokens: QKV 9.4 vs 12.8 us, gate/up 29 vs 40 us, down 14.4 vs 19.5 us)
 
 
 def tile_width(M: int, N: int) -> int:
@@ -39,6 +42,8 @@ class Linear:
         mode = K.TC_ACCUMULATE if accumulate else K.TC_STORE
         if x.shape[0] <= GEMV_TOKENS and K.gemv_supported(x, self.weight):
             K.gemv(x, self.weight, out, mode)
+        elif x.shape[0] <= STREAM_TOKENS and K.tc_stream_supported(x, self.weight, mode):
+            K.tc_stream(x, self.weight, out, mode)
         elif K.tc_gemm_supported(x, self.weight):
             K.tc_gemm(x, self.weight, out, mode, tile_width(x.shape[0], self.out_features))
         else:
@@ -73,6 +78,8 @@ class GatedLinear:
         out = torch.empty(x.shape[0], self.intermediate, dtype=act_dtype, device=x.device)
         if self.block and x.shape[0] <= GATED_GEMV_TOKENS and K.gemv_supported(x, self.weight):
             K.gemv(x, self.weight, out, K.TC_SILU_MUL, self.block)
+        elif self.block and x.shape[0] <= STREAM_TOKENS and K.tc_stream_supported(x, self.weight, K.TC_SILU_MUL, self.block):
+            K.tc_stream(x, self.weight, out, K.TC_SILU_MUL, self.block)
         elif self.block and K.tc_gemm_supported(x, self.weight):
             K.tc_gemm(x, self.weight, out, K.TC_SILU_MUL, 2 * self.block)
         else:

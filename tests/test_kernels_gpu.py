@@ -423,6 +423,54 @@ def test_tc_gemm_silu_mul(K, M, I, K_, bn):
     K.check_status(DEV)
 
 
+# ------------------------------------------------------------------ the tensor-core product that streams W (up to 128 tokens)
+@pytest.mark.parametrize("M,N,K_", [(17, 3072, 2048), (64, 2048, 8192), (1, 130, 72), (33, 200, 1000), (128, 520, 136),
+                                     (100, 128, 64), (48, 2048, 2048), (16, 136, 8), (65, 1000, 520)])
+def test_tc_stream(K, M, N, K_):
+    torch.manual_seed(M + N)
+    a = torch.randn(M, K_).bfloat16()
+    w = torch.randn(N, K_).bfloat16()
+    ref = a.double() @ w.double().t()
+    assert K.tc_stream_supported(a.to(DEV), w.to(DEV))
+    for odt, tol in ((torch.float32, 3e-6), (torch.bfloat16, 4e-3)):
+        out = torch.full((M, N), 9.0, dtype=odt, device=DEV)
+        K.tc_stream(a.to(DEV), w.to(DEV), out)
+        close(out, ref, tol, f"store {odt}")
+    base = torch.randn(M, N)
+    acc = base.clone().to(DEV)
+    K.tc_stream(a.to(DEV), w.to(DEV), acc, mode=K.TC_ACCUMULATE)
+    close(acc, ref + base.double(), 3e-6, "accumulate")
+    again = base.clone().to(DEV)
+    K.tc_stream(a.to(DEV), w.to(DEV), again, mode=K.TC_ACCUMULATE)
+    assert torch.equal(acc, again), "the pieces of K are added in a fixed order: two runs agree bit for bit"
+    K.check_status(DEV)
+
+
+@pytest.mark.parametrize("M,I,K_,block", [(20, 8192, 2048, 128), (64, 1024, 2048, 128), (64, 192, 64, 64), (33, 256, 1000, 128),
+                                           (128, 256, 72, 128), (17, 320, 208, 64), (5, 128, 136, 128)])
+def test_tc_stream_silu_mul(K, M, I, K_, block):
+    torch.manual_seed(I)
+    a = torch.randn(M, K_).bfloat16()
+    g, u = (torch.randn(I, K_) * 0.2).bfloat16(), (torch.randn(I, K_) * 0.2).bfloat16()
+    ref = P.silu(a.double() @ g.double().t()) * (a.double() @ u.double().t())
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    w = interleave(g, u, block).to(DEV)
+    assert K.tc_stream_supported(a.to(DEV), w, K.TC_SILU_MUL, block)
+    K.tc_stream(a.to(DEV), w, out, mode=K.TC_SILU_MUL, pair=block)
+    close(out, ref, 4e-3)
+    K.check_status(DEV)
+
+
+def test_tc_stream_refuses_what_it_cannot_do(K):
+    a = torch.randn(4, 12, device=DEV).bfloat16()
+    w = torch.randn(4, 12, device=DEV).bfloat16()
+    assert not K.tc_stream_supported(a, w)                                        # rows of 24 bytes
+    big = torch.randn(129, 64, device=DEV).bfloat16()
+    assert not K.tc_stream_supported(big, torch.randn(8, 64, device=DEV).bfloat16())     # more than 128 tokens
+    with pytest.raises(K.KernelError, match="1 to 128 tokens"):
+        K.tc_stream(big, torch.randn(8, 64, device=DEV).bfloat16(), torch.empty(129, 8, device=DEV))
+
+
 def test_tc_gemm_refuses_rows_that_tma_cannot_fetch(K):
     a = torch.randn(4, 12, device=DEV).bfloat16()
     w = torch.randn(4, 12, device=DEV).bfloat16()

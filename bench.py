@@ -221,6 +221,18 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=torch.float32 if mode == K.TC_ACCUMULATE else bf, device=dev)
         run = lambda i: K.tc_gemm(a, ws[i % n_buf], out, mode, bn)
         flops = 2.0 * T * N * Kd
+    elif name in ("stream_qkv", "stream_o", "stream_gate_up", "stream_down"):
+        # the products of a decode step of 64 sequences: tc_stream.cu
+        N, Kd, mode, pair = {"stream_qkv": (3072, H, K.TC_STORE, 0), "stream_o": (H, H, K.TC_ACCUMULATE, 0),
+                             "stream_gate_up": (2 * I, H, K.TC_SILU_MUL, 128),
+                             "stream_down": (H, I, K.TC_ACCUMULATE, 0)}[name]
+        n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [rnd(N, Kd) for _ in range(n_buf)]
+        x = rnd(64, Kd)
+        out = torch.zeros(64, N // 2 if mode == K.TC_SILU_MUL else N,
+                          dtype=torch.float32 if mode == K.TC_ACCUMULATE else bf, device=dev)
+        run = lambda i: K.tc_stream(x, ws[i % n_buf], out, mode, pair)
+        bytes_ = N * Kd * 2.0
     elif name in ("gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_head"):
         N, Kd, mode = {"gemv_qkv": (3072, H, K.TC_STORE), "gemv_o": (H, H, K.TC_ACCUMULATE),
                        "gemv_gate_up": (2 * I, H, K.TC_SILU_MUL), "gemv_down": (H, I, K.TC_ACCUMULATE),
@@ -305,7 +317,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode|decode_layers|step_b8) instead of the step")
+                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode|decode_layers|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()

@@ -265,14 +265,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Args& args, int t
 
 int tiles_of(int N, int mode, int pair) { return mode == MODE_SILU_MUL ? N / (2 * pair) : (N + BW - 1) / BW; }
 
+// Pieces of K = CTAs of a cluster: a power of two (clusters of other sizes pack badly into a GPC), as many as give
+// about two CTAs per SM in one wave, each with at least one block of K.
 int pieces_of(int tiles, int K) {
     const int num_kb = (K + BK - 1) / BK;
-    int want = (2 * sm_count() + tiles - 1) / tiles;               // about two CTAs per SM
-    if (want > MAX_SPLITS) want = MAX_SPLITS;
-    if (want > num_kb) want = num_kb;
-    if (want < 1) want = 1;
-    const int per = (num_kb + want - 1) / want;
-    return (num_kb + per - 1) / per;                               // every piece holds at least one block of K
+    int pieces = 1;
+    while (pieces * 2 <= MAX_SPLITS && pieces * 2 <= num_kb && tiles * pieces * 2 <= 2 * sm_count()) pieces *= 2;
+    while (pieces > 1 && (pieces - 1) * ((num_kb + pieces - 1) / pieces) >= num_kb) pieces /= 2;      // no empty piece
+    return pieces;
 }
 
 }  // namespace

@@ -113,7 +113,7 @@ rmsnorm_row_kernel(const float* __restrict__ x, const void* __restrict__ w, int 
 
 // One warp per row, the row in registers (NV float4 per lane), eight rows per block: every lane has all its loads
 // in flight at once and the row sum needs no shared memory. For H = 128·NV.
-template <int NV>
+template <int NV, bool WBF16>
 __global__ void __launch_bounds__(256)
 rmsnorm_warp_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt, void* __restrict__ out,
                     int out_dt, const int* __restrict__ rows, int n_rows, int H, float eps) {
@@ -124,6 +124,13 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const void* __restrict__ w, int
     float4 v[NV];
 #pragma unroll
     for (int i = 0; i < NV; ++i) v[i] = src[lane + 32 * i];
+    // bfloat16 weights are asked for before the row's sum is known: one trip to memory instead of two in a row
+    // (float32 weights would not fit the registers next to the row)
+    uint2 wb[WBF16 ? NV : 1];
+    if (WBF16) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i) wb[i] = ((const uint2*)w)[lane + 32 * i];
+    }
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -136,9 +143,8 @@ rmsnorm_warp_kernel(const float* __restrict__ x, const void* __restrict__ w, int
     for (int i = 0; i < NV; ++i) {
         const int c = lane + 32 * i;
         float wv[4];
-        if (w_dt == SP_DT_BF16) {
-            const uint2 wb = ((const uint2*)w)[c];
-            const __nv_bfloat162 w01 = *(const __nv_bfloat162*)&wb.x, w23 = *(const __nv_bfloat162*)&wb.y;
+        if (WBF16) {
+            const __nv_bfloat162 w01 = *(const __nv_bfloat162*)&wb[i].x, w23 = *(const __nv_bfloat162*)&wb[i].y;
             wv[0] = __low2float(w01); wv[1] = __high2float(w01); wv[2] = __low2float(w23); wv[3] = __high2float(w23);
         } else {
             const float4 wf = ((const float4*)w)[c];
@@ -166,7 +172,10 @@ SP_API int sp_rmsnorm(const float* x, const void* w, int w_dt, void* out, int ou
     const bool aligned = ((((uintptr_t)x | (uintptr_t)out | (uintptr_t)w) & 15) == 0);
 #define SP_NORM_WARP(NV)                                                                                        \
     if (aligned && H == 128 * NV) {                                                                             \
-        rmsnorm_warp_kernel<NV><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
+        if (w_dt == SP_DT_BF16)                                                                                 \
+            rmsnorm_warp_kernel<NV, true><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
+        else                                                                                                    \
+            rmsnorm_warp_kernel<NV, false><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
         SP_CHECK_LAUNCH("rmsnorm");                                                                             \
         return 0;                                                                                               \
     }

@@ -67,7 +67,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O HD
     constexpr uint32_t COL_S = 0, COL_O = 128;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p, bar_o;
+    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p[2], bar_o;
     __shared__ uint32_t tmem_slot;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -102,7 +102,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         }
         mbar_init(smem_u32(&bar_s[0]), 1);
         mbar_init(smem_u32(&bar_s[1]), 1);
-        mbar_init(smem_u32(&bar_p), 4);                           // one arrival per softmax warp
+        // one arrival per softmax warp. Two of them, by block parity: a row warp may be one block ahead of the others
+        // (the next block's scores are there early), and its arrival must not count for the block they are still on.
+        mbar_init(smem_u32(&bar_p[0]), 4);
+        mbar_init(smem_u32(&bar_p[1]), 4);
         mbar_init(smem_u32(&bar_o), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -162,7 +165,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 // still holds the probabilities of block j-1 for the product issued before: the pipe runs in order.
                 if (j + 1 < n_blocks) ok = issue_s(j + 1);
                 if (!ok) break;
-                ok = mbar_wait(smem_u32(&bar_p), (uint32_t)j & 1u, status, 114);
+                ok = mbar_wait(smem_u32(&bar_p[j & 1]), (uint32_t)(j >> 1) & 1u, status, 114);
                 if (!ok) break;
                 tc_fence_after();
                 const int s = j % KV_STAGES;
@@ -251,7 +254,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             tc_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&bar_p));
+            if (lane == 0) mbar_arrive(smem_u32(&bar_p[j & 1]));
         }
         if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 1) & 1u, status, 117);
         tc_fence_after();

@@ -563,6 +563,29 @@ def test_flash_prefill_tc_ignores_junk_beyond_the_sequence(K, hd):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
+def test_flash_prefill_tc_repeats_bit_for_bit(K, hd):
+    """Nothing in the kernel depends on timing: many launches on the same inputs (ragged lengths, many heads, so that
+    CTAs and row warps finish in every order) give the same bits, and those of the first launch are right."""
+    torch.manual_seed(5)
+    nh, nkv = 16, 4
+    new_counts, before = [300, 77, 129, 513], [0, 50, 0, 100]
+    meta = KH.paged_meta(new_counts, before, DEV, 9)
+    qs = [torch.randn(t, nh, hd).bfloat16().float() for t in meta.total_len]
+    ks = [torch.randn(t, nkv, hd).bfloat16().float() for t in meta.total_len]
+    vs = [torch.randn(t, nkv, hd).bfloat16().float() for t in meta.total_len]
+    k_pool, v_pool = KH.fill_cache(meta, ks, vs, nkv, hd, torch.bfloat16, DEV)
+    q = torch.cat([qb[-n:] for qb, n in zip(qs, new_counts)], 0).reshape(-1, nh * hd).bfloat16().to(DEV)
+    fn = flash_tc_fn(K)
+    first = torch.empty_like(q)
+    fn(q, k_pool, v_pool, first, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
+    close(first, KH.plain_attention_rows(qs, ks, vs, new_counts), 6e-3, "first launch")
+    for i in range(30):
+        out = torch.empty_like(q)
+        fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
+        assert torch.equal(out, first), f"launch {i + 2} differs from the first"
+
+
+@pytest.mark.parametrize("hd", [64, 128])
 def test_flash_prefill_tc_reference_maximum_moves_late(K, hd):
     """Scores that keep growing along the keys: the row's reference maximum has to move (and the output so far be
     rescaled) in every block, also late ones; random inputs alone would move it once."""

@@ -256,6 +256,10 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_p[j & 1]));
         }
+        // The last product. A row warp may be one block ahead of the others, so the product before the last may not
+        // even be issued yet; a wait by parity alone would take the completion of the one before that for it.
+        // Waiting for the product before the last first makes the parity of the last one unambiguous.
+        if (ok && n_blocks > 1) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 2) & 1u, status, 117);
         if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 1) & 1u, status, 117);
         tc_fence_after();
         if (ok && !(status && *(volatile int*)status != 0)) {

@@ -579,7 +579,7 @@ def test_flash_prefill_tc_repeats_bit_for_bit(K, hd):
     first = torch.empty_like(q)
     fn(q, k_pool, v_pool, first, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
     close(first, KH.plain_attention_rows(qs, ks, vs, new_counts), 6e-3, "first launch")
-    for i in range(30):
+    for i in range(300):
         out = torch.empty_like(q)
         fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
         assert torch.equal(out, first), f"launch {i + 2} differs from the first"
@@ -614,3 +614,56 @@ def test_gather_i32(K):
     dst = torch.full((7,), -5, dtype=torch.int32, device=DEV)
     K.gather_i32(src, idx, dst)
     assert dst.tolist() == [103, 100, 139, 107, 107, 0, 0]          # rows outside the source give 0
+
+
+# ------------------------------------------------------------------ no kernel's result depends on timing
+@pytest.mark.parametrize("which", ["flash_prefill", "flash_decode_fused", "flash_decode_two_kernels"])
+def test_attention_kernels_repeat_bit_for_bit(K, which):
+    torch.manual_seed(8)
+    nh, nkv, hd = 8, 2, 64
+    if which == "flash_prefill":
+        new_counts, before, fn = [300, 77, 129], [0, 50, 0], flash_prefill_fn(K)
+    else:
+        new_counts, before = [1, 1, 1, 1], [0, 700, 64, 333]
+        fn = flash_decode_fn(K, 2, which == "flash_decode_fused")
+    meta = KH.paged_meta(new_counts, before, DEV, 4)
+    qs = [torch.randn(t, nh, hd).bfloat16().float() for t in meta.total_len]
+    ks = [torch.randn(t, nkv, hd).bfloat16().float() for t in meta.total_len]
+    vs = [torch.randn(t, nkv, hd).bfloat16().float() for t in meta.total_len]
+    k_pool, v_pool = KH.fill_cache(meta, ks, vs, nkv, hd, torch.bfloat16, DEV)
+    q = torch.cat([qb[-n:] for qb, n in zip(qs, new_counts)], 0).reshape(-1, nh * hd).bfloat16().to(DEV)
+    first = torch.empty_like(q)
+    fn(q, k_pool, v_pool, first, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
+    for i in range(20):
+        out = torch.empty_like(q)
+        fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, None, 1.0 / math.sqrt(hd))
+        assert torch.equal(out, first), f"{which}: launch {i + 2} differs from the first"
+
+
+@pytest.mark.parametrize("M,N,K_,bn", [(300, 520, 264, 128), (2048, 512, 2048, 256), (64, 3072, 2048, 128), (17, 2048, 8192, 128)])
+def test_tc_gemm_repeats_bit_for_bit(K, M, N, K_, bn):
+    torch.manual_seed(3)
+    a = torch.randn(M, K_).bfloat16().to(DEV)
+    w = torch.randn(N, K_).bfloat16().to(DEV)
+    base = torch.randn(M, N, device=DEV)
+    first = base.clone()
+    K.tc_gemm(a, w, first, mode=K.TC_ACCUMULATE, bn=bn)
+    for i in range(10):
+        out = base.clone()
+        K.tc_gemm(a, w, out, mode=K.TC_ACCUMULATE, bn=bn)
+        assert torch.equal(out, first), f"launch {i + 2} differs from the first"
+    K.check_status(DEV)
+
+
+@pytest.mark.parametrize("M,N,K_", [(8, 3072, 2048), (16, 2048, 8192), (3, 100, 200)])
+def test_gemv_repeats_bit_for_bit(K, M, N, K_):
+    torch.manual_seed(4)
+    x = torch.randn(M, K_).bfloat16().to(DEV)
+    w = torch.randn(N, K_).bfloat16().to(DEV)
+    base = torch.randn(M, N, device=DEV)
+    first = base.clone()
+    K.gemv(x, w, first, K.TC_ACCUMULATE)
+    for i in range(10):
+        out = base.clone()
+        K.gemv(x, w, out, K.TC_ACCUMULATE)
+        assert torch.equal(out, first), f"launch {i + 2} differs from the first"

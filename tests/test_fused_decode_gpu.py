@@ -139,3 +139,21 @@ def test_long_context_far_key(folders, tmp_path):
         for i in range(steps):
             err = float((rows[i, b].double() - ref[n + i]).abs().max()) / float(ref.abs().max())
             assert err <= allowed, f"sequence {b} step {i}: {err:.3e} (allowed {allowed:.3e})"
+
+
+def test_real_layer_sizes_repeat_bit_for_bit():
+    """Two layers of the 1B shape, eight sequences of a few hundred tokens, sixty decode steps, twice: every kernel
+    on the way (tensor-core products and attention for the prompts, the one-kernel decode path, the head) has fixed
+    orders of summation, so the two runs agree bit for bit whatever the timing of their CTAs and warps."""
+    from spissa_b200 import LlamaConfig
+    from test_big_shapes_gpu import LLAMA_1B_2L
+    cfg = LlamaConfig.from_dict(LLAMA_1B_2L)
+    engine = Engine.from_config(cfg, seed=5, dtype="bfloat16", max_tokens=8 * 1024, max_seqs=8, use_graphs=False)
+    V = cfg.vocab_size
+    lens = [300 + 37 * b for b in range(8)]
+    seqs = [tiny.random_prompt(V, n + 60, 3 * n) for n in lens]
+    first = decode_rows(engine, seqs, lens, 60)
+    assert engine.model._fused.runs == 60
+    again = decode_rows(engine, seqs, lens, 60)
+    assert torch.isfinite(first).all()
+    assert torch.equal(first, again)

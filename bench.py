@@ -1,13 +1,14 @@
 """Measures decoding and prefill of the Llama-3.2-1B shape with random bfloat16 weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--context T]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
 events over exactly K decode steps after W warm-up steps; ``e2e`` is the same through the
 Python entry point (``Engine.generate``: host token lists in, host token lists out).
 ``prefill`` is one 2,048-token prompt; ``points`` holds decoding at batch 1 and 64;
-``roofline`` compares the decode step with the bytes it has to read.
+``roofline`` compares the decode step with the bytes it has to read. ``--context T`` decodes from prompts of
+about T tokens instead (the cache then holds 2T per sequence); the prefill measurement stays at 2,048 tokens.
 Token ids are synthetic (seeded, uniform over the vocabulary), weights are N(0, 0.02).
 Every decode step reads all weights (2.47 GB), far more than the 126 MB L2, so no
 flush is needed between timed iterations.
@@ -37,6 +38,7 @@ CONFIG_1B = dict(
     tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072)
 CONTEXT = 4096
 PROMPT = 2048
+PREFILL_TOKENS = 2048                       # the prefill measurement is always of this many tokens
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 
@@ -307,12 +309,15 @@ def kernel_case(name: str, reps: int) -> int:
 
 
 def main() -> int:
+    global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=PROMPT,
+                    help="mean prompt length of the decode runs (the cache holds twice as much per sequence)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
@@ -336,6 +341,11 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.context != PROMPT:
+        if args.context < 64:
+            print("bench.py: --context must be at least 64")
+            return 2
+        PROMPT, CONTEXT = args.context, max(2 * args.context, PREFILL_TOKENS + 64)
 
     import torch
     from spissa_b200 import Engine, LlamaConfig, SamplingParams
@@ -434,13 +444,13 @@ def main() -> int:
                runs=[round(r[0], 1) for r in runs])
 
     # ---------------------------------------------------------------- prefill of 2,048 tokens
-    prompt = [rng.randrange(V) for _ in range(PROMPT)]
+    prompt = [rng.randrange(V) for _ in range(PREFILL_TOKENS)]
 
     def prefill_once():
         s = engine.acquire()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        logits = engine.step([(s, prompt, [PROMPT - 1])])
+        logits = engine.step([(s, prompt, [PREFILL_TOKENS - 1])])
         sampler.sample(logits, greedy, [0], 0)
         e1.record()
         torch.cuda.synchronize()
@@ -450,8 +460,8 @@ def main() -> int:
     for _ in range(3):
         prefill_once()
     pre_ms = sorted(prefill_once() for _ in range(5))[2]
-    flops = prefill_flops(cfg, PROMPT)
-    prefill = dict(value=round(PROMPT / (pre_ms * 1e-3), 1), tokens=PROMPT, ms=round(pre_ms, 3),
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    prefill = dict(value=round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), tokens=PREFILL_TOKENS, ms=round(pre_ms, 3),
                    frac=round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4))
 
     # ---------------------------------------------------------------- other batch sizes

@@ -426,7 +426,7 @@ __device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, 
 
 // ---------------------------------------------------------------- attention: chunks of keys, then their combination
 // GROUPS groups of four warps, each with tiles of its own, work on different (sequence, kv head, chunk) items.
-template <int HD, int ST, int GROUPS>
+template <int HD, int ST, int GROUPS, int NH>
 __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const LayerDesc& L, uint8_t* scratch_all) {
     using TL = Tile<HD>;
     constexpr int GROUP_BYTES = 16 * TL::ROW + 2 * ST * TL::BYTES + MAX_CHUNK_PAGES * 4;
@@ -476,13 +476,15 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
         }
         cp_async_commit();
 
-        uint32_t qf[HD / 16][4];
-        float o[HD / 8][4];
+        uint32_t qb[HD / 16][NH][2];
+        float o[HD / 16][NH][4], m[NH][2], l[NH][2];
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-        const int hi[2] = {pos, pos};
-        const int lo[2] = {0, 0};
+        for (int i = 0; i < NH; ++i) {
+            m[i][0] = m[i][1] = -INFINITY;
+            l[i][0] = l[i][1] = 0.0f;
+#pragma unroll
+            for (int dt = 0; dt < HD / 16; ++dt) o[dt][i][0] = o[dt][i][1] = o[dt][i][2] = o[dt][i][3] = 0.0f;
+        }
         // each warp fetches and uses its own 16 keys of every page: no barrier among the warps inside the loop
         // the warp's 16 keys of a page are 16·HD consecutive elements: lane takes 16-byte pieces lane, lane + 32, ...
         constexpr int PIECES = 16 * TL::CHUNKS / 32;
@@ -506,7 +508,15 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
         }
         cp_async_wait<ST - 1>();
         bar_sync(bar, 128);
-        load_q_frags<HD>(q_tile, 0, lane, qf);
+        // Qᵀ as the B operand: lane (g, t) holds dims 2t, 2t+1 and 2t+8, 2t+9 of head g of each head tile
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+            for (int i = 0; i < NH; ++i) {
+                const uint32_t a = q_tile + (i * 8 + (lane >> 2)) * TL::ROW + (kk * 16 + 2 * (lane & 3)) * 2;
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(qb[kk][i][0]) : "r"(a));
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(qb[kk][i][1]) : "r"(a + 16));
+            }
         for (int j = j_first; j <= j_last; ++j) {
             const int i = j - j_first, stage = i % ST;
             if (j + ST - 1 <= j_last) fetch(j + ST - 1, (i + ST - 1) % ST);
@@ -514,31 +524,36 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
             cp_async_wait<ST - 1>();
             __syncwarp();
             if (j * KT + KT - 1 <= pos)
-                flash_step<HD, 2, false>(qf, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, lo,
-                                         hi, L.scale_log2, o, m, l, lane);
+                decode_step_t<HD, NH, false>(qb, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, 0,
+                                             pos, L.scale_log2, o, m, l, lane);
             else
-                flash_step<HD, 2, true>(qf, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, lo,
-                                        hi, L.scale_log2, o, m, l, lane);
+                decode_step_t<HD, NH, true>(qb, k_tiles + stage * TL::BYTES, v_tiles + stage * TL::BYTES, warp * 16, j * KT, 0,
+                                            pos, L.scale_log2, o, m, l, lane);
             __syncwarp();
         }
         cp_async_wait<0>();
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-            l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-        }
-        bar_sync(bar, 128);                                        // every warp is done with the key tiles: they become the merge buffer
-        const int t = lane & 3;
+        for (int i = 0; i < NH; ++i)
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            float* dst = merge + ((size_t)warp * 16 + (lane >> 2) + r * 8) * MS;
-#pragma unroll
-            for (int i = 0; i < HD / 8; ++i) {
-                dst[i * 8 + 2 * t] = o[i][2 * r];
-                dst[i * 8 + 2 * t + 1] = o[i][2 * r + 1];
+            for (int c = 0; c < 2; ++c) {                          // the lanes that share t hold the same head's other keys
+                l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 4);
+                l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 8);
+                l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 16);
             }
-            if (t == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
-        }
+        bar_sync(bar, 128);                                        // every warp is done with the key tiles: they become the merge buffer
+        const int lg = lane >> 2, lt = lane & 3;
+#pragma unroll
+        for (int i = 0; i < NH; ++i)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {                          // head 8i + 2·lt + c: dims lg and lg + 8 of every 16
+                float* dst = merge + ((size_t)warp * 16 + i * 8 + 2 * lt + c) * MS;
+#pragma unroll
+                for (int dt = 0; dt < HD / 16; ++dt) {
+                    dst[dt * 16 + lg] = o[dt][i][c];
+                    dst[dt * 16 + lg + 8] = o[dt][i][c + 2];
+                }
+                if (lg == 0) { dst[HD] = m[i][c]; dst[HD + 1] = l[i][c]; }
+            }
         bar_sync(bar, 128);
         for (int e = tid; e < Gq * HD; e += 128) {
             const int row = e / HD, d = e % HD;
@@ -707,7 +722,10 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
         grid_sync(p, sh, epoch);
 
         // ---- attention
-        if (warp < 4 * AG) attention_chunks<HD, ST, AG>(p, sh, L, uni);
+        if (warp < 4 * AG) {                         // head tiles of 8: one for up to 8 query heads per kv head, else two
+            if (L.nh <= 8 * L.nkv) attention_chunks<HD, ST, AG, 1>(p, sh, L, uni);
+            else attention_chunks<HD, ST, AG, 2>(p, sh, L, uni);
+        }
         grid_sync(p, sh, epoch);
         attention_combine<HD>(p, L);
         grid_sync(p, sh, epoch);

@@ -166,6 +166,97 @@ __device__ __forceinline__ void flash_step(const uint32_t (&qf)[HD / 16][4], uin
     }
 }
 
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {   // the 8x8 matrix of 16-bit values a warp holds, transposed
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
+// Decoding: few query rows (the heads that share a kv head), many keys. Here the KEYS are the M of the
+// instruction and the heads its N (8 per tile), so up to 8 heads cost one mma per 16 keys and 16 dims, where
+// the form with the heads as M costs two with most of its rows idle.
+//   Sᵀ[key, head] = K[key, :] · Qᵀ       A = K tile (ldmatrix), B = fragments of Qᵀ (``qb``)
+//   Oᵀ[d, head]  += Vᵀ[d, key] · Pᵀ      A = V tile (ldmatrix.trans), B = Pᵀ = the transposed fragment of Sᵀ
+// One warp, keys [key0, key0 + 16) of the tile; a lane holds keys g, g + 8 of heads 2t, 2t + 1 of each head
+// tile (g = lane / 4, t = lane % 4). ``m`` is the reference maximum per head in the log2 domain, the same in
+// the 8 lanes that share t. It moves only when a score exceeds it by more than 8 (then the lanes agree on the
+// new maximum and rescale o and l); otherwise P = 2^(s - m) ≤ 256 and no lane talks to another. The result
+// o / l does not depend on the reference. ``l`` is per lane (its own keys); the caller adds the lanes.
+template <int HD, int NH, bool MASKED>
+__device__ __forceinline__ void decode_step_t(const uint32_t (&qb)[HD / 16][NH][2], uint32_t k_tile, uint32_t v_tile,
+                                              int key0, int tile_pos0, int lo, int hi, float scale_log2,
+                                              float (&o)[HD / 16][NH][4], float (&m)[NH][2], float (&l)[NH][2],
+                                              int lane) {
+    using T = Tile<HD>;
+    const int g = lane >> 2;
+    float s[NH][4], s2[NH][4];                        // two chains of products: an mma need not wait for the one before
+#pragma unroll
+    for (int i = 0; i < NH; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[i][e] = s2[i][e] = 0.0f;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(k_tile + (key0 + (lane & 15)) * T::ROW + (kk * 16 + ((lane >> 4) << 3)) * 2, a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+            if (kk & 1) mma_bf16(s2[i], a, qb[kk][i][0], qb[kk][i][1]);
+            else mma_bf16(s[i], a, qb[kk][i][0], qb[kk][i][1]);
+        }
+    }
+    bool move = false;
+#pragma unroll
+    for (int i = 0; i < NH; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float v = (s[i][e] + s2[i][e]) * scale_log2;
+            if (MASKED) {
+                const int key = tile_pos0 + key0 + g + ((e >> 1) << 3);
+                if (key > hi || key < lo) v = -INFINITY;
+            }
+            s[i][e] = v;
+        }
+        move = move || fmaxf(s[i][0], s[i][2]) > m[i][0] + 8.0f || fmaxf(s[i][1], s[i][3]) > m[i][1] + 8.0f;
+    }
+    if (__any_sync(0xffffffffu, move)) {
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float mx = fmaxf(s[i][c], s[i][c + 2]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float mnew = fmaxf(m[i][c], mx);
+                const float corr = fast_exp2(m[i][c] - ((mnew == -INFINITY) ? 0.0f : mnew));     // m = -inf gives 0
+                m[i][c] = mnew;
+                l[i][c] *= corr;
+#pragma unroll
+                for (int dt = 0; dt < HD / 16; ++dt) { o[dt][i][c] *= corr; o[dt][i][c + 2] *= corr; }
+            }
+        }
+    }
+    uint32_t pb[NH][2];
+#pragma unroll
+    for (int i = 0; i < NH; ++i) {
+        const float m0 = (m[i][0] == -INFINITY) ? 0.0f : m[i][0], m1 = (m[i][1] == -INFINITY) ? 0.0f : m[i][1];
+        const float p0 = fast_exp2(s[i][0] - m0), p1 = fast_exp2(s[i][1] - m1);
+        const float p2 = fast_exp2(s[i][2] - m0), p3 = fast_exp2(s[i][3] - m1);
+        l[i][0] += p0 + p2;
+        l[i][1] += p1 + p3;
+        pb[i][0] = movmatrix_trans(pack_bf16(p0, p1));            // keys key0 .. +7 of head g
+        pb[i][1] = movmatrix_trans(pack_bf16(p2, p3));            // keys key0 + 8 .. +15
+    }
+#pragma unroll
+    for (int dt = 0; dt < HD / 16; ++dt) {
+        uint32_t a[4];
+        ldmatrix_x4_trans(v_tile + (key0 + (lane & 7) + ((lane >> 4) << 3)) * T::ROW + (dt * 16 + (((lane >> 3) & 1) << 3)) * 2,
+                          a[0], a[1], a[2], a[3]);
+#pragma unroll
+        for (int i = 0; i < NH; ++i) mma_bf16(o[dt][i], a, pb[i][0], pb[i][1]);
+    }
+}
+
 template <int HD>
 __device__ __forceinline__ void load_q_frags(uint32_t q_tile, int row0, int lane, uint32_t (&qf)[HD / 16][4]) {
     using T = Tile<HD>;

@@ -141,6 +141,26 @@ def test_long_context_far_key(folders, tmp_path):
             assert err <= allowed, f"sequence {b} step {i}: {err:.3e} (allowed {allowed:.3e})"
 
 
+@pytest.mark.parametrize("heads, kv_heads", [(10, 1), (16, 2), (5, 5)])
+def test_head_groups_of_other_sizes(tmp_path, heads, kv_heads):
+    """The kernel's attention holds the query heads of a kv head as columns of 8: ten heads per kv head need a
+    second, partly empty column tile, eight fill one exactly, one head per kv head leaves seven of eight idle."""
+    cfg = dict(tiny.TINY_E, num_attention_heads=heads, num_key_value_heads=kv_heads, num_hidden_layers=2)
+    folder = tiny.make_folder(cfg, tiny.TINY_E_INIT, tmp_path / "groups")
+    pcfg, w = P.read_model_folder(folder)
+    V = cfg["vocab_size"]
+    lens = [125, 40, 200]
+    steps = 6
+    seqs = [tiny.random_prompt(V, n + steps, 5 * n + heads) for n in lens]
+    engine = Engine.from_folder(str(folder), dtype="bfloat16", max_tokens=64 * 16, use_graphs=False)
+    rows = decode_rows(engine, seqs, lens, steps)
+    assert engine.model._fused.runs == steps
+    for b, (q, n) in enumerate(zip(seqs, lens)):
+        ref = P.model_logits(pcfg, w, q, torch.float64)
+        err = float((rows[:, b].double() - ref[n:n + steps]).abs().max()) / float(ref.abs().max())
+        assert err <= TOL, f"{heads} heads, {kv_heads} kv heads, sequence {b}: {err:.3e}"
+
+
 def test_real_layer_sizes_repeat_bit_for_bit():
     """Two layers of the 1B shape, eight sequences of a few hundred tokens, sixty decode steps, twice: every kernel
     on the way (tensor-core products and attention for the prompts, the one-kernel decode path, the head) has fixed

@@ -246,13 +246,15 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=bf if mode == K.TC_SILU_MUL else torch.float32, device=dev)
         run = lambda i: K.gemv(x, ws[i % n_buf], out, mode, 128)
         bytes_ = N * Kd * 2.0
-    elif name in ("flash_prefill", "flash_prefill_tc", "flash_decode", "flash_prefill_128", "flash_prefill_tc_128"):
+    elif name in ("flash_prefill", "flash_prefill_tc", "flash_decode", "flash_decode_b64", "flash_prefill_128",
+                  "flash_prefill_tc_128"):
         if name.endswith("_128"):          # the 8B shape's attention: 32 heads of 128, 8 kv heads
             hd, name = 128, name[:-4]
-        B = 1 if name != "flash_decode" else 8
-        n_new = T if name != "flash_decode" else 1
+        decode_batch = {"flash_decode": 8, "flash_decode_b64": 64}.get(name, 0)
+        B = decode_batch or 1
+        n_new = 1 if decode_batch else T
         pages = B * (T // 64)
-        n_buf = 1 if name != "flash_decode" else 40           # 40 x 8.4 MB of keys and values > L2
+        n_buf = 320 // decode_batch if decode_batch else 1    # 40 x 8.4 MB (5 x 67 MB) of keys and values > L2
         pools = [(rnd(pages, nkv, 64, hd), rnd(pages, nkv, 64, hd)) for _ in range(n_buf)]
         table = torch.arange(pages, dtype=torch.int32, device=dev).view(B, T // 64)
         ar = torch.arange(B, dtype=torch.int32, device=dev)
@@ -322,7 +324,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode|decode_layers|step_b8) instead of the step")
+                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|decode_layers|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()

@@ -160,7 +160,7 @@ __device__ __forceinline__ void combine_if_last(const float* part_o, const float
 
 // ------------------------------------------------------------------ decode
 // grid (chunks, kv heads, sequences). part_o [B][nh][chunks][HD], part_ml [B][nh][chunks][2] (m in log2 units).
-template <int HD>
+template <int HD, int NH>
 __global__ void __launch_bounds__(128)
 flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* __restrict__ seq_len, int nh,
                     int window, float scale_log2, int chunk_tiles, float* __restrict__ part_o,
@@ -200,13 +200,16 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     }
     cp_async_commit();                                             // group 0: the queries
 
-    uint32_t qf[HD / 16][4];
-    float o[HD / 8][4];
+    // keys are the M of the products, the group's heads their N, in NH tiles of 8 (decode_step_t)
+    uint32_t qb[HD / 16][NH][2];
+    float o[HD / 16][NH][4], m[NH][2], l[NH][2];
 #pragma unroll
-    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    const int hi[2] = {p, p};
-    const int lo[2] = {first_key, first_key};
+    for (int i = 0; i < NH; ++i) {
+        m[i][0] = m[i][1] = -INFINITY;
+        l[i][0] = l[i][1] = 0.0f;
+#pragma unroll
+        for (int dt = 0; dt < HD / 16; ++dt) o[dt][i][0] = o[dt][i][1] = o[dt][i][2] = o[dt][i][3] = 0.0f;
+    }
 
     // Each warp fetches and uses only its own 16 keys of every tile, so inside the loop the warps
     // need no barrier among themselves: a warp waits for its own copies and goes on.
@@ -227,7 +230,15 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     }
     cp_async_wait<DEC_STAGES - 1>();                               // the queries have landed (all later groups may fly)
     __syncthreads();
-    load_q_frags<HD>(q_tile, 0, lane, qf);
+    // Qᵀ as the B operand: lane (g, t) holds dims 2t, 2t+1 and 2t+8, 2t+9 of head g of each head tile
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+        for (int i = 0; i < NH; ++i) {
+            const uint32_t a = q_tile + (i * 8 + (lane >> 2)) * T::ROW + (kk * 16 + 2 * (lane & 3)) * 2;
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(qb[kk][i][0]) : "r"(a));
+            asm volatile("ld.shared.b32 %0, [%1];" : "=r"(qb[kk][i][1]) : "r"(a + 16));
+        }
 
     for (int j = j_first; j <= j_last; ++j) {
         const int it = j - j_first;
@@ -237,34 +248,33 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         cp_async_wait<DEC_STAGES - 1>();
         __syncwarp();
         if (j * KT + KT - 1 <= p && j * KT >= first_key)
-            flash_step<HD, 2, false>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
-                                     hi, scale_log2, o, m, l, lane);
+            decode_step_t<HD, NH, false>(qb, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT,
+                                         first_key, p, scale_log2, o, m, l, lane);
         else
-            flash_step<HD, 2, true>(qf, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT, lo,
-                                    hi, scale_log2, o, m, l, lane);
+            decode_step_t<HD, NH, true>(qb, k_tiles + stage * T::BYTES, v_tiles + stage * T::BYTES, warp * 16, j * KT,
+                                        first_key, p, scale_log2, o, m, l, lane);
         __syncwarp();                                              // the stage is free for this warp's next fetch
     }
     cp_async_wait<0>();
 
     // merge the four warps' (m, l, o): each covered other keys of the same rows
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-    }
     constexpr int MS = HD + 2;
-    const int t = lane & 3;
+    const int lg = lane >> 2, lt = lane & 3;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-        const int row = (lane >> 2) + r * 8;
-        float* dst = merge + ((size_t)warp * 16 + row) * MS;
+    for (int i = 0; i < NH; ++i)
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            dst[i * 8 + 2 * t] = o[i][2 * r];
-            dst[i * 8 + 2 * t + 1] = o[i][2 * r + 1];
+        for (int c = 0; c < 2; ++c) {                              // head 8i + 2·lt + c: dims lg and lg + 8 of every 16
+            l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 4);   // the lanes that share lt hold the head's other keys
+            l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 8);
+            l[i][c] += __shfl_xor_sync(0xffffffffu, l[i][c], 16);
+            float* dst = merge + ((size_t)warp * 16 + i * 8 + 2 * lt + c) * MS;
+#pragma unroll
+            for (int dt = 0; dt < HD / 16; ++dt) {
+                dst[dt * 16 + lg] = o[dt][i][c];
+                dst[dt * 16 + lg + 8] = o[dt][i][c + 2];
+            }
+            if (lg == 0) { dst[HD] = m[i][c]; dst[HD + 1] = l[i][c]; }
         }
-        if (t == 0) { dst[HD] = m[r]; dst[HD + 1] = l[r]; }
-    }
     __syncthreads();
     for (int e = tid; e < G * HD; e += 128) {
         const int row = e / HD, d = e % HD;
@@ -360,6 +370,31 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     return 0;
 }
 
+namespace {
+// One instantiation per head size and number of head tiles (query heads per kv head: up to 8, up to 16).
+template <int HD, int NH>
+int launch_flash_decode_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, const PagedKV& kv, const int* seq_len,
+                           int nh, int window, float sl, int chunk_tiles, float* part_o, float* part_ml, int* counters,
+                           void* out, int out_dt) {
+    static bool ok = false;
+    if (!ok) { if (opt_in_smem(flash_decode_kernel<HD, NH>, decode_smem<HD>(), "flash_decode")) return 1; ok = true; }
+    flash_decode_kernel<HD, NH><<<grid, 128, decode_smem<HD>(), stream>>>(q, kv, seq_len, nh, window, sl, chunk_tiles,
+                                                                         part_o, part_ml, counters, out, out_dt);
+    return 0;
+}
+int launch_flash_decode(int hd, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, const PagedKV& kv,
+                        const int* seq_len, int nh, int window, float sl, int chunk_tiles, float* part_o, float* part_ml,
+                        int* counters, void* out, int out_dt) {
+    const bool one = nh <= 8 * kv.nkv;
+    if (hd == 64)
+        return one ? launch_flash_decode_as<64, 1>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt)
+                   : launch_flash_decode_as<64, 2>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+    return one ? launch_flash_decode_as<128, 1>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt)
+               : launch_flash_decode_as<128, 2>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+}
+
+}  // namespace
+
 // Floats of scratch the decode kernels need: part_o then part_ml. ``counters`` (optional, n_seqs·nkv ints,
 // zero before the first launch; the kernel returns them to zero) lets the last CTA combine the chunks;
 // without it a second kernel does.
@@ -384,19 +419,9 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     float* part_ml = scratch + (size_t)n_seqs * nh * n_chunks * hd;
     dim3 grid(n_chunks, nkv, n_seqs);
     const float sl = scale * LOG2E;
-    if (hd == 64) {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_decode_kernel<64>, decode_smem<64>(), "flash_decode")) return 1; ok = true; }
-        SP_CHECK_CALL("flash_decode", sp_launch_cluster(flash_decode_kernel<64>, grid, dim3(128), decode_smem<64>(), stream, 1,
-                                                   (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles,
-                                                   part_o, part_ml, counters, out, out_dt));
-    } else {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_decode_kernel<128>, decode_smem<128>(), "flash_decode")) return 1; ok = true; }
-        SP_CHECK_CALL("flash_decode", sp_launch_cluster(flash_decode_kernel<128>, grid, dim3(128), decode_smem<128>(), stream,
-                                                   1, (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles,
-                                                   part_o, part_ml, counters, out, out_dt));
-    }
+    if (launch_flash_decode(hd, grid, stream, (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o,
+                            part_ml, counters, out, out_dt)) return 1;
+    SP_CHECK_LAUNCH("flash_decode");
     if (counters) return 0;                  // the last CTA of every (sequence, kv head) has combined
     if (out_dt == SP_DT_BF16)
         decode_combine_kernel<__nv_bfloat16><<<n_seqs * nh, hd <= 64 ? 64 : 128, 0, stream>>>(part_o, part_ml, (__nv_bfloat16*)out, n_chunks, hd);
@@ -462,17 +487,8 @@ SP_API int sp_flash_decode_static(const void* q, void* out, int out_dt, const vo
     PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
     dim3 grid(n_chunks, nkv, n_seqs);
     const float sl = scale * LOG2E;
-    if (hd == 64) {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_decode_kernel<64>, decode_smem<64>(), "flash_decode")) return 1; ok = true; }
-        flash_decode_kernel<64><<<grid, 128, decode_smem<64>(), stream>>>(
-            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
-    } else {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_decode_kernel<128>, decode_smem<128>(), "flash_decode")) return 1; ok = true; }
-        flash_decode_kernel<128><<<grid, 128, decode_smem<128>(), stream>>>(
-            (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
-    }
+    if (launch_flash_decode(hd, grid, stream, (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o,
+                            part_ml, counters, out, out_dt)) return 1;
     SP_CHECK_LAUNCH("flash_decode (static scratch)");
     return 0;
 }

@@ -301,7 +301,8 @@ def test_flash_prefill_window(K, window):
     attention_case(K, flash_prefill_fn(K), 4, 2, 64, torch.bfloat16, [40, 1, 230], [0, 250, 20], window, window, 6e-3)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (32, 8, 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (32, 8, 64), (10, 1, 64),
+                                       (16, 2, 64), (9, 1, 128)])
 @pytest.mark.parametrize("chunk_tiles", [None, 1, 3])
 @pytest.mark.parametrize("fused", [True, False])
 def test_flash_decode(K, nh, nkv, hd, chunk_tiles, fused):

@@ -57,7 +57,7 @@ constexpr int STAGE_BYTES = (KC / BOXC) * BOX_BYTES;
 constexpr int MAX_STAGES = 12;
 constexpr int MAXT = 16;                        // tokens per step
 constexpr int RED_FLOATS = CWARPS * 2 * 32 * 4; // one buffer of the K-slice sums
-constexpr int MAX_CHUNKS = 16;                  // key chunks per sequence (their partial results are combined in one batch of loads)
+constexpr int MAX_CHUNKS = 32;                  // key chunks per sequence (a single long sequence still gives most warp groups an item)
 constexpr int MAX_CHUNK_PAGES = 512;            // pages per chunk (their table entries wait in shared memory)
 constexpr int SMEM_LIMIT = 232448;              // per CTA on sm_100
 constexpr int STATIC_SMEM = 1536;               // barriers and small arrays below, rounded up
@@ -96,6 +96,7 @@ struct Params {
     const CUtensorMap* maps;        // [layers][4]: QKV, output, gate/up, down; see sp_decode_layers_encode_map
     unsigned long long* trace;      // optional: the global timer at each grid barrier, see sp_decode_layers_set_trace
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
+    const int* plan;                // optional, on the device: {chunk_pages, n_chunks} instead of the two above
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -427,7 +428,8 @@ __device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, 
 // ---------------------------------------------------------------- attention: chunks of keys, then their combination
 // GROUPS groups of four warps, each with tiles of its own, work on different (sequence, kv head, chunk) items.
 template <int HD, int ST, int GROUPS, int NH>
-__device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const LayerDesc& L, uint8_t* scratch_all) {
+__device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const LayerDesc& L, uint8_t* scratch_all,
+                                              int chunk_pages, int n_chunks) {
     using TL = Tile<HD>;
     constexpr int GROUP_BYTES = 16 * TL::ROW + 2 * ST * TL::BYTES + MAX_CHUNK_PAGES * 4;
     constexpr int MS = HD + 2;
@@ -442,17 +444,17 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
     float* merge = (float*)(scratch + 16 * TL::ROW);               // [4 warps][16 rows][HD + 2], over the key tiles once they are used up
     int* pt_s = (int*)(scratch + 16 * TL::ROW + 2 * ST * TL::BYTES);         // the chunk's page-table entries
     const int Gq = L.nh / L.nkv;
-    const int n_items = p.T * L.nkv * p.n_chunks;
+    const int n_items = p.T * L.nkv * n_chunks;
     for (int it = blockIdx.x * GROUPS + wg; it < n_items; it += gridDim.x * GROUPS) {
-        const int b = it / (L.nkv * p.n_chunks), g = (it / p.n_chunks) % L.nkv, chunk = it % p.n_chunks;
+        const int b = it / (L.nkv * n_chunks), g = (it / n_chunks) % L.nkv, chunk = it % n_chunks;
         const int pos = p.positions[b];
-        const int j_first = chunk * p.chunk_pages;
-        const int j_last = min(pos / KT, j_first + p.chunk_pages - 1);
-        const size_t part_base = ((size_t)b * L.nh + (size_t)g * Gq) * p.n_chunks + chunk;
+        const int j_first = chunk * chunk_pages;
+        const int j_last = min(pos / KT, j_first + chunk_pages - 1);
+        const size_t part_base = ((size_t)b * L.nh + (size_t)g * Gq) * n_chunks + chunk;
         if (j_first > j_last) {                                    // no keys in this chunk (the same for all 128 threads)
             for (int i = tid; i < Gq; i += 128) {
-                p.part_ml[(part_base + (size_t)i * p.n_chunks) * 2] = -INFINITY;
-                p.part_ml[(part_base + (size_t)i * p.n_chunks) * 2 + 1] = 0.0f;
+                p.part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
+                p.part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
             }
             continue;
         }
@@ -569,7 +571,7 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
                 acc += src[d] * f;
                 ll += src[HD + 1] * f;
             }
-            const size_t pi = part_base + (size_t)row * p.n_chunks;
+            const size_t pi = part_base + (size_t)row * n_chunks;
             p.part_o[pi * HD + d] = acc;
             if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
         }
@@ -579,11 +581,11 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
 
 // out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order; one warp per (token, head)
 template <int HD>
-__device__ __noinline__ void attention_combine(const Params& p, const LayerDesc& L) {
-    constexpr int CB = MAX_CHUNKS;                                 // chunks whose loads are issued together: all of them
+__device__ __noinline__ void attention_combine(const Params& p, const LayerDesc& L, int n_chunks) {
+    constexpr int CB = 16;                                         // chunks whose loads are issued together
     constexpr int DPL = HD / 32;                                   // output dims per lane
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nc = p.n_chunks;
+    const int nc = n_chunks;
     for (int r = blockIdx.x * CWARPS + warp; r < p.T * L.nh; r += gridDim.x * CWARPS) {
         const size_t bh = (size_t)r;
         // lane c holds (m, l) of chunk c, c + 32, ...: the maximum over all chunks first
@@ -637,6 +639,18 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
     float* ssq_a = p.ssq;                                      // written by the output projection
     float* ssq_b = p.ssq + (size_t)gp * 16;                    // written by the down projection (and here, first)
 
+    // the split of the keys: launch arguments, or two words on the device that the host refreshes before a replay
+    // of a captured launch (the same graph then serves every context length)
+    int chunk_pages = p.chunk_pages, n_chunks = p.n_chunks;
+    if (p.plan) {
+        chunk_pages = __ldg(p.plan);
+        n_chunks = __ldg(p.plan + 1);
+        if (chunk_pages < 1 || chunk_pages > MAX_CHUNK_PAGES || n_chunks < 1 || n_chunks > MAX_CHUNKS) {
+            if (tid == 0 && p.status) atomicCAS(p.status, 0, 204);          // refuse a split the scratch was not sized for
+            chunk_pages = MAX_CHUNK_PAGES;
+            n_chunks = 1;
+        }
+    }
     if (tid < 2) sh->ptc_key[tid][0] = -1;
     if (tid < T) {
         const int pos = p.positions[tid];
@@ -723,11 +737,11 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 
         // ---- attention
         if (warp < 4 * AG) {                         // head tiles of 8: one for up to 8 query heads per kv head, else two
-            if (L.nh <= 8 * L.nkv) attention_chunks<HD, ST, AG, 1>(p, sh, L, uni);
-            else attention_chunks<HD, ST, AG, 2>(p, sh, L, uni);
+            if (L.nh <= 8 * L.nkv) attention_chunks<HD, ST, AG, 1>(p, sh, L, uni, chunk_pages, n_chunks);
+            else attention_chunks<HD, ST, AG, 2>(p, sh, L, uni, chunk_pages, n_chunks);
         }
         grid_sync(p, sh, epoch);
-        attention_combine<HD>(p, L);
+        attention_combine<HD>(p, L, n_chunks);
         grid_sync(p, sh, epoch);
 
         // ---- output projection into the residual
@@ -869,6 +883,20 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
+// The split of the keys: about one (sequence, kv head, chunk) item per warp group of the grid.
+int plan_split(int G, int T, int hd, int len_pages, int max_nkv, int* chunk_pages, int* n_chunks) {
+    if (len_pages < 1) len_pages = 1;
+    int want = G * (hd == 64 ? 2 : 1) / (T * (max_nkv > 0 ? max_nkv : 1));
+    if (want < 1) want = 1;
+    if (want > MAX_CHUNKS) want = MAX_CHUNKS;
+    if (want > len_pages) want = len_pages;
+    if (want * MAX_CHUNK_PAGES < len_pages) want = (len_pages + MAX_CHUNK_PAGES - 1) / MAX_CHUNK_PAGES;
+    if (want > MAX_CHUNKS) SP_FAIL("decode_layers: %d pages per sequence are more than %d chunks of %d hold", len_pages, MAX_CHUNKS, MAX_CHUNK_PAGES);
+    *chunk_pages = (len_pages + want - 1) / want;
+    *n_chunks = (len_pages + *chunk_pages - 1) / *chunk_pages;
+    return 0;
+}
+
 }  // namespace
 
 // Optional: 1024 64-bit words on the device into which CTA 0 writes the global timer: [1] at its start, [2e] as it
@@ -902,6 +930,13 @@ SP_API int sp_decode_layers_map_bytes() { return (int)sizeof(CUtensorMap); }
 
 // CTAs of the kernel = SMs of the device: the host sizes ``ssq`` ([2][CTAs][16] floats) with it.
 SP_API int sp_decode_layers_ctas() { return sm_count(); }
+// out[0] = pages per chunk, out[1] = chunks, for ``T`` sequences of at most ``len_pages`` pages
+SP_API int sp_decode_layers_plan(int T, int hd, int len_pages, int max_nkv, int* out) {
+    const int G = sm_count();
+    if (G <= 0) SP_FAIL("decode_layers: cannot read the number of SMs");
+    if (T < 1) T = 1;
+    return plan_split(G, T, hd, len_pages, max_nkv, out, out + 1);
+}
 SP_API int sp_decode_layers_max_chunks() { return MAX_CHUNKS; }
 SP_API int sp_decode_layers_max_pages() { return MAX_CHUNKS * MAX_CHUNK_PAGES; }
 SP_API int sp_decode_layers_desc_bytes() { return (int)sizeof(LayerDesc); }
@@ -927,10 +962,13 @@ SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int m
 // ``layers``: n_layers descriptors on the device. ``len_pages``: pages that the longest sequence of the step
 // may hold (it only shapes the split of the keys; any actual length is handled). ``max_nkv``: most kv heads of
 // any layer. part_o / part_ml hold T·max(nh)·MAX_CHUNKS·(hd + 2) floats together; sync: 3 zeroed words.
+// ``plan`` (optional, two int32 on the device: what sp_decode_layers_plan gives) replaces the split made from
+// ``len_pages``: a captured launch then serves every length, the host refreshing the two words before a replay.
 SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, int T, int H, int hd, float* x, void* q, void* attn,
                             void* act, void* xw, float* ssq, float* part_o, float* part_ml, const int* positions,
                             const int* seq_row, const int* page_table, int max_pages, int page_size, int len_pages,
-                            int max_nkv, int max_heads_per_kv, unsigned* sync, int* status, cudaStream_t stream) {
+                            int max_nkv, int max_heads_per_kv, const int* plan, unsigned* sync, int* status,
+                            cudaStream_t stream) {
     if (n_layers <= 0) return 0;
     if (!sp_decode_layers_supported(T, H, hd, page_size, max_heads_per_kv)) return 1;
     const int G = sm_count();
@@ -953,16 +991,8 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     int stages = (SMEM_LIMIT - STATIC_SMEM - 2 * RED_FLOATS * 4 - uni) / STAGE_BYTES;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.n_stages = stages;
-    // split of the keys: about one (sequence, kv head, chunk) item per CTA
-    if (len_pages < 1) len_pages = 1;
-    int want = G * (hd == 64 ? 2 : 1) / (T * (max_nkv > 0 ? max_nkv : 1));
-    if (want < 1) want = 1;
-    if (want > MAX_CHUNKS) want = MAX_CHUNKS;
-    if (want > len_pages) want = len_pages;
-    if (want * MAX_CHUNK_PAGES < len_pages) want = (len_pages + MAX_CHUNK_PAGES - 1) / MAX_CHUNK_PAGES;
-    if (want > MAX_CHUNKS) SP_FAIL("decode_layers: %d pages per sequence are more than %d chunks of %d hold", len_pages, MAX_CHUNKS, MAX_CHUNK_PAGES);
-    p.chunk_pages = (len_pages + want - 1) / want;
-    p.n_chunks = (len_pages + p.chunk_pages - 1) / p.chunk_pages;
+    p.plan = plan;
+    if (plan_split(G, T, hd, len_pages, max_nkv, &p.chunk_pages, &p.n_chunks)) return 1;
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;
 
     void* args[] = {(void*)&p};

@@ -221,6 +221,7 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                201: "decode layers: the copy warp waited too long for a free stage of the weight ring",
                202: "decode layers: a consumer warp waited too long for a weight tile",
                203: "decode layers: a CTA waited too long at the grid barrier",
+               204: "decode layers: the split of the keys read from the device is outside what the scratch holds",
                111: "attention: the loader waited too long for a free key/value stage",
                112: "attention: the MMA issuer waited too long for the queries",
                113: "attention: the MMA issuer waited too long for keys and values",
@@ -454,11 +455,12 @@ def decode_layers_encode_map(w: torch.Tensor, pair: int) -> bytes:
 
 
 def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, part_o, part_ml, positions, seq_row, page_table,
-                  page_size, len_pages, max_nkv, max_heads_per_kv, sync):
+                  page_size, len_pages, max_nkv, max_heads_per_kv, sync, plan=None):
     """Every layer of a decode step (one token per sequence, T ≤ 16) on the residual ``x`` [T, H] float32, in place.
 
     ``table``: the layers' descriptors on the device (``decode_layers_desc_bytes()`` each). One cooperative launch;
-    counts as one kernel.
+    counts as one kernel. ``plan`` (two int32 on the device, from ``decode_layers_plan``) overrides the split of
+    the keys that ``len_pages`` would give: a captured launch reads it anew at every replay.
     """
     lib = load("decode_layers")
     _need_contig(x, q, attn, act, page_table)
@@ -468,8 +470,17 @@ def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, par
         c_void_p(_ptr(table)), c_void_p(_ptr(maps)), int(n_layers), int(T), int(H), int(hd), c_void_p(_ptr(x)), c_void_p(_ptr(q)),
         c_void_p(_ptr(attn)), c_void_p(_ptr(act)), c_void_p(_ptr(xw)), c_void_p(_ptr(ssq)), c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)),
         c_void_p(_ptr(positions)), c_void_p(_ptr(seq_row)), c_void_p(_ptr(page_table)), page_table.shape[1],
-        int(page_size), int(len_pages), int(max_nkv), int(max_heads_per_kv), c_void_p(_ptr(sync)),
+        int(page_size), int(len_pages), int(max_nkv), int(max_heads_per_kv),
+        c_void_p(_ptr(plan) if plan is not None else 0), c_void_p(_ptr(sync)),
         c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))
+
+
+def decode_layers_plan(T: int, hd: int, len_pages: int, max_nkv: int) -> tuple:
+    """(pages per chunk, chunks) of the keys for ``T`` sequences of at most ``len_pages`` pages."""
+    lib = load("decode_layers")
+    out = (ctypes.c_int * 2)()
+    _check("decode_layers", lib.sp_decode_layers_plan(int(T), int(hd), int(len_pages), int(max_nkv), out))
+    return int(out[0]), int(out[1])
 
 
 # ------------------------------------------------------------------ weight-streaming tensor-core product (17..128 tokens)

@@ -251,13 +251,20 @@ class Engine:
         """The graph for this decode step, or None when the step runs kernel by kernel."""
         if any(len(t) != 1 for _, t, _ in ents):
             return None
-        from .graph import DecodeGraph, length_bucket
-        key = (len(ents), length_bucket(max(lengths) + 1, self.page_size))
+        from .graph import DecodeGraph, length_bucket, wide_bucket
+        max_len = max(lengths) + 1
+        # where one kernel runs all layers and reads its split of the keys from the device, only the width of the
+        # page tables depends on the length: a few wide buckets instead of one every 512 tokens
+        fused = getattr(self.model, "_fused", None) or None
+        if fused is not None and not fused.takes_sizes(len(ents), wide_bucket(max_len, self.page_size), self.cache):
+            fused = None
+        bucket = wide_bucket(max_len, self.page_size) if fused is not None else length_bucket(max_len, self.page_size)
+        key = (len(ents), bucket, fused is not None)
         g = self._graphs.get(key)
         if g is None:
             seen = self._graph_seen.get(key, 0) + 1
             self._graph_seen[key] = seen
             if seen < 2 or len(self._graphs) >= self.max_graphs:
                 return None                      # the first step of a kind also warms every kernel up
-            g = self._graphs[key] = DecodeGraph(self, *key)
+            g = self._graphs[key] = DecodeGraph(self, key[0], key[1], fused)
         return g

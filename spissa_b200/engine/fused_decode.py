@@ -35,6 +35,7 @@ class FusedDecode:
         self.runs = 0                          # steps run through the kernel so far
         self.cache_id = None
         self.group = None
+        self._splits = {}                      # (sequences, pages) -> the kernel's split of the keys
 
     # ------------------------------------------------------------------ planning
     @classmethod
@@ -69,15 +70,29 @@ class FusedDecode:
         return plan
 
     def takes(self, step, cache) -> bool:
-        if not step.all_single or step.n_tokens > MAX_TOKENS:
+        return step.all_single and self.takes_sizes(step.n_tokens, step.max_len, cache)
+
+    def takes_sizes(self, n_seqs: int, max_len: int, cache) -> bool:
+        """Whether a decode step of ``n_seqs`` sequences, the longest of ``max_len`` tokens, goes through the kernel."""
+        if n_seqs > MAX_TOKENS:
             return False
-        if (step.max_len + cache.page_size - 1) // cache.page_size > K.decode_layers_max_pages():
+        if (max_len + cache.page_size - 1) // cache.page_size > K.decode_layers_max_pages():
             return False
-        if not K.decode_layers_supported(step.n_tokens, self.H, self.hd, cache.page_size, self.max_group):
+        if not K.decode_layers_supported(n_seqs, self.H, self.hd, cache.page_size, self.max_group):
             return False
         if self.cache_id != id(cache):
             self._bind_cache(cache)
         return self.table is not None
+
+    def key_split(self, n_seqs: int, max_len: int, page_size: int) -> tuple:
+        """(pages per chunk, chunks) for a step: what a captured launch reads from the device before it runs."""
+        key = (n_seqs, (max_len + page_size - 1) // page_size)
+        got = self._splits.get(key)
+        if got is None:
+            if len(self._splits) > 4096:
+                self._splits.clear()
+            got = self._splits[key] = K.decode_layers_plan(n_seqs, self.hd, key[1], self.max_nkv)
+        return got
 
     def _bind_cache(self, cache) -> None:
         """The descriptor table for this cache: every entry's pools must lie in one group of full keys."""
@@ -131,4 +146,4 @@ class FusedDecode:
         len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
         K.decode_layers(self.table, self.maps, len(self.fields), step.n_tokens, self.H, self.hd, h, self.q, self.attn, self.act,
                         self.xw, self.ssq, self.part_o, self.part_ml, step.positions, step.seq_row, pt, cache.page_size,
-                        len_pages, self.max_nkv, self.max_group, self.sync)
+                        len_pages, self.max_nkv, self.max_group, self.sync, plan=step.key_split)

@@ -5,6 +5,11 @@ fixes the width of the page tables and the way the decode attention splits the k
 every launch in the graph has fixed arguments. The step's varying data (tokens, positions,
 slots, lengths, page tables) live in static device buffers that are refreshed with one small
 copy before each replay; page tables are copied only when they changed.
+
+Where all layers of the step run as one kernel, that kernel reads its split of the keys from two words
+among the varying data, so nothing in the graph depends on the length but the width of the page tables:
+such graphs are keyed by powers of two (``wide_bucket``) and a sequence that grows from 2,000 to 4,000
+tokens replays one graph all the way instead of capturing a new one every 512 tokens.
 """
 from __future__ import annotations
 
@@ -26,16 +31,27 @@ def length_bucket(max_len: int, page_size: int) -> int:
     return b if max_len <= b else -(-max_len // step) * step
 
 
+def wide_bucket(max_len: int, page_size: int) -> int:
+    """The power of two (at least 4 pages) that holds ``max_len`` tokens."""
+    b = 4 * page_size
+    while b < max_len:
+        b *= 2
+    return b
+
+
 class DecodeGraph:
     RING = 4
 
-    def __init__(self, engine, n_seqs: int, bucket: int):
+    def __init__(self, engine, n_seqs: int, bucket: int, fused=None):
+        """``fused``: the one-kernel decode runner when it takes these steps (the split of the keys is then data)."""
         self.engine, self.B, self.bucket = weakref.proxy(engine), n_seqs, bucket      # no cycle: engines free at once
+        self.fused = fused
         dev = engine.device
         B = n_seqs
         self.P = bucket // engine.page_size
         self.groups = list(engine.cache.kv_groups)
-        self.n_dyn = 5 * B            # tokens, positions, slots, lengths, and where a step's tokens lie in a device tensor
+        # tokens, positions, slots, lengths, where a step's tokens lie in a device tensor, and the split of the keys
+        self.n_dyn = 5 * B + 2
         self.n_tab = B * self.P
         total = self.n_dyn + self.n_tab * len(self.groups)
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
@@ -49,7 +65,7 @@ class DecodeGraph:
             n_tokens=B, n_seqs=B, tokens=self.dev[0:B], positions=self.dev[B:2 * B], token_seq=ar[:B],
             seq_start=ar, seq_slot=self.dev[2 * B:3 * B], seq_row=ar[:B], seq_len=self.dev[3 * B:4 * B],
             want_rows=ar[:B], n_want=B, max_new=1, max_len=bucket, all_single=True, n_q_tiles=B,
-            page_tables=tables, host={})
+            page_tables=tables, host={}, key_split=self.dev[5 * B:5 * B + 2] if fused is not None else None)
         self.last_tables = None
         self.graph = None
         self.logits = None
@@ -63,8 +79,9 @@ class DecodeGraph:
         if self.events[i] is not None:
             self.events[i].synchronize()
         buf = self.pinned[i]
+        split = self.fused.key_split(B, max(positions) + 1, self.engine.page_size) if self.fused is not None else (0, 0)
         dyn = (list(tokens) if tokens is not None else [0] * B) + list(positions) + list(slots) + \
-            [p + 1 for p in positions] + (list(rows) if rows is not None else [0] * B)
+            [p + 1 for p in positions] + (list(rows) if rows is not None else [0] * B) + list(split)
         buf[:self.n_dyn] = torch.tensor(dyn, dtype=torch.int32)
         first = 0 if tokens is not None else B      # leave the token block alone when the device fills it
         flat_tables = [tables[g] for g in self.groups]

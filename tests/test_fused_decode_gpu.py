@@ -141,6 +141,28 @@ def test_long_context_far_key(folders, tmp_path):
             assert err <= allowed, f"sequence {b} step {i}: {err:.3e} (allowed {allowed:.3e})"
 
 
+def test_one_captured_step_serves_growing_lengths(folders):
+    """With CUDA graphs the kernel reads its split of the keys from the device, so one graph per batch size and
+    power-of-two length is replayed while the sequences grow page by page and the split changes under it."""
+    folder, pcfg, w = folders["E"]
+    V = pcfg["vocab_size"]
+    lens = [262, 40]
+    steps = 200                                                      # 262 -> 462 tokens: 5 to 8 pages, one wide bucket
+    seqs = [tiny.random_prompt(V, n + steps, 3 * n + 1) for n in lens]
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 16, use_graphs=True)
+    rows = decode_rows(engine, seqs, lens, steps)
+    fused = engine.model._fused
+    assert fused is not None and fused.runs >= 1
+    assert len({split for (n, pages), split in fused._splits.items() if n == 2}) >= 3, "the split never changed"
+    wide = [k for k in engine._graphs if k[2]]
+    assert len(wide) == 1 and len(engine._graphs) == 1, f"graphs captured: {list(engine._graphs)}"
+    for b, (q, n) in enumerate(zip(seqs, lens)):
+        ref = P.model_logits(pcfg, w, q, torch.float64)
+        scale = float(ref.abs().max())
+        err = float((rows[:, b].double() - ref[n:n + steps]).abs().max()) / scale
+        assert err <= TOL, f"sequence {b}: {err:.3e}"
+
+
 @pytest.mark.parametrize("heads, kv_heads", [(10, 1), (16, 2), (5, 5)])
 def test_head_groups_of_other_sizes(tmp_path, heads, kv_heads):
     """The kernel's attention holds the query heads of a kv head as columns of 8: ten heads per kv head need a

@@ -626,25 +626,34 @@ SP_API int sp_gather_i32(const int* src, const int* idx, int* dst, int n, int n_
 }
 
 // ============================================================== argmax
-// One block per row; the lowest index among equal maxima wins, as a serial scan with
-// a strict ``>`` would choose. NaNs never win.
+// The lowest index among equal maxima wins, as a serial scan with a strict ``>`` would choose. NaNs never
+// win. A row is cut over the CTAs of a thread-block cluster (one CTA for short rows); rank 0 takes the best
+// of the CTAs' finds through distributed shared memory.
+constexpr int ARGMAX_CLUSTER = 8;
+
+__device__ __forceinline__ void argmax_take(float& bv, int& bi, float ov, int oi) {
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
+
+template <int CLUSTER>
 __global__ void argmax_rows_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int ld) {
     __shared__ float sv[32];
     __shared__ int si[32];
-    const float* row = logits + (size_t)blockIdx.x * ld;
+    __shared__ float cta_v;
+    __shared__ int cta_i;
+    unsigned rank = 0;
+    if (CLUSTER > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int row_id = blockIdx.x / CLUSTER;
+    const float* row = logits + (size_t)row_id * ld;
+    const int per = (V + CLUSTER - 1) / CLUSTER;
+    const int i0 = min(V, (int)rank * per), i1 = min(V, i0 + per);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int c = threadIdx.x; c < V; c += blockDim.x) {
-        const float v = row[c];
-        if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
-    }
+    for (int c = i0 + threadIdx.x; c < i1; c += blockDim.x) argmax_take(bv, bi, row[c], c);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
     if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
     __syncthreads();
     if (warp == 0) {
@@ -652,19 +661,42 @@ __global__ void argmax_rows_kernel(const float* __restrict__ logits, int* __rest
         bv = lane < nw ? sv[lane] : -INFINITY;
         bi = lane < nw ? si[lane] : 0x7fffffff;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-        }
-        if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+        for (int o = 16; o > 0; o >>= 1)
+            argmax_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) { cta_v = bv; cta_i = bi; }
     }
+    if (CLUSTER == 1) {
+        if (threadIdx.x == 0) out[row_id] = (bi == 0x7fffffff) ? 0 : bi;
+        return;
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (rank == 0 && threadIdx.x == 0) {
+        bv = -INFINITY;
+        bi = 0x7fffffff;
+        for (unsigned r = 0; r < (unsigned)CLUSTER; ++r) {
+            unsigned av, ai;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(av) : "r"((unsigned)__cvta_generic_to_shared(&cta_v)), "r"(r));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ai) : "r"((unsigned)__cvta_generic_to_shared(&cta_i)), "r"(r));
+            float ov;
+            int oi;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ov) : "r"(av) : "memory");
+            asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(oi) : "r"(ai) : "memory");
+            argmax_take(bv, bi, ov, oi);
+        }
+        out[row_id] = (bi == 0x7fffffff) ? 0 : bi;
+    }
+    // no CTA leaves while rank 0 may still read its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (V <= 0) SP_FAIL("argmax: empty rows");
-    SP_CHECK_CALL("argmax_rows", sp_launch_cluster(argmax_rows_kernel, dim3(rows), dim3(V >= 4096 ? 1024 : 256), 0, stream, 1,
-                                              logits, out, V, ld));
+    if (V >= 16384)
+        SP_CHECK_CALL("argmax_rows", sp_launch_cluster(argmax_rows_kernel<ARGMAX_CLUSTER>, dim3(rows * ARGMAX_CLUSTER), dim3(1024), 0,
+                                                  stream, ARGMAX_CLUSTER, logits, out, V, ld));
+    else
+        SP_CHECK_CALL("argmax_rows", sp_launch_cluster(argmax_rows_kernel<1>, dim3(rows), dim3(V >= 4096 ? 1024 : 256), 0, stream, 1,
+                                                  logits, out, V, ld));
     return 0;
 }

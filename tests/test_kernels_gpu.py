@@ -263,6 +263,78 @@ def test_sampling_follows_the_reference_walk(K, V):
                     assert abs(rank - order.index(want)) <= 1, (V, temp, k, p, r, got[r], want)
 
 
+def test_sampling_row_too_long_for_shared_memory(K):
+    """Above 262,144 tokens a slice of the row no longer fits the shared memory and the passes read the
+    probabilities from the scratch row; above 524,287 the kernel refuses."""
+    V, rows = 270001, 2
+    torch.manual_seed(5)
+    logits = torch.randn(rows, V) * 4
+    scratch = torch.empty(K.sample_scratch_keys(rows, V), dtype=torch.int64, device=DEV)
+    for temp, k, p in [(0.9, 0, 0.9), (1.0, 30, 1.0)]:
+        us = [P.seeded_unit_f32(17 + r) for r in range(rows)]
+        out = torch.empty(rows, dtype=torch.int32, device=DEV)
+        K.sample_rows(logits.to(DEV), temp, k, p, torch.tensor(us, device=DEV), scratch, out)
+        for r in range(rows):
+            order, cum, kept, target, edge = walk64(logits[r], temp, k, p, us[r])
+            rank = order.index(int(out[r]))
+            assert rank <= kept
+            lo = float(cum[rank - 1]) if rank > 0 else 0.0
+            hi = float(cum[min(rank, kept - 1)])
+            slack = 1e-5 * float(cum[kept - 1]) + (edge if p < 1.0 else 0.0)
+            assert lo - slack <= target <= hi + slack, (temp, k, p, r, int(out[r]), lo, target, hi)
+    big = torch.zeros(1, 600000, device=DEV)
+    with pytest.raises(Exception, match="beyond this kernel"):
+        K.sample_rows(big, 1.0, 0, 1.0, torch.zeros(1, device=DEV), torch.empty(300000, dtype=torch.int64, device=DEV),
+                      torch.empty(1, dtype=torch.int32, device=DEV))
+
+
+def test_sampling_ties_and_repeats(K):
+    """Groups of exactly equal probabilities are walked by rising index, and the same draw gives the same token
+    every time (the sums are integers: no order of addition can change them)."""
+    V, rows = 128256, 4
+    torch.manual_seed(11)
+    logits = torch.randn(rows, V)
+    logits[0, :] = -10.0
+    logits[0, 1000:1016] = 10.0                                # 16 equal tokens hold all the mass but 2e-5
+    logits[1] = torch.round(logits[1] * 2) / 2                 # thousands of ties everywhere
+    logits[2, 77] = 40.0                                       # one token holds all of it
+    scratch = torch.empty(K.sample_scratch_keys(rows, V), dtype=torch.int64, device=DEV)
+    dev_logits = logits.to(DEV)
+    for temp, k, p in [(1.0, 0, 0.9), (0.5, 8, 1.0), (1.0, 0, 1.0)]:
+        firsts = None
+        for seed in range(6):
+            us = [P.seeded_unit_f32(seed * 31 + r) for r in range(rows)]
+            u = torch.tensor(us, device=DEV)
+            out = torch.empty(rows, dtype=torch.int32, device=DEV)
+            K.sample_rows(dev_logits, temp, k, p, u, scratch, out)
+            got = out.tolist()
+            for _ in range(3):
+                again = torch.empty(rows, dtype=torch.int32, device=DEV)
+                K.sample_rows(dev_logits, temp, k, p, u, scratch, again)
+                assert again.tolist() == got
+            assert got[2] == 77
+            # row 0: the draw falls into the 16 equal tokens, the u-th of them by index (their mass is ~1)
+            probs = torch.softmax(logits[0].double() / temp, 0)
+            each, rest = float(probs[1000]), float(probs[0])
+            kept = 16 if (k == 0 or k >= 16) else k
+            if p < 1.0 and p <= kept * each:
+                kept = min(kept, int(-(-p // each)))
+            if k == 0 and p == 1.0:
+                want_rank = int(us[0] * 1.0 / each) if us[0] < 16 * each else None
+            else:
+                want_rank = min(kept - 1, int(us[0] * kept))
+            if want_rank is not None and abs(us[0] * kept - round(us[0] * kept)) > 1e-3:
+                assert got[0] == 1000 + want_rank, (temp, k, p, seed, got[0], want_rank)
+            for r in (1, 3):
+                order, cum, kept_r, target, edge = walk64(logits[r], temp, k, p, us[r])
+                rank = order.index(got[r])
+                assert rank <= kept_r
+                lo = float(cum[rank - 1]) if rank > 0 else 0.0
+                hi = float(cum[min(rank, kept_r - 1)])
+                slack = 1e-5 * float(cum[kept_r - 1]) + (edge if p < 1.0 else 0.0)
+                assert lo - slack <= target <= hi + slack, (temp, k, p, seed, r, got[r], lo, target, hi)
+
+
 # ------------------------------------------------------------------ tensor-core attention (bfloat16)
 def flash_prefill_fn(K):
     def fn(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):

@@ -281,6 +281,18 @@ def kernel_case(name: str, reps: int) -> int:
             run = lambda i: K.flash_decode(q, pools[i % n_buf][0], pools[i % n_buf][1], out, meta, seq_len, nh, nkv,
                                            hd, None, scale, ct, nc, scratch)
             bytes_ = B * T * nkv * hd * 2 * 2.0
+    elif name in ("sample_b8", "sample_b64", "argmax_b8"):
+        # the sampler on rows of 128,256 logits (standard deviation 4 after the temperature): temperature 0.8, top-p 0.95
+        B = 64 if name.endswith("b64") else 8
+        logits = [torch.randn(B, V, device=dev) * 3.2 for _ in range(4)]
+        u = torch.rand(B, device=dev)
+        out = torch.empty(B, dtype=torch.int32, device=dev)
+        scratch = torch.empty(K.sample_scratch_keys(B, V), dtype=torch.int64, device=dev)
+        if name.startswith("argmax"):
+            run = lambda i: K.argmax_rows(logits[i % 4], out)
+        else:
+            run = lambda i: K.sample_rows(logits[i % 4], 0.8, 0, 0.95, u, scratch, out)
+        bytes_ = B * V * 4.0
     else:
         print("unknown kernel case", name)
         return 2
@@ -324,7 +336,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|decode_layers|step_b8) instead of the step")
+                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()

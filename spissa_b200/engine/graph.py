@@ -1,6 +1,6 @@
 """CUDA graphs for decode steps: one token per sequence, launch-bound when run kernel by kernel.
 
-A graph is captured per (batch size, length bucket): the bucket (steps of 512 tokens)
+A graph is captured per (batch size, length bucket): the bucket (steps of 512 tokens, wider for long sequences)
 fixes the width of the page tables and the way the decode attention splits the keys, so that
 every launch in the graph has fixed arguments. The step's varying data (tokens, positions,
 slots, lengths, page tables) live in static device buffers that are refreshed with one small
@@ -22,13 +22,19 @@ from .batch import StepBatch
 
 
 def length_bucket(max_len: int, page_size: int) -> int:
-    """Powers of two up to 8 pages, then steps of 8 pages: the bucket fixes how the keys are split, and a
-    split made for a much longer bucket leaves most chunks empty."""
+    """Powers of two up to 8 pages, then steps of 8 pages, steps that double while they are under a sixteenth of
+    the length: the bucket fixes how the keys are split, and a split made for a much longer bucket leaves most
+    chunks empty; a capture costs tens of milliseconds, so it should not come more often than every few hundred
+    steps either."""
     b = 4 * page_size
     while b < max_len and b < 8 * page_size:
         b *= 2
+    if max_len <= b:
+        return b
     step = 8 * page_size
-    return b if max_len <= b else -(-max_len // step) * step
+    while step * 16 < max_len:
+        step *= 2
+    return -(-max_len // step) * step
 
 
 def wide_bucket(max_len: int, page_size: int) -> int:

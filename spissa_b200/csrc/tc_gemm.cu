@@ -114,9 +114,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    // two accumulators, each at a power-of-two column (tensor memory is handed out in powers of two)
+    constexpr uint32_t ACC_STRIDE = BN <= 128 ? 128u : 256u, TMEM_COLS = 2u * ACC_STRIDE;
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_slot)), "r"((uint32_t)(2 * BN)) : "memory");
+                     ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -153,7 +155,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), (use & 1u) ^ 1u, status, 104);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + buf * (uint32_t)BN;
+                const uint32_t tmem_d = tmem_base + buf * ACC_STRIDE;
                 for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
                     const int s = kbc % STAGES;
                     const uint32_t phase = (kbc / STAGES) & 1u;
@@ -183,7 +185,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             tc_fence_after();
             if (!ok || (status && *(volatile int*)status != 0)) break;
             const int row = m0 + q * 32 + lane;
-            const uint32_t taddr = tmem_base + buf * (uint32_t)BN + ((uint32_t)(q * 32) << 16);
+            const uint32_t taddr = tmem_base + buf * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
             constexpr int SPAN = 32;
             const int c_end = (mode == MODE_SILU_MUL) ? BN / 2 : BN;
 #pragma unroll 1
@@ -224,7 +226,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -504,7 +506,8 @@ SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, in
     if (sp_tc_gemm_supported(A, W, K, lda, ldw)) return 1;
     if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_gemm: accumulation needs a float32 C");
     if (mode < 0 || mode > 2) SP_FAIL("tc_gemm: unknown mode %d", mode);
-    if (bn != 128 && bn != 256) SP_FAIL("tc_gemm: tile width %d is not built (128 or 256)", bn);
+    if (bn != 128 && bn != 192 && bn != 256) SP_FAIL("tc_gemm: tile width %d is not built (128, 192 or 256)", bn);
+    if (bn == 192 && pick_splits(M, N, K, bn) > 1) bn = 256;      // the kernel that splits K is built for 128 and 256
     if (mode == MODE_SILU_MUL && (N % bn)) SP_FAIL("tc_gemm: the fused silu epilogue needs N (%d) to be a multiple of the tile width %d", N, bn);
     CUtensorMap ma, mw;
     if (make_map(&ma, A, M, K, lda, BM)) return 1;
@@ -515,5 +518,6 @@ SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, in
         return launch_splitk<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, splits, status, stream);
     }
     if (bn == 128) return launch<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
+    if (bn == 192) return launch<192, 5>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
     return launch<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
 }

@@ -20,9 +20,19 @@ STREAM_TOKENS = 64        # from there up to this many tokens the weight streams
 
 
 def tile_width(M: int, N: int) -> int:
-    """256-wide tiles (half the shared-memory traffic per FLOP) when they still occupy most SMs, else 128-wide."""
-    tiles_256 = ((M + 127) // 128) * ((N + 255) // 256)
-    return 256 if tiles_256 >= (SM_COUNT * 2) // 3 else 128
+    """256-wide tiles (half the shared-memory traffic per FLOP) when they still occupy most SMs, else 128-wide;
+    192-wide when that saves a round of tiles: 2,048 tokens x 3,072 outputs are 192 tiles of 256 columns, two
+    rounds on 148 SMs of which the second is a third full, but 256 tiles of 192 columns, two rounds of shorter tiles."""
+    m_tiles = (M + 127) // 128
+    tiles_256 = m_tiles * ((N + 255) // 256)
+    if tiles_256 < (SM_COUNT * 2) // 3:
+        return 128
+    if M > 128:
+        cost_256 = -(-tiles_256 // SM_COUNT) * 256
+        cost_192 = -(-(m_tiles * ((N + 191) // 192)) // SM_COUNT) * 192
+        if cost_192 * 10 <= cost_256 * 9:
+            return 192
+    return 256
 
 
 class Linear:

@@ -466,7 +466,9 @@ def test_gemv_is_repeatable_and_row_independent(K):
                                        (257, 520, 136, 256), (2048, 3072, 2048, 256), (129, 256, 8, 256),
                                        # one row of tiles and a long K: the cluster splits K
                                        (64, 3072, 2048, 128), (17, 2048, 8192, 128), (128, 200, 1000, 128),
-                                       (100, 130, 520, 256), (33, 2048, 2048, 256)])
+                                       (100, 130, 520, 256), (33, 2048, 2048, 256),
+                                       # 192-wide tiles: whole, ragged in M and N, many tiles per CTA, one row of tiles
+                                       (2048, 3072, 2048, 192), (300, 200, 136, 192), (129, 5120, 72, 192), (64, 3072, 2048, 192)])
 def test_tc_gemm(K, M, N, K_, bn):
     torch.manual_seed(M + N)
     a = torch.randn(M, K_).bfloat16()
@@ -713,7 +715,8 @@ def test_attention_kernels_repeat_bit_for_bit(K, which):
         assert torch.equal(out, first), f"{which}: launch {i + 2} differs from the first"
 
 
-@pytest.mark.parametrize("M,N,K_,bn", [(300, 520, 264, 128), (2048, 512, 2048, 256), (64, 3072, 2048, 128), (17, 2048, 8192, 128)])
+@pytest.mark.parametrize("M,N,K_,bn", [(300, 520, 264, 128), (2048, 512, 2048, 256), (64, 3072, 2048, 128), (17, 2048, 8192, 128),
+                                       (1000, 3072, 264, 192)])
 def test_tc_gemm_repeats_bit_for_bit(K, M, N, K_, bn):
     torch.manual_seed(3)
     a = torch.randn(M, K_).bfloat16().to(DEV)

@@ -19,8 +19,10 @@
 //     each warp a slice of the tile's columns, K permuted alike in both operands so that fragments are plain
 //     16-byte loads), add their slices in warp order through shared memory and run the epilogue: rotate and
 //     store q / write k and v into the cache; add into the 32-bit residual; silu(gate)·up;
-//   * attention runs inside: the keys of every (sequence, kv head) in chunks over the CTAs, two groups of four
-//     warps per CTA with cp.async double buffering, then one warp per (token, head) combines the chunks;
+//   * attention runs inside: the keys of every (sequence, kv head) in chunks over the CTAs (the split comes as
+//     launch arguments or, for a launch replayed from a CUDA graph, as two words on the device), two groups of
+//     four warps per CTA with cp.async double buffering, the keys as the M of mma.sync and the query heads of
+//     the kv head as its N (flash_common.cuh: decode_step_t), then one warp per (token, head) combines the chunks;
 //   * phases that need every CTA's result are separated by a grid barrier (cooperative launch; an atomic
 //     counter; bounded spin).
 // RMSNorm costs no pass of its own: whoever adds into the residual also stores it multiplied by the next norm's

@@ -92,7 +92,8 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
     step late, so a request that stopped may have run one step too many: that step's token is dropped.
     """
     import torch
-    device = engine.device
+    device = torch.device(engine.device)
+    on_gpu = device.type == "cuda"                 # a scripted engine on the CPU drives the same decisions in tests
     done = set()                                   # requests that ended (their slots are released)
     emitted = {req: len(results[req].tokens) for req, _ in live}       # tokens out, counting those still in flight
     token_source = torch.tensor([results[req].tokens[-1] for req, _ in live], dtype=torch.int32).to(device)
@@ -102,7 +103,8 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
 
     def settle(entry):
         rows, pinned, event = entry
-        event.synchronize()
+        if event is not None:
+            event.synchronize()
         for (req, slot), tok in zip(rows, pinned.tolist()):
             if req in done:
                 continue                           # it stopped a step earlier: this token was never asked for
@@ -126,10 +128,12 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
         logits = engine.step_device([slot for _, slot in order], token_source, rows)
         step_no = emitted[order[0][0]]             # every request of a batch has the same count: they started together
         token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
-        pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=True)
+        pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=on_gpu)
         pinned.copy_(token_source, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
+        event = None
+        if on_gpu:
+            event = torch.cuda.Event()
+            event.record()
         for req, _ in order:
             emitted[req] += 1
         in_flight.append((order, pinned, event))

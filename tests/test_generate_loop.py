@@ -171,3 +171,51 @@ def test_sampling_params_are_checked():
     with pytest.raises(ValueError):
         SamplingParams(top_k=-1)
     assert SamplingParams().greedy and not SamplingParams(temperature=0.5).greedy
+
+
+# ------------------------------------------------------------------ decoding one step ahead of the host
+class DeviceFakeEngine(FakeEngine):
+    """A scripted engine that also offers ``step_device``: the step's tokens come from a tensor, as on the GPU."""
+    device = "cpu"
+
+    def step_device(self, slots, token_source, rows):
+        toks = [int(token_source[r]) for r in rows]
+        self.steps.append([(s, [t], [0]) for s, t in zip(slots, toks)])
+        for s in slots:
+            assert s in self.length, "a released slot was stepped"
+            self.length[s] += 1
+        return [(s, t, self.length[s]) for s, t in zip(slots, toks)]
+
+
+class TensorScriptSampler(ScriptSampler):
+    def sample(self, logits, params, requests, step):
+        import torch
+        self.calls.append((list(requests), step))
+        return torch.tensor([self.script[r][step] for r in requests], dtype=torch.int32)
+
+
+def test_one_step_ahead_sees_a_stop_token_late_and_drops_the_extra_token():
+    eng = DeviceFakeEngine(max_seqs=4)
+    # request 0 stops at its third token (99), request 1 runs to the length limit, request 2 stops at once
+    script = {0: [5, 6, 99, 41, 42, 43], 1: [7, 8, 9, 10, 11, 12], 2: [99, 1, 2, 3, 4, 5]}
+    smp = TensorScriptSampler(script)
+    results, metrics = generate(eng, smp, [[1, 2, 3], [4], [5, 6]], 5, SamplingParams(), stop_ids=[99])
+    assert [r.tokens for r in results] == [[5, 6, 99], [7, 8, 9, 10, 11], [99]]
+    assert [r.finish_reason for r in results] == ["stop", "length", "stop"]
+    assert sorted(eng.released) == sorted(eng.acquired) and len(set(eng.released)) == 3 and not eng.length
+    # the prompt step, then decode steps: request 0's stop shows one step late, so it is fed once more (its token 41
+    # is never kept); the length limit is known when a step is queued, so request 1 runs no extra step
+    fed = [[t[0] for _, t, _ in step] for step in eng.steps[1:]]
+    assert fed == [[5, 7], [6, 8], [99, 9], [10]]
+    assert metrics.generated_tokens == 3 + 5 + 1 and metrics.steps == 1 + 4
+    # every draw was asked for with the request's own step number
+    assert smp.calls[0] == ([0, 1, 2], 0) and smp.calls[1] == ([0, 1], 1) and smp.calls[-1] == ([1], 4)
+
+
+def test_one_step_ahead_runs_batches_one_after_another_on_reused_slots():
+    eng = DeviceFakeEngine(max_seqs=2)
+    script = {r: [10 + r, 20 + r, 30 + r] for r in range(5)}
+    results, metrics = generate(eng, TensorScriptSampler(script), [[1]] * 5, 3, SamplingParams(), stop_ids=[])
+    assert [r.tokens for r in results] == [[10 + r, 20 + r, 30 + r] for r in range(5)]
+    assert metrics.batches == 3 and len(eng.acquired) == 5 and sorted(eng.released) == sorted(eng.acquired)
+    assert not eng.length

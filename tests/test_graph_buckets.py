@@ -17,3 +17,15 @@ def test_buckets_hold_their_lengths_and_stay_tight():
     assert len(seen) < 400                      # a capture every few hundred steps at most
     assert length_bucket(2048, page) == 2048 and length_bucket(2049, page) == 2560
     assert wide_bucket(2049, page) == 4096
+
+
+def test_tile_width_of_the_tensor_core_product():
+    """256 columns when the tiles fill most SMs, 128 when they do not, 192 where that saves a round of tiles."""
+    from spissa_b200.parts.linear import tile_width
+    assert tile_width(2048, 16384) == 256          # 1,024 tiles: seven rounds either way
+    assert tile_width(2048, 2048) == 256           # 128 tiles: one round
+    assert tile_width(2048, 3072) == 192           # 192 tiles of 256 columns are two rounds, the second a third full
+    assert tile_width(2048, 5120) == 192
+    assert tile_width(2048, 6144) == 256           # three rounds of 256 against four of 192
+    assert tile_width(300, 3072) == 128            # 36 tiles of 256 columns leave most SMs idle
+    assert tile_width(64, 3072) == 128             # one row of tiles: never 192 (the kernel that splits K has no such tile)

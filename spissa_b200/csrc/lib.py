@@ -68,9 +68,15 @@ def _ptr(t):
 launches = 0          # kernels launched through these bindings since import (bench.py reports the difference)
 
 
+# the current stream's handle without building a Stream object for every launch (a fifth of a launch's host time)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> int:
     global launches
     launches += 1
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

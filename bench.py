@@ -213,7 +213,8 @@ def kernel_case(name: str, reps: int) -> int:
                           "fused_steps": eng.model._fused.runs if eng.model._fused else 0}))
         return 0
     if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
-        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, 256), "gemm_o": (H, H, K.TC_ACCUMULATE, 256),
+        from spissa_b200.parts.linear import tile_width
+        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, tile_width(T, 3072)), "gemm_o": (H, H, K.TC_ACCUMULATE, tile_width(T, H)),
                            "gemm_gate_up": (2 * I, H, K.TC_SILU_MUL, 256),
                            "gemm_down": (H, I, K.TC_ACCUMULATE, 256)}[name]
         n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)

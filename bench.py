@@ -214,7 +214,7 @@ def kernel_case(name: str, reps: int) -> int:
         return 0
     if name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down"):
         from spissa_b200.parts.linear import tile_width
-        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, tile_width(T, 3072)), "gemm_o": (H, H, K.TC_ACCUMULATE, tile_width(T, H)),
+        N, Kd, mode, bn = {"gemm_qkv": (3072, H, K.TC_STORE, tile_width(T, 3072, 148)), "gemm_o": (H, H, K.TC_ACCUMULATE, tile_width(T, H, 148)),
                            "gemm_gate_up": (2 * I, H, K.TC_SILU_MUL, 256),
                            "gemm_down": (H, I, K.TC_ACCUMULATE, 256)}[name]
         n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
@@ -404,11 +404,13 @@ def main() -> int:
                     room -= n
                 if room == 0:
                     break
-            engine.step(ents)
+            engine.step(ents, check=False)
+        engine.check()
         toks = [rng.randrange(V) for _ in range(batch)]
 
         def one():
-            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)])
+            # launched back to back: the steps are confirmed (status word read) by ``engine.check()`` after the timing
+            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)], check=False)
             return sampler.sample(logits, greedy, list(range(batch)), 0)
 
         for _ in range(warmup):
@@ -424,6 +426,7 @@ def main() -> int:
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
         launches = lib.launches - l0
+        engine.check()
         for s in slots:
             engine.release(s)
         return ms, kv_tokens, launches

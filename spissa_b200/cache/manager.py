@@ -11,10 +11,20 @@ same needs form a *group* with storage of its own:
 * a state group owns ``state`` [caches, slots, *shape]; a slot's rows are zeroed when
   the slot is acquired.
 
+* beside them every slot has a small header on the device, ``header`` [slots, 4] int32:
+  position (tokens cached), draws (tokens sampled for the sequence so far), the last
+  sampled token (−1: none) and a spare word. It is zeroed with the slot's state, written
+  by the sampler and read by a decode step that takes its tokens from the device.
+
 The reference keeps one append-only array per layer for its single sequence
 (crates/spissa-runtime/src/rotary.rs:195-318: append checks capacity before it
-changes anything, truncate undoes). Here all lengths live on the host; a step first
-reserves everything it needs and changes nothing if that fails.
+changes anything, truncate undoes; a failed step truncates every layer's cache back,
+crates/spissa-runtime/src/models/llama/session/mod.rs:745-771). Here all lengths live
+on the host. A step is a transaction: ``reserve`` takes every page it needs or changes
+nothing; ``advance`` moves the lengths once the step is launched; ``confirm`` makes that
+final when the device reported no fault, ``rollback`` undoes it (lengths back, pages taken
+by the reservation handed back, fixed-size state and header rows restored from the copy
+that ``checkpoint`` made before the step ran).
 """
 from __future__ import annotations
 
@@ -32,6 +42,33 @@ class SequenceState:
     slot: int
     length: int = 0
     pages: dict = field(default_factory=dict)         # kv group name -> list of pages (None = returned)
+    draws: int = 0                                    # tokens sampled for this sequence (host copy of the header's word)
+
+
+HEADER_WORDS = 4
+HEADER_POSITION, HEADER_DRAWS, HEADER_LAST_TOKEN = 0, 1, 2
+
+
+@dataclass
+class Reservation:
+    """One step's claim on the cache, from ``reserve`` to ``confirm`` or ``rollback``."""
+    counts: list                                      # [(slot, new tokens)]
+    seqs: list                                        # the sequences' records (a slot number may be reused later)
+    tables: dict                                      # kv group name -> per entry the sequence's page list (returned pages as 0)
+    taken: dict                                       # kv group name -> per entry how many pages this reservation added
+    draws: list = field(default_factory=list)         # per entry the sequence's draw counter when the step began
+    after: dict = field(default_factory=dict)         # entry -> the sequence's length once this step is in
+    state: str = "reserved"                           # reserved -> advanced -> confirmed | rolled back
+    checkpointed: bool = False
+
+    def __getitem__(self, group):                     # a reservation reads like its tables
+        return self.tables[group]
+
+    def __iter__(self):
+        return iter(self.tables)
+
+    def items(self):
+        return self.tables.items()
 
 
 class KVGroup:
@@ -58,6 +95,8 @@ class StateGroup:
         self.name, self.request, self.cache_ids = name, request, list(cache_ids)
         shape = (len(self.cache_ids), n_slots) + tuple(request.shape)
         self.state = torch.zeros(shape, dtype=request.dtype, device=device) if allocate else None
+        # the rows as they were before the step in flight: what ``rollback`` puts back
+        self.shadow = torch.zeros(shape, dtype=request.dtype, device=device) if allocate else None
         self.index = {c: i for i, c in enumerate(self.cache_ids)}
 
 
@@ -97,6 +136,11 @@ class CacheManager:
                 raise TypeError(f"unknown cache request {req!r}")
             for c in cids:
                 self.cache_group[c] = name
+        # the per-slot header, on the device beside the state; its shadow serves ``rollback``
+        self.header = None
+        if allocate:
+            self._fresh_header = torch.tensor([0, 0, -1, 0], dtype=torch.int32, device=device)
+            self.header = self._fresh_header.repeat(max_seqs, 1).contiguous()
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:
@@ -105,6 +149,8 @@ class CacheManager:
         for g in self.state_groups.values():
             if g.state is not None:
                 g.state[:, slot].zero_()
+        if self.header is not None:
+            self.header[slot] = self._fresh_header
         return slot
 
     def release(self, slot: int) -> None:
@@ -121,6 +167,9 @@ class CacheManager:
     def length(self, slot: int) -> int:
         return self._seq(slot).length
 
+    def draws(self, slot: int) -> int:
+        return self._seq(slot).draws
+
     def _seq(self, slot: int) -> SequenceState:
         try:
             return self.seqs[slot]
@@ -134,10 +183,10 @@ class CacheManager:
         return min(g.pages.free_count for g in self.kv_groups.values()) * self.page_size
 
     # ------------------------------------------------------------------ a step
-    def reserve(self, slot_counts: list) -> dict:
+    def reserve(self, slot_counts: list) -> Reservation:
         """Take the pages that ``[(slot, new_tokens)]`` need. All or nothing.
 
-        Returns kv group name -> per entry the sequence's page list (returned pages as 0).
+        The reservation's ``tables``: kv group name -> per entry the sequence's page list (returned pages as 0).
         """
         seen = set()
         for slot, n in slot_counts:
@@ -153,34 +202,118 @@ class CacheManager:
             if need > g.pages.free_count:
                 raise CacheFull(f"cache group {g.name}: the step needs {need} more pages of {self.page_size} "
                                 f"tokens, {g.pages.free_count} of {g.n_pages} are free")
-        tables = {}
+        tables, taken = {}, {}
         for g in self.kv_groups.values():
-            rows = []
+            rows, added = [], []
             for s, n in slot_counts:
                 seq = self.seqs[s]
                 have = seq.pages[g.name]
                 want = g.pages_for(seq.length + n)
+                added.append(max(0, want - len(have)))
                 have.extend(g.pages.acquire_many(want - len(have)))
                 rows.append([p if p is not None else 0 for p in have])
             tables[g.name] = rows
-        return tables
+            taken[g.name] = added
+        seqs = [self.seqs[s] for s, _ in slot_counts]
+        return Reservation([(int(s), int(n)) for s, n in slot_counts], seqs, tables, taken, [q.draws for q in seqs])
 
-    def commit(self, slot_counts: list) -> None:
-        """The step ran: lengths grow; windowed groups return pages no key can be read from."""
-        for slot, n in slot_counts:
-            seq = self.seqs[slot]
+    def _live(self, res: Reservation):
+        """The reservation's entries whose sequence still holds its slot (a slot may have been released since)."""
+        for i, ((slot, n), seq) in enumerate(zip(res.counts, res.seqs)):
+            if self.seqs.get(slot) is seq:
+                yield i, seq, n
+
+    def advance(self, res: Reservation) -> None:
+        """The step is launched: lengths grow. Still undoable."""
+        if res.state != "reserved":
+            raise CacheMisuse(f"a reservation that is {res.state} cannot advance")
+        res.after = {}
+        for i, seq, n in self._live(res):
             seq.length += n
+            res.after[i] = seq.length
+        res.state = "advanced"
+
+    def confirm(self, res: Reservation) -> None:
+        """The step ran without a fault: windowed groups return pages no key can be read from any more."""
+        if res.state != "advanced":
+            raise CacheMisuse(f"a reservation that is {res.state} cannot be confirmed")
+        res.state = "confirmed"
+        for i, seq, _n in self._live(res):
+            after = res.after.get(i, seq.length)          # later steps may be in flight: this step's own end counts
             for g in self.kv_groups.values():
                 w = g.request.window
                 if not w:
                     continue
-                # the next query stands at seq.length and sees keys ≥ seq.length - w + 1
-                first_needed = max(0, seq.length - w + 1) // self.page_size
+                # the next query stands at ``after`` and sees keys >= after - w + 1
+                first_needed = max(0, after - w + 1) // self.page_size
                 pages = seq.pages[g.name]
                 for i in range(min(first_needed, len(pages))):
                     if pages[i] is not None:
                         g.pages.release(pages[i])
                         pages[i] = None
+
+    def rollback(self, res: Reservation) -> None:
+        """Undo a reservation that was not confirmed: lengths back, its pages handed back, state and header rows
+        as ``checkpoint`` saved them. Reservations are rolled back in the reverse of the order they were made in."""
+        if res.state not in ("reserved", "advanced"):
+            raise CacheMisuse(f"a reservation that is {res.state} cannot be rolled back")
+        advanced = res.state == "advanced"
+        res.state = "rolled back"
+        restore = []
+        for i, seq, n in self._live(res):
+            if advanced:
+                seq.length -= n
+            for g in self.kv_groups.values():
+                pages = seq.pages[g.name]
+                for _ in range(res.taken[g.name][i]):
+                    p = pages.pop()
+                    if p is not None:
+                        g.pages.release(p)
+            seq.draws = res.draws[i]
+            restore.append(seq)
+        if restore and self.header is not None:
+            # the header from the host's books; the token a rolled-back step led to is forgotten
+            rows = torch.tensor([[q.length, q.draws, -1, 0] for q in restore], dtype=torch.int32)
+            idx = torch.tensor([q.slot for q in restore], dtype=torch.long)
+            self.header.index_copy_(0, idx.to(self.header.device), rows.to(self.header.device))
+            if res.checkpointed:
+                self._copy_state_rows([q.slot for q in restore], back=True)
+
+    def commit(self, res) -> None:
+        """``advance`` and ``confirm`` in one: for a step whose success is known when it returns."""
+        self.advance(res)
+        self.confirm(res)
+
+    # ------------------------------------------------------------------ fixed-size state as part of the transaction
+    def has_state(self) -> bool:
+        return bool(self.state_groups)
+
+    def checkpoint(self, res: Reservation) -> None:
+        """Before the step runs: keep the fixed-size state rows of its sequences, so that ``rollback`` can put them
+        back: state cannot be truncated the way a length can. (Keys and values need none: what a rolled-back step
+        wrote lies beyond the lengths. The header is rewritten from the host's books.) Only one step with a
+        checkpoint can be in flight: the next one would overwrite the copy."""
+        if not any(g.state is not None for g in self.state_groups.values()):
+            return
+        self._copy_state_rows([seq.slot for _, seq, _ in self._live(res)], back=False)
+        res.checkpointed = True
+
+    def _copy_state_rows(self, slots: list, back: bool) -> None:
+        idx = None
+        for g in self.state_groups.values():
+            if g.state is None:
+                continue
+            if idx is None:
+                idx = torch.tensor(slots, dtype=torch.long).to(g.state.device)
+            src, dst = (g.shadow, g.state) if back else (g.state, g.shadow)
+            dst.index_copy_(1, idx, src.index_select(1, idx))
+
+    def note_sampled(self, slots: list) -> None:
+        """The host's copy of the header's draw counter: one more token was sampled for each of ``slots``."""
+        for s in slots:
+            seq = self.seqs.get(s)
+            if seq is not None:
+                seq.draws += 1
 
     # ------------------------------------------------------------------ views
     def view(self, cache_id: int, step, writes: bool):

@@ -341,6 +341,9 @@ int check_common(int hd, int nh, int nkv, int page_size) {
 }  // namespace
 
 // Whether the flash kernels are built for this shape (1) or the generic kernel has to run (0).
+// Query rows per CTA of the prefill kernel (= the page size its key tiles have): the host counts tiles with it.
+SP_API int sp_flash_query_tile() { return KT; }
+
 SP_API int sp_flash_supported(int hd, int nh, int nkv, int page_size) {
     return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && page_size == KT;
 }
@@ -356,13 +359,13 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
     if (hd == 64) {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_prefill_kernel<64>, prefill_smem<64>(), "flash_prefill")) return 1; ok = true; }
+        static SpPerDevice ok;
+        if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<64>, prefill_smem<64>(), "flash_prefill")) return 1; ok.mark(); }
         flash_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
     } else {
-        static bool ok = false;
-        if (!ok) { if (opt_in_smem(flash_prefill_kernel<128>, prefill_smem<128>(), "flash_prefill")) return 1; ok = true; }
+        static SpPerDevice ok;
+        if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<128>, prefill_smem<128>(), "flash_prefill")) return 1; ok.mark(); }
         flash_prefill_kernel<128><<<grid, 128, prefill_smem<128>(), stream>>>(
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
     }
@@ -376,8 +379,8 @@ template <int HD, int NH>
 int launch_flash_decode_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, const PagedKV& kv, const int* seq_len,
                            int nh, int window, float sl, int chunk_tiles, float* part_o, float* part_ml, int* counters,
                            void* out, int out_dt) {
-    static bool ok = false;
-    if (!ok) { if (opt_in_smem(flash_decode_kernel<HD, NH>, decode_smem<HD>(), "flash_decode")) return 1; ok = true; }
+    static SpPerDevice ok;            // the opt-in holds for one device: asked for on each device's first launch
+    if (!ok.done()) { if (opt_in_smem(flash_decode_kernel<HD, NH>, decode_smem<HD>(), "flash_decode")) return 1; ok.mark(); }
     flash_decode_kernel<HD, NH><<<grid, 128, decode_smem<HD>(), stream>>>(q, kv, seq_len, nh, window, sl, chunk_tiles,
                                                                          part_o, part_ml, counters, out, out_dt);
     return 0;

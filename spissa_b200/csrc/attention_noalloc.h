@@ -18,9 +18,14 @@
  * never falls back to allocating.
  *
  * Set-up. The first call on a device looks up the device addresses of the arrays with
- * cudaGetSymbolAddress while that device is current and remembers them for that device; make this
- * first call outside any stream capture. No call allocates or frees anything, through CUDA or any
- * other library.
+ * cudaGetSymbolAddress while that device is current and remembers them for that device. The first
+ * call on a device of each kernel variant (one per head size, 64 or 128, and per number of query
+ * heads per kv head, up to 8 or up to 16) also asks that device for the kernel's shared memory and
+ * loads the kernel. Make these first calls, one per shape you will use on each device, outside any
+ * stream capture. What is remembered is written without a lock: two host threads that make a first
+ * call at the same moment both do the set-up and store the same values, which is harmless, but let
+ * one thread finish its first call where you can. No call allocates or frees anything, through CUDA
+ * or any other library.
  *
  * Sharing. All calls on a device use the same array. A call clears the counters it is going to use
  * (cudaMemsetAsync on its stream) and overwrites the partial results it needs, so what an earlier

@@ -114,3 +114,36 @@ static inline cudaError_t sp_launch_cluster(void (*kern)(KArgs...), dim3 grid, d
         cudaError_t e_ = (call);                                                   \
         if (e_ != cudaSuccess) SP_FAIL("%s: launch failed: %s", name, cudaGetErrorString(e_)); \
     } while (0)
+
+
+// ---------------------------------------------------------------- once per device
+// cudaFuncSetAttribute and the like hold for the device that is current when they are called, so "done once" has
+// to be remembered per device: a bit per device index (devices beyond 63 are set up at every call). Two host threads
+// that make the first call on a device at the same time both do the set-up, with the same values.
+struct SpPerDevice {
+    unsigned long long mask = 0;
+    int device() const {
+        int d = -1;
+        return cudaGetDevice(&d) == cudaSuccess ? d : -1;
+    }
+    bool done() const {
+        const int d = device();
+        return d >= 0 && d < 64 && ((mask >> d) & 1ull);
+    }
+    void mark() {
+        const int d = device();
+        if (d >= 0 && d < 64) mask |= 1ull << d;
+    }
+};
+
+// streaming multiprocessors of the current device (0 when it cannot be read)
+static inline int sp_sm_count() {
+    static int count[64];
+    int d = -1;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0) return 0;
+    if (d < 64 && count[d] > 0) return count[d];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d) != cudaSuccess || n <= 0) return 0;
+    if (d < 64) count[d] = n;
+    return n;
+}

@@ -1,7 +1,7 @@
 // All layers of a decode step (one new token per sequence, up to 16 sequences) in ONE persistent kernel.
 //
-// A layer here is the pre-norm block of the reference (crates/spissa-runtime/src/model.rs: norm → attention
-// → residual, norm → feed-forward → residual; kernels in rotary.rs): RMSNorm, stacked QKV projection,
+// A layer here is the pre-norm block of the reference (crates/spissa-runtime/src/models/llama/generate.rs:190-778: norm → attention
+// → residual, norm → feed-forward → residual; kernels in rotary.rs and ops.rs): RMSNorm, stacked QKV projection,
 // rotate-half position encoding, grouped-query attention over the paged cache, output projection, RMSNorm,
 // gate/up projections with silu(gate)·up, down projection. Which tensors, sizes and constants a layer has
 // comes from a table of descriptors that the host builds from the parts of the model; the kernel knows no
@@ -857,15 +857,7 @@ constexpr int attention_bytes(int st, int groups) {
 }
 constexpr int ATT_BYTES_64 = attention_bytes<64>(2, 2), ATT_BYTES_128 = attention_bytes<128>(2, 1);
 
-int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) n = 0;
-    }
-    return n;
-}
+int sm_count() { return sp_sm_count(); }
 
 unsigned long long* trace_buffer = nullptr;
 
@@ -999,15 +991,15 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
 
     void* args[] = {(void*)&p};
     const void* fn = hd == 64 ? (const void*)decode_layers_kernel<64, 2, 2> : (const void*)decode_layers_kernel<128, 2, 1>;
-    static bool configured[2] = {false, false};
+    static SpPerDevice configured[2];
     const int which = hd == 64 ? 0 : 1;
-    if (!configured[which]) {
+    if (!configured[which].done()) {
         cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - STATIC_SMEM);
         if (e != cudaSuccess) SP_FAIL("decode_layers: cannot reserve shared memory: %s", cudaGetErrorString(e));
         int per_sm = 0;
         e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, THREADS, smem);
         if (e != cudaSuccess || per_sm < 1) SP_FAIL("decode_layers: one CTA of %d bytes does not fit an SM", smem);
-        configured[which] = true;
+        configured[which].mark();
     }
     SP_CHECK_CALL("decode_layers", cudaLaunchCooperativeKernel(fn, dim3(G), dim3(THREADS), args, (size_t)smem, stream));
     return 0;

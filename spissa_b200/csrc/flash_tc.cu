@@ -327,6 +327,9 @@ int make_map(CUtensorMap* map, const void* ptr, long long rows, int cols, long l
 }  // namespace
 
 // Whether this kernel takes the shape (1) or another attention kernel has to run (0).
+// Query rows per CTA: the host counts tiles (the grid) with it.
+SP_API int sp_flash_tc_query_tile() { return QT; }
+
 SP_API int sp_flash_tc_supported(int hd, int nh, int nkv, int page_size, int window) {
     return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && page_size == PAGE && window <= 0;
 }
@@ -348,21 +351,21 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
     if (make_map(&mv, vpool, n_pages * nkv * PAGE, hd, hd, PAGE)) return 1;
     if (n_q_tiles > 65535) SP_FAIL("flash_tc: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
-    static bool configured[2] = {false, false};
+    static SpPerDevice configured[2];
     if (hd == 64) {
-        if (!configured[0]) {
+        if (!configured[0].done()) {
             cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<64>::TOTAL);
             if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
-            configured[0] = true;
+            configured[0].mark();
         }
         flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
             scale * LOG2E, status);
     } else {
-        if (!configured[1]) {
+        if (!configured[1].done()) {
             cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
             if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<128>::TOTAL, cudaGetErrorString(e));
-            configured[1] = true;
+            configured[1].mark();
         }
         flash_prefill_tc_kernel<128><<<grid, 192, Smem<128>::TOTAL, stream>>>(
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,

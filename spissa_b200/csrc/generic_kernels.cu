@@ -14,7 +14,7 @@
 //   attention       crates/spissa-runtime/src/rotary.rs:335-415, :549-569
 //   silu            crates/spissa-runtime/src/ops.rs:192-194
 //   argmax          crates/spissa-runtime/src/ops.rs:309-324  (first maximum wins)
-#include "common.cuh"
+#include "async_copy.cuh"
 
 SP_API const char* sp_generic_last_error() { return sp_error_text; }
 
@@ -26,7 +26,7 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
     if (t >= T) return;
     const int id = ids[t];
     const bool ok = (id >= 0 && id < V);
-    if (!ok && threadIdx.x == 0 && status) atomicExch(status, 1);
+    if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0, 301);     // a token id outside the table
     for (int c = threadIdx.x; c < H; c += blockDim.x)
         out[(size_t)t * H + c] = ok ? sp_ld(table, (size_t)id * H + c) : 0.0f;
 }
@@ -698,5 +698,58 @@ SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld
     else
         SP_CHECK_CALL("argmax_rows", sp_launch_cluster(argmax_rows_kernel<1>, dim3(rows), dim3(V >= 4096 ? 1024 : 256), 0, stream, 1,
                                                   logits, out, V, ld));
+    return 0;
+}
+
+
+// ============================================================== the per-slot header
+// header [slots, 4] int32: position (tokens cached), draws (tokens sampled so far), last sampled token, spare.
+// After a step's logits were turned into tokens: sequence b of the step sits in slot seq_slot[b] and is
+// seq_len[b] tokens long now. A slot outside the header is skipped.
+__global__ void header_note_kernel(int* __restrict__ header, int n_slots, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ seq_len, const int* __restrict__ tokens, int n) {
+    const int b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n) return;
+    const int slot = seq_slot[b];
+    if (slot < 0 || slot >= n_slots) return;
+    int* h = header + (size_t)slot * 4;
+    h[0] = seq_len[b];
+    h[1] += 1;
+    h[2] = tokens[b];
+}
+
+SP_API int sp_header_note(int* header, int n_slots, const int* seq_slot, const int* seq_len, const int* tokens, int n,
+                          cudaStream_t stream) {
+    if (n <= 0) return 0;
+    header_note_kernel<<<(n + 127) / 128, 128, 0, stream>>>(header, n_slots, seq_slot, seq_len, tokens, n);
+    SP_CHECK_LAUNCH("header_note");
+    return 0;
+}
+
+// ============================================================== a wait that runs out (for tests of the fault path)
+// One thread waits on a shared-memory barrier on which nobody ever arrives, with the same bounded wait that the
+// tensor-core kernels use but a limit the caller gives (at most 10 ms). When the limit is reached the wait gives
+// up, records ``code`` in ``status`` and the kernel returns: the way every kernel of this library ends a wait that
+// does not complete. Nothing faults, traps or spins beyond the limit.
+__global__ void wait_runs_out_kernel(int* status, int code, unsigned long long limit_ns, unsigned long long* waited_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    const unsigned long long t0 = global_ns();
+    bool done = false;
+    while (!(done = mbar_try_wait(smem_u32(&bar), 0))) {
+        if (global_ns() - t0 > limit_ns) {
+            if (status) atomicCAS(status, 0, code);
+            break;
+        }
+    }
+    if (waited_ns) *waited_ns = done ? 0ull : global_ns() - t0;
+}
+
+SP_API int sp_wait_runs_out(int* status, int code, long long limit_us, unsigned long long* waited_ns, cudaStream_t stream) {
+    if (limit_us < 1 || limit_us > 10000) SP_FAIL("wait_runs_out: the limit is 1 to 10000 microseconds, got %lld", limit_us);
+    if (code <= 0) SP_FAIL("wait_runs_out: the code to record must be positive");
+    wait_runs_out_kernel<<<1, 1, 0, stream>>>(status, code, (unsigned long long)limit_us * 1000ull, waited_ns);
+    SP_CHECK_LAUNCH("wait_runs_out");
     return 0;
 }

@@ -185,6 +185,27 @@ def gather_i32(src, idx, dst):
                                         src.numel(), c_void_p(_stream())))
 
 
+def header_note(header, seq_slot, seq_len, tokens):
+    """header[seq_slot[b]] = (seq_len[b], draws + 1, tokens[b], .) for every sequence b of a step."""
+    lib = load("generic")
+    _need_contig(header, seq_slot, seq_len, tokens)
+    if any(t.dtype != torch.int32 for t in (header, seq_slot, seq_len, tokens)) or header.dim() != 2 or header.shape[1] != 4:
+        raise KernelError("header_note takes int32 tensors and a header of four words per slot")
+    n = tokens.numel()
+    if seq_slot.numel() < n or seq_len.numel() < n:
+        raise KernelError("header_note needs a slot and a length for every token")
+    _check("generic", lib.sp_header_note(c_void_p(_ptr(header)), header.shape[0], c_void_p(_ptr(seq_slot)),
+                                         c_void_p(_ptr(seq_len)), c_void_p(_ptr(tokens)), n, c_void_p(_stream())))
+
+
+def wait_runs_out(device, code: int, limit_us: int, waited_ns=None):
+    """Launch a kernel whose only wait, on a barrier nobody arrives on, gives up after ``limit_us`` microseconds and
+    records ``code`` in the device's status word: how a bounded wait ends, for tests of the fault path."""
+    lib = load("generic")
+    _check("generic", lib.sp_wait_runs_out(c_void_p(_ptr(status_word(device))), int(code), c_longlong(int(limit_us)),
+                                           c_void_p(_ptr(waited_ns)), c_void_p(_stream())))
+
+
 def argmax_rows(logits, out):
     """out[r] = index of the first maximum of logits[r,:] (float32)."""
     lib = load("generic")
@@ -234,7 +255,9 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                114: "attention: the MMA issuer waited too long for the probabilities",
                115: "attention: the softmax warps waited too long for the scores",
                116: "attention: the softmax warps waited too long for the previous block's output",
-               117: "attention: the softmax warps waited too long for the last block's output"}
+               117: "attention: the softmax warps waited too long for the last block's output",
+               301: "embedding: a token id outside the vocabulary",
+               900: "a wait that was meant to run out (test of the fault path)"}
 
 
 def status_word(device) -> torch.Tensor:
@@ -295,13 +318,28 @@ def flash_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd
     """Whether the tensor-core attention kernels take this shape; else the generic kernel runs."""
     if q.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16:
         return False
-    return hd in (64, 128) and nkv > 0 and nh % nkv == 0 and nh // nkv <= 16 and page_size == 64
+    return bool(load("attention").sp_flash_supported(int(hd), int(nh), int(nkv), int(page_size)))
+
+
+def flash_query_tile() -> int:
+    """Query rows per CTA of ``flash_prefill``: a step has sum over sequences of ceil(new tokens / this) tiles."""
+    return int(load("attention").sp_flash_query_tile())
+
+
+def flash_tc_query_tile() -> int:
+    """The same for ``flash_prefill_tc``."""
+    return int(load("flash_tc").sp_flash_tc_query_tile())
+
+
+def query_tiles(new_counts, tile: int) -> int:
+    return sum((int(n) + tile - 1) // tile for n in new_counts)
 
 
 def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
     """Causal attention of a step's tokens (any number per sequence) over the paged cache.
 
-    ``seq_start`` [B+1] int32 on the device; ``n_q_tiles`` = sum over sequences of ceil(new tokens / 64).
+    ``seq_start`` [B+1] int32 on the device; ``n_q_tiles`` = sum over sequences of ceil(new tokens /
+    ``flash_query_tile()``).
     """
     lib = load("attention")
     _need_contig(q, out)
@@ -408,14 +446,14 @@ def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
 # ------------------------------------------------------------------ prefill attention on tcgen05
 def flash_tc_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int, window) -> bool:
     """Whether the tcgen05 prefill attention takes this shape (head 64 or 128, pages of 64, no window, bfloat16)."""
-    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and hd in (64, 128) and nkv > 0 and nh % nkv == 0
-            and page_size == 64 and not window and k_pool.is_contiguous())
+    return (q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and k_pool.is_contiguous()
+            and bool(load("flash_tc").sp_flash_tc_supported(int(hd), int(nh), int(nkv), int(page_size), int(window or 0))))
 
 
 def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh, nkv, hd, window, scale):
     """Causal attention of a step's tokens over the paged cache on the tcgen05 tensor cores.
 
-    ``n_q_tiles`` = sum over sequences of ceil(new tokens / 128). S, P and O live in tensor memory.
+    ``n_q_tiles`` = sum over sequences of ceil(new tokens / ``flash_tc_query_tile()``). S, P and O live in tensor memory.
     """
     lib = load("flash_tc")
     _need_contig(q, out, k_pool, v_pool)

@@ -288,15 +288,15 @@ SP_API int sp_sample_rows(const float* logits, int ld, int rows, int V, float te
         SP_FAIL("sample: scratch holds %lld words, %lld are needed", scratch_keys, sp_sample_scratch_keys(rows, V));
     const int cached = fits ? per : 0;
     const size_t cache_bytes = fits ? (((size_t)per * 4 + 15) / 16) * 16 : 0;
-    static bool configured = false;
-    if (!configured) {
+    static SpPerDevice configured;
+    if (!configured.done()) {
         cudaError_t e = cudaFuncSetAttribute(sample_rows_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              SS_CACHE_BYTES + SS_SEGS * 256 * 8);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(sample_rows_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      SS_CACHE_BYTES / 2 + SS_SEGS * 1024 * 8);
         if (e != cudaSuccess) SP_FAIL("sample: cannot reserve shared memory: %s", cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     // few rows: 1,024 threads per CTA (one CTA per SM, a quarter of the tokens per thread); many rows: 256, several CTAs per SM
     if (rows * SS_CLUSTER <= 128 && cache_bytes <= SS_CACHE_BYTES / 2)

@@ -439,19 +439,14 @@ template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc, int mode,
            int* status, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
-    static bool configured = false;
-    if (!configured) {
+    static SpPerDevice configured;
+    if (!configured.done()) {
         cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
-    static int sm_count = 0;
-    if (!sm_count) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sm_count <= 0)
-            sm_count = 148;
-    }
+    const int sm_count = sp_sm_count();
+    if (sm_count <= 0) SP_FAIL("tc_gemm: cannot read the number of SMs");
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status);
@@ -463,11 +458,11 @@ template <int BN, int STAGES>
 int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc,
                   int mode, int splits, int* status, cudaStream_t stream) {
     using L = SmemLayout<BN, STAGES>;
-    static bool configured = false;
-    if (!configured) {
+    static SpPerDevice configured;
+    if (!configured.done()) {
         cudaError_t e = cudaFuncSetAttribute(tc_gemm_splitk_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     const int n_tiles = (N + BN - 1) / BN;
     SP_CHECK_CALL("tc_gemm_splitk", sp_launch_cluster(tc_gemm_splitk_kernel<BN, STAGES>, dim3(n_tiles * splits), dim3(192),

@@ -240,23 +240,18 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 }
 
 int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
+    const int n = sp_sm_count();
+    return n > 0 ? n : 1;
 }
 
 template <int NT, bool GATED>
 int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Args& args, int tiles, cudaStream_t stream) {
     using L = Layout<NT, GATED>;
-    static bool configured = false;
-    if (!configured) {
+    static SpPerDevice configured;
+    if (!configured.done()) {
         cudaError_t e = cudaFuncSetAttribute(tc_stream_kernel<NT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         if (e != cudaSuccess) SP_FAIL("tc_stream: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
-        configured = true;
+        configured.mark();
     }
     SP_CHECK_CALL("tc_stream", sp_launch_cluster(tc_stream_kernel<NT, GATED>, dim3(tiles * args.pieces), dim3(192),
                                                  (size_t)L::TOTAL, stream, args.pieces, mw, ma, args));

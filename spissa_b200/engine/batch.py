@@ -29,7 +29,6 @@ class StepBatch:
     max_new: int                    # most tokens any sequence brings
     max_len: int                    # longest sequence after this step
     all_single: bool                # every sequence brings exactly one token (a decode step)
-    n_q_tiles: int = 0              # sum over sequences of ceil(new tokens / 64): grid of the prefill attention
     page_tables: dict = field(default_factory=dict)   # kv group name -> int32 [B, P] device tensor
     host: dict = field(default_factory=dict)          # the same arrays as Python lists, for host logic
     h2d_bytes: int = 0              # bytes this step's arrays took on their way to the device
@@ -85,7 +84,6 @@ def pack_step(entries, lengths_before, kv_tables: dict, device, pinned: bool = T
         n_tokens=T, n_seqs=B, tokens=views[0], positions=views[1], token_seq=views[2], seq_start=views[3],
         seq_slot=views[4], seq_row=views[5], seq_len=views[6], want_rows=views[7], n_want=W,
         max_new=max(new_counts), max_len=max(seq_len), all_single=all(c == 1 for c in new_counts),
-        n_q_tiles=sum((c + 63) // 64 for c in new_counts),
         page_tables=page_tables, h2d_bytes=total * 4,
         host=dict(seq_start=seq_start, seq_len=seq_len, new_counts=new_counts, seq_slot=seq_slot,
                   want_rows=want_rows),

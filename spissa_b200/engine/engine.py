@@ -17,6 +17,7 @@ from pathlib import Path
 import torch
 
 from ..cache import CacheManager
+from ..cache.manager import HEADER_LAST_TOKEN, HEADER_WORDS
 from ..config import load_config
 from ..csrc import lib as K
 from ..csrc.lib import KernelError
@@ -38,6 +39,21 @@ class StepEntry:
     slot: int
     tokens: list
     want: list
+
+
+@dataclass
+class StepNote:
+    """What a sampler needs to note its tokens in the headers of the last step's sequences: ``header`` [slots, 4]
+    int32 on the device, and the step's own arrays ``seq_slot`` / ``seq_len`` [B] (row b of the logits is sequence
+    b). ``done()`` keeps the host's draw counters in step."""
+    cache: object
+    header: torch.Tensor
+    slots: list
+    seq_slot: torch.Tensor
+    seq_len: torch.Tensor
+
+    def done(self) -> None:
+        self.cache.note_sampled(self.slots)
 
 
 def _require_gpu(device) -> torch.device:
@@ -73,9 +89,13 @@ class Engine:
         self.h2d_bytes = 0            # bytes of step arrays copied to the device so far
         # decode steps replay CUDA graphs once a (batch size, length bucket) has been seen before
         self.use_graphs = use_graphs and self.model.graph_safe()
-        self._graphs: dict = {}
-        self._graph_seen: dict = {}
+        from .graph import GraphTable
         self.max_graphs = 24
+        self._graphs = GraphTable(self.max_graphs)
+        # steps launched but not yet confirmed: [(reservation, pinned copy of the status word, event)] oldest first
+        self._pending: list = []
+        self._status_host: list = []
+        self._last_step = None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -130,23 +150,19 @@ class Engine:
             self._sampler = Sampler(self.device)
         if stop_ids is None:
             stop_ids = self.config.stop_token_ids() if hasattr(self.config, "stop_token_ids") else []
-        from ..csrc.lib import check_status
         with torch.cuda.device(self.device):
-            out = run(self, self._sampler, [list(p) for p in prompts], max_new_tokens,
-                      sampling or SamplingParams(), stop_ids, max_batch, on_token, return_logits)
-            check_status(self.device)
+            try:
+                out = run(self, self._sampler, [list(p) for p in prompts], max_new_tokens,
+                          sampling or SamplingParams(), stop_ids, max_batch, on_token, return_logits)
+            except BaseException:
+                self._abandon()
+                raise
+            self.check()
             return out
 
-    # ------------------------------------------------------------------ the step
-    def step(self, entries) -> torch.Tensor:
-        """Run the given tokens; return logits [number of wanted places, vocab] as float32 on the device.
-
-        ``entries``: ``StepEntry`` objects or (slot, tokens, want) tuples. ``want`` holds indices into
-        that entry's ``tokens``. Rows come back in the order of the entries and of their ``want``.
-        Everything is checked before anything runs; a refused step leaves the cache as it was.
-        """
-        ents = [(e.slot, list(e.tokens), list(e.want)) if isinstance(e, StepEntry)
-                else (e[0], list(e[1]), list(e[2])) for e in entries]
+    # ------------------------------------------------------------------ the step as a transaction
+    def _validate(self, ents) -> tuple:
+        """Everything that can be refused is refused here, before anything runs. Returns (lengths, packed tokens)."""
         if not ents:
             raise StepError("a step needs at least one sequence")
         lengths = []
@@ -172,46 +188,172 @@ class Engine:
             for w in want:
                 if not (0 <= int(w) < len(toks)):
                     raise StepError(f"slot {slot}: wanted place {w} is outside the {len(toks)} tokens given")
-            lengths.append(self.cache.length(slot))
+            before = self.cache.length(slot)
+            self._check_position(slot, before, len(toks))
+            lengths.append(before)
+        return lengths, packed
+
+    def _check_position(self, slot: int, before: int, new: int) -> None:
+        # the reference refuses a turn that would pass max_seq_len before anything runs
+        # (crates/spissa-runtime/src/session.rs:307-320)
+        if self.max_position and before + new > self.max_position:
+            raise StepError(f"slot {slot}: {before} cached + {new} new tokens pass the model's "
+                            f"{self.max_position} positions")
+
+    def _begin(self, counts):
+        """Reserve the step's pages (all or nothing). Models with fixed-size state keep one step in flight at most:
+        its rows are copied aside first, so that a fault can put them back."""
+        self._settle(wait=False)
+        if self.cache.has_state():
+            self._settle(wait=True)
+        res = self.cache.reserve(counts)
+        if self.cache.has_state():
+            self.cache.checkpoint(res)
+        return res
+
+    def _launched(self, res, step_arrays) -> None:
+        """The step's kernels are queued: lengths move on, and the status word is asked for behind them."""
+        self.cache.advance(res)
+        self._last_step = ([s for s, _ in res.counts], step_arrays[0], step_arrays[1])
+        host = self._status_host.pop() if self._status_host else torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        host.copy_(K.status_word(self.device), non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        self._pending.append((res, host, event))
+        self.steps_run += 1
+
+    def _settle(self, wait: bool) -> None:
+        """Confirm the steps in flight whose status has arrived (``wait``: all of them), oldest first. The first one
+        whose status word is not zero ends it: that step and every later one are rolled back and ``KernelError`` is
+        raised; the engine goes on from the last confirmed state."""
+        while self._pending:
+            res, host, event = self._pending[0]
+            if not wait and not event.query():
+                return
+            event.synchronize()
+            code = int(host[0])
+            if code:
+                self._fail(code)
+            self.cache.confirm(res)
+            self._pending.pop(0)
+            self._status_host.append(host)
+
+    def _fail(self, code: int) -> None:
+        torch.cuda.synchronize(self.device)
+        for res, host, _ in reversed(self._pending):
+            self.cache.rollback(res)
+            self._status_host.append(host)
+        self._pending.clear()
+        K.status_word(self.device).zero_()
+        raise KernelError(f"a kernel of a step reported a fault (code {code}: {K.STATUS_TEXT.get(code, 'unknown')}); "
+                          f"the step and those launched after it were rolled back")
+
+    def _abandon(self) -> None:
+        """After an error that left steps in flight whose slots were given back: forget them (nothing to roll back
+        for a released sequence) and clear the status word, so that the engine can go on."""
+        torch.cuda.synchronize(self.device)
+        for res, host, _ in reversed(self._pending):
+            if res.state in ("reserved", "advanced"):
+                self.cache.rollback(res)
+            self._status_host.append(host)
+        self._pending.clear()
+        K.status_word(self.device).zero_()
+
+    def check(self) -> None:
+        """Wait for every step launched so far and confirm it, or roll back and raise ``KernelError``. ``step`` does
+        this by itself unless called with ``check=False``; ``step_device`` never does, its caller settles a step when
+        it reads the step's tokens."""
+        with torch.cuda.device(self.device):
+            self._settle(wait=True)
+            K.check_status(self.device)
+
+    def settle(self, wait: bool = False) -> None:
+        """Confirm the steps whose status has arrived; raises like ``check`` when one of them failed."""
+        with torch.cuda.device(self.device):
+            self._settle(wait)
+
+    def step_note(self):
+        """Where the sampler notes the tokens it chooses for the sequences of the last step: the per-slot header
+        (position, draws, last token) on the device. ``step_device`` called without a token source reads them there."""
+        if self._last_step is None or self.cache.header is None:
+            return None
+        slots, seq_slot, seq_len = self._last_step
+        return StepNote(self.cache, self.cache.header, slots, seq_slot, seq_len)
+
+    def step(self, entries, check: bool = True) -> torch.Tensor:
+        """Run the given tokens; return logits [number of wanted places, vocab] as float32 on the device.
+
+        ``entries``: ``StepEntry`` objects or (slot, tokens, want) tuples. ``want`` holds indices into
+        that entry's ``tokens``. Rows come back in the order of the entries and of their ``want``.
+        Everything is checked before anything runs; a refused step leaves the cache as it was.
+
+        The step is a transaction. With ``check`` (the default) it waits for the device's status word and
+        confirms the new lengths only when no kernel reported a fault; otherwise the lengths stay, the pages it took
+        go back, fixed-size state is restored and ``KernelError`` is raised: the next step runs as if this one had
+        never been asked for. ``check=False`` returns without waiting; such steps are settled by the next checked
+        step, by ``check()`` or ``settle()``, and until then ``length`` counts them.
+        """
+        ents = [(e.slot, list(e.tokens), list(e.want)) if isinstance(e, StepEntry)
+                else (e[0], list(e[1]), list(e[2])) for e in entries]
+        lengths, packed = self._validate(ents)
         counts = [(slot, len(toks)) for slot, toks, _ in ents]
         with torch.cuda.device(self.device):
-            tables = self.cache.reserve(counts)
-            graph = self._decode_graph(ents, lengths) if self.use_graphs else None
-            full = None
-            if graph is not None:
-                try:
-                    full = graph.run([t[0] for _, t, _ in ents], lengths, [s for s, _, _ in ents], tables)
-                except (RuntimeError, KernelError) as e:
-                    if graph.graph is not None:
-                        raise                        # a replay failed: that is a real fault
-                    # the capture itself was refused: run this and all later steps kernel by kernel
-                    print(f"[spissa_b200] CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
-                          f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
-                    self.use_graphs = False
-                    self._graphs.clear()
-            if full is not None:
-                if all(len(w) == 1 for _, _, w in ents):
-                    logits = full.clone()        # the graph's own tensor is overwritten by the next replay
+            res = self._begin(counts)
+            try:
+                tables = res.tables
+                graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+                full = None
+                if graph is not None:
+                    try:
+                        full = graph.run([t[0] for _, t, _ in ents], lengths, [s for s, _, _ in ents], tables)
+                    except (RuntimeError, KernelError) as e:
+                        if graph.graph is not None:
+                            raise                        # a replay failed: that is a real fault
+                        self._capture_refused(e)
+                if full is not None:
+                    arrays = (graph.batch.seq_slot, graph.batch.seq_len)
+                    if all(len(w) == 1 for _, _, w in ents):
+                        logits = full.clone()        # the graph's own tensor is overwritten by the next replay
+                    else:
+                        rows = [b for b, (_, _, w) in enumerate(ents) for _ in w]
+                        logits = full[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else full[:0]
                 else:
-                    rows = [b for b, (_, _, w) in enumerate(ents) for _ in w]
-                    logits = full[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else full[:0]
-            else:
-                batch = pack_step([(sl, packed.get(i, tk), w) for i, (sl, tk, w) in enumerate(ents)], lengths, tables,
-                                  self.device)
-                self.h2d_bytes += batch.h2d_bytes
-                logits = self.model.forward(batch, self.cache)
-        self.cache.commit(counts)
-        self.steps_run += 1
+                    batch = pack_step([(sl, packed.get(i, tk), w) for i, (sl, tk, w) in enumerate(ents)], lengths,
+                                      tables, self.device)
+                    self.h2d_bytes += batch.h2d_bytes
+                    logits = self.model.forward(batch, self.cache)
+                    arrays = (batch.seq_slot, batch.seq_len)
+            except BaseException:
+                self.cache.rollback(res)
+                raise
+            self._launched(res, arrays)
+            if check:
+                self._settle(wait=True)
         return logits
 
-    def step_device(self, slots, token_source: torch.Tensor, rows) -> torch.Tensor:
-        """A decode step whose tokens are already on the device: sequence i takes ``token_source[rows[i]]``
-        (int32, for instance the sampler's output of the step before), so the host never waits for them.
+    def _capture_refused(self, e) -> None:
+        # the capture itself was refused: run this and all later steps kernel by kernel
+        print(f"[spissa_b200] CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
+              f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
+        self.use_graphs = False
+        self._graphs.clear()
+
+    def step_device(self, slots, token_source: torch.Tensor | None = None, rows=None) -> torch.Tensor:
+        """A decode step whose tokens are already on the device, so the host never waits for them: sequence i takes
+        ``token_source[rows[i]]`` (int32, for instance the sampler's output of the step before) or, without a token
+        source, the last token that the sampler noted in the sequence's header (see ``step_note``).
 
         Returns logits [len(slots), vocab] (float32); the tensor may be the step's own buffer and holds only
-        until the next step. Token ids are not checked on the host: they come from this library's sampler.
+        until the next step. Token ids are not checked on the host (they come from this library's sampler); one
+        outside the vocabulary makes the embedding report a fault. The step is not settled here: call ``settle``
+        or ``check`` (the generation loop does when it reads a step's tokens).
         """
         slots = [int(s) for s in slots]
+        if token_source is None:
+            if self.cache.header is None:
+                raise StepError("this cache has no header on the device to take tokens from")
+            token_source = self.cache.header.view(-1)
+            rows = [s * HEADER_WORDS + HEADER_LAST_TOKEN for s in slots]
         rows = [int(r) for r in rows]
         if not slots or len(rows) != len(slots):
             raise StepError("a step needs at least one sequence and one token row for each")
@@ -220,31 +362,36 @@ class Engine:
         if any(not (0 <= r < token_source.numel()) for r in rows):
             raise StepError("a token row lies outside the token source")
         lengths = [self.cache.length(s) for s in slots]
+        for s, before in zip(slots, lengths):
+            self._check_position(s, before, 1)
         counts = [(s, 1) for s in slots]
         ents = [(s, [0], [0]) for s in slots]
         with torch.cuda.device(self.device):
-            tables = self.cache.reserve(counts)
-            graph = self._decode_graph(ents, lengths) if self.use_graphs else None
-            logits = None
-            if graph is not None:
-                try:
-                    logits = graph.run(None, lengths, slots, tables, token_source, rows)
-                except (RuntimeError, KernelError) as e:
-                    if graph.graph is not None:
-                        raise                        # a replay failed: that is a real fault
-                    print(f"[spissa_b200] CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
-                          f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
-                    self.use_graphs = False
-                    self._graphs.clear()
-            if logits is None:
-                # kernel by kernel: the packed arrays, with the tokens filled in on the device
-                batch = pack_step(ents, lengths, tables, self.device)
-                self.h2d_bytes += batch.h2d_bytes
-                idx = torch.tensor(rows, dtype=torch.int32).to(self.device)
-                K.gather_i32(token_source, idx, batch.tokens)
-                logits = self.model.forward(batch, self.cache)
-        self.cache.commit(counts)
-        self.steps_run += 1
+            res = self._begin(counts)
+            try:
+                tables = res.tables
+                graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+                logits = None
+                if graph is not None:
+                    try:
+                        logits = graph.run(None, lengths, slots, tables, token_source, rows)
+                        arrays = (graph.batch.seq_slot, graph.batch.seq_len)
+                    except (RuntimeError, KernelError) as e:
+                        if graph.graph is not None:
+                            raise                        # a replay failed: that is a real fault
+                        self._capture_refused(e)
+                if logits is None:
+                    # kernel by kernel: the packed arrays, with the tokens filled in on the device
+                    batch = pack_step(ents, lengths, tables, self.device)
+                    self.h2d_bytes += batch.h2d_bytes
+                    idx = torch.tensor(rows, dtype=torch.int32).to(self.device)
+                    K.gather_i32(token_source, idx, batch.tokens)
+                    logits = self.model.forward(batch, self.cache)
+                    arrays = (batch.seq_slot, batch.seq_len)
+            except BaseException:
+                self.cache.rollback(res)
+                raise
+            self._launched(res, arrays)
         return logits
 
     def _decode_graph(self, ents, lengths):
@@ -262,9 +409,9 @@ class Engine:
         key = (len(ents), bucket, fused is not None)
         g = self._graphs.get(key)
         if g is None:
-            seen = self._graph_seen.get(key, 0) + 1
-            self._graph_seen[key] = seen
-            if seen < 2 or len(self._graphs) >= self.max_graphs:
+            if not self._graphs.wants_capture(key):
                 return None                      # the first step of a kind also warms every kernel up
-            g = self._graphs[key] = DecodeGraph(self, key[0], key[1], fused)
+            # an evicted graph's buffers go back to the allocator only when no replay of it is in flight any more
+            g = self._graphs.put(key, DecodeGraph(self, key[0], key[1], fused),
+                                 before_evict=lambda old: torch.cuda.synchronize(self.device))
         return g

@@ -100,11 +100,18 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
     order = list(live)                             # row i of token_source belongs to order[i]
     in_flight = []                                 # [(order, pinned tokens, event)] oldest first
     steps = 0
+    engine_settles = hasattr(engine, "settle")
+    # an engine with per-slot headers on the device: the sampler notes its tokens there and a step takes them from
+    # there by slot; otherwise a step takes them from the tensor that the sampler returned, by row
+    headers = hasattr(engine, "step_note") and engine.step_note() is not None
 
     def settle(entry):
         rows, pinned, event = entry
         if event is not None:
             event.synchronize()
+        if engine_settles:
+            engine.settle()                        # the step's status word arrived before its tokens: confirm it, or
+                                                   # roll it and the one in flight back and raise
         for (req, slot), tok in zip(rows, pinned.tolist()):
             if req in done:
                 continue                           # it stopped a step earlier: this token was never asked for
@@ -125,9 +132,15 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
             break
         rows = [i for i, _ in nxt]
         order = [rs for _, rs in nxt]
-        logits = engine.step_device([slot for _, slot in order], token_source, rows)
+        if headers:
+            logits = engine.step_device([slot for _, slot in order])
+        else:
+            logits = engine.step_device([slot for _, slot in order], token_source, rows)
         step_no = emitted[order[0][0]]             # every request of a batch has the same count: they started together
-        token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
+        if headers:
+            token_source = sampler.sample(logits, params, [req for req, _ in order], step_no, note=engine.step_note())
+        else:
+            token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
         pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=on_gpu)
         pinned.copy_(token_source, non_blocking=True)
         event = None
@@ -158,6 +171,13 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
     for i, p in enumerate(prompts):
         if len(p) == 0:
             raise ValueError(f"request {i} has an empty prompt")
+    limit = getattr(engine, "max_position", None)
+    if limit:
+        # the last token is returned but not fed: a request stands at prompt + max_new_tokens - 1 positions at most
+        for i, p in enumerate(prompts):
+            if len(p) + max_new_tokens - 1 > limit:
+                raise ValueError(f"request {i}: {len(p)} prompt tokens and {max_new_tokens} new ones pass the "
+                                 f"model's {limit} positions")
     stop = set(int(s) for s in stop_ids)
     page = getattr(engine, "page_size", 64)
     budget = token_budget if token_budget is not None else engine.free_tokens()
@@ -197,7 +217,9 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
         try:
             t0 = time.perf_counter()
             logits = engine.step([(slot, prompts[req], [len(prompts[req]) - 1]) for req, slot in live])
-            tokens = sampler.sample(logits, params, [r for r, _ in live], 0).tolist()
+            note = engine.step_note() if hasattr(engine, "step_note") else None
+            first = sampler.sample(logits, params, [r for r, _ in live], 0, **({"note": note} if note is not None else {}))
+            tokens = first.tolist()
             t1 = time.perf_counter()
             metrics.steps += 1
             metrics.prompt_tokens += sum(len(prompts[r]) for r, _ in live)

@@ -45,6 +45,55 @@ def wide_bucket(max_len: int, page_size: int) -> int:
     return b
 
 
+class GraphTable:
+    """Captured graphs by key, with a cap: when it is reached, the graph replayed longest ago makes room for the new
+    one, so that a kind of step that keeps coming is never left to run kernel by kernel for the rest of the engine's
+    life. A key is captured the second time it is seen (the first step of a kind warms its kernels up)."""
+
+    def __init__(self, cap: int):
+        self.cap = int(cap)
+        self.graphs: dict = {}
+        self.seen: dict = {}
+        self.clock = 0
+        self.evictions = 0
+
+    def __len__(self):
+        return len(self.graphs)
+
+    def __iter__(self):
+        return iter(self.graphs)
+
+    def clear(self):
+        self.graphs.clear()
+        self.seen.clear()
+
+    def get(self, key):
+        g = self.graphs.get(key)
+        if g is not None:
+            self.clock += 1
+            g.last_used = self.clock
+        return g
+
+    def wants_capture(self, key) -> bool:
+        """Count one more sighting of ``key``; True from the second on."""
+        if len(self.seen) > 8 * max(1, self.cap):
+            self.seen.clear()                    # the counts are a hint only: they must not grow without bound
+        n = self.seen[key] = self.seen.get(key, 0) + 1
+        return n >= 2
+
+    def put(self, key, graph, before_evict=None):
+        while self.cap > 0 and len(self.graphs) >= self.cap:
+            oldest = min(self.graphs, key=lambda k: getattr(self.graphs[k], "last_used", 0))
+            if before_evict is not None:
+                before_evict(self.graphs[oldest])
+            del self.graphs[oldest]
+            self.evictions += 1
+        self.clock += 1
+        graph.last_used = self.clock
+        self.graphs[key] = graph
+        return graph
+
+
 class DecodeGraph:
     RING = 4
 
@@ -70,7 +119,7 @@ class DecodeGraph:
         self.batch = StepBatch(
             n_tokens=B, n_seqs=B, tokens=self.dev[0:B], positions=self.dev[B:2 * B], token_seq=ar[:B],
             seq_start=ar, seq_slot=self.dev[2 * B:3 * B], seq_row=ar[:B], seq_len=self.dev[3 * B:4 * B],
-            want_rows=ar[:B], n_want=B, max_new=1, max_len=bucket, all_single=True, n_q_tiles=B,
+            want_rows=ar[:B], n_want=B, max_new=1, max_len=bucket, all_single=True,
             page_tables=tables, host={}, key_split=self.dev[5 * B:5 * B + 2] if fused is not None else None)
         self.last_tables = None
         self.graph = None

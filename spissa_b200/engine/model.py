@@ -67,7 +67,7 @@ class Model:
     # ------------------------------------------------------------------ forward
     def forward(self, step, cache) -> torch.Tensor:
         """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer."""
-        h = self.embedding.forward(step.tokens)
+        h = self.embedding.forward(step)
         if self.fuse_decode and self._fused is False:
             from .fused_decode import FusedDecode
             self._fused = FusedDecode.plan(self)

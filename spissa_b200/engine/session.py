@@ -35,7 +35,11 @@ class ChatSession:
         self.history: list = []
         self.pending = None                  # the last generated token, not yet in the cache
         self.turn = 0
-        self.max_seq_len = max_seq_len or engine.free_tokens() + engine.length(self.slot)
+        room = engine.free_tokens() + engine.length(self.slot)
+        model_limit = getattr(engine, "max_position", None)
+        if model_limit:
+            room = min(room, model_limit)            # the reference caps a session by max_seq_len (session.rs:307-320)
+        self.max_seq_len = min(max_seq_len, room) if max_seq_len else room
 
     def close(self):
         if self.slot is not None:

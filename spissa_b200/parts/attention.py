@@ -119,12 +119,13 @@ class GQAAttention(Mixer):
                                self.counters if T * nkv <= self.counters.numel() else None)
             elif T >= 256 and K.flash_tc_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size, self.window):
                 # long prompts: 128-token tiles on the tcgen05 tensor cores (S, P and O in tensor memory)
-                tiles = sum((n + 127) // 128 for n in step.host["new_counts"])
+                tiles = K.query_tiles(step.host["new_counts"], K.flash_tc_query_tile())
                 K.flash_prefill_tc(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs, tiles,
                                    nh, nkv, hd, self.window, self.scale)
             else:
+                tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
                 K.flash_prefill(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_start, step.n_seqs,
-                                step.n_q_tiles, nh, nkv, hd, self.window, self.scale)
+                                tiles, nh, nkv, hd, self.window, self.scale)
         else:
             K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
         self.o(ctx, out=residual, accumulate=True)

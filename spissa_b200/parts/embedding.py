@@ -31,11 +31,14 @@ class TokenEmbedding(Part):
     def bind(self, tensors, rt):
         super().bind(tensors, rt)
         self.weight = tensors[self.weight_name].contiguous()
-        self.status = torch.zeros(1, dtype=torch.int32, device=rt.device)
 
-    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, step) -> torch.Tensor:
+        """The residual stream [T, H] (float32) of the step's tokens. An embedding that needs more than the token ids
+        (positions, for a learned position table) finds it in ``step``. A token id outside the table gives a zero row
+        and a fault code in the device's status word (ids that come from the host are checked there already)."""
+        ids = step.tokens
         out = torch.empty(ids.shape[0], self.hidden_size, dtype=torch.float32, device=ids.device)
-        K.embed_gather(self.weight, ids, out, self.status)
+        K.embed_gather(self.weight, ids, out, K.status_word(ids.device))
         return out
 
 

@@ -12,17 +12,26 @@ import torch
 
 from ..csrc import lib as K
 
-SM_COUNT = 148
+_SM_COUNT: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current CUDA device when None), asked once per device."""
+    index = torch.cuda.current_device() if device is None else (torch.device(device).index or 0)
+    if index not in _SM_COUNT:
+        _SM_COUNT[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _SM_COUNT[index]
 GEMV_TOKENS = 16          # up to this many tokens the weight-streaming kernel runs instead of 128-row tiles
 GATED_GEMV_TOKENS = 16    # the same for the gate/up product
 STREAM_TOKENS = 64        # from there up to this many tokens the weight streams through tcgen05 with the tokens as the
 #                           instruction's N (at 64 tokens: QKV 9.4 vs 12.8 us, gate/up 29 vs 40 us, down 14.4 vs 19.5 us)
 
 
-def tile_width(M: int, N: int) -> int:
+def tile_width(M: int, N: int, sms: int | None = None) -> int:
     """256-wide tiles (half the shared-memory traffic per FLOP) when they still occupy most SMs, else 128-wide;
     192-wide when that saves a round of tiles: 2,048 tokens x 3,072 outputs are 192 tiles of 256 columns, two
     rounds on 148 SMs of which the second is a third full, but 256 tiles of 192 columns, two rounds of shorter tiles."""
+    SM_COUNT = sms if sms else sm_count()
     m_tiles = (M + 127) // 128
     tiles_256 = m_tiles * ((N + 255) // 256)
     if tiles_256 < (SM_COUNT * 2) // 3:
@@ -55,7 +64,7 @@ class Linear:
         elif x.shape[0] <= STREAM_TOKENS and K.tc_stream_supported(x, self.weight, mode):
             K.tc_stream(x, self.weight, out, mode)
         elif K.tc_gemm_supported(x, self.weight):
-            K.tc_gemm(x, self.weight, out, mode, tile_width(x.shape[0], self.out_features))
+            K.tc_gemm(x, self.weight, out, mode, tile_width(x.shape[0], self.out_features, sm_count(x.device)))
         else:
             K.gemm_generic(x, self.weight, out, accumulate=accumulate)
         return out

@@ -65,8 +65,11 @@ class Sampler:
         self.device = torch.device(device)
         self._scratch = None
 
-    def sample(self, logits: torch.Tensor, params: SamplingParams, requests, step: int) -> torch.Tensor:
-        """One token per row (int32 on the device). ``requests`` are the rows' request indices."""
+    def sample(self, logits: torch.Tensor, params: SamplingParams, requests, step: int, note=None) -> torch.Tensor:
+        """One token per row (int32 on the device). ``requests`` are the rows' request indices.
+
+        ``note`` (an engine's ``step_note()``): the tokens are also written into the per-slot headers of the step's
+        sequences on the device (last token, draw counter, position), where the next decode step can take them."""
         from ..csrc import lib as K
         rows, V = logits.shape
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
@@ -74,10 +77,20 @@ class Sampler:
             return out
         if params.greedy:
             K.argmax_rows(logits, out)
-            return out
-        need = K.sample_scratch_keys(rows, V)
-        if self._scratch is None or self._scratch.numel() < need:
-            self._scratch = torch.empty(need, dtype=torch.int64, device=logits.device)
-        u = torch.tensor(uniforms(params, requests, step), dtype=torch.float32).to(logits.device)
-        K.sample_rows(logits, params.temperature, params.top_k, params.top_p, u, self._scratch, out)
+        else:
+            need = K.sample_scratch_keys(rows, V)
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.int64, device=logits.device)
+            u = torch.tensor(uniforms(params, requests, step), dtype=torch.float32).to(logits.device)
+            K.sample_rows(logits, params.temperature, params.top_k, params.top_p, u, self._scratch, out)
+        if note is not None:
+            self.note(out, note)
         return out
+
+    @staticmethod
+    def note(tokens: torch.Tensor, note) -> None:
+        from ..csrc import lib as K
+        if tokens.numel() != len(note.slots):
+            raise ValueError(f"{tokens.numel()} tokens cannot be noted for the {len(note.slots)} sequences of the step")
+        K.header_note(note.header, note.seq_slot, note.seq_len, tokens)
+        note.done()

@@ -46,15 +46,15 @@ def test_reserve_commit_release_accounts_pages():
     t = m.reserve([(s0, 65), (s1, 1)])
     (g,) = m.kv_groups
     assert [len(r) for r in t[g]] == [2, 1]
-    m.commit([(s0, 65), (s1, 1)])
+    m.commit(t)
     assert m.length(s0) == 65 and m.length(s1) == 1
     m.check()
     t = m.reserve([(s0, 63), (s1, 63)])               # 128 and 64 tokens: still 2 and 1 pages
     assert [len(r) for r in t[g]] == [2, 1]
-    m.commit([(s0, 63), (s1, 63)])
+    m.commit(t)
     t = m.reserve([(s1, 1)])
     assert len(t[g][0]) == 2
-    m.commit([(s1, 1)])
+    m.commit(t)
     assert m.kv_groups[g].pages.held_count == 4
     m.release(s0)
     assert m.kv_groups[g].pages.held_count == 2
@@ -70,8 +70,7 @@ def test_reserve_commit_release_accounts_pages():
 def test_refused_step_changes_nothing():
     m = manager(max_tokens=256)                       # 4 pages
     s0, s1 = m.acquire(), m.acquire()
-    m.reserve([(s0, 100)])
-    m.commit([(s0, 100)])
+    m.commit(m.reserve([(s0, 100)]))
     (g,) = m.kv_groups
     before = (m.kv_groups[g].pages.free_count, m.length(s0), m.length(s1))
     with pytest.raises(CacheFull, match="needs 4 more pages"):
@@ -88,13 +87,11 @@ def test_exact_budget_of_rounded_lengths():
     # three live requests of 1, 64 and 65 tokens need 64 + 64 + 128 tokens and not one more
     m = manager(max_tokens=256, max_seqs=3)
     s = [m.acquire() for _ in range(3)]
-    m.reserve([(s[0], 1), (s[1], 64), (s[2], 65)])
-    m.commit([(s[0], 1), (s[1], 64), (s[2], 65)])
+    m.commit(m.reserve([(s[0], 1), (s[1], 64), (s[2], 65)]))
     assert m.free_tokens() == 0
     with pytest.raises(CacheFull):
         m.reserve([(s[1], 1)])
-    m.reserve([(s[0], 63)])                           # room inside the page it already holds
-    m.commit([(s[0], 63)])
+    m.commit(m.reserve([(s[0], 63)]))                           # room inside the page it already holds
     m.release(s[2])
     assert m.free_tokens() == 128
     m.check()
@@ -104,15 +101,14 @@ def test_window_group_returns_pages_out_of_reach():
     m = manager(max_tokens=64 * 20, window=100)
     s = m.acquire()
     wname = m.cache_group[2]
-    m.reserve([(s, 300)])
-    m.commit([(s, 300)])
+    m.commit(m.reserve([(s, 300)]))
     # next query at 300 sees keys >= 201: pages 0..2 (positions 0..191) are returned
     assert m.seqs[s].pages[wname][:3] == [None, None, None] and m.seqs[s].pages[wname][3] is not None
     assert m.kv_groups[wname].pages.held_count == 2
     assert m.kv_groups[m.cache_group[0]].pages.held_count == 5
     t = m.reserve([(s, 1)])
     assert len(t[wname][0]) == 5 and t[wname][0][:3] == [0, 0, 0]
-    m.commit([(s, 1)])
+    m.commit(t)
     m.check()
     m.release(s)
     m.check()
@@ -120,30 +116,72 @@ def test_window_group_returns_pages_out_of_reach():
 
 
 def test_random_traffic_keeps_the_books():
+    """Steps in flight (advanced, not yet confirmed), confirmed oldest first or rolled back newest first, with slots
+    released in between: lengths follow the confirmed and pending steps, no page is lost or owned twice."""
     rng = random.Random(0)
     m = manager(max_tokens=64 * 12, max_seqs=5, window=70)
-    live = {}
-    for _ in range(2000):
+    live = {}                      # slot -> length counting confirmed and pending steps
+    pending = []                   # [(reservation, step)] oldest first
+    rolled = confirmed = 0
+    for _ in range(3000):
         r = rng.random()
-        if r < 0.25 and m.slots.free_count:
+        if r < 0.2 and m.slots.free_count:
             live[m.acquire()] = 0
-        elif r < 0.4 and live:
+        elif r < 0.3 and live:
             s = rng.choice(list(live))
-            m.release(s)
+            m.release(s)           # its pending steps stay in the list: confirm and rollback skip a released sequence
             del live[s]
-        elif live:
+        elif r < 0.65 and live and len(pending) < 3:
             k = rng.randint(1, len(live))
             step = [(s, rng.choice([1, 1, 1, 5, 64, 130])) for s in rng.sample(list(live), k)]
             try:
-                m.reserve(step)
+                res = m.reserve(step)
             except CacheFull:
                 continue
-            m.commit(step)
+            m.advance(res)
+            pending.append((res, step, {s: m.seqs[s] for s, _ in step}))
             for s, n in step:
                 live[s] += n
+        elif r < 0.9 and pending:
+            res, _, _ = pending.pop(0)
+            m.confirm(res)
+            confirmed += 1
+        elif pending:
+            while pending:         # a fault: everything in flight is undone, newest first
+                res, step, seqs = pending.pop()
+                m.rollback(res)
+                rolled += 1
+                for s, n in step:
+                    if s in live and m.seqs.get(s) is seqs[s]:
+                        live[s] -= n
         m.check()
         assert {s: m.length(s) for s in live} == live
+    while pending:
+        m.confirm(pending.pop(0)[0])
+    assert rolled > 20 and confirmed > 100
     for s in list(live):
         m.release(s)
     m.check()
     assert all(g.pages.free_count == g.n_pages for g in m.kv_groups.values())
+
+
+def test_rollback_returns_pages_and_lengths():
+    m = manager(max_tokens=640)
+    s0, s1 = m.acquire(), m.acquire()
+    m.commit(m.reserve([(s0, 60), (s1, 3)]))
+    (g,) = m.kv_groups
+    free = m.kv_groups[g].pages.free_count
+    a = m.reserve([(s0, 10), (s1, 1)])                # s0 takes a second page
+    m.advance(a)
+    b = m.reserve([(s0, 70)])                         # and a third
+    m.advance(b)
+    assert m.length(s0) == 140 and m.kv_groups[g].pages.free_count == free - 2
+    with pytest.raises(CacheMisuse):
+        m.confirm(m.reserve([(s1, 1)]))               # confirming what never advanced
+    m.rollback(b)
+    assert m.length(s0) == 70 and m.kv_groups[g].pages.free_count == free - 1
+    m.rollback(a)
+    assert (m.length(s0), m.length(s1)) == (60, 3) and m.kv_groups[g].pages.free_count == free
+    with pytest.raises(CacheMisuse):
+        m.rollback(a)                                 # once only
+    m.check()

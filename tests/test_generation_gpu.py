@@ -19,7 +19,8 @@ def folders(tmp_path_factory):
     out = {}
     for name, (cfg, init) in tiny.TINIES.items():
         f = tmp_path_factory.mktemp(f"gen_{name}")
-        tiny.make_folder(cfg, init, f, std=0.06)           # wider weights: logits well apart
+        # wider weights: logits well apart; room for the long runs below (the limit itself is tested elsewhere)
+        tiny.make_folder({**cfg, "max_position_embeddings": max(2048, cfg["max_position_embeddings"])}, init, f, std=0.06)
         out[name] = (str(f),) + P.read_model_folder(f)
     return out
 
@@ -196,7 +197,11 @@ def test_step_refusals_leave_the_cache_alone(folders):
         with pytest.raises(StepError):
             engine.step(bad)
     with pytest.raises(CacheFull):
-        engine.step([(s, [1] * 126, [])])
+        engine.step([(s, [1] * 126, [])])                  # 129 tokens in a cache of 128
+    s2 = engine.acquire()
+    with pytest.raises(CacheFull):
+        engine.step([(s, [1], []), (s2, [1] * 70, [])])    # two pages for s2, one is left
+    engine.release(s2)
     assert engine.length(s) == 3
     engine.cache.check()
     out = engine.step([(s, [4], [0])])

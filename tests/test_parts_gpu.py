@@ -35,7 +35,7 @@ def step_of(meta, T):
     return SimpleNamespace(n_tokens=T, token_seq=meta.token_seq, positions=meta.positions, seq_row=meta.seq_slot,
                            seq_slot=meta.seq_slot, seq_len=meta.seq_len, seq_start=meta.seq_start,
                            n_seqs=len(meta.rows), all_single=all(c == 1 for c in meta.new_counts),
-                           n_q_tiles=sum((c + 63) // 64 for c in meta.new_counts), max_new=T,
+                           host=dict(new_counts=list(meta.new_counts)), max_new=T,
                            max_len=max(meta.total_len))
 
 
@@ -124,7 +124,8 @@ def test_embedding_and_head_parts(dtype):
         E = E.bfloat16().float()
     emb = bound("embedding", PartSpec("embedding", dict(vocab_size=V, hidden_size=H), prefix="e."), {"e.weight": E}, dtype)
     ids = torch.tensor([5, 332, 0], dtype=torch.int32, device=DEV)
-    assert torch.equal(emb.forward(ids).cpu(), E[[5, 332, 0]])
+    from types import SimpleNamespace
+    assert torch.equal(emb.forward(SimpleNamespace(tokens=ids)).cpu(), E[[5, 332, 0]])
     head = bound("head", PartSpec("lm_head", dict(vocab_size=V, hidden_size=H, tied_to="e.weight"), prefix="h."),
                  {"e.weight": E}, dtype)
     assert head.weight_specs() == []

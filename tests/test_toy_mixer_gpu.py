@@ -141,3 +141,39 @@ def test_toy_mixer_with_state_runs_through_the_engine(toy, tmp_path, dtype):
     engine.cache.check()
     # a layer that offers no description of itself keeps the whole model out of the one-kernel decode path
     assert engine.model._fused is None
+
+
+def test_state_is_what_it_was_after_a_refused_step_and_after_a_step_that_failed_on_the_device(toy, tmp_path):
+    """Fixed-size state cannot be truncated the way a length can: the cache copies the rows of a step's sequences
+    aside before the step runs and puts them back when the step is rolled back."""
+    from spissa_b200.csrc import lib as K
+    from spissa_b200.csrc.lib import KernelError
+    from spissa_b200.engine.engine import StepError
+    cfg = config_from_dict(dict(architectures=["ToyDecayForCausalLM"]))
+    write_random_model(cfg, tmp_path, seed=3, std=0.05)
+    pcfg, w = P.read_model_folder(tmp_path)
+    engine = Engine.from_folder(tmp_path, dtype="float32", max_tokens=64 * 6, max_seqs=3)
+    (group,) = engine.cache.state_groups.values()
+    reqs = [tiny.random_prompt(256, n, n) for n in (20, 33)]
+    refs = [plain_toy({**tiny.TINY_A}, w, r) for r in reqs]
+    slots = [engine.acquire() for _ in reqs]
+    engine.step([(s, r[:-2], []) for s, r in zip(slots, reqs)])
+    before = group.state.clone()
+    assert float(before.abs().sum()) > 0
+    with pytest.raises(StepError):
+        engine.step([(slots[0], [5], [0]), (slots[1], [100000], [0])])          # refused on the host
+    assert torch.equal(group.state, before)
+    K.status_word("cuda:0").fill_(123)
+    with pytest.raises(KernelError, match="code 123"):
+        engine.step([(s, [r[-2]], [0]) for s, r in zip(slots, reqs)])            # ran, then rolled back
+    assert torch.equal(group.state, before)
+    assert [engine.length(s) for s in slots] == [len(r) - 2 for r in reqs]
+    scale = max(float(r.abs().max()) for r in refs)
+    for i in (2, 1):
+        rows = engine.step([(s, [r[-i]], [0]) for s, r in zip(slots, reqs)]).cpu()
+        for b, ref in enumerate(refs):
+            assert float((rows[b].double() - ref[len(reqs[b]) - i]).abs().max()) / scale <= tiny.TOL["float32"]
+    # through the generation loop a model with state keeps one step in flight, and the result is the plain one
+    for s in slots:
+        engine.release(s)
+    engine.cache.check()

@@ -20,7 +20,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def one_case(K, lib, seed, lengths, nh, nkv, hd, chunk_tiles):
+def one_case(K, lib, seed, lengths, nh, nkv, hd, chunk_tiles, out_dtype=torch.bfloat16, window=None):
     torch.manual_seed(seed)
     B = len(lengths)
     meta = KH.paged_meta([1] * B, [n - 1 for n in lengths], DEV, seed)
@@ -31,25 +31,27 @@ def one_case(K, lib, seed, lengths, nh, nkv, hd, chunk_tiles):
     scale = 1.0 / math.sqrt(hd)
     n_chunks = -(-((max(lengths) + 63) // 64) // chunk_tiles)
 
-    want = torch.empty_like(q)
+    want = torch.empty(q.shape, dtype=out_dtype, device=DEV)
     scratch = torch.empty(K.flash_decode_scratch_floats(B, nh, hd, n_chunks), device=DEV)
     counters = torch.zeros(B * nkv, dtype=torch.int32, device=DEV)
-    K.flash_decode(q, k_pool, v_pool, want, meta, meta.seq_len, nh, nkv, hd, None, scale, chunk_tiles, n_chunks,
+    K.flash_decode(q, k_pool, v_pool, want, meta, meta.seq_len, nh, nkv, hd, window, scale, chunk_tiles, n_chunks,
                    scratch, counters)
 
-    got = torch.full_like(q, float("nan"))
+    got = torch.full_like(want, float("nan"))
     rc = lib.sp_flash_decode_static(
-        c_void_p(q.data_ptr()), c_void_p(got.data_ptr()), 1, c_void_p(k_pool.data_ptr()), c_void_p(v_pool.data_ptr()),
+        c_void_p(q.data_ptr()), c_void_p(got.data_ptr()), 1 if out_dtype == torch.bfloat16 else 0,
+        c_void_p(k_pool.data_ptr()), c_void_p(v_pool.data_ptr()),
         c_void_p(meta.seq_len.data_ptr()), c_void_p(meta.seq_slot.data_ptr()), c_void_p(meta.page_table.data_ptr()),
-        meta.page_table.shape[1], 64, B, nh, nkv, hd, 0, c_float(scale), chunk_tiles, n_chunks,
+        meta.page_table.shape[1], 64, B, nh, nkv, hd, int(window or 0), c_float(scale), chunk_tiles, n_chunks,
         c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, lib.sp_attention_last_error().decode()
     torch.cuda.synchronize()
     ref = KH.plain_attention_rows([torch.cat([torch.zeros(n - 1, nh, hd), q[b].float().cpu().reshape(1, nh, hd)])
-                                   for b, n in enumerate(lengths)], ks, vs, [1] * B)
+                                   for b, n in enumerate(lengths)], ks, vs, [1] * B, window=window)
     scale_ref = float(ref.abs().max())
-    assert float((got.float().cpu() - want.float().cpu()).abs().max()) <= 6e-3 * scale_ref
-    assert float((got.double().cpu() - ref).abs().max()) <= 6e-3 * scale_ref
+    # the same kernel, the same split of the keys, the chunks combined in the same order: not a bit may differ
+    assert torch.equal(got, want)
+    assert float((got.double().cpu() - ref.reshape(B, -1)).abs().max()) <= 6e-3 * scale_ref
 
 
 def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
@@ -59,6 +61,16 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice_in_a_row():
     torch.cuda.set_device(0)
     one_case(K, lib, 1, [700, 64, 129, 300], 8, 2, 64, 2)
     one_case(K, lib, 2, [33, 1000], 4, 1, 128, 3)
+
+
+def test_static_scratch_entry_point_with_float32_output_and_with_a_window():
+    from spissa_b200.csrc import lib as K
+    lib = K.load("attention")
+    lib.sp_attention_last_error.restype = ctypes.c_char_p
+    torch.cuda.set_device(0)
+    one_case(K, lib, 3, [500, 90], 8, 2, 64, 2, out_dtype=torch.float32)
+    one_case(K, lib, 4, [700, 64, 300], 4, 2, 64, 3, window=100)
+    one_case(K, lib, 5, [260, 131], 20, 2, 128, 2, out_dtype=torch.float32, window=70)      # ten query heads per kv head
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():

@@ -20,7 +20,16 @@ SP_API const char* sp_gemv_last_error() { return sp_error_text; }
 
 namespace {
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ROPE_KV = 3 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ROPE_KV = 3, MODE_ARGMAX = 4 };
+
+// MODE_ARGMAX keeps, per token, only the best (value, row) of the rows a warp owns, as the reference's greedy head
+// does while it streams the rows (crates/spissa-runtime/src/streaming/linear_argmax.rs:13,
+// crates/spissa-runtime/src/streaming/argmax.rs:30-51, :85-97: a strict ``>`` so that the lowest row wins among equal
+// values). ``out`` is then a table of candidates [token][warp tile]; a second, tiny kernel takes the best of a row.
+struct Candidate { float value; int index; };
+__device__ __forceinline__ void take_better(float& bv, int& bi, float ov, int oi) {
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }       // a NaN never wins
+}
 constexpr int MAX_KS = 8;
 
 // Where MODE_ROPE_KV sends its rows: W is [q heads | k heads | v heads] x head_dim rows; q and k are
@@ -329,6 +338,28 @@ gemv_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         load(buf0, kb + 2 * U);
         compute(buf1, kb + U);
     }
+    if (mode == MODE_ARGMAX) {
+        // lane (g, t) holds tokens g and g + 8 of rows 2t and 2t + 1 of every row group: the best of the warp's
+        // rows per token, first among the lane's own, then over the four lanes that share g
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int r = 0; r < RT; ++r)
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int row = row_base[r] + 2 * t + c;
+                    if (row < N) take_better(bv, bi, acc[r][2 * h + c], row);
+                }
+#pragma unroll
+            for (int o = 1; o <= 2; o <<= 1)
+                take_better(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+            const int m = g + 8 * h;
+            if (t == 0 && m < M) ((Candidate*)out)[(size_t)m * ldo + tile] = Candidate{bv, bi};
+        }
+        return;
+    }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         const int m = g + (e >> 1) * 8;
@@ -452,4 +483,24 @@ SP_API int sp_gemv_qkv_rope(const void* x, int ldx, const void* W, int ldw, int 
     RopeOut rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, positions, token_seq, seq_row,
                  page_table, inv_freq, max_pages, page_size, nh, nkv, hd};
     return launch_gemv(x, W, nullptr, SP_DT_BF16, M, N, K, ldx, ldw, 0, MODE_ROPE_KV, hd / 2, rope, stream);
+}
+
+
+// The greedy head for up to 16 tokens: the product with W [N, K] (the vocabulary's rows) of which only each warp's
+// best (value, row) per token is kept. ``cand`` holds [M][sp_gemv_argmax_candidates(N)] pairs of (float, int32);
+// the lowest row wins among equal values, rows beyond N and NaNs never win (a tile without a winner has row
+// 0x7fffffff). A second kernel (argmax_candidates of the generic library) takes the best of each token's row.
+SP_API int sp_gemv_argmax_candidates(int N) { return (N + 7) / 8; }
+
+SP_API int sp_gemv_argmax(const void* x, const void* W, void* cand, int M, int N, int K, int ldx, int ldw, int ld_cand,
+                          cudaStream_t stream) {
+    if (N <= 0 || M <= 0) return 0;
+    if (M > 16) SP_FAIL("gemv (argmax): built for 1 to 16 tokens, got %d", M);
+    if (sp_gemv_supported(x, W, M, K, ldx, ldw)) return 1;
+    const int tiles = sp_gemv_argmax_candidates(N);
+    if (ld_cand < tiles) SP_FAIL("gemv (argmax): the candidate table has %d columns, %d are needed", ld_cand, tiles);
+    gemv_stream_kernel<1, 8><<<(tiles + 3) / 4, 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, cand,
+                                                                   SP_DT_F32, M, N, K, ldx, ldw, ld_cand, MODE_ARGMAX, 0, tiles);
+    SP_CHECK_LAUNCH("gemv_argmax");
+    return 0;
 }

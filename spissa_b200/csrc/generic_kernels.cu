@@ -702,6 +702,67 @@ SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld
 }
 
 
+// ============================================================== the best of a row of candidates
+// Second stage of the greedy head: the head's product kept, per token, one (value, row) candidate for each of its
+// tiles (``cand`` [rows][ld] pairs of float, int32; a tile without a winner has row 0x7fffffff). One CTA per token
+// takes the best of them: the largest value, the lowest row among equal values, as a serial scan of the logits with
+// a strict ``>`` would (crates/spissa-runtime/src/ops.rs:309-324). With ``header`` the token is also noted in the
+// header of the token's sequence (see header_note below), so that a greedy step needs no kernel after this one.
+struct Candidate { float value; int index; };
+
+__global__ void argmax_candidates_kernel(const Candidate* __restrict__ cand, int n_cand, int ld, int* __restrict__ out,
+                                         int* __restrict__ header, int n_slots, const int* __restrict__ seq_slot,
+                                         const int* __restrict__ seq_len) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int r = blockIdx.x;
+    const Candidate* row = cand + (size_t)r * ld;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = threadIdx.x; c < n_cand; c += blockDim.x) {
+        const Candidate k = row[c];
+        if (k.index != 0x7fffffff) argmax_take(bv, bi, k.value, k.index);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+        argmax_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) { sv[warp] = bv; si[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = (blockDim.x + 31) >> 5;
+        bv = lane < nw ? sv[lane] : -INFINITY;
+        bi = lane < nw ? si[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+            argmax_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+        if (lane == 0) {
+            const int tok = (bi == 0x7fffffff) ? 0 : bi;
+            out[r] = tok;
+            if (header) {
+                const int slot = seq_slot[r];
+                if (slot >= 0 && slot < n_slots) {
+                    int* h = header + (size_t)slot * 4;
+                    h[0] = seq_len[r];
+                    h[1] += 1;
+                    h[2] = tok;
+                }
+            }
+        }
+    }
+}
+
+SP_API int sp_argmax_candidates(const void* cand, int rows, int n_cand, int ld, int* out, int* header, int n_slots,
+                                const int* seq_slot, const int* seq_len, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n_cand <= 0 || ld < n_cand) SP_FAIL("argmax_candidates: %d candidates in rows of %d", n_cand, ld);
+    if (header && (!seq_slot || !seq_len)) SP_FAIL("argmax_candidates: noting tokens needs the step's slots and lengths");
+    argmax_candidates_kernel<<<rows, n_cand >= 4096 ? 1024 : 256, 0, stream>>>((const Candidate*)cand, n_cand, ld, out, header,
+                                                                                  n_slots, seq_slot, seq_len);
+    SP_CHECK_LAUNCH("argmax_candidates");
+    return 0;
+}
+
 // ============================================================== the per-slot header
 // header [slots, 4] int32: position (tokens cached), draws (tokens sampled so far), last sampled token, spare.
 // After a step's logits were turned into tokens: sequence b of the step sits in slot seq_slot[b] and is

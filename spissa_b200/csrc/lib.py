@@ -216,6 +216,54 @@ def argmax_rows(logits, out):
                                          logits.stride(0), c_void_p(_stream())))
 
 
+# ------------------------------------------------------------------ the greedy head: no logits
+HEAD_ARGMAX_TOKENS = 64
+
+
+def head_argmax_candidates(M: int, N: int) -> int:
+    """Candidates per token that ``head_argmax`` needs room for (pairs of float32 and int32), 0 when it does not take M."""
+    if M <= 16:
+        return int(load("gemv").sp_gemv_argmax_candidates(int(N)))
+    if M <= HEAD_ARGMAX_TOKENS:
+        return int(load("tc_stream").sp_tc_stream_argmax_candidates(int(N)))
+    return 0
+
+
+def head_argmax_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    M = x.shape[0]
+    if M <= 16:
+        return gemv_supported(x, w)
+    return M <= HEAD_ARGMAX_TOKENS and tc_stream_supported(x, w, 3)
+
+
+def head_argmax(x, w, cand, out, note=None):
+    """out[m] = argmax_n x[m]·w[n] (int32) without the logits: the product keeps one (value, row) candidate per tile
+    of ``w`` and token in ``cand`` (float32 [M, head_argmax_candidates, 2] viewed as pairs), a second kernel takes the
+    best of each row; the lowest row wins among equal values. ``note`` (an engine's ``step_note()``): the tokens also
+    go into the headers of the step's sequences. Two kernels."""
+    M, K = x.shape
+    N = w.shape[0]
+    n_cand = head_argmax_candidates(M, N)
+    if n_cand == 0 or cand.dtype != torch.float32 or cand.numel() < M * n_cand * 2 or not cand.is_contiguous():
+        raise KernelError(f"head_argmax: {M} tokens x {N} rows need a float32 table of {M}x{n_cand}x2")
+    if out.dtype != torch.int32 or out.numel() < M:
+        raise KernelError("head_argmax: the tokens go to an int32 tensor with one entry per row")
+    if M <= 16:
+        _check("gemv", load("gemv").sp_gemv_argmax(
+            c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(cand)), M, N, K, x.stride(0), w.stride(0), n_cand,
+            c_void_p(_stream())))
+    else:
+        _check("tc_stream", load("tc_stream").sp_tc_stream(
+            c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(cand)), F32, M, N, K, x.stride(0), w.stride(0),
+            n_cand, 3, 0, c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))
+    header = note.header if note is not None else None
+    _check("generic", load("generic").sp_argmax_candidates(
+        c_void_p(_ptr(cand)), M, n_cand, n_cand, c_void_p(_ptr(out)), c_void_p(_ptr(header)),
+        header.shape[0] if header is not None else 0,
+        c_void_p(_ptr(note.seq_slot) if note is not None else None),
+        c_void_p(_ptr(note.seq_len) if note is not None else None), c_void_p(_stream())))
+
+
 # ------------------------------------------------------------------ sampling
 def sample_scratch_keys(rows: int, V: int) -> int:
     lib = load("sampling")

@@ -26,7 +26,22 @@ constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle
 constexpr int UMMA_K = 16;
 constexpr int MAX_SPLITS = 8;
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ARGMAX = 3 };
+
+// MODE_ARGMAX (the greedy head): of a tile's 128 rows of W only the best (value, row) per token is kept, the lowest
+// row among equal values (crates/spissa-runtime/src/streaming/argmax.rs:30-51, :85-97); C is then a table of
+// candidates [token][tile] and a second, tiny kernel takes the best of each token's row.
+struct Candidate { float value; int index; };
+// a float as an unsigned key of the same order; NaN -> 1 and "no row" -> 0 lie below every number
+__device__ __forceinline__ uint32_t order_key(float v, bool valid) {
+    if (!valid) return 0u;
+    if (v != v) return 1u;
+    const uint32_t u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_value(uint32_t key) {
+    return __uint_as_float((key & 0x80000000u) ? (key ^ 0x80000000u) : ~key);
+}
 
 // NT: tokens padded to a multiple of 16 (the N of the instruction); GATED: two W tiles per CTA
 template <int NT, bool GATED>
@@ -56,6 +71,8 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES], bar_empty[STAGES], bar_acc;
     __shared__ uint32_t tmem_slot;
+    __shared__ uint32_t best_key[4][NT];                          // MODE_ARGMAX: each epilogue warp's best per token
+    __shared__ int best_row[4][NT];
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,9 +162,33 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                 tc_ld_32x32(lane_base + (uint32_t)c0, rg);
                 if (GATED) tc_ld_32x32(lane_base + (uint32_t)(NT + c0), ru);
                 tc_ld_wait();
-                if (healthy) {
+                if (!GATED && a.mode == MODE_ARGMAX) {
+                    // lanes are rows of W in rising order: the warp's largest key, and the lowest lane that holds it
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t key = order_key(__uint_as_float(rg[j]), col_ok);
+                        const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+                        const uint32_t who = __ballot_sync(0xffffffffu, key == top);
+                        if (lane == 0) {
+                            best_key[q][c0 + j] = top;
+                            best_row[q][c0 + j] = top > 1u ? tile * BW + q * 32 + (__ffs(who) - 1) : 0x7fffffff;
+                        }
+                    }
+                } else if (healthy) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) emit(c0 + j, __uint_as_float(rg[j]), GATED ? __uint_as_float(ru[j]) : 0.0f);
+                }
+            }
+            if (!GATED && a.mode == MODE_ARGMAX) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
+                const int j = (warp - 2) * 32 + lane;              // one token per thread
+                if (healthy && j < a.M && j < NT) {
+                    uint32_t top = 0u;
+                    int row_of = 0x7fffffff;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w)                     // warps hold rising rows: a strict > keeps the lowest
+                        if (best_key[w][j] > top) { top = best_key[w][j]; row_of = best_row[w][j]; }
+                    ((Candidate*)a.C)[(size_t)j * a.ldc + tile] = Candidate{top > 1u ? key_value(top) : -INFINITY, row_of};
                 }
             }
         } else {
@@ -273,6 +314,8 @@ int pieces_of(int tiles, int K) {
 }  // namespace
 
 SP_API int sp_tc_stream_max_tokens() { return 128; }
+// Candidates per token that MODE_ARGMAX writes for a weight of N rows (C is then [M][this] pairs of float, int32).
+SP_API int sp_tc_stream_argmax_candidates(int N) { return (N + BW - 1) / BW; }
 
 // Whether this kernel takes the product (0) or another has to (1, the reason as the last error).
 SP_API int sp_tc_stream_supported(const void* A, const void* W, int M, int N, int K, int lda, int ldw, int mode, int pair) {
@@ -289,14 +332,15 @@ SP_API int sp_tc_stream_supported(const void* A, const void* W, int M, int N, in
 SP_API int sp_tc_stream(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
                         int mode, int pair, int* status, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (mode < 0 || mode > 2) SP_FAIL("tc_stream: unknown mode %d", mode);
+    if (mode < 0 || mode > 3) SP_FAIL("tc_stream: unknown mode %d", mode);
     if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_stream: accumulation needs a float32 C");
     if (sp_tc_stream_supported(A, W, M, N, K, lda, ldw, mode, pair)) return 1;
     const int tiles = tiles_of(N, mode, pair);
     Args args;
     args.C = C; args.status = status;
     args.c_dt = c_dt; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.mode = mode; args.pair = pair;
-    args.pieces = pieces_of(tiles, K);
+    // the greedy head keeps candidates per tile: one CTA computes a tile over all of K
+    args.pieces = mode == MODE_ARGMAX ? 1 : pieces_of(tiles, K);
     const int nt = M <= 32 ? 32 : M <= 64 ? 64 : 128;
     CUtensorMap mw, ma;
     // gate/up tiles are ``pair`` rows each (the box still has 128 rows: those beyond belong to the next block and are ignored)

@@ -67,6 +67,7 @@ class Engine:
     """``Engine.from_folder(dir, dtype=..., max_tokens=...)`` or ``Engine.from_config(cfg, seed=...)``."""
 
     PAGE_SIZE = 64
+    greedy_steps = True            # ``step`` and ``step_device`` take ``greedy=True`` and return tokens instead of logits
 
     def __init__(self, config, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
                  device="cuda:0", use_graphs: bool = True, fuse_decode: bool = True):
@@ -280,8 +281,13 @@ class Engine:
         slots, seq_slot, seq_len = self._last_step
         return StepNote(self.cache, self.cache.header, slots, seq_slot, seq_len)
 
-    def step(self, entries, check: bool = True) -> torch.Tensor:
+    def step(self, entries, check: bool = True, greedy: bool = False) -> torch.Tensor:
         """Run the given tokens; return logits [number of wanted places, vocab] as float32 on the device.
+
+        With ``greedy`` the result is the index of the largest logit at each wanted place instead (int32 [wanted
+        places], the lowest index among equal logits): the head then keeps only the best candidate while it streams
+        its rows and no logits are written. When every sequence wants exactly one place, these tokens are also noted
+        in the sequences' headers (see ``step_note``).
 
         ``entries``: ``StepEntry`` objects or (slot, tokens, want) tuples. ``want`` holds indices into
         that entry's ``tokens``. Rows come back in the order of the entries and of their ``want``.
@@ -301,7 +307,8 @@ class Engine:
             res = self._begin(counts)
             try:
                 tables = res.tables
-                graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+                one_each = all(len(w) == 1 for _, _, w in ents)
+                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs else None
                 full = None
                 if graph is not None:
                     try:
@@ -312,7 +319,7 @@ class Engine:
                         self._capture_refused(e)
                 if full is not None:
                     arrays = (graph.batch.seq_slot, graph.batch.seq_len)
-                    if all(len(w) == 1 for _, _, w in ents):
+                    if one_each:
                         logits = full.clone()        # the graph's own tensor is overwritten by the next replay
                     else:
                         rows = [b for b, (_, _, w) in enumerate(ents) for _ in w]
@@ -321,12 +328,15 @@ class Engine:
                     batch = pack_step([(sl, packed.get(i, tk), w) for i, (sl, tk, w) in enumerate(ents)], lengths,
                                       tables, self.device)
                     self.h2d_bytes += batch.h2d_bytes
-                    logits = self.model.forward(batch, self.cache)
                     arrays = (batch.seq_slot, batch.seq_len)
+                    note = self._note_for(arrays, [s for s, _, _ in ents]) if greedy and one_each else None
+                    logits = self.model.forward(batch, self.cache, greedy, note)
             except BaseException:
                 self.cache.rollback(res)
                 raise
             self._launched(res, arrays)
+            if greedy and one_each and (full is None or graph.noted):
+                self.cache.note_sampled([s for s, _, _ in ents])
             if check:
                 self._settle(wait=True)
         return logits
@@ -338,12 +348,18 @@ class Engine:
         self.use_graphs = False
         self._graphs.clear()
 
-    def step_device(self, slots, token_source: torch.Tensor | None = None, rows=None) -> torch.Tensor:
+    def _note_for(self, arrays, slots):
+        if self.cache.header is None:
+            return None
+        return StepNote(self.cache, self.cache.header, slots, arrays[0], arrays[1])
+
+    def step_device(self, slots, token_source: torch.Tensor | None = None, rows=None, greedy: bool = False) -> torch.Tensor:
         """A decode step whose tokens are already on the device, so the host never waits for them: sequence i takes
         ``token_source[rows[i]]`` (int32, for instance the sampler's output of the step before) or, without a token
         source, the last token that the sampler noted in the sequence's header (see ``step_note``).
 
-        Returns logits [len(slots), vocab] (float32); the tensor may be the step's own buffer and holds only
+        Returns logits [len(slots), vocab] (float32), or with ``greedy`` the indices of their largest entries (int32
+        [len(slots)], also noted in the headers); the tensor may be the step's own buffer and holds only
         until the next step. Token ids are not checked on the host (they come from this library's sampler); one
         outside the vocabulary makes the embedding report a fault. The step is not settled here: call ``settle``
         or ``check`` (the generation loop does when it reads a step's tokens).
@@ -370,7 +386,7 @@ class Engine:
             res = self._begin(counts)
             try:
                 tables = res.tables
-                graph = self._decode_graph(ents, lengths) if self.use_graphs else None
+                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs else None
                 logits = None
                 if graph is not None:
                     try:
@@ -386,15 +402,17 @@ class Engine:
                     self.h2d_bytes += batch.h2d_bytes
                     idx = torch.tensor(rows, dtype=torch.int32).to(self.device)
                     K.gather_i32(token_source, idx, batch.tokens)
-                    logits = self.model.forward(batch, self.cache)
                     arrays = (batch.seq_slot, batch.seq_len)
+                    logits = self.model.forward(batch, self.cache, greedy, self._note_for(arrays, slots) if greedy else None)
             except BaseException:
                 self.cache.rollback(res)
                 raise
             self._launched(res, arrays)
+            if greedy and self.cache.header is not None:
+                self.cache.note_sampled(slots)
         return logits
 
-    def _decode_graph(self, ents, lengths):
+    def _decode_graph(self, ents, lengths, greedy: bool = False):
         """The graph for this decode step, or None when the step runs kernel by kernel."""
         if any(len(t) != 1 for _, t, _ in ents):
             return None
@@ -406,12 +424,12 @@ class Engine:
         if fused is not None and not fused.takes_sizes(len(ents), wide_bucket(max_len, self.page_size), self.cache):
             fused = None
         bucket = wide_bucket(max_len, self.page_size) if fused is not None else length_bucket(max_len, self.page_size)
-        key = (len(ents), bucket, fused is not None)
+        key = (len(ents), bucket, fused is not None, bool(greedy))
         g = self._graphs.get(key)
         if g is None:
             if not self._graphs.wants_capture(key):
                 return None                      # the first step of a kind also warms every kernel up
             # an evicted graph's buffers go back to the allocator only when no replay of it is in flight any more
-            g = self._graphs.put(key, DecodeGraph(self, key[0], key[1], fused),
+            g = self._graphs.put(key, DecodeGraph(self, key[0], key[1], fused, greedy),
                                  before_evict=lambda old: torch.cuda.synchronize(self.device))
         return g

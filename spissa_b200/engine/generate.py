@@ -83,7 +83,7 @@ def plan_batches(prompt_lens: list, max_new_tokens: int, token_budget: int, max_
     return batches
 
 
-def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics) -> int:
+def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics, greedy=False) -> int:
     """Decode ``live`` = [(request, slot)] to the end, one step ahead of the host. Returns the steps run.
 
     Every live request has its last token in ``results`` and on the host. A launch takes its tokens from the
@@ -132,14 +132,15 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
             break
         rows = [i for i, _ in nxt]
         order = [rs for _, rs in nxt]
-        if headers:
-            logits = engine.step_device([slot for _, slot in order])
-        else:
-            logits = engine.step_device([slot for _, slot in order], token_source, rows)
         step_no = emitted[order[0][0]]             # every request of a batch has the same count: they started together
-        if headers:
+        if greedy:
+            # the head keeps only the best candidate of each row: no logits exist, the step returns the tokens
+            token_source = engine.step_device([slot for _, slot in order], greedy=True)
+        elif headers:
+            logits = engine.step_device([slot for _, slot in order])
             token_source = sampler.sample(logits, params, [req for req, _ in order], step_no, note=engine.step_note())
         else:
+            logits = engine.step_device([slot for _, slot in order], token_source, rows)
             token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
         pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=on_gpu)
         pinned.copy_(token_source, non_blocking=True)
@@ -189,6 +190,9 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
             r.logits = []
     metrics = GenerationMetrics()
     t_start = time.perf_counter()
+    # greedy and nobody wants the logits: the engine's head returns the tokens and never writes a row of logits
+    # (the reference's greedy head does the same, crates/spissa-runtime/src/models/llama/session/mod.rs:662-669)
+    greedy = params.greedy and not return_logits and getattr(engine, "greedy_steps", False)
 
     def take(live, tokens, logits):
         """Record one new token per live request; return those that go on."""
@@ -216,9 +220,13 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
         live = [(req, engine.acquire()) for req in batch]
         try:
             t0 = time.perf_counter()
-            logits = engine.step([(slot, prompts[req], [len(prompts[req]) - 1]) for req, slot in live])
-            note = engine.step_note() if hasattr(engine, "step_note") else None
-            first = sampler.sample(logits, params, [r for r, _ in live], 0, **({"note": note} if note is not None else {}))
+            entries = [(slot, prompts[req], [len(prompts[req]) - 1]) for req, slot in live]
+            if greedy:
+                logits, first = None, engine.step(entries, greedy=True)
+            else:
+                logits = engine.step(entries)
+                note = engine.step_note() if hasattr(engine, "step_note") else None
+                first = sampler.sample(logits, params, [r for r, _ in live], 0, **({"note": note} if note is not None else {}))
             tokens = first.tolist()
             t1 = time.perf_counter()
             metrics.steps += 1
@@ -231,13 +239,18 @@ def generate(engine, sampler, prompts: list, max_new_tokens: int, params: Sampli
             step_no = 1
             if live and on_token is None and not return_logits and hasattr(engine, "step_device"):
                 t0 = time.perf_counter()
-                metrics.steps += _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics)
+                metrics.steps += _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, metrics,
+                                               greedy)
                 metrics.decode_ms += (time.perf_counter() - t0) * 1000.0
                 live = []
             while live:
                 t0 = time.perf_counter()
-                logits = engine.step([(slot, [results[req].tokens[-1]], [0]) for req, slot in live])
-                tokens = sampler.sample(logits, params, [r for r, _ in live], step_no).tolist()
+                entries = [(slot, [results[req].tokens[-1]], [0]) for req, slot in live]
+                if greedy:
+                    logits, tokens = None, engine.step(entries, greedy=True).tolist()
+                else:
+                    logits = engine.step(entries)
+                    tokens = sampler.sample(logits, params, [r for r, _ in live], step_no).tolist()
                 metrics.decode_ms += (time.perf_counter() - t0) * 1000.0
                 metrics.steps += 1
                 live = take(live, tokens, logits)

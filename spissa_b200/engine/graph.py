@@ -97,10 +97,14 @@ class GraphTable:
 class DecodeGraph:
     RING = 4
 
-    def __init__(self, engine, n_seqs: int, bucket: int, fused=None):
-        """``fused``: the one-kernel decode runner when it takes these steps (the split of the keys is then data)."""
+    def __init__(self, engine, n_seqs: int, bucket: int, fused=None, greedy: bool = False):
+        """``fused``: the one-kernel decode runner when it takes these steps (the split of the keys is then data).
+        ``greedy``: the captured step ends in the head's argmax and notes its tokens in the sequences' headers; what
+        ``run`` returns is then the tokens (int32 [B]), not logits."""
         self.engine, self.B, self.bucket = weakref.proxy(engine), n_seqs, bucket      # no cycle: engines free at once
         self.fused = fused
+        self.greedy = greedy
+        self.noted = greedy and engine.cache.header is not None
         dev = engine.device
         B = n_seqs
         self.P = bucket // engine.page_size
@@ -179,8 +183,12 @@ class DecodeGraph:
             gc.collect()
             gc.disable()
             try:
+                note = None
+                if self.noted:
+                    from .engine import StepNote
+                    note = StepNote(eng.cache, eng.cache.header, [], self.batch.seq_slot, self.batch.seq_len)
                 with torch.cuda.graph(graph, capture_error_mode="relaxed"):
-                    self.logits = eng.model.forward(self.batch, eng.cache)
+                    self.logits = eng.model.forward(self.batch, eng.cache, self.greedy, note)
             finally:
                 if was_enabled:
                     gc.enable()

@@ -65,8 +65,10 @@ class Model:
         return out
 
     # ------------------------------------------------------------------ forward
-    def forward(self, step, cache) -> torch.Tensor:
-        """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer."""
+    def forward(self, step, cache, greedy: bool = False, note=None) -> torch.Tensor:
+        """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer; with
+        ``greedy`` the indices of their largest entries instead (int32 [step.n_want]; the logits are never written
+        where the head has a kernel for that). ``note``: see ``LMHead.greedy``."""
         h = self.embedding.forward(step)
         if self.fuse_decode and self._fused is False:
             from .fused_decode import FusedDecode
@@ -77,6 +79,19 @@ class Model:
             for e in self.spec.schedule:
                 self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))
         if step.n_want == 0:
+            if greedy:
+                return torch.empty(0, dtype=torch.int32, device=h.device)
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=h.device)
         x = self.final_norm.forward(h, rows=step.want_rows)
-        return self.head.forward(x)
+        if not greedy:
+            return self.head.forward(x)
+        tokens = self.head.greedy(x, note) if hasattr(self.head, "greedy") else None
+        if tokens is None:
+            # a head without such a kernel, or operands it does not take (32-bit, odd sizes): the logits, then their argmax
+            from ..csrc import lib as K
+            logits = self.head.forward(x)
+            tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+            K.argmax_rows(logits, tokens)
+            if note is not None:
+                K.header_note(note.header, note.seq_slot, note.seq_len, tokens)
+        return tokens

@@ -58,8 +58,17 @@ class ChatSession:
         stop = set(int(s) for s in stop_ids)
         t0 = time.perf_counter()
         feed = ([self.pending] if self.pending is not None else []) + list(user_tokens)
-        logits = self.engine.step([(self.slot, feed, [len(feed) - 1])])
-        tok = int(self.sampler.sample(logits, self.params, [0], self.turn * 1_000_003).tolist()[0])
+        # greedy and nobody wants the logits: the head returns the token and writes no logits, as the reference's does
+        # (crates/spissa-runtime/src/models/llama/session/mod.rs:662-669)
+        greedy = self.params.greedy and not keep_logits and getattr(self.engine, "greedy_steps", False)
+
+        def next_token(tokens, want, draw):
+            if greedy:
+                return int(self.engine.step([(self.slot, tokens, want)], greedy=True).tolist()[0]), None
+            logits = self.engine.step([(self.slot, tokens, want)])
+            return int(self.sampler.sample(logits, self.params, [0], draw).tolist()[0]), logits
+
+        tok, logits = next_token(feed, [len(feed) - 1], self.turn * 1_000_003)
         t1 = time.perf_counter()
         first_logits = logits[0].float().cpu() if keep_logits else None
         self.history.extend(user_tokens)
@@ -76,8 +85,7 @@ class ChatSession:
                 break
             if len(out) >= max_new_tokens:
                 break
-            logits = self.engine.step([(self.slot, [tok], [0])])
-            tok = int(self.sampler.sample(logits, self.params, [0], self.turn * 1_000_003 + step).tolist()[0])
+            tok, _ = next_token([tok], [0], self.turn * 1_000_003 + step)
             step += 1
         t2 = time.perf_counter()
         self.turn += 1

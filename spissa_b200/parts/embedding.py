@@ -63,3 +63,19 @@ class LMHead(Part):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.proj(x, out_dtype=torch.float32)
+
+    def greedy(self, x: torch.Tensor, note=None):
+        """The index of the largest logit of every row (int32 [rows]) without the logits, as the reference's greedy
+        head keeps only (best index, best value) while it streams the rows
+        (crates/spissa-runtime/src/streaming/linear_argmax.rs:13, streaming/argmax.rs:30-51): the lowest index wins
+        among equal logits. None when no kernel takes these operands (the caller then asks for the logits).
+        ``note``: the tokens also go into the per-slot headers (an engine's ``step_note()``)."""
+        w = self.proj.weight
+        if not K.head_argmax_supported(x, w):
+            return None
+        rows = x.shape[0]
+        n_cand = K.head_argmax_candidates(rows, w.shape[0])
+        cand = torch.empty(rows, n_cand, 2, dtype=torch.float32, device=x.device)
+        out = torch.empty(rows, dtype=torch.int32, device=x.device)
+        K.head_argmax(x, w, cand, out, note)
+        return out

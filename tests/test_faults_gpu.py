@@ -87,7 +87,7 @@ def test_a_forward_pass_that_raises_gives_the_pages_back(model, monkeypatch):
     engine.step([(slot, [1, 2, 3], [])])
     before = books(engine)
 
-    def boom(step, cache):
+    def boom(*args, **kwargs):
         raise KernelError("injected")
     monkeypatch.setattr(engine.model, "forward", boom)
     with pytest.raises(KernelError, match="injected"):

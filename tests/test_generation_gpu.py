@@ -277,3 +277,29 @@ def test_command_line_generate(folders, tmp_path):
     first = torch.tensor(json.loads(logits_out.read_text())["first_step_logits"][0], dtype=torch.float64)
     ref = P.model_logits(pcfg, w, [5, 6, 7], torch.float64)[-1]
     assert float((first - ref).abs().max()) <= tiny.TOL["float32"] * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("name,n_seqs", [("A", 3), ("E", 5), ("E", 20)])
+def test_greedy_generation_in_bfloat16_never_writes_logits(folders, name, n_seqs, monkeypatch):
+    """Greedy and nobody asked for logits: the head keeps the best candidate while it streams its rows (up to 16
+    sequences through the weight-streaming kernel, more through the tensor-core one) and returns tokens."""
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    prompts = [tiny.random_prompt(V, 3 + 7 * i, 11 * i + 1) for i in range(n_seqs)]
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 2 * n_seqs, max_seqs=n_seqs)
+
+    def no_logits(x):
+        raise AssertionError("the head was asked for logits in a greedy generation")
+    monkeypatch.setattr(engine.model.head, "forward", no_logits)
+    results, _ = engine.generate(prompts, 9, SamplingParams(), stop_ids=[])
+    heard = []
+    stepwise, _ = engine.generate(prompts[:2], 5, SamplingParams(), stop_ids=[], on_token=lambda r, t: heard.append(t) or True)
+    assert len(heard) == 10 and [r.tokens for r in stepwise] == [r.tokens[:5] for r in results[:2]]
+    for p, r in list(zip(prompts, results))[:6]:
+        ids = list(p)
+        assert len(r.tokens) == 9
+        for tok in r.tokens:                               # teacher-forced along the engine's own tokens
+            row = P.model_logits(pcfg, w, ids, torch.float64)[-1]
+            assert float(row.max() - row[tok]) <= tiny.TOL["bfloat16"] * float(row.abs().max()) * 2
+            ids.append(tok)
+    engine.cache.check()

@@ -743,3 +743,62 @@ def test_gemv_repeats_bit_for_bit(K, M, N, K_):
         out = base.clone()
         K.gemv(x, w, out, K.TC_ACCUMULATE)
         assert torch.equal(out, first), f"launch {i + 2} differs from the first"
+
+
+# ------------------------------------------------------------------ the greedy head: argmax without logits
+def _head_argmax(K, x, w):
+    M, N = x.shape[0], w.shape[0]
+    n_cand = K.head_argmax_candidates(M, N)
+    cand = torch.full((M, n_cand, 2), float("nan"), dtype=torch.float32, device=DEV)
+    out = torch.full((M,), -7, dtype=torch.int32, device=DEV)
+    K.head_argmax(x, w, cand, out)
+    return out.cpu()
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,Kd", [(333, 72), (1000, 200), (5000, 512), (128256, 256)])
+def test_head_argmax_equals_the_argmax_of_the_logits(K, M, N, Kd):
+    torch.manual_seed(M * 1000 + N)
+    x = torch.randn(M, Kd, device=DEV).bfloat16()
+    w = torch.randn(N, Kd, device=DEV).bfloat16()
+    logits = x.double() @ w.double().t()
+    got = _head_argmax(K, x, w)
+    want = logits.argmax(dim=1).cpu()
+    top2 = logits.topk(2, dim=1).values
+    for m in range(M):
+        # the product's float32 sums may order two logits that lie within rounding of each other differently
+        if int(got[m]) != int(want[m]):
+            assert float(top2[m, 0] - logits[m, int(got[m])]) <= 1e-3 * float(top2[m, 0].abs()), (m, int(got[m]), int(want[m]))
+
+
+@pytest.mark.parametrize("M", [2, 16, 40])
+def test_head_argmax_takes_the_lowest_of_equal_maxima(K, M):
+    """Equal maxima in rows that different lanes, warps, tiles and CTAs own: the lowest index wins, as a serial scan
+    with a strict ``>`` chooses (crates/spissa-runtime/src/ops.rs:309-324, streaming/argmax.rs:85-97)."""
+    N, Kd = 20000, 64
+    torch.manual_seed(3)
+    w = (torch.randn(N, Kd, device=DEV) * 0.01).bfloat16()
+    x = torch.zeros(M, Kd, device=DEV).bfloat16()
+    x[:, 0] = 1.0
+    twins = [[5, 6], [3, 5 + 8], [7, 40], [130, 129], [9000, 31], [19999, 17000, 12345], [256, 128], [1, 0]]
+    for m in range(M):
+        rows = twins[m % len(twins)]
+        wm = w.clone()
+        wm[:, 0] = 0.0
+        for r in rows:
+            wm[r] = 0.0
+            wm[r, 0] = 2.0                      # exactly equal logits, larger than all others
+        got = _head_argmax(K, x[m:m + 1].expand(M, Kd).contiguous(), wm)
+        assert got.tolist() == [min(rows)] * M, (rows, got.tolist())
+
+
+def test_head_argmax_ignores_nan_and_rows_beyond_the_table(K):
+    N, Kd = 1003, 64                            # the last tile of 8 and of 128 rows is ragged
+    torch.manual_seed(5)
+    w = torch.randn(N, Kd, device=DEV).bfloat16()
+    w[77] = float("nan")
+    for M in (4, 20):
+        x = torch.randn(M, Kd, device=DEV).bfloat16()
+        logits = x.double() @ w.double().t()
+        logits[:, 77] = -float("inf")
+        assert torch.equal(_head_argmax(K, x, w), logits.argmax(dim=1).cpu().int())

@@ -172,6 +172,30 @@ def kernel_case(name: str, reps: int) -> int:
         torch.cuda.synchronize()
         print(json.dumps({"kernel_case": name, "launches": K.launches}))
         return 0
+    if name == "prefill":
+        # prompts of 2,048 tokens one after another through the engine's own step (the launch list of this run is
+        # what profiles/prefill_launches.md summarises)
+        from spissa_b200 import Engine, LlamaConfig
+        cfg = dict(CONFIG_1B)
+        if KERNEL_CASE_LAYERS:
+            cfg["num_hidden_layers"] = KERNEL_CASE_LAYERS
+        eng = Engine.from_config(LlamaConfig.from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=2 * CONTEXT, max_seqs=2)
+        rng = random.Random(0)
+        times = []
+        for i in range(max(2, reps)):
+            sl = eng.acquire()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            l0 = K.launches
+            e0.record()
+            eng.step([(sl, [rng.randrange(V) for _ in range(T)], [T - 1])], greedy=True, check=False)
+            e1.record()
+            torch.cuda.synchronize()
+            eng.check()
+            times.append(e0.elapsed_time(e1))
+            eng.release(sl)
+        print(json.dumps({"kernel_case": name, "layers": cfg["num_hidden_layers"], "ms": [round(t, 3) for t in times],
+                          "launches_per_step": K.launches - l0}))
+        return 0
     if name == "decode_layers":
         # the one-kernel decode path alone: eight 2,048-token prompts, then decode steps launched one by one; the
         # last one records the global timer as CTA 0 enters and leaves each grid barrier (phase times per layer)
@@ -224,6 +248,35 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=torch.float32 if mode == K.TC_ACCUMULATE else bf, device=dev)
         run = lambda i: K.tc_gemm(a, ws[i % n_buf], out, mode, bn)
         flops = 2.0 * T * N * Kd
+    elif name in ("fused_qkv", "fused_o", "fused_gate_up", "fused_down"):
+        # the same products with the epilogues of a fused prompt step (engine/fused_prefill.py)
+        from spissa_b200.parts.linear import tile_width
+        N, Kd = {"fused_qkv": (3072, H), "fused_o": (H, H), "fused_gate_up": (2 * I, H), "fused_down": (H, I)}[name]
+        n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [rnd(N, Kd) for _ in range(n_buf)]
+        a = rnd(T, Kd)
+        ssq = torch.rand(T, 8, device=dev) + 1.0
+        flops = 2.0 * T * N * Kd
+        if name == "fused_qkv":
+            bn = tile_width(T, N, 148)
+            pages = T // 64
+            kp, vp = rnd(pages, nkv, 64, hd), rnd(pages, nkv, 64, hd)
+            q = torch.empty(T, nh * hd, dtype=bf, device=dev)
+            cs = torch.rand(T, hd // 2, 2, device=dev)
+            pos = torch.arange(T, dtype=torch.int32, device=dev)
+            tok_page = (pos // 64).int()
+            rope = dict(cs=cs, tok_page=tok_page, positions=pos, q_out=q, k_pool=kp, v_pool=vp, nh=nh, nkv=nkv, hd=hd, page_size=64)
+            run = lambda i: K.tc_gemm_fused(a, ws[i % n_buf], None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H, eps=1e-5, rope=rope)
+        elif name == "fused_gate_up":
+            out = torch.empty(T, I, dtype=bf, device=dev)
+            run = lambda i: K.tc_gemm_fused(a, ws[i % n_buf], out, K.TC_SILU_MUL, 256, row_ssq=ssq, norm_width=H, eps=1e-5)
+        else:
+            bn = tile_width(T, N, 148)
+            out = torch.zeros(T, N, device=dev)
+            xw = torch.empty(T, N, dtype=bf, device=dev)
+            nw = rnd(N)
+            so = torch.empty(T, K.tc_gemm_n_tiles(N, bn), device=dev)
+            run = lambda i: K.tc_gemm_fused(a, ws[i % n_buf], out, K.TC_ACCUMULATE, bn, xw=xw, next_w=nw, ssq_out=so)
     elif name in ("stream_qkv", "stream_o", "stream_gate_up", "stream_down"):
         # the products of a decode step of 64 sequences: tc_stream.cu
         N, Kd, mode, pair = {"stream_qkv": (3072, H, K.TC_STORE, 0), "stream_o": (H, H, K.TC_ACCUMULATE, 0),
@@ -337,7 +390,7 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8) instead of the step")
+                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()
@@ -409,9 +462,9 @@ def main() -> int:
         toks = [rng.randrange(V) for _ in range(batch)]
 
         def one():
-            # launched back to back: the steps are confirmed (status word read) by ``engine.check()`` after the timing
-            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)], check=False)
-            return sampler.sample(logits, greedy, list(range(batch)), 0)
+            # launched back to back: the steps are confirmed (status word read) by ``engine.check()`` after the timing;
+            # greedy: the head returns the tokens (no logits are written), as in ``Engine.generate``
+            return engine.step([(s, [t], [0]) for s, t in zip(slots, toks)], check=False, greedy=True)
 
         for _ in range(warmup):
             one()
@@ -468,10 +521,10 @@ def main() -> int:
         s = engine.acquire()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        logits = engine.step([(s, prompt, [PREFILL_TOKENS - 1])])
-        sampler.sample(logits, greedy, [0], 0)
+        engine.step([(s, prompt, [PREFILL_TOKENS - 1])], check=False, greedy=True)       # ends with the first token chosen
         e1.record()
         torch.cuda.synchronize()
+        engine.check()
         engine.release(s)
         return e0.elapsed_time(e1)
 

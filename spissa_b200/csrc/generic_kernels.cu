@@ -702,6 +702,61 @@ SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld
 }
 
 
+// ============================================================== per-step tables for fused prompt kernels
+// Once per step and cache group, for every token of the step: the cosines and sines of its rotation angles
+// (angle = position · inv_freq[i], float32, accurate cosf / sinf: crates/spissa-runtime/src/rotary.rs:454-465) and the
+// cache page that holds its position. Every layer's QKV product reads them in its epilogue.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                  const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
+                                  int page_size, const float* __restrict__ inv_freq, int half, int T,
+                                  float2* __restrict__ cs, int* __restrict__ tok_page) {
+    const int t = blockIdx.x;
+    if (t >= T) return;
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float ang = (float)pos * inv_freq[i];
+        cs[(size_t)t * half + i] = make_float2(cosf(ang), sinf(ang));
+    }
+    if (threadIdx.x == 0 && tok_page)
+        tok_page[t] = page_table[(size_t)seq_row[token_seq[t]] * max_pages + pos / page_size];
+}
+
+SP_API int sp_rope_table(const int* positions, const int* token_seq, const int* seq_row, const int* page_table,
+                         int max_pages, int page_size, const float* inv_freq, int half, int T, void* cs, int* tok_page,
+                         cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (half <= 0 || !inv_freq) SP_FAIL("rope_table: a frequency table of at least one entry is needed");
+    if (tok_page && (!page_table || page_size <= 0)) SP_FAIL("rope_table: the tokens' pages need the page table");
+    rope_table_kernel<<<T, half >= 64 ? 64 : 32, 0, stream>>>(positions, token_seq, seq_row, page_table, max_pages, page_size,
+                                                            inv_freq, half, T, (float2*)cs, tok_page);
+    SP_CHECK_LAUNCH("rope_table");
+    return 0;
+}
+
+// The first norm of a fused prompt step: xw = x ⊙ w (bfloat16, the next product's input) and the rows' sums of
+// squares; the product multiplies its result by 1/rms (crates/spissa-runtime/src/ops.rs:159-179 is the norm).
+__global__ void norm_prepare_kernel(const float* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                    __nv_bfloat16* __restrict__ xw, float* __restrict__ ssq, int T, int H) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    if (r >= T) return;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float v = x[(size_t)r * H + c];
+        ss = fmaf(v, v, ss);
+        xw[(size_t)r * H + c] = __float2bfloat16_rn(v * __bfloat162float(w[c]));
+    }
+    ss = sp_block_sum(ss, scratch);
+    if (threadIdx.x == 0) ssq[r] = ss;
+}
+
+SP_API int sp_norm_prepare(const float* x, const void* w, void* xw, float* ssq, int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    norm_prepare_kernel<<<T, 256, 0, stream>>>(x, (const __nv_bfloat16*)w, (__nv_bfloat16*)xw, ssq, T, H);
+    SP_CHECK_LAUNCH("norm_prepare");
+    return 0;
+}
+
 // ============================================================== the best of a row of candidates
 // Second stage of the greedy head: the head's product kept, per token, one (value, row) candidate for each of its
 // tiles (``cand`` [rows][ld] pairs of float, int32; a tile without a winner has row 0x7fffffff). One CTA per token

@@ -361,6 +361,92 @@ def tc_gemm(a, w, out, mode=TC_STORE, bn=128):
         c_void_p(_stream())))
 
 
+class _EpiArgs(ctypes.Structure):
+    """Mirror of ``EpiArgs`` in tc_gemm.cu."""
+    _fields_ = [("row_ssq", c_void_p), ("n_ssq", c_int), ("norm_width", c_int), ("eps", c_float), ("pad0", c_int),
+                ("xw", c_void_p), ("next_w", c_void_p), ("ssq_out", c_void_p),
+                ("cs", c_void_p), ("tok_page", c_void_p), ("positions", c_void_p),
+                ("q_out", c_void_p), ("kpool", c_void_p), ("vpool", c_void_p),
+                ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("page_size", c_int)]
+
+
+TC_QKV_ROPE = 3
+
+
+def tc_gemm_n_tiles(N: int, bn: int) -> int:
+    return (int(N) + int(bn) - 1) // int(bn)
+
+
+def tc_gemm_fused(a, w, out, mode, bn, row_ssq=None, norm_width=0, eps=0.0, xw=None, next_w=None, ssq_out=None,
+                  rope=None):
+    """``tc_gemm`` with an epilogue that saves a pass over a prompt's activations.
+
+    ``row_ssq`` [M, n] float32: ``a`` holds x ⊙ w of an RMS norm over ``norm_width`` columns without its 1/rms; the
+    result is multiplied by 1/sqrt(sum(row_ssq[m]) / norm_width + eps).
+    ``xw``, ``next_w``, ``ssq_out`` (mode TC_ACCUMULATE): besides out += a·wᵀ, xw = new out ⊙ next_w (bfloat16) and
+    ssq_out[m, tile] = the new row's sum of squares over each tile's columns ([M, tc_gemm_n_tiles(N, bn)]).
+    ``rope`` (mode TC_QKV_ROPE; ``out`` None): dict(cs, tok_page, positions, q_out, k_pool, v_pool, nh, nkv, hd,
+    page_size): q and k are rotated with the (cos, sin) table, q stored, k and v written into the paged cache.
+    """
+    lib = load("tc_gemm")
+    M, K = a.shape
+    N = w.shape[0]
+    ep = _EpiArgs()
+    if row_ssq is not None:
+        if row_ssq.dtype != torch.float32 or row_ssq.dim() != 2 or row_ssq.shape[0] < M or not row_ssq.is_contiguous():
+            raise KernelError("tc_gemm_fused: the row statistics are a contiguous float32 [M, n] tensor")
+        ep.row_ssq, ep.n_ssq, ep.norm_width, ep.eps = _ptr(row_ssq), row_ssq.shape[1], int(norm_width), float(eps)
+    if xw is not None:
+        n_tiles = tc_gemm_n_tiles(N, bn)
+        if (xw.dtype != torch.bfloat16 or tuple(xw.shape) != (M, N) or not xw.is_contiguous() or next_w.dtype != torch.bfloat16
+                or next_w.numel() != N or ssq_out.dtype != torch.float32 or tuple(ssq_out.shape) != (M, n_tiles)
+                or not ssq_out.is_contiguous()):
+            raise KernelError(f"tc_gemm_fused: xw [M, N] and next_w [N] are bfloat16, ssq_out float32 [M, {n_tiles}]")
+        ep.xw, ep.next_w, ep.ssq_out = _ptr(xw), _ptr(next_w), _ptr(ssq_out)
+    if mode == TC_QKV_ROPE:
+        r = rope
+        _need_contig(r["cs"], r["tok_page"], r["positions"], r["q_out"])
+        if r["q_out"].dtype != torch.bfloat16 or r["k_pool"].dtype != torch.bfloat16 or r["cs"].dtype != torch.float32:
+            raise KernelError("tc_gemm_fused: q and the cache are bfloat16, the angle table float32")
+        ep.cs, ep.tok_page, ep.positions = _ptr(r["cs"]), _ptr(r["tok_page"]), _ptr(r["positions"])
+        ep.q_out, ep.kpool, ep.vpool = _ptr(r["q_out"]), _ptr(r["k_pool"]), _ptr(r["v_pool"])
+        ep.nh, ep.nkv, ep.hd, ep.page_size = int(r["nh"]), int(r["nkv"]), int(r["hd"]), int(r["page_size"])
+        c_ptr, c_dt, ldc = None, BF16, 0
+    else:
+        want_cols = N // 2 if mode == TC_SILU_MUL else N
+        if out.shape[0] != M or out.shape[1] != want_cols or out.stride(1) != 1:
+            raise KernelError(f"tc_gemm_fused: out {tuple(out.shape)} does not fit a {tuple(a.shape)}, w {tuple(w.shape)}")
+        c_ptr, c_dt, ldc = _ptr(out), dt_code(out), out.stride(0)
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError("tc_gemm takes bfloat16 operands")
+    _check("tc_gemm", lib.sp_tc_gemm_fused(
+        c_void_p(_ptr(a)), c_void_p(_ptr(w)), c_void_p(c_ptr), c_dt, M, N, K, a.stride(0), w.stride(0), ldc,
+        int(mode), int(bn), ctypes.byref(ep), c_void_p(_ptr(status_word(a.device))), c_void_p(_stream())))
+
+
+def rope_table(meta, inv_freq, half, cs, tok_page):
+    """cs[t, i] = (cos, sin)(position[t] · inv_freq[i]) and tok_page[t] = the cache page of token t's position."""
+    lib = load("generic")
+    T = cs.shape[0]
+    pt = meta.page_table
+    _need_contig(cs, tok_page, inv_freq)
+    _check("generic", lib.sp_rope_table(
+        c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.seq_slot)),
+        c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, c_void_p(_ptr(inv_freq)), int(half), T, c_void_p(_ptr(cs)),
+        c_void_p(_ptr(tok_page)), c_void_p(_stream())))
+
+
+def norm_prepare(x, w, xw, ssq):
+    """xw = x ⊙ w (bfloat16) and ssq[r] = sum of x[r]² for the float32 residual ``x`` [T, H]."""
+    lib = load("generic")
+    T, H = x.shape
+    _need_contig(x, w, xw, ssq)
+    if x.dtype != torch.float32 or w.dtype != torch.bfloat16 or xw.dtype != torch.bfloat16 or ssq.dtype != torch.float32:
+        raise KernelError("norm_prepare: float32 residual and sums, bfloat16 weight and output")
+    _check("generic", lib.sp_norm_prepare(c_void_p(_ptr(x)), c_void_p(_ptr(w)), c_void_p(_ptr(xw)), c_void_p(_ptr(ssq)),
+                                          T, H, c_void_p(_stream())))
+
+
 # ------------------------------------------------------------------ flash attention (bfloat16)
 def flash_supported(q: torch.Tensor, k_pool: torch.Tensor, nh: int, nkv: int, hd: int, page_size: int) -> bool:
     """Whether the tensor-core attention kernels take this shape; else the generic kernel runs."""

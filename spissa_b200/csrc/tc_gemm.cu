@@ -17,6 +17,16 @@
 // Every wait on an mbarrier is bounded by a wall-clock limit; when it runs out the kernel
 // records a code in ``status``, every role falls through to the common exit, and tensor
 // memory is freed. No load uses cluster multicast.
+//
+// Epilogues that save a pass over the activations of a prompt (the reference's block does norm, projections,
+// rotation and cache append phase by phase, crates/spissa-runtime/src/models/llama/generate.rs:193-199, :373-390,
+// :410-416, :459-471):
+//   * an RMS norm costs no kernel: whoever adds into the 32-bit residual (the output and down projections) also
+//     stores the new residual times the NEXT norm's weight in bfloat16 (the next product's A) and the row's sum of
+//     squares over its tile's columns; the next product adds those partial sums in tile order and multiplies its
+//     RESULT by 1/rms: y = rstd · (x ⊙ w)·Wᵀ;
+//   * the QKV product rotates q and k (rotate-half, cosines and sines from a per-token table made once per step),
+//     stores q and writes k and v into the paged cache at each token's position.
 #include "tcgen05.cuh"
 
 SP_API const char* sp_tc_gemm_last_error() { return sp_error_text; }
@@ -27,14 +37,45 @@ constexpr int BM = 128;
 constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle span
 constexpr int UMMA_K = 16;
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_QKV_ROPE = 3 };
+
+// What the fused epilogues need beyond C; all zero for the plain ones. The host mirrors this layout.
+struct EpiArgs {
+    // the rows of A are x ⊙ w of an RMS norm without its 1/rms: the result is multiplied by it here
+    const float* row_ssq;          // [M][n_ssq] partial sums of squares of the residual rows (null: no scaling)
+    int n_ssq, norm_width;         // norm_width: the residual's width H (1/rms = 1/sqrt(sum/H + eps))
+    float eps;
+    int pad0;
+    // MODE_ACCUMULATE: also prepare the next norm's input
+    __nv_bfloat16* xw;             // [M][N] new C ⊙ next_w (null: plain accumulation)
+    const __nv_bfloat16* next_w;   // [N]
+    float* ssq_out;                // [M][tiles along N] sums of squares of the new C over each tile's columns
+    // MODE_QKV_ROPE: W = [q heads | k heads | v heads] x head_dim rows
+    const float2* cs;              // [M][hd / 2] (cos, sin) of each token's angles
+    const int* tok_page;           // [M] the cache page that holds the token's position
+    const int* positions;          // [M]
+    __nv_bfloat16* q_out;          // [M][nh * hd]
+    __nv_bfloat16* kpool;          // [pages][nkv][page_size][hd]
+    __nv_bfloat16* vpool;
+    int nh, nkv, hd, page_size;
+};
+static_assert(sizeof(EpiArgs) == 112, "the host packs this layout");
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    uint4 w;
+    w.x = *(uint32_t*)&p0; w.y = *(uint32_t*)&p1; w.z = *(uint32_t*)&p2; w.w = *(uint32_t*)&p3;
+    return w;
+}
 
 template <int BN, int STAGES>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024;      // + slack to align to 1024
+    static constexpr int TRANSPOSE_BYTES = 4 * 32 * 36 * 4;        // a 32 x 32 float tile (rows padded to 36) per epilogue warp
+    static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + TRANSPOSE_BYTES;      // + slack to align to 1024
 };
 
 // Stores 32 consecutive columns of one row, held as float32 in ``v``, the way ``mode`` asks.
@@ -87,7 +128,8 @@ __device__ __forceinline__ void store_row32(void* C, int c_dt, size_t base, int 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-               void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status) {
+               void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status,
+               const __grid_constant__ EpiArgs ep) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -181,13 +223,196 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
             const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
             const uint32_t buf = it & 1u, use = it >> 1;
+            const int row = m0 + q * 32 + lane;
+            constexpr int SPAN = 32;
+            // What the epilogue reads from global memory does not depend on the accumulator: it is asked for now,
+            // while the tile's products still run, and costs no waiting afterwards. (A load's round trip is a
+            // microsecond under load; a tile has up to eight chunks.)
+            float ssq_sum = 0.0f;                                   // the row's partial sums of squares, in tile order
+            if (ep.row_ssq && row < M)
+                for (int i = 0; i < ep.n_ssq; ++i) ssq_sum += __ldg(ep.row_ssq + (size_t)row * ep.n_ssq + i);
+            // The accumulating epilogue that also prepares the next norm regroups each 32 x 32 chunk so that eight
+            // lanes cover the 128 bytes of one row (a lane: 4 columns of rows sub, sub + 4, ... sub + 28): a warp's
+            // load or store of the residual then touches 4 whole lines instead of a piece of 32 lines.
+            const bool emit = mode == MODE_ACCUMULATE && ep.xw != nullptr;
+            const int sub = lane >> 3, c4 = (lane & 7) * 4;
+            const int rows_here = min(32, M - (m0 + q * 32));                       // rows of this warp that exist (may be <= 0)
+            const bool wide_ok = ((ldc & 3) == 0) && ((N & 3) == 0) && ((((uintptr_t)C | (uintptr_t)ep.xw) & 15) == 0);
+            float* cbase = (float*)C + (size_t)(m0 + q * 32 + sub) * ldc + n0 + c4;
+            constexpr int AHEAD = 2;                                // chunks of the old residual in flight
+            float4 old[AHEAD][8];
+            auto fetch_old = [&](int c0, float4 (&o)[8]) {
+                if (c0 < BN && n0 + c0 + c4 + 4 <= N) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        if (sub + 4 * k < rows_here) o[k] = *(const float4*)(cbase + (size_t)(4 * k) * ldc + c0);
+                }
+            };
+            if (emit && wide_ok) {
+#pragma unroll
+                for (int u = 0; u < AHEAD; ++u) fetch_old(u * SPAN, old[u]);
+            }
+            float4 cs_reg[16];                                      // (cos, sin) of 32 dims of this thread's token
+            int pos = 0, page = 0;
+            if (mode == MODE_QKV_ROPE && row < M) {
+                pos = __ldg(ep.positions + row);
+                page = __ldg(ep.tok_page + row);
+                const float4* t4 = (const float4*)(ep.cs + (size_t)row * (ep.hd >> 1));
+#pragma unroll
+                for (int j = 0; j < 16; ++j) cs_reg[j] = __ldg(t4 + j);
+            }
             const bool ok = mbar_wait(smem_u32(&bar_acc_full[buf]), use & 1u, status, 103);
             tc_fence_after();
             if (!ok || (status && *(volatile int*)status != 0)) break;
-            const int row = m0 + q * 32 + lane;
             const uint32_t taddr = tmem_base + buf * ACC_STRIDE + ((uint32_t)(q * 32) << 16);
-            constexpr int SPAN = 32;
             const int c_end = (mode == MODE_SILU_MUL) ? BN / 2 : BN;
+            // 1/rms of this thread's row
+            const float rstd = ep.row_ssq ? 1.0f / sqrtf(ssq_sum / (float)ep.norm_width + ep.eps) : 1.0f;
+            if (mode == MODE_QKV_ROPE) {
+                // the tile holds whole heads; dims d and d + hd/2 of a head are rotation partners
+                const int hd = ep.hd, half = hd >> 1, heads_here = BN / hd;
+#pragma unroll 1
+                for (int hh = 0; hh < heads_here; ++hh) {
+                    const int col0 = n0 + hh * hd;
+                    const int blk = col0 / hd;                          // q heads, then k heads, then v heads
+                    const bool live = row < M && col0 < N;
+                    __nv_bfloat16* dst = nullptr;
+                    if (live) {
+                        if (blk < ep.nh) dst = ep.q_out + ((size_t)row * ep.nh + blk) * hd;
+                        else {
+                            const bool is_k = blk < ep.nh + ep.nkv;
+                            const int kvh = is_k ? blk - ep.nh : blk - ep.nh - ep.nkv;
+                            dst = (is_k ? ep.kpool : ep.vpool) +
+                                  (((size_t)page * ep.nkv + kvh) * ep.page_size + pos % ep.page_size) * hd;
+                        }
+                    }
+                    const bool rotate = blk < ep.nh + ep.nkv;
+#pragma unroll 1
+                    for (int c = 0; c < half; c += SPAN) {
+                        uint32_t ra[32], rb[32];
+                        if (half > SPAN && live && rotate && !(hh == 0 && c == 0)) {
+                            // head size 128: the table's other half (one half per head otherwise: loaded once per tile)
+                            const float4* t4 = (const float4*)(ep.cs + (size_t)row * half + c);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) cs_reg[j] = __ldg(t4 + j);
+                        }
+                        tc_ld_32x32(taddr + (uint32_t)(hh * hd + c), ra);
+                        tc_ld_32x32(taddr + (uint32_t)(hh * hd + half + c), rb);
+                        tc_ld_wait();
+                        if (hh == heads_here - 1 && c + SPAN >= half) {
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                        }
+                        if (!live) continue;
+                        float lo[32], hi[32];
+                        if (rotate) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float4 cc = cs_reg[j >> 1];                       // cos, sin of two dims
+                                const float a0 = __uint_as_float(ra[j]) * rstd, b0 = __uint_as_float(rb[j]) * rstd;
+                                const float a1 = __uint_as_float(ra[j + 1]) * rstd, b1 = __uint_as_float(rb[j + 1]) * rstd;
+                                lo[j] = a0 * cc.x - b0 * cc.y;
+                                hi[j] = b0 * cc.x + a0 * cc.y;
+                                lo[j + 1] = a1 * cc.z - b1 * cc.w;
+                                hi[j + 1] = b1 * cc.z + a1 * cc.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                lo[j] = __uint_as_float(ra[j]) * rstd;
+                                hi[j] = __uint_as_float(rb[j]) * rstd;
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            *(uint4*)(dst + c + j) = pack8_bf16(lo + j);
+                            *(uint4*)(dst + half + c + j) = pack8_bf16(hi + j);
+                        }
+                    }
+                }
+                continue;
+            }
+            if (emit) {
+                // new residual = C + product; its product with the next norm's weight; its sum of squares
+                float* tr = (float*)(smem_raw + (smem_base - smem_u32(smem_raw)) + STAGES * L::STAGE_BYTES) + q * (32 * 36);
+                __nv_bfloat16* xbase = ep.xw + (size_t)(m0 + q * 32 + sub) * N + n0 + c4;
+                float part[8];                                        // this lane's share of the sums of squares of its 8 rows
+#pragma unroll
+                for (int k = 0; k < 8; ++k) part[k] = 0.0f;
+#pragma unroll
+                for (int ci = 0; ci < BN / SPAN; ++ci) {
+                    const int c0 = ci * SPAN;
+                    uint32_t r[32];
+                    tc_ld_32x32(taddr + (uint32_t)c0, r);
+                    tc_ld_wait();
+                    if (c0 + SPAN >= BN) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                    }
+                    // lane = row becomes (lane / 8 = row mod 4, lane % 8 = four columns): through this warp's own tile
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *(float4*)(tr + lane * 36 + 4 * j) = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                    __syncwarp();
+                    float4 acc[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] = *(const float4*)(tr + (sub + 4 * k) * 36 + c4);
+                    __syncwarp();
+                    const int col = n0 + c0 + c4;
+                    if (wide_ok && col + 4 <= N) {
+                        const uint2 wq = __ldg((const uint2*)(ep.next_w + col));
+                        const float2 w01 = __bfloat1622float2(*(const __nv_bfloat162*)&wq.x);
+                        const float2 w23 = __bfloat1622float2(*(const __nv_bfloat162*)&wq.y);
+                        float4 (&o)[8] = old[ci % AHEAD];
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            if (sub + 4 * k < rows_here) {
+                                const float4 v = make_float4(o[k].x + acc[k].x, o[k].y + acc[k].y, o[k].z + acc[k].z, o[k].w + acc[k].w);
+                                *(float4*)(cbase + (size_t)(4 * k) * ldc + c0) = v;
+                                __nv_bfloat162 p0 = __floats2bfloat162_rn(v.x * w01.x, v.y * w01.y);
+                                __nv_bfloat162 p1 = __floats2bfloat162_rn(v.z * w23.x, v.w * w23.y);
+                                uint2 pk;
+                                pk.x = *(uint32_t*)&p0; pk.y = *(uint32_t*)&p1;
+                                *(uint2*)(xbase + (size_t)(4 * k) * N + c0) = pk;
+                                part[k] = fmaf(v.x, v.x, part[k]); part[k] = fmaf(v.y, v.y, part[k]);
+                                part[k] = fmaf(v.z, v.z, part[k]); part[k] = fmaf(v.w, v.w, part[k]);
+                            }
+                        }
+                    } else {
+                        // ragged or unaligned edges: element by element
+#pragma unroll
+                        for (int k = 0; k < 8; ++k) {
+                            const float a4[4] = {acc[k].x, acc[k].y, acc[k].z, acc[k].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                if (sub + 4 * k < rows_here && col + e < N) {
+                                    float* cp = cbase + (size_t)(4 * k) * ldc + c0 + e;
+                                    const float v = *cp + a4[e];
+                                    *cp = v;
+                                    xbase[(size_t)(4 * k) * N + c0 + e] = __float2bfloat16_rn(v * __bfloat162float(ep.next_w[col + e]));
+                                    part[k] = fmaf(v, v, part[k]);
+                                }
+                            }
+                        }
+                    }
+                    // the buffer this chunk used takes the chunk AHEAD further on
+                    if (wide_ok) fetch_old(c0 + AHEAD * SPAN, old[ci % AHEAD]);
+                }
+                // the rows' sums over this tile's columns: the eight lanes of a row added in a fixed (butterfly) order
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    float s_row = part[k];
+                    s_row += __shfl_xor_sync(0xffffffffu, s_row, 1);
+                    s_row += __shfl_xor_sync(0xffffffffu, s_row, 2);
+                    s_row += __shfl_xor_sync(0xffffffffu, s_row, 4);
+                    if ((lane & 7) == 0 && sub + 4 * k < rows_here)
+                        ep.ssq_out[(size_t)(m0 + q * 32 + sub + 4 * k) * n_tiles + (tile / m_tiles)] = s_row;
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < c_end; c0 += SPAN) {
                 uint32_t r[32];
@@ -200,13 +425,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     tc_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const float g = __uint_as_float(r[j]);
-                        v[j] = (g / (1.0f + expf(-g))) * __uint_as_float(u[j]);
+                        const float g = __uint_as_float(r[j]) * rstd;
+                        v[j] = (g / (1.0f + expf(-g))) * (__uint_as_float(u[j]) * rstd);
                     }
                 } else {
                     tc_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+                    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * rstd;
                 }
                 if (c0 + SPAN >= c_end) {            // all of this tile has left tensor memory: hand the buffer back
                     tc_fence_before();
@@ -437,7 +662,7 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
 
 template <int BN, int STAGES>
 int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc, int mode,
-           int* status, cudaStream_t stream) {
+           int* status, cudaStream_t stream, const EpiArgs& ep) {
     using L = SmemLayout<BN, STAGES>;
     static SpPerDevice configured;
     if (!configured.done()) {
@@ -449,7 +674,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
     if (sm_count <= 0) SP_FAIL("tc_gemm: cannot read the number of SMs");
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status);
+    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, ep);
     SP_CHECK_LAUNCH("tc_gemm");
     return 0;
 }
@@ -493,26 +718,64 @@ SP_API int sp_tc_gemm_supported(const void* A, const void* W, int K, int lda, in
     return 0;
 }
 
+// The product with a fused epilogue (see EpiArgs; ``ep`` null or all zero: the plain epilogues of sp_tc_gemm).
+//   ep->row_ssq: the result is multiplied by each row's 1/rms (modes 0, 2 and 3);
+//   mode 1 with ep->xw: C += A·Wᵀ, and xw = new C ⊙ next_w (bfloat16) and ssq_out[row][tile along N] are written;
+//     ssq_out holds sp_tc_gemm_n_tiles(N, bn) floats per row;
+//   mode 3: W = [q | k | v] heads x head_dim rows; q and k are rotated with the per-token (cos, sin) table, q goes
+//     to q_out and k, v into the paged cache; C is not used. bn must be a multiple of head_dim (64 or 128).
+// These epilogues belong to the tile kernel: K is never split over a cluster here.
+SP_API int sp_tc_gemm_n_tiles(int N, int bn) { return bn > 0 ? (N + bn - 1) / bn : 0; }
+
+static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                       int mode, int bn, const EpiArgs* epp, int* status, cudaStream_t stream);
+
+SP_API int sp_tc_gemm_fused(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw,
+                            int ldc, int mode, int bn, const void* ep, int* status, cudaStream_t stream) {
+    return tc_gemm_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, bn, (const EpiArgs*)ep, status, stream);
+}
+
 // mode 0: C = A·Wᵀ (C bfloat16 or float32); 1: C (float32) += A·Wᵀ;
 // mode 2: W holds gate and up rows interleaved in blocks of bn/2 and C [M, N/2] = silu(gate)·up.
 SP_API int sp_tc_gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
                       int mode, int bn, int* status, cudaStream_t stream) {
+    if (mode == MODE_QKV_ROPE) SP_FAIL("tc_gemm: the rotate-and-store epilogue needs sp_tc_gemm_fused");
+    return tc_gemm_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, bn, nullptr, status, stream);
+}
+
+static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                       int mode, int bn, const EpiArgs* epp, int* status, cudaStream_t stream) {
+    EpiArgs ep;
+    memset(&ep, 0, sizeof(ep));
+    if (epp) ep = *epp;
+    const bool fused = ep.row_ssq || ep.xw || mode == MODE_QKV_ROPE;
     if (M <= 0 || N <= 0) return 0;
     if (sp_tc_gemm_supported(A, W, K, lda, ldw)) return 1;
     if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_gemm: accumulation needs a float32 C");
-    if (mode < 0 || mode > 2) SP_FAIL("tc_gemm: unknown mode %d", mode);
+    if (mode < 0 || mode > 3) SP_FAIL("tc_gemm: unknown mode %d", mode);
     if (bn != 128 && bn != 192 && bn != 256) SP_FAIL("tc_gemm: tile width %d is not built (128, 192 or 256)", bn);
-    if (bn == 192 && pick_splits(M, N, K, bn) > 1) bn = 256;      // the kernel that splits K is built for 128 and 256
+    if (!fused && bn == 192 && pick_splits(M, N, K, bn) > 1) bn = 256;      // the kernel that splits K is built for 128 and 256
+    if (ep.row_ssq && (ep.n_ssq <= 0 || ep.norm_width <= 0)) SP_FAIL("tc_gemm: the row statistics need their count and the norm's width");
+    if (ep.xw && (mode != MODE_ACCUMULATE || !ep.next_w || !ep.ssq_out))
+        SP_FAIL("tc_gemm: preparing the next norm's input belongs to the accumulating epilogue and needs its weight and a place for the sums");
+    if (mode == MODE_QKV_ROPE) {
+        if ((ep.hd != 64 && ep.hd != 128) || (bn % ep.hd)) SP_FAIL("tc_gemm: the rotate-and-store epilogue is built for head sizes 64 and 128 in tiles of whole heads (head %d, tile %d)", ep.hd, bn);
+        if (ep.nh <= 0 || ep.nkv <= 0 || N != (ep.nh + 2 * ep.nkv) * ep.hd) SP_FAIL("tc_gemm: W has %d rows, %d q and %d kv heads of %d need %d", N, ep.nh, ep.nkv, ep.hd, (ep.nh + 2 * ep.nkv) * ep.hd);
+        if (!ep.cs || !ep.tok_page || !ep.positions || !ep.q_out || !ep.kpool || !ep.vpool || ep.page_size <= 0)
+            SP_FAIL("tc_gemm: the rotate-and-store epilogue needs the angle table, the tokens' pages and positions, q and the cache");
+        if (((uintptr_t)ep.q_out | (uintptr_t)ep.kpool | (uintptr_t)ep.vpool | (uintptr_t)ep.cs) & 15)
+            SP_FAIL("tc_gemm: q, the cache and the angle table must start on a 16-byte boundary");
+    }
     if (mode == MODE_SILU_MUL && (N % bn)) SP_FAIL("tc_gemm: the fused silu epilogue needs N (%d) to be a multiple of the tile width %d", N, bn);
     CUtensorMap ma, mw;
     if (make_map(&ma, A, M, K, lda, BM)) return 1;
     if (make_map(&mw, W, N, K, ldw, bn)) return 1;
-    const int splits = pick_splits(M, N, K, bn);
+    const int splits = fused ? 1 : pick_splits(M, N, K, bn);
     if (splits > 1) {
         if (bn == 128) return launch_splitk<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, splits, status, stream);
         return launch_splitk<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, splits, status, stream);
     }
-    if (bn == 128) return launch<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
-    if (bn == 192) return launch<192, 5>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
-    return launch<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream);
+    if (bn == 128) return launch<128, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
+    if (bn == 192) return launch<192, 5>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
+    return launch<256, 4>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
 }

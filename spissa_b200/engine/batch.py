@@ -32,6 +32,7 @@ class StepBatch:
     page_tables: dict = field(default_factory=dict)   # kv group name -> int32 [B, P] device tensor
     host: dict = field(default_factory=dict)          # the same arrays as Python lists, for host logic
     h2d_bytes: int = 0              # bytes this step's arrays took on their way to the device
+    scratch: dict = field(default_factory=dict)       # what parts make once per step and share between layers
     key_split: Optional[torch.Tensor] = None   # int32 [2] on the device: how the one-kernel decode path splits the keys
                                                # (pages per chunk, chunks); set by a captured step, refreshed per replay
 

@@ -70,13 +70,14 @@ class Engine:
     greedy_steps = True            # ``step`` and ``step_device`` take ``greedy=True`` and return tokens instead of logits
 
     def __init__(self, config, tensors: dict, dtype, max_tokens: int, max_seqs: int | None = None,
-                 device="cuda:0", use_graphs: bool = True, fuse_decode: bool = True):
+                 device="cuda:0", use_graphs: bool = True, fuse_decode: bool = True, fuse_prefill: bool = True):
         self.device = _require_gpu(device)
         self.config = config
         self.dtype = _DTYPES[dtype]
         self.rt = Runtime(self.device, self.dtype, self.PAGE_SIZE)
         self.model = Model(config.to_spec())
         self.model.fuse_decode = fuse_decode
+        self.model.fuse_prefill = fuse_prefill
         with torch.cuda.device(self.device):
             self.model.bind(tensors, self.rt)
             n_pages = (max_tokens + self.PAGE_SIZE - 1) // self.PAGE_SIZE
@@ -101,24 +102,26 @@ class Engine:
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", max_tokens: int = 4096, max_seqs: int | None = None,
-                    device="cuda:0", use_graphs: bool = True, fuse_decode: bool = True) -> "Engine":
+                    device="cuda:0", use_graphs: bool = True, fuse_decode: bool = True,
+                    fuse_prefill: bool = True) -> "Engine":
         dev = _require_gpu(device)
         config = load_config(folder)
         model = Model(config.to_spec())
         tensors = load_tensors(folder, model.weight_specs(), dev, _DTYPES[dtype] == torch.float32)
-        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs, fuse_decode)
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs, fuse_decode, fuse_prefill)
 
     @classmethod
     def from_config(cls, config, seed: int = 0, dtype="bfloat16", max_tokens: int = 4096,
                     max_seqs: int | None = None, device="cuda:0", std: float = 0.02,
-                    norm_std: float = 0.0, use_graphs: bool = True, fuse_decode: bool = True) -> "Engine":
+                    norm_std: float = 0.0, use_graphs: bool = True, fuse_decode: bool = True,
+                    fuse_prefill: bool = True) -> "Engine":
         """Random weights drawn on the device (no file); the same generator rule as the folder writer."""
         dev = _require_gpu(device)
         model = Model(config.to_spec())
         tensors = random_tensors(model.weight_specs(), seed, std, norm_std, torch.bfloat16, device=dev)
         if _DTYPES[dtype] == torch.float32:
             tensors = {k: (v.float() if v.is_floating_point() else v) for k, v in tensors.items()}
-        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs, fuse_decode)
+        return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs, fuse_decode, fuse_prefill)
 
     # ------------------------------------------------------------------ slots
     def acquire(self) -> int:

@@ -18,6 +18,36 @@ from ..csrc import lib as K
 MAX_TOKENS = 16
 
 
+def collect_fused_fields(model):
+    """Per schedule entry what the blocks say of themselves through ``fused_fields()``, when every entry is a
+    pre-norm block of an RMS norm, a rotary grouped-query attention that writes its own cache and a SwiGLU, all
+    bfloat16 and of one width and head size; else None. Shared by the one-kernel decode path and the fused prompt path."""
+    if model.rt is None or model.rt.act_dtype != torch.bfloat16 or not model.spec.schedule:
+        return None
+    fields = []
+    for e in model.spec.schedule:
+        blk = model.layers[e.layer]
+        f = blk.fused_fields() if e.writes_cache else None
+        if not f or f.get("kind") != "prenorm" or f["mixer"].get("kind") != "gqa_rotary" \
+                or f["ffn"].get("kind") != "swiglu" or f["mixer_norm"].get("kind") != "rmsnorm" \
+                or f["ffn_norm"].get("kind") != "rmsnorm":
+            return None
+        fields.append(f)
+    H, hd = fields[0]["mixer"]["hidden_size"], fields[0]["mixer"]["head_dim"]
+    for f in fields:
+        m, ff = f["mixer"], f["ffn"]
+        if m["hidden_size"] != H or m["head_dim"] != hd or ff["hidden_size"] != H:
+            return None
+        if f["mixer_norm"]["size"] != H or f["ffn_norm"]["size"] != H:
+            return None
+        if ff["pair"] % 8 or ff["intermediate_size"] % 8 or (m["num_heads"] * hd) % 8 or H % 16:
+            return None
+        for w in (m["qkv"], m["o"], ff["gate_up"], ff["down"]):
+            if not w.is_contiguous() or w.data_ptr() % 16:
+                return None
+    return fields
+
+
 class FusedDecode:
     """The descriptor table and scratch buffers of one model on one cache."""
 
@@ -41,29 +71,10 @@ class FusedDecode:
     @classmethod
     def plan(cls, model):
         """A runner for ``model`` or None when some layer has to run part by part."""
-        if model.rt is None or model.rt.act_dtype != torch.bfloat16 or not model.spec.schedule:
+        fields = collect_fused_fields(model)
+        if fields is None:
             return None
-        fields = []
-        for e in model.spec.schedule:
-            blk = model.layers[e.layer]
-            f = blk.fused_fields() if e.writes_cache else None
-            if not f or f.get("kind") != "prenorm" or f["mixer"].get("kind") != "gqa_rotary" \
-                    or f["ffn"].get("kind") != "swiglu" or f["mixer_norm"].get("kind") != "rmsnorm" \
-                    or f["ffn_norm"].get("kind") != "rmsnorm":
-                return None
-            fields.append(f)
         H, hd = fields[0]["mixer"]["hidden_size"], fields[0]["mixer"]["head_dim"]
-        for f in fields:
-            m, ff = f["mixer"], f["ffn"]
-            if m["hidden_size"] != H or m["head_dim"] != hd or ff["hidden_size"] != H:
-                return None
-            if f["mixer_norm"]["size"] != H or f["ffn_norm"]["size"] != H:
-                return None
-            if ff["pair"] % 8 or ff["intermediate_size"] % 8 or (m["num_heads"] * hd) % 8 or H % 16:
-                return None
-            for w in (m["qkv"], m["o"], ff["gate_up"], ff["down"]):
-                if not w.is_contiguous() or w.data_ptr() % 16:
-                    return None
         plan = cls(model, fields)
         if not K.decode_layers_supported(1, H, hd, model.rt.page_size, plan.max_group):
             return None

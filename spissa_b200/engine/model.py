@@ -33,6 +33,8 @@ class Model:
         self.rt = None
         self.fuse_decode = True        # run a decode step's layers as one kernel when every layer's parts allow it
         self._fused = False            # False: not planned yet; None: the parts do not allow it
+        self.fuse_prefill = True       # fold norms, rotation and cache write into a prompt step's products likewise
+        self._fused_prefill = False
 
     # ------------------------------------------------------------------ weights
     def parts(self) -> list:
@@ -73,8 +75,13 @@ class Model:
         if self.fuse_decode and self._fused is False:
             from .fused_decode import FusedDecode
             self._fused = FusedDecode.plan(self)
+        if self.fuse_prefill and self._fused_prefill is False:
+            from .fused_prefill import FusedPrefill
+            self._fused_prefill = FusedPrefill.plan(self)
         if self.fuse_decode and self._fused is not None and self._fused.takes(step, cache):
             self._fused.run(h, step, cache)
+        elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):
+            self._fused_prefill.run(h, step, cache)
         else:
             for e in self.spec.schedule:
                 self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))

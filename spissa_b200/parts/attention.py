@@ -108,12 +108,19 @@ class GQAAttention(Mixer):
             if self.position is not None and not rotary:
                 self.position.apply(qkv, step, nh, nkv, hd)
             K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
+        self.o(self.attend(q, step, cache), out=residual, accumulate=True)
+
+    def attend(self, q, step, cache):
+        """The heads' outputs [T, heads·head_dim] for queries ``q`` (positions applied) over the keys and values that
+        the cache holds for each token's sequence, the step's own tokens included."""
+        nh, nkv, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        T = q.shape[0]
         ctx = torch.empty_like(q)
         if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
             if step.all_single:
                 chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, step.max_len, cache.page_size)
                 need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
-                scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+                scratch = torch.empty(need, dtype=torch.float32, device=q.device)
                 K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,
                                self.scale, chunk_tiles, n_chunks, scratch,
                                self.counters if T * nkv <= self.counters.numel() else None)
@@ -128,4 +135,4 @@ class GQAAttention(Mixer):
                                 tiles, nh, nkv, hd, self.window, self.scale)
         else:
             K.attention_generic(q, cache.k_pool, cache.v_pool, ctx, cache, nh, nkv, hd, self.window, self.scale)
-        self.o(ctx, out=residual, accumulate=True)
+        return ctx

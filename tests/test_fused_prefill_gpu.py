@@ -1,0 +1,70 @@
+"""Prompt steps with the norms, the rotation and the cache write folded into the products (engine/fused_prefill.py)
+against the same steps part by part and against the plain implementation."""
+import pytest
+import torch
+
+import tiny
+from plain import llama_plain as P
+from spissa_b200 import Engine
+from spissa_b200.csrc import lib as K
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for name in ("E", "F"):
+        cfg, init = tiny.TINIES[name]
+        f = tmp_path_factory.mktemp(f"fusedpre_{name}")
+        tiny.make_folder(cfg, init, f)
+        out[name] = (str(f),) + P.read_model_folder(f)
+    return out
+
+
+@pytest.mark.parametrize("name", ["E", "F"])
+def test_fused_prompt_steps_match_plain_and_the_parts(folders, name):
+    folder, pcfg, w = folders[name]
+    V, L = pcfg["vocab_size"], pcfg["num_hidden_layers"]
+    lens = [300, 250, 40]
+    first = [160, 90, 20]                              # the prompts arrive in two steps: the second reads the first's keys
+    seqs = [tiny.random_prompt(V, n, 5 * n) for n in lens]
+    refs = [P.model_logits(pcfg, w, s, torch.float64) for s in seqs]
+    scale = max(float(r.abs().max()) for r in refs)
+    rows = {}
+    launches = {}
+    for fused in (True, False):
+        engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 12, fuse_prefill=fused)
+        slots = [engine.acquire() for _ in seqs]
+        l0 = K.launches
+        a = engine.step([(s, q[:n], list(range(n))) for s, q, n in zip(slots, seqs, first)]).cpu()
+        launches[fused] = K.launches - l0
+        b = engine.step([(s, q[n:], list(range(len(q) - n))) for s, q, n in zip(slots, seqs, first)]).cpu()
+        got, ia, ib = [], 0, 0
+        for q, n in zip(seqs, first):
+            got.append(torch.cat([a[ia:ia + n], b[ib:ib + len(q) - n]]))
+            ia += n
+            ib += len(q) - n
+        rows[fused] = got
+        runs = engine.model._fused_prefill.runs if engine.model._fused_prefill else 0
+        assert runs == (2 if fused else 0)
+        worst = max(float((g.double() - r).abs().max()) / scale for g, r in zip(got, refs))
+        print(f"{name} fused={fused}: worst error {worst:.2e} of the largest logit")
+        assert worst <= tiny.TOL["bfloat16"]
+        engine.cache.check()
+    for g, p in zip(rows[True], rows[False]):
+        assert float((g - p).abs().max()) / scale <= tiny.TOL["bfloat16"]
+    # per layer: norm, rotate-and-store and norm are gone; one launch prepares the first norm, one the angle table
+    assert launches[True] == launches[False] - 3 * L + 2, launches
+
+
+def test_short_prompts_and_other_models_run_part_by_part(folders):
+    folder, pcfg, w = folders["E"]
+    engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 8)
+    s = engine.acquire()
+    engine.step([(s, tiny.random_prompt(777, 100, 1), [99])])         # up to 128 tokens: K is split over a cluster instead
+    assert engine.model._fused_prefill is not None and engine.model._fused_prefill.runs == 0
+    e32 = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 8)
+    s = e32.acquire()
+    e32.step([(s, tiny.random_prompt(777, 200, 1), [199])])
+    assert e32.model._fused_prefill is None                          # the 32-bit path has no such kernels

@@ -802,3 +802,99 @@ def test_head_argmax_ignores_nan_and_rows_beyond_the_table(K):
         logits = x.double() @ w.double().t()
         logits[:, 77] = -float("inf")
         assert torch.equal(_head_argmax(K, x, w), logits.argmax(dim=1).cpu().int())
+
+
+# ------------------------------------------------------------------ tc_gemm with fused epilogues (prompt steps)
+@pytest.mark.parametrize("M,N,Kd,bn", [(300, 520, 264, 128), (129, 2048, 512, 256), (513, 1160, 128, 192), (2048, 256, 2048, 256)])
+def test_tc_gemm_accumulate_prepares_the_next_norm(K, M, N, Kd, bn):
+    """C += A·Wᵀ, and in the same epilogue C ⊙ w_next in bfloat16 and the rows' sums of squares per tile."""
+    torch.manual_seed(M + N)
+    a = (torch.randn(M, Kd, device=DEV) * 0.5).bfloat16()
+    w = (torch.randn(N, Kd, device=DEV) * 0.1).bfloat16()
+    c0 = torch.randn(M, N, device=DEV)
+    next_w = (1 + 0.2 * torch.randn(N, device=DEV)).bfloat16()
+    c = c0.clone()
+    xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ssq = torch.full((M, K.tc_gemm_n_tiles(N, bn)), float("nan"), device=DEV)
+    K.tc_gemm_fused(a, w, c, K.TC_ACCUMULATE, bn, xw=xw, next_w=next_w, ssq_out=ssq)
+    ref = c0.double() + a.double() @ w.double().t()
+    close(c, ref, 2e-5, "residual")
+    close(xw.float(), ref * next_w.double(), 6e-3, "residual times the next norm's weight")
+    close(ssq.sum(1), (ref ** 2).sum(1), 2e-5, "sums of squares")
+    # the consumer: a product on xw whose result is scaled by 1/rms equals the product on the normed rows
+    w2 = (torch.randn(384, N, device=DEV) * 0.1).bfloat16()
+    out = torch.empty(M, 384, dtype=torch.bfloat16, device=DEV)
+    K.tc_gemm_fused(xw, w2, out, K.TC_STORE, 128, row_ssq=ssq, norm_width=N, eps=1e-5)
+    normed = P.rms_norm(ref, next_w.double().cpu().to(ref.device), 1e-5)
+    close(out.float(), normed @ w2.double().t(), 1.2e-2, "product of the normed rows")
+    again = c0.clone()
+    xw2, ssq2 = torch.empty_like(xw), torch.empty_like(ssq)
+    K.tc_gemm_fused(a, w, again, K.TC_ACCUMULATE, bn, xw=xw2, next_w=next_w, ssq_out=ssq2)
+    assert torch.equal(again, c) and torch.equal(xw2, xw) and torch.equal(ssq2, ssq)      # a fixed order of sums
+
+
+@pytest.mark.parametrize("M,I,H,pair", [(200, 384, 264, 64), (1030, 1024, 512, 128)])
+def test_tc_gemm_silu_epilogue_with_row_scaling(K, M, I, H, pair):
+    torch.manual_seed(M)
+    x = torch.randn(M, H, device=DEV)
+    nw = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    xw = (x * nw.float()).bfloat16()
+    ssq = (x.double() ** 2).sum(1, keepdim=True).float()
+    gate = (torch.randn(I, H, device=DEV) * 0.1).bfloat16()
+    up = (torch.randn(I, H, device=DEV) * 0.1).bfloat16()
+    wgu = torch.stack([gate.reshape(I // pair, pair, H), up.reshape(I // pair, pair, H)], dim=1).reshape(2 * I, H).contiguous()
+    out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
+    K.tc_gemm_fused(xw, wgu, out, K.TC_SILU_MUL, 2 * pair, row_ssq=ssq, norm_width=H, eps=1e-6)
+    rstd = 1.0 / torch.sqrt(ssq.double() / H + 1e-6)
+    g = (xw.double() @ gate.double().t()) * rstd
+    u = (xw.double() @ up.double().t()) * rstd
+    close(out.float(), P.silu(g) * u, 8e-3, "silu(gate)·up of scaled rows")
+
+
+@pytest.mark.parametrize("hd,nh,nkv,bn", [(64, 6, 2, 128), (64, 5, 1, 192), (64, 32, 8, 256), (128, 4, 2, 256), (128, 3, 1, 128)])
+def test_tc_gemm_qkv_epilogue_rotates_and_writes_the_cache(K, hd, nh, nkv, bn):
+    """q = rotate(rstd·x·Wqᵀ) stored, k rotated and v plain written into the pages of each token's position, for
+    sequences that start at different lengths in one step."""
+    torch.manual_seed(hd + nh)
+    H = 264
+    new_counts, before = [130, 7, 70], [0, 100, 61]
+    T = sum(new_counts)
+    meta = KH.paged_meta(new_counts, before, DEV, seed=hd)
+    x = torch.randn(T, H, device=DEV)
+    nw = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+    xw = (x * nw.float()).bfloat16()
+    ssq = (x.double() ** 2).sum(1, keepdim=True).float()
+    N = (nh + 2 * nkv) * hd
+    w = (torch.randn(N, H, device=DEV) * 0.1).bfloat16()
+    inv_freq = P.rope_inv_freq(10000.0, hd).to(DEV)
+    cs = torch.empty(T, hd // 2, 2, device=DEV)
+    tok_page = torch.empty(T, dtype=torch.int32, device=DEV)
+    K.rope_table(meta, inv_freq, hd // 2, cs, tok_page)
+    ang = meta.positions.float()[:, None] * inv_freq[None, :]
+    assert torch.equal(cs[..., 0], torch.cos(ang)) or float((cs[..., 0] - torch.cos(ang)).abs().max()) < 1e-6
+    k_pool = torch.full((meta.n_pages, nkv, 64, hd), 7.0, dtype=torch.bfloat16, device=DEV)
+    v_pool = torch.full((meta.n_pages, nkv, 64, hd), -7.0, dtype=torch.bfloat16, device=DEV)
+    q = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.tc_gemm_fused(xw, w, None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H, eps=1e-5,
+                    rope=dict(cs=cs, tok_page=tok_page, positions=meta.positions, q_out=q, k_pool=k_pool, v_pool=v_pool,
+                              nh=nh, nkv=nkv, hd=hd, page_size=64))
+    rstd = 1.0 / torch.sqrt(ssq.double() / H + 1e-5)
+    qkv = (xw.double() @ w.double().t()) * rstd
+    pos = meta.positions.cpu()
+    qr = P.apply_rope(qkv[:, :nh * hd].reshape(T, nh, hd).cpu(), pos, inv_freq.double().cpu())
+    kr = P.apply_rope(qkv[:, nh * hd:(nh + nkv) * hd].reshape(T, nkv, hd).cpu(), pos, inv_freq.double().cpu())
+    vr = qkv[:, (nh + nkv) * hd:].reshape(T, nkv, hd).cpu()
+    close(q.float().reshape(T, nh, hd), qr, 8e-3, "rotated queries")
+    kc, vc = k_pool.float().cpu(), v_pool.float().cpu()
+    t = 0
+    touched = torch.zeros(meta.n_pages, 64, dtype=torch.bool)
+    for b, (n, b0) in enumerate(zip(new_counts, before)):
+        for i in range(n):
+            p = b0 + i
+            page, off = meta.rows[b][p // 64], p % 64
+            touched[page, off] = True
+            assert float((kc[page, :, off] - kr[t]).abs().max()) <= 8e-3 * float(kr.abs().max())
+            assert float((vc[page, :, off] - vr[t]).abs().max()) <= 8e-3 * float(vr.abs().max())
+            t += 1
+    kc, vc = kc.permute(0, 2, 1, 3), vc.permute(0, 2, 1, 3)                              # [page, offset, head, dim]
+    assert bool((kc[~touched] == 7.0).all()) and bool((vc[~touched] == -7.0).all())      # nothing else was written

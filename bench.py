@@ -1,6 +1,7 @@
 """Measures decoding and prefill of the Llama-3.2-1B shape with random bfloat16 weights on one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--batch B] [--context T]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--config 1b|3b|8b] [--batch B]
+                    [--context T] [--profile-phases]
 
 Prints ONE JSON line. ``value`` is decoded tokens per second at batch 8 from prompts of
 about 2,048 tokens in a cache of 4,096 tokens per sequence, timed on the device with CUDA
@@ -9,6 +10,10 @@ Python entry point (``Engine.generate``: host token lists in, host token lists o
 ``prefill`` is one 2,048-token prompt; ``points`` holds decoding at batch 1 and 64;
 ``roofline`` compares the decode step with the bytes it has to read. ``--context T`` decodes from prompts of
 about T tokens instead (the cache then holds 2T per sequence); the prefill measurement stays at 2,048 tokens.
+``--config 3b`` and ``--config 8b`` run the secondary workloads (3B shape: batch 8, prompts uniform in [256, 2048],
+256 decode steps, 4,096-token cache per sequence; 8B shape: batch 16, prompts uniform in [512, 4096], 512 steps,
+8,192 tokens per sequence) and print the same line. ``--profile-phases`` adds per-phase timings (CUDA events around
+the kernel groups of one prompt step and of part-by-part decode steps).
 Token ids are synthetic (seeded, uniform over the vocabulary), weights are N(0, 0.02).
 Every decode step reads all weights (2.47 GB), far more than the 126 MB L2, so no
 flush is needed between timed iterations.
@@ -36,8 +41,30 @@ CONFIG_1B = dict(
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072)
+CONFIG_3B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=28, hidden_size=3072,
+    num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192, vocab_size=128256,
+    rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=True, rms_norm_eps=1e-5, max_position_embeddings=131072)
+CONFIG_8B = dict(
+    architectures=["LlamaForCausalLM"], model_type="llama", num_hidden_layers=32, hidden_size=4096,
+    num_attention_heads=32, num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+    rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=False, rms_norm_eps=1e-5, max_position_embeddings=131072)
+# name -> configuration, batch, cache per sequence, prompt lengths (mean of a narrow band, or a uniform range), decode
+# steps, extra batch sizes: the headline workload and the two secondary ones
+WORKLOADS = {
+    "1b": dict(cfg=CONFIG_1B, model="llama-3.2-1b-shape", batch=8, context=4096, prompt=2048, span=None, steps=64, points="1,64"),
+    "3b": dict(cfg=CONFIG_3B, model="llama-3.2-3b-shape", batch=8, context=4096, prompt=None, span=(256, 2048), steps=256, points=""),
+    "8b": dict(cfg=CONFIG_8B, model="llama-3.1-8b-shape", batch=16, context=8192, prompt=None, span=(512, 4096), steps=512, points=""),
+}
 CONTEXT = 4096
 PROMPT = 2048
+SPAN = None                                 # (lowest, highest) prompt length when the workload draws them uniformly
 PREFILL_TOKENS = 2048                       # the prefill measurement is always of this many tokens
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
@@ -125,6 +152,8 @@ def prefill_flops(cfg, T):
 
 def ragged_lengths(batch, seed):
     rng = random.Random(seed)
+    if SPAN is not None:
+        return [rng.randint(SPAN[0], SPAN[1]) for _ in range(batch)]
     if batch == 1:
         return [PROMPT]
     half = PROMPT // 8
@@ -380,14 +409,17 @@ def main() -> int:
     global PROMPT, CONTEXT
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=None, help="timed decode steps (default: the workload's: 64, 256 or 512)")
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=PROMPT,
+    ap.add_argument("--config", default="1b", choices=sorted(WORKLOADS), help="the headline workload (1b) or a secondary one")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--context", type=int, default=None,
                     help="mean prompt length of the decode runs (the cache holds twice as much per sequence)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--points", default="1,64", help="extra decode batch sizes, comma separated ('' = none)")
+    ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' = none)")
+    ap.add_argument("--profile-phases", action="store_true", dest="profile_phases",
+                    help="add per-phase timings of one prompt step and of part-by-part decode steps")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
                          "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
@@ -409,7 +441,15 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
-    if args.context != PROMPT:
+    global SPAN
+    work = WORKLOADS[args.config]
+    args.steps = args.steps or work["steps"]
+    args.batch = args.batch or work["batch"]
+    args.points = work["points"] if args.points is None else args.points
+    CONTEXT, SPAN = work["context"], work["span"]
+    PROMPT = work["prompt"] or (SPAN[0] + SPAN[1]) // 2
+    if args.context is not None and args.context != PROMPT:
+        SPAN = None
         if args.context < 64:
             print("bench.py: --context must be at least 64")
             return 2
@@ -420,7 +460,7 @@ def main() -> int:
     from spissa_b200.csrc import lib
 
     peaks = load_peaks()
-    cfg_dict = dict(CONFIG_1B)
+    cfg_dict = dict(work["cfg"])
     full_layers = cfg_dict["num_hidden_layers"]
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
@@ -482,12 +522,12 @@ def main() -> int:
         engine.check()
         for s in slots:
             engine.release(s)
-        return ms, kv_tokens, launches
+        return ms, kv_tokens, launches, [len(p) for p in prompts]
 
     # ---------------------------------------------------------------- decode, device timed
     clocks = ClockSampler()
     clocks.start()
-    ms_step, kv_tokens, launches = decode_run(args.batch, args.steps, args.warmup)
+    ms_step, kv_tokens, launches, prompt_lens = decode_run(args.batch, args.steps, args.warmup)
     clock_info = clocks.stop()
     value = args.batch * 1000.0 / ms_step
     step_bytes = nums["weight_bytes"] + kv_tokens * nums["kv_bytes_per_token"]
@@ -495,7 +535,7 @@ def main() -> int:
 
     # ---------------------------------------------------------------- end to end through Engine.generate
     e2e_prompts = prompts_for(args.batch)
-    e2e_new = max(8, min(args.steps, 64))
+    e2e_new = max(8, min(args.steps, 64)) if args.config == "1b" else args.steps
     engine.generate(e2e_prompts, 4, greedy, stop_ids=[])          # warm the path: the same shapes, so their graphs exist
     torch.cuda.synchronize()
     # three runs, the median one is reported (the host takes part in this number: it varies more than the device's)
@@ -538,20 +578,49 @@ def main() -> int:
     # ---------------------------------------------------------------- other batch sizes
     pts = {}
     for b in points:
-        ms_b, _, _ = decode_run(b, max(8, args.steps // 2), 3)
+        ms_b, _, _, _ = decode_run(b, max(8, args.steps // 2), 3)
         pts[f"decode_b{b}"] = round(b * 1000.0 / ms_b, 1)
 
+    # ---------------------------------------------------------------- per-phase timings, on request
+    phases_out = None
+    if args.profile_phases:
+        from spissa_b200 import phases as ph
+        engine.profile_phases = True
+        engine.phase_totals.clear()
+        s = engine.acquire()
+        engine.step([(s, prompt, [PREFILL_TOKENS - 1])], greedy=True)
+        engine.release(s)
+        short = [prompts_for(args.batch)[b][:256] for b in range(args.batch)]
+        slots = [engine.acquire() for _ in range(args.batch)]
+        engine.step([(sl, p, []) for sl, p in zip(slots, short)], check=True)
+        engine.phase_totals.pop("decode", None)
+        n_dec = 4
+        for i in range(n_dec):
+            engine.step([(sl, [7 + i], [0]) for sl in slots], greedy=True)
+        for sl in slots:
+            engine.release(sl)
+        engine.profile_phases = False
+        L = len(engine.model.spec.schedule)
+        pre = engine.phase_totals["prefill"]
+        dec = engine.phase_totals["decode"]
+        # the prompt entry sums the 2,048-token prompt and the short prompts that the decode steps start from
+        phases_out = {"prompt_steps": dict(steps=pre["steps"], tokens=pre["tokens"], **ph.summary(dict(pre["ms"]), L)),
+                      "decode_part_by_part_per_step": dict(batch=args.batch, context=256,
+                                                           **ph.summary({k: v / n_dec for k, v in dec["ms"].items()}, L))}
+
     line = {
-        "metric": "decode tokens/s (Llama-3.2-1B shape, batch %d, ~%d-token prompts)" % (args.batch, PROMPT),
+        "metric": "decode tokens/s (%s, batch %d, ~%d-token prompts)" % (work["model"], args.batch, PROMPT),
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic token ids, random N(0,0.02) weights", "impl": "ours",
         "config": {
-            "model": "llama-3.2-1b-shape", "layers": cfg.num_hidden_layers, "layers_full": full_layers,
+            "model": work["model"], "layers": cfg.num_hidden_layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
             "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len_mean": PROMPT, "page_size": engine.page_size,
-            "parallelism": "single-gpu", "l2": "inputs larger than L2 (2.47 GB of weights per step)",
+            "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len_mean": round(sum(prompt_lens) / len(prompt_lens)),
+            "prompt_len_min": min(prompt_lens), "prompt_len_max": max(prompt_lens), "page_size": engine.page_size,
+            "tied_head": bool(cfg_dict.get("tie_word_embeddings")), "decode_steps": args.steps,
+            "parallelism": "single-gpu", "l2": "inputs larger than L2 (%.2f GB of weights per step)" % (nums["weight_bytes"] / 1e9),
             "peaks": peaks["source"],
         },
         "clocks": clock_info,
@@ -562,6 +631,8 @@ def main() -> int:
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": pts,
     }
+    if phases_out is not None:
+        line["phases"] = phases_out
     print(json.dumps(line))
     return 0
 

@@ -28,6 +28,9 @@ def _sampling_args(p, max_new_default):
     p.add_argument("--seed", type=int, default=0, help="seed of the sampling draws")
     p.add_argument("--dtype", default="bf16", choices=["bf16", "fp32", "bfloat16", "float32"])
     p.add_argument("--device", default="cuda:0")
+    p.add_argument("--profile-phases", action="store_true", dest="profile_phases",
+                   help="time every phase of the block with CUDA events (steps then run kernel by kernel, part by part) "
+                        "and print the sums, as the reference's llama-test --profile-phases does")
 
 
 def _engine(args, n_seqs):
@@ -45,6 +48,16 @@ def _engine(args, n_seqs):
                               device=args.device)
 
 
+def _phase_report(engine) -> dict:
+    """Per kind of step (prefill, decode): steps, tokens and the phases' milliseconds summed over the run."""
+    from . import phases
+    out = {}
+    for kind, acc in engine.phase_totals.items():
+        out[kind] = dict(steps=acc["steps"], tokens=acc["tokens"],
+                         **phases.summary(acc["ms"], len(engine.model.spec.schedule)))
+    return out
+
+
 def cmd_generate(args) -> int:
     from . import SamplingParams
     prompts = [[int(x) for x in ids.split(",") if x.strip()] for ids in (args.token_ids or [])]
@@ -56,6 +69,7 @@ def cmd_generate(args) -> int:
     if not prompts:
         raise SystemExit("give --token-ids a,b,c (repeatable) or --prompt TEXT")
     engine = _engine(args, len(prompts))
+    engine.profile_phases = bool(args.profile_phases)
     params = SamplingParams(args.temp, args.top_k, args.top_p, args.seed)
     stop = [int(x) for x in args.stop_ids.split(",")] if args.stop_ids else None
     results, m = engine.generate(prompts, args.max_new_tokens, params, stop_ids=stop,
@@ -69,6 +83,8 @@ def cmd_generate(args) -> int:
     print(json.dumps({"ttft_ms": round(m.ttft_ms, 3), "prefill_ms": round(m.prefill_ms, 3),
                       "decode_ms": round(m.decode_ms, 3), "decode_tok_s": round(m.decode_tok_s, 2),
                       "batches": m.batches, "steps": m.steps}), file=sys.stderr)
+    if args.profile_phases:
+        print(json.dumps({"phases": _phase_report(engine)}), file=sys.stderr)
     if args.logits_out:
         # the first step's logits of every request, like the reference's --logits-out
         with open(args.logits_out, "w") as fh:
@@ -98,6 +114,7 @@ def cmd_chat(args) -> int:
     from .tokenizer import Tokenizer
     tok = Tokenizer(args.model)
     engine = _engine(args, 1)
+    engine.profile_phases = bool(args.profile_phases)
     session = ChatSession(engine, SamplingParams(args.temp, args.top_k, args.top_p, args.seed), max_seq_len=args.ctx)
     stop = set(engine.config.stop_token_ids())
     if args.chat_template == "llama3":
@@ -131,6 +148,9 @@ def cmd_chat(args) -> int:
         ended = res.finish_reason == "stop"
         has_context = True
         print(f"  [{len(res.tokens)} tok, {res.decode_tok_s:.1f} tok/s, ctx {res.context_len}]", file=sys.stderr)
+        if args.profile_phases:
+            print("  " + json.dumps({"phases": _phase_report(engine)}), file=sys.stderr)
+            engine.phase_totals.clear()
     session.close()
     return 0
 

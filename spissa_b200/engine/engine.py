@@ -98,6 +98,11 @@ class Engine:
         self._pending: list = []
         self._status_host: list = []
         self._last_step = None
+        # per-phase timings (CUDA events around kernel groups): steps then run kernel by kernel and part by part and
+        # leave their phases in ``last_phases``; ``phase_totals`` adds them up until it is cleared
+        self.profile_phases = False
+        self.last_phases = None
+        self.phase_totals: dict = {}
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -311,7 +316,7 @@ class Engine:
             try:
                 tables = res.tables
                 one_each = all(len(w) == 1 for _, _, w in ents)
-                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs else None
+                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs and not self.profile_phases else None
                 full = None
                 if graph is not None:
                     try:
@@ -333,7 +338,7 @@ class Engine:
                     self.h2d_bytes += batch.h2d_bytes
                     arrays = (batch.seq_slot, batch.seq_len)
                     note = self._note_for(arrays, [s for s, _, _ in ents]) if greedy and one_each else None
-                    logits = self.model.forward(batch, self.cache, greedy, note)
+                    logits = self._forward(batch, greedy, note)
             except BaseException:
                 self.cache.rollback(res)
                 raise
@@ -350,6 +355,22 @@ class Engine:
               f"decode steps run kernel by kernel from here on", file=sys.stderr, flush=True)
         self.use_graphs = False
         self._graphs.clear()
+
+    def _forward(self, batch, greedy, note):
+        if not self.profile_phases:
+            return self.model.forward(batch, self.cache, greedy, note)
+        from .. import phases
+        with phases.profile() as timer:
+            out = self.model.forward(batch, self.cache, greedy, note)
+        totals = timer.totals()
+        self.last_phases = phases.summary(totals, len(self.model.spec.schedule))
+        kind = "decode" if batch.all_single else "prefill"
+        acc = self.phase_totals.setdefault(kind, {"steps": 0, "tokens": 0, "ms": {}})
+        acc["steps"] += 1
+        acc["tokens"] += batch.n_tokens
+        for k, v in totals.items():
+            acc["ms"][k] = acc["ms"].get(k, 0.0) + v
+        return out
 
     def _note_for(self, arrays, slots):
         if self.cache.header is None:
@@ -389,7 +410,7 @@ class Engine:
             res = self._begin(counts)
             try:
                 tables = res.tables
-                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs else None
+                graph = self._decode_graph(ents, lengths, greedy) if self.use_graphs and not self.profile_phases else None
                 logits = None
                 if graph is not None:
                     try:
@@ -406,7 +427,7 @@ class Engine:
                     idx = torch.tensor(rows, dtype=torch.int32).to(self.device)
                     K.gather_i32(token_source, idx, batch.tokens)
                     arrays = (batch.seq_slot, batch.seq_len)
-                    logits = self.model.forward(batch, self.cache, greedy, self._note_for(arrays, slots) if greedy else None)
+                    logits = self._forward(batch, greedy, self._note_for(arrays, slots) if greedy else None)
             except BaseException:
                 self.cache.rollback(res)
                 raise

@@ -24,6 +24,7 @@ import torch
 from ..csrc import lib as K
 from ..parts.linear import sm_count, tile_width
 from .fused_decode import collect_fused_fields
+from ..phases import phase
 
 MIN_TOKENS = 129         # up to 128 tokens the products split K over a cluster instead; those steps run part by part
 
@@ -91,39 +92,46 @@ class FusedPrefill:
         schedule = self.model.spec.schedule
         xw = torch.empty(T, H, dtype=bf, device=dev)
         ssq = torch.empty(T, 1, dtype=torch.float32, device=dev)
-        K.norm_prepare(h, self.fields[0]["mixer_norm"]["weight"], xw, ssq)
+        with phase("attention_norm_ms"):
+            K.norm_prepare(h, self.fields[0]["mixer_norm"]["weight"], xw, ssq)
         for i, (e, f) in enumerate(zip(schedule, self.fields)):
             m, ff = f["mixer"], f["ffn"]
             mixer = self.model.layers[e.layer].mixer
             view = cache.view(e.cache, step, True)
             nh, nkv = m["num_heads"], m["num_kv_heads"]
             # ---- QKV, rotation, cache write
-            cs, tok_page = self._tables(step, view, m["inv_freq"], self.rope_id[i])
+            with phase("rotary_table_ms"):
+                cs, tok_page = self._tables(step, view, m["inv_freq"], self.rope_id[i])
             q = torch.empty(T, nh * hd, dtype=bf, device=dev)
             n_qkv = m["qkv"].shape[0]
             bn = tile_width(T, n_qkv, sms)
             if bn % hd:
                 bn = 256
-            K.tc_gemm_fused(xw, m["qkv"], None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H,
-                            eps=f["mixer_norm"]["eps"],
-                            rope=dict(cs=cs, tok_page=tok_page, positions=step.positions, q_out=q, k_pool=view.k_pool,
-                                      v_pool=view.v_pool, nh=nh, nkv=nkv, hd=hd, page_size=view.page_size))
+            with phase("attention_norm+qkv_projection+rotary+kv_append_ms"):
+                K.tc_gemm_fused(xw, m["qkv"], None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H,
+                                eps=f["mixer_norm"]["eps"],
+                                rope=dict(cs=cs, tok_page=tok_page, positions=step.positions, q_out=q, k_pool=view.k_pool,
+                                          v_pool=view.v_pool, nh=nh, nkv=nkv, hd=hd, page_size=view.page_size))
             # ---- attention, then the output projection into the residual, preparing the second norm
-            ctx = mixer.attend(q, step, view)
+            with phase("attention_ms"):
+                ctx = mixer.attend(q, step, view)
             bn = tile_width(T, H, sms)
             xw = torch.empty(T, H, dtype=bf, device=dev)
             ssq = torch.empty(T, K.tc_gemm_n_tiles(H, bn), dtype=torch.float32, device=dev)
-            K.tc_gemm_fused(ctx, m["o"], h, K.TC_ACCUMULATE, bn, xw=xw, next_w=f["ffn_norm"]["weight"], ssq_out=ssq)
+            with phase("o_projection+attention_residual_ms"):
+                K.tc_gemm_fused(ctx, m["o"], h, K.TC_ACCUMULATE, bn, xw=xw, next_w=f["ffn_norm"]["weight"], ssq_out=ssq)
             # ---- gate/up with silu(gate)·up on the normed residual
             act = torch.empty(T, ff["intermediate_size"], dtype=bf, device=dev)
-            K.tc_gemm_fused(xw, ff["gate_up"], act, K.TC_SILU_MUL, 2 * ff["pair"], row_ssq=ssq, norm_width=H,
-                            eps=f["ffn_norm"]["eps"])
+            with phase("mlp_norm+gate_projection+up_projection+activation_multiply_ms"):
+                K.tc_gemm_fused(xw, ff["gate_up"], act, K.TC_SILU_MUL, 2 * ff["pair"], row_ssq=ssq, norm_width=H,
+                                eps=f["ffn_norm"]["eps"])
             # ---- down projection into the residual, preparing the next layer's first norm
-            if i + 1 < len(self.fields):
-                bn = tile_width(T, H, sms)
-                xw = torch.empty(T, H, dtype=bf, device=dev)
-                ssq = torch.empty(T, K.tc_gemm_n_tiles(H, bn), dtype=torch.float32, device=dev)
-                K.tc_gemm_fused(act, ff["down"], h, K.TC_ACCUMULATE, bn, xw=xw,
-                                next_w=self.fields[i + 1]["mixer_norm"]["weight"], ssq_out=ssq)
-            else:
-                K.tc_gemm(act, ff["down"], h, K.TC_ACCUMULATE, tile_width(T, H, sms))
+            with phase("down_projection+mlp_residual_ms"):
+                if i + 1 < len(self.fields):
+                    bn = tile_width(T, H, sms)
+                    xw = torch.empty(T, H, dtype=bf, device=dev)
+                    ssq = torch.empty(T, K.tc_gemm_n_tiles(H, bn), dtype=torch.float32, device=dev)
+                    K.tc_gemm_fused(act, ff["down"], h, K.TC_ACCUMULATE, bn, xw=xw,
+                                    next_w=self.fields[i + 1]["mixer_norm"]["weight"], ssq_out=ssq)
+                else:
+                    K.tc_gemm(act, ff["down"], h, K.TC_ACCUMULATE, tile_width(T, H, sms))

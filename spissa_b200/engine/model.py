@@ -13,6 +13,7 @@ from ..config.spec import ModelSpec
 from ..parts import registry as part_registry
 from ..parts.base import Runtime
 from .. import parts as _parts  # noqa: F401  (registers the built-in parts)
+from ..phases import phase, profiling
 
 
 class Model:
@@ -71,14 +72,15 @@ class Model:
         """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer; with
         ``greedy`` the indices of their largest entries instead (int32 [step.n_want]; the logits are never written
         where the head has a kernel for that). ``note``: see ``LMHead.greedy``."""
-        h = self.embedding.forward(step)
+        with phase("embedding_ms"):
+            h = self.embedding.forward(step)
         if self.fuse_decode and self._fused is False:
             from .fused_decode import FusedDecode
             self._fused = FusedDecode.plan(self)
         if self.fuse_prefill and self._fused_prefill is False:
             from .fused_prefill import FusedPrefill
             self._fused_prefill = FusedPrefill.plan(self)
-        if self.fuse_decode and self._fused is not None and self._fused.takes(step, cache):
+        if self.fuse_decode and self._fused is not None and not profiling() and self._fused.takes(step, cache):
             self._fused.run(h, step, cache)
         elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):
             self._fused_prefill.run(h, step, cache)
@@ -89,10 +91,13 @@ class Model:
             if greedy:
                 return torch.empty(0, dtype=torch.int32, device=h.device)
             return torch.empty(0, self.spec.vocab_size, dtype=torch.float32, device=h.device)
-        x = self.final_norm.forward(h, rows=step.want_rows)
+        with phase("final_norm_ms"):
+            x = self.final_norm.forward(h, rows=step.want_rows)
         if not greedy:
-            return self.head.forward(x)
-        tokens = self.head.greedy(x, note) if hasattr(self.head, "greedy") else None
+            with phase("lm_head_ms"):
+                return self.head.forward(x)
+        with phase("lm_head_ms"):
+            tokens = self.head.greedy(x, note) if hasattr(self.head, "greedy") else None
         if tokens is None:
             # a head without such a kernel, or operands it does not take (32-bit, odd sizes): the logits, then their argmax
             from ..csrc import lib as K

@@ -23,6 +23,7 @@ from ..csrc import lib as K
 from .base import KVCacheRequest, Mixer, WeightSpec
 from .linear import GEMV_TOKENS, Linear
 from .registry import build_part, register_part
+from ..phases import phase
 
 
 @register_part("mixer", "attention")
@@ -97,18 +98,24 @@ class GQAAttention(Mixer):
         if (writes and rotary and rd == hd and hd % 16 == 0 and T <= GEMV_TOKENS and q.dtype == torch.bfloat16
                 and cache.k_pool.dtype == torch.bfloat16 and K.gemv_supported(x, w)):
             # a few tokens: one kernel does the QKV product, the rotation and the cache write
-            K.gemv_qkv_rope(x, w, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd)
+            with phase("qkv_projection+rotary+kv_append_ms"):
+                K.gemv_qkv_rope(x, w, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd)
         else:
-            proj = self.qkv if writes else self.q_only
-            qkv = proj(x, out_dtype=torch.float32)             # rotation reads unrounded products
-            if not writes:
-                pad = torch.empty(T, (nh + 2 * nkv) * hd, dtype=torch.float32, device=x.device)
-                pad[:, :nh * hd] = qkv
-                qkv = pad
-            if self.position is not None and not rotary:
-                self.position.apply(qkv, step, nh, nkv, hd)
-            K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
-        self.o(self.attend(q, step, cache), out=residual, accumulate=True)
+            with phase("qkv_projection_ms"):
+                proj = self.qkv if writes else self.q_only
+                qkv = proj(x, out_dtype=torch.float32)             # rotation reads unrounded products
+                if not writes:
+                    pad = torch.empty(T, (nh + 2 * nkv) * hd, dtype=torch.float32, device=x.device)
+                    pad[:, :nh * hd] = qkv
+                    qkv = pad
+            with phase("rotary+kv_append_ms"):
+                if self.position is not None and not rotary:
+                    self.position.apply(qkv, step, nh, nkv, hd)
+                K.rope_kv_write(qkv, q, cache.k_pool, cache.v_pool, cache, inv_freq, nh, nkv, hd, rd, write_kv=writes)
+        with phase("attention_ms"):
+            ctx = self.attend(q, step, cache)
+        with phase("o_projection+attention_residual_ms"):
+            self.o(ctx, out=residual, accumulate=True)
 
     def attend(self, q, step, cache):
         """The heads' outputs [T, heads·head_dim] for queries ``q`` (positions applied) over the keys and values that

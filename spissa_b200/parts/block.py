@@ -8,6 +8,7 @@ from __future__ import annotations
 
 from .base import Block
 from .registry import build_part, register_part
+from ..phases import phase
 
 
 @register_part("block", "prenorm")
@@ -33,5 +34,9 @@ class PreNormBlock(Block):
         return None if any(v is None for v in f.values()) else f
 
     def forward(self, h, step, cache):
-        self.mixer.forward(self.mixer_norm.forward(h), step, cache, h)
-        self.ffn.forward(self.ffn_norm.forward(h), step, h)
+        with phase("attention_norm_ms"):
+            x = self.mixer_norm.forward(h)
+        self.mixer.forward(x, step, cache, h)
+        with phase("mlp_norm_ms"):
+            x = self.ffn_norm.forward(h)
+        self.ffn.forward(x, step, h)

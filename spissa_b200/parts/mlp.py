@@ -11,6 +11,7 @@ import torch
 from .base import FeedForward, WeightSpec
 from .linear import GatedLinear, Linear
 from .registry import register_part
+from ..phases import phase
 
 
 @register_part("ffn", "swiglu")
@@ -46,5 +47,7 @@ class SwiGLU(FeedForward):
                     hidden_size=self.hidden_size, intermediate_size=self.intermediate_size)
 
     def forward(self, x, step, residual):
-        act = self.gate_up(x, self.rt.act_dtype)
-        self.down(act, out=residual, accumulate=True)
+        with phase("gate_projection+up_projection+activation_multiply_ms"):
+            act = self.gate_up(x, self.rt.act_dtype)
+        with phase("down_projection+mlp_residual_ms"):
+            self.down(act, out=residual, accumulate=True)

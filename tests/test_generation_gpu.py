@@ -303,3 +303,34 @@ def test_greedy_generation_in_bfloat16_never_writes_logits(folders, name, n_seqs
             assert float(row.max() - row[tok]) <= tiny.TOL["bfloat16"] * float(row.abs().max()) * 2
             ids.append(tok)
     engine.cache.check()
+
+
+def test_profiled_steps_report_their_phases_and_change_no_result(folders):
+    """``profile_phases``: CUDA events around the kernel groups of a step, named after the reference's phase timings
+    (crates/spissa-runtime/src/session.rs:14-101); such steps run kernel by kernel and part by part."""
+    folder, pcfg, w = folders["E"]
+    toks = tiny.random_prompt(777, 200, 3)
+    rows = {}
+    for profiled in (False, True):
+        engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 8)
+        engine.profile_phases = profiled
+        s = engine.acquire()
+        a = engine.step([(s, toks[:190], [189])]).cpu()
+        if profiled:
+            pre = engine.last_phases
+            assert pre["profiled_layers"] == 3 and pre["lm_head_ms"] > 0 and pre["embedding_ms"] > 0
+            assert "attention_ms" in pre["transformer_detail"]
+            assert any("qkv_projection" in k for k in pre["transformer_detail"])
+            assert abs(pre["total_ms"] - (pre["embedding_ms"] + pre["transformer_ms"] + pre["final_norm_ms"]
+                                          + pre["lm_head_ms"])) < 1e-2
+        b = [engine.step([(s, [t], [0])]).cpu() for t in toks[190:]]
+        if profiled:
+            dec = engine.last_phases["transformer_detail"]
+            # a decode step part by part: the norms and the fused QKV + rotation + cache write show as phases of their own
+            assert {"attention_norm_ms", "mlp_norm_ms", "attention_ms", "qkv_projection+rotary+kv_append_ms"} <= set(dec)
+            assert engine.phase_totals["decode"]["steps"] == 10 and engine.phase_totals["prefill"]["tokens"] == 190
+            assert len(engine._graphs) == 0                       # nothing was captured while profiling
+        rows[profiled] = torch.cat([a] + b)
+    ref = P.model_logits(pcfg, w, toks, torch.float64)[189:]
+    for got in rows.values():
+        assert float((got.double() - ref).abs().max()) / float(ref.abs().max()) <= tiny.TOL["bfloat16"]

@@ -19,6 +19,7 @@
 #include "flash_common.cuh"
 
 SP_API const char* sp_attention_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(attention)
 
 namespace {
 
@@ -53,7 +54,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     const int pos0 = positions[t0];
     const int h = blockIdx.x;
     const int g = h / (nh / kv.nkv);
-    const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
+    const int* pt = kv.page_table + (size_t)sp_checked_row(kv.seq_row[b], kv.rg) * kv.max_pages;
 
     const int last_pos = pos0 + n_rows - 1;
     const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
@@ -61,7 +62,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
 
     load_tile_async<HD>(q_tile, q + (size_t)t0 * nh * HD + (size_t)h * HD, (size_t)nh * HD, n_rows, tid, 128);
     {
-        const size_t off = ((size_t)pt[j_lo] * kv.nkv + g) * KT * HD;
+        const size_t off = ((size_t)sp_checked_page(pt[sp_checked_entry(j_lo, kv.max_pages, kv.rg)], kv.rg) * kv.nkv + g) * KT * HD;
         load_tile_async<HD>(k_tiles, kv.k + off, HD, KT, tid, 128);
         load_tile_async<HD>(v_tiles, kv.v + off, HD, KT, tid, 128);
     }
@@ -82,7 +83,7 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     for (int j = j_lo; j <= j_hi; ++j) {
         const int stage = (j - j_lo) & 1;
         if (j < j_hi) {
-            const size_t off = ((size_t)pt[j + 1] * kv.nkv + g) * KT * HD;
+            const size_t off = ((size_t)sp_checked_page(pt[sp_checked_entry(j + 1, kv.max_pages, kv.rg)], kv.rg) * kv.nkv + g) * KT * HD;
             load_tile_async<HD>(k_tiles + (stage ^ 1) * T::BYTES, kv.k + off, HD, KT, tid, 128);
             load_tile_async<HD>(v_tiles + (stage ^ 1) * T::BYTES, kv.v + off, HD, KT, tid, 128);
         }
@@ -189,7 +190,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
         if (counters) combine_if_last<HD>(part_o, part_ml, counters, out, out_dt, b, g, G, nh, kv.nkv, n_chunks, &is_last);
         return;
     }
-    const int* pt = kv.page_table + (size_t)kv.seq_row[b] * kv.max_pages;
+    const int* pt = kv.page_table + (size_t)sp_checked_row(kv.seq_row[b], kv.rg) * kv.max_pages;
 
     // the G heads of this kv head as rows 0..G-1 of a 16-row tile
     for (int c = tid; c < 16 * T::CHUNKS; c += 128) {
@@ -214,7 +215,7 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     // Each warp fetches and uses only its own 16 keys of every tile, so inside the loop the warps
     // need no barrier among themselves: a warp waits for its own copies and goes on.
     auto fetch = [&](int j, int stage) {
-        const size_t off = ((size_t)pt[j] * kv.nkv + g) * KT * HD + (size_t)warp * 16 * HD;
+        const size_t off = ((size_t)sp_checked_page(pt[sp_checked_entry(j, kv.max_pages, kv.rg)], kv.rg) * kv.nkv + g) * KT * HD + (size_t)warp * 16 * HD;
         const uint32_t kd = k_tiles + stage * T::BYTES + warp * 16 * T::ROW;
         const uint32_t vd = v_tiles + stage * T::BYTES + warp * 16 * T::ROW;
         for (int c = lane; c < 16 * T::CHUNKS; c += 32) {
@@ -354,7 +355,7 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
                             float scale, cudaStream_t stream) {
     if (n_q_tiles <= 0) return 0;
     if (check_common(hd, nh, nkv, page_size)) return 1;
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host};
     if (n_q_tiles > 65535) SP_FAIL("flash_prefill: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
@@ -417,7 +418,7 @@ SP_API int sp_flash_decode(const void* q, void* out, int out_dt, const void* kpo
     if (n_seqs > 65535) SP_FAIL("flash decode: %d sequences are beyond this kernel's grid", n_seqs);
     const long long need = sp_flash_decode_scratch_floats(n_seqs, nh, hd, n_chunks);
     if (scratch_floats < need) SP_FAIL("flash decode: scratch holds %lld floats, %lld are needed", scratch_floats, need);
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)n_seqs * nh * n_chunks * hd;
     dim3 grid(n_chunks, nkv, n_seqs);
@@ -487,7 +488,7 @@ SP_API int sp_flash_decode_static(const void* q, void* out, int out_dt, const vo
     e = cudaMemsetAsync(counters, 0, (size_t)n_seqs * nkv * sizeof(int), stream);
     if (e != cudaSuccess) SP_FAIL("flash decode (static scratch): clearing the counters failed: %s", cudaGetErrorString(e));
 
-    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv};
+    PagedKV kv{(const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, page_table, seq_row, max_pages, nkv, sp_range_host};
     dim3 grid(n_chunks, nkv, n_seqs);
     const float sl = scale * LOG2E;
     if (launch_flash_decode(hd, grid, stream, (const __nv_bfloat16*)q, kv, seq_len, nh, window, sl, chunk_tiles, part_o,

@@ -25,6 +25,21 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo", "--shared",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
+# The debug build: every kernel that takes an index from a table the host packed checks it against the bounds the
+# host declares, records a code in the status word and leaves the access out (see common.cuh). It is a separate set
+# of libraries (the flag is part of their names' hash), chosen for a whole process by SPISSA_B200_RANGE_CHECK=1.
+RANGE_CHECK_FLAG = "-DSP_RANGE_CHECK"
+
+
+def range_check_enabled() -> bool:
+    return os.environ.get("SPISSA_B200_RANGE_CHECK", "") not in ("", "0")
+
+
+def flags(range_check=None) -> list:
+    on = range_check_enabled() if range_check is None else bool(range_check)
+    return NVCC_FLAGS + ([RANGE_CHECK_FLAG] if on else [])
+
+
 # module name -> source file
 MODULES = {
     "generic": "generic_kernels.cu",
@@ -81,23 +96,28 @@ def build_dir() -> Path:
     raise BuildError(f"no writable folder for built kernels (tried {local} and {fallback})")
 
 
-def _digest(source: str) -> str:
+def _digest(source: str, range_check=None) -> str:
     h = hashlib.sha256()
     for name in [source] + HEADERS:
         h.update(name.encode())
         h.update((CSRC / name).read_bytes())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(flags(range_check)).encode())
     return h.hexdigest()[:16]
 
 
-def library_path(module: str, folder: Path | None = None) -> Path:
+def _stem(module: str, range_check=None) -> str:
+    on = range_check_enabled() if range_check is None else bool(range_check)
+    return f"libspissa_{module}_" + ("checked_" if on else "")
+
+
+def library_path(module: str, folder: Path | None = None, range_check=None) -> Path:
     source = MODULES[module]
-    return (folder or build_dir()) / f"libspissa_{module}_{_digest(source)}.so"
+    return (folder or build_dir()) / f"{_stem(module, range_check)}{_digest(source, range_check)}.so"
 
 
-def find_built(module: str) -> Path | None:
+def find_built(module: str, range_check=None) -> Path | None:
     """An up-to-date library of ``module`` in any of the known folders, if there is one."""
-    name = f"libspissa_{module}_{_digest(MODULES[module])}.so"
+    name = f"{_stem(module, range_check)}{_digest(MODULES[module], range_check)}.so"
     folders = [CSRC / "_build", Path(tempfile.gettempdir()) / f"spissa_b200_build_{os.getuid()}"]
     env = os.environ.get("SPISSA_B200_BUILD_DIR")
     if env:
@@ -108,19 +128,21 @@ def find_built(module: str) -> Path | None:
     return None
 
 
-def build_module(module: str, verbose: bool = True, extra_flags=()) -> Path:
-    """Compile ``module`` if no up-to-date library exists; return the library's path."""
+def build_module(module: str, verbose: bool = True, extra_flags=(), range_check=None) -> Path:
+    """Compile ``module`` if no up-to-date library exists; return the library's path. ``range_check`` None: as the
+    environment says (the regular build unless SPISSA_B200_RANGE_CHECK=1)."""
     if module not in MODULES:
         raise BuildError(f"unknown kernel module {module!r}; known: {sorted(MODULES)}")
-    have = find_built(module)
+    have = find_built(module, range_check)
     if have is not None:
         return have
-    out = library_path(module)
+    out = library_path(module, None, range_check)
     nvcc = find_nvcc()
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
-    cmd = [nvcc] + NVCC_FLAGS + list(extra_flags) + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / MODULES[module])]
+    cmd = [nvcc] + flags(range_check) + list(extra_flags) + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / MODULES[module])]
     if verbose:
-        _say(f"compiling {MODULES[module]} for sm_100a (first use) ...")
+        kind = " (debug build with range checks)" if RANGE_CHECK_FLAG in cmd else ""
+        _say(f"compiling {MODULES[module]} for sm_100a{kind} (first use) ...")
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             env=dict(os.environ, TMPDIR=str(out.parent)))
@@ -140,8 +162,9 @@ def build_module(module: str, verbose: bool = True, extra_flags=()) -> Path:
             pass
         raise BuildError(f"nvcc failed on {MODULES[module]}:\n{log}")
     os.replace(tmp, out)
+    checked = "_checked_" in out.name
     for old in out.parent.glob(f"libspissa_{module}_*.so"):
-        if old != out:
+        if old != out and ("_checked_" in old.name) == checked:
             try:
                 old.unlink()
             except OSError:
@@ -151,8 +174,8 @@ def build_module(module: str, verbose: bool = True, extra_flags=()) -> Path:
     return out
 
 
-def build_all(verbose: bool = True) -> dict:
-    return {m: build_module(m, verbose) for m in MODULES}
+def build_all(verbose: bool = True, range_check=None) -> dict:
+    return {m: build_module(m, verbose, range_check=range_check) for m in MODULES}
 
 
 if __name__ == "__main__":

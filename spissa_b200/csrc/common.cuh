@@ -147,3 +147,46 @@ static inline int sp_sm_count() {
     if (d < 64) count[d] = n;
     return n;
 }
+
+
+// ---------------------------------------------------------------- range checks of the debug build
+// Built with -DSP_RANGE_CHECK, every kernel that takes an index from a table that the host packed (a page from a
+// page table, a row of that table from ``seq_row``, a page slot from a position) compares it with the bounds the
+// host declared for the call, records a code in the status word when it lies outside and leaves the access out (a
+// write is skipped, a read goes to page or row 0 instead): no trap, no assert, the kernel ends normally and the host
+// raises. It stands in for a memory checker where none can be run. In the regular build the checks compile to
+// nothing. Codes: 401 a page beyond the pools, 402 a row beyond the page table, 403 a position beyond the table's width.
+struct SpRange {
+    int n_pages;      // pages the key/value pools hold
+    int n_rows;       // rows of the page table
+    int* status;
+};
+static SpRange sp_range_host = {0, 0, nullptr};        // one per library: what the next launches are given
+
+#ifdef SP_RANGE_CHECK
+#define SP_RANGE_CHECKED 1
+#else
+#define SP_RANGE_CHECKED 0
+#endif
+
+__device__ __forceinline__ bool sp_index_ok(long long v, long long n, const SpRange& rg, int code) {
+#ifdef SP_RANGE_CHECK
+    if (v < 0 || v >= n) {
+        if (rg.status) atomicCAS(rg.status, 0, code);
+        return false;
+    }
+#endif
+    return true;
+}
+__device__ __forceinline__ int sp_checked_page(int page, const SpRange& rg) { return sp_index_ok(page, rg.n_pages, rg, 401) ? page : 0; }
+__device__ __forceinline__ int sp_checked_row(int row, const SpRange& rg) { return sp_index_ok(row, rg.n_rows, rg, 402) ? row : 0; }
+__device__ __forceinline__ int sp_checked_entry(int entry, int width, const SpRange& rg) { return sp_index_ok(entry, width, rg, 403) ? entry : 0; }
+
+// Every library exports whether it is the debug build and takes the bounds for its next launches.
+#define SP_DEFINE_RANGE_API(module)                                                                  \
+    SP_API int sp_##module##_range_checked() { return SP_RANGE_CHECKED; }                            \
+    SP_API void sp_##module##_set_bounds(int n_pages, int n_rows, int* status) {                     \
+        sp_range_host.n_pages = n_pages;                                                             \
+        sp_range_host.n_rows = n_rows;                                                               \
+        sp_range_host.status = status;                                                               \
+    }

@@ -44,6 +44,7 @@
 #include <cuda.h>
 
 SP_API const char* sp_decode_layers_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(decode_layers)
 
 namespace {
 
@@ -99,6 +100,7 @@ struct Params {
     unsigned long long* trace;      // optional: the global timer at each grid barrier, see sp_decode_layers_set_trace
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
     const int* plan;                // optional, on the device: {chunk_pages, n_chunks} instead of the two above
+    SpRange rg;                     // what the debug build checks table entries against
 };
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
@@ -468,9 +470,10 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
         const bool hit = small && key[0] == b && key[1] == j_first && key[2] == j_last;
         const int* pts = small ? sh->ptc[wg] : pt_s;
         if (!hit) {
-            const int* pt = p.page_table + (size_t)p.seq_row[b] * p.max_pages + j_first;
+            const int* pt = p.page_table + (size_t)sp_checked_row(p.seq_row[b], p.rg) * p.max_pages;
             int* dst = small ? sh->ptc[wg] : pt_s;
-            for (int i = tid; i < cnt; i += 128) dst[i] = pt[i];
+            for (int i = tid; i < cnt; i += 128)
+                dst[i] = sp_checked_page(pt[sp_checked_entry(j_first + i, p.max_pages, p.rg)], p.rg);
         }
         for (int c = tid; c < 16 * TL::CHUNKS; c += 128) {
             const int r = c / TL::CHUNKS, k = c % TL::CHUNKS;
@@ -657,7 +660,9 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
     if (tid < T) {
         const int pos = p.positions[tid];
         sh->tok_pos[tid] = pos;
-        sh->tok_page[tid] = p.page_table[(size_t)p.seq_row[tid] * p.max_pages + pos / KT];
+        // a bad page is kept as it is (the cache write checks it again and leaves the write out)
+        sh->tok_page[tid] = p.page_table[(size_t)sp_checked_row(p.seq_row[tid], p.rg) * p.max_pages +
+                                         sp_checked_entry(pos / KT, p.max_pages, p.rg)];
     }
     // sums of squares of the incoming residual and its product with the first norm's weight: CTA m does token m
     {
@@ -730,6 +735,7 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
                         const bool is_k = blk < nqk;
                         const int kvh = is_k ? blk - L.nh : blk - nqk;
                         const int page = sh->tok_page[m];
+                        if (!sp_index_ok(page, p.rg.n_pages, p.rg, 401)) return;      // debug build: reported, not written
                         dst = (is_k ? L.k_pool : L.v_pool) + (((size_t)page * L.nkv + kvh) * KT + pos % KT) * HD;
                     }
                     dst[d] = __float2bfloat16_rn(lo);
@@ -986,6 +992,7 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.n_stages = stages;
     p.plan = plan;
+    p.rg = sp_range_host;
     if (plan_split(G, T, hd, len_pages, max_nkv, &p.chunk_pages, &p.n_chunks)) return 1;
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;
 

@@ -275,6 +275,7 @@ struct PagedKV {
     const int* seq_row;         // [B] row of each sequence in the table
     int max_pages;
     int nkv;
+    SpRange rg;                 // what the debug build checks table entries against
 };
 
 }  // namespace

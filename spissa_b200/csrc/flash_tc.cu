@@ -25,6 +25,7 @@
 #include "tcgen05.cuh"
 
 SP_API const char* sp_flash_tc_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(flash_tc)
 
 namespace {
 
@@ -60,7 +61,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
                         const int* __restrict__ seq_start, const int* __restrict__ positions,
                         const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
-                        int n_seqs, int nh, int nkv, float scale_log2, int* status) {
+                        int n_seqs, int nh, int nkv, float scale_log2, int* status, SpRange rg) {
     static_assert(HD == 64 || HD == 128, "scores 2 x 64 columns and the output HD columns of 256 in tensor memory");
     using L = Smem<HD>;
     constexpr int KV_STAGES = kv_stages<HD>();
@@ -92,7 +93,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const int h = blockIdx.x;
     const int g = h / (nh / nkv);
     const int n_blocks = live ? (pos0 + n_rows - 1) / KB + 1 : 0;
-    const int* pt = page_table + (size_t)(live ? seq_row[b] : 0) * max_pages;
+    const int* pt = page_table + (size_t)(live ? sp_checked_row(seq_row[b], rg) : 0) * max_pages;
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar_q), 1);
@@ -131,7 +132,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 if (!mbar_wait(smem_u32(&bar_kv_empty[s]), phase ^ 1u, status, 111)) break;
                 const uint32_t k_dst = kv_smem + s * L::STAGE_BYTES, v_dst = k_dst + L::K_BYTES;
                 mbar_expect_tx(smem_u32(&bar_kv_full[s]), L::STAGE_BYTES);
-                const int r0 = (pt[j] * nkv + g) * PAGE;
+                const int r0 = (sp_checked_page(pt[sp_checked_entry(j, max_pages, rg)], rg) * nkv + g) * PAGE;
 #pragma unroll
                 for (int c = 0; c < L::BOXES; ++c) {
                     tma_load_2d(k_dst + c * L::KV_BOX, &map_k, c * 64, r0, smem_u32(&bar_kv_full[s]));
@@ -360,7 +361,7 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
         }
         flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status);
+            scale * LOG2E, status, sp_range_host);
     } else {
         if (!configured[1].done()) {
             cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
@@ -369,7 +370,7 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
         }
         flash_prefill_tc_kernel<128><<<grid, 192, Smem<128>::TOTAL, stream>>>(
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status);
+            scale * LOG2E, status, sp_range_host);
     }
     SP_CHECK_LAUNCH("flash_prefill_tc");
     return 0;

@@ -17,6 +17,7 @@
 #include "common.cuh"
 
 SP_API const char* sp_gemv_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(gemv)
 
 namespace {
 
@@ -45,6 +46,7 @@ struct RopeOut {
     const int* page_table;
     const float* inv_freq;   // [hd / 2]
     int max_pages, page_size, nh, nkv, hd;
+    SpRange rg;              // what the debug build checks table entries against
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -246,7 +248,10 @@ gemv_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict
                     } else {
                         const bool is_k = blk < rope.nh + rope.nkv;
                         const int kvh = is_k ? blk - rope.nh : blk - rope.nh - rope.nkv;
-                        const int page = rope.page_table[(size_t)rope.seq_row[rope.token_seq[m]] * rope.max_pages + pos / rope.page_size];
+                        const int prow = rope.seq_row[rope.token_seq[m]];
+                        if (!sp_index_ok(prow, rope.rg.n_rows, rope.rg, 402) || !sp_index_ok(pos / rope.page_size, rope.max_pages, rope.rg, 403)) continue;
+                        const int page = rope.page_table[(size_t)prow * rope.max_pages + pos / rope.page_size];
+                        if (!sp_index_ok(page, rope.rg.n_pages, rope.rg, 401)) continue;      // debug build: reported, not written
                         __nv_bfloat16* dst = (is_k ? rope.kpool : rope.vpool) +
                             (((size_t)page * rope.nkv + kvh) * rope.page_size + pos % rope.page_size) * rope.hd;
                         dst[d] = __float2bfloat16_rn(lo);
@@ -481,7 +486,7 @@ SP_API int sp_gemv_qkv_rope(const void* x, int ldx, const void* W, int ldw, int 
     if (hd % 16) SP_FAIL("gemv (qkv): head_dim %d must be a multiple of 16 for the fused rotation", hd);
     if (check_gemv(x, W, M, N, K, ldx, ldw, SP_DT_BF16, MODE_ROPE_KV, hd / 2)) return 1;
     RopeOut rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, positions, token_seq, seq_row,
-                 page_table, inv_freq, max_pages, page_size, nh, nkv, hd};
+                 page_table, inv_freq, max_pages, page_size, nh, nkv, hd, sp_range_host};
     return launch_gemv(x, W, nullptr, SP_DT_BF16, M, N, K, ldx, ldw, 0, MODE_ROPE_KV, hd / 2, rope, stream);
 }
 

@@ -17,6 +17,7 @@
 #include "async_copy.cuh"
 
 SP_API const char* sp_generic_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(generic)
 
 // ============================================================== embedding
 template <typename TW>
@@ -287,7 +288,16 @@ struct KvPlace {
     const int* page_table;    // [slots][max_pages]
     int max_pages;
     int page_size;
+    SpRange rg;               // what the debug build checks table entries against
 };
+
+// the page that holds position ``pos`` of the sequence of token ``t``; false (debug build) when a table entry is bad
+__device__ __forceinline__ bool kv_page_of(const KvPlace& pl, int t, int pos, int& page) {
+    const int slot = pl.seq_slot[pl.token_seq[t]];
+    if (!sp_index_ok(slot, pl.rg.n_rows, pl.rg, 402) || !sp_index_ok(pos / pl.page_size, pl.max_pages, pl.rg, 403)) return false;
+    page = pl.page_table[(size_t)slot * pl.max_pages + pos / pl.page_size];
+    return sp_index_ok(page, pl.rg.n_pages, pl.rg, 401);
+}
 
 template <typename TIN, typename TQ, typename TC>
 __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict__ q_out,
@@ -302,8 +312,7 @@ __global__ void rope_kv_write_kernel(const TIN* __restrict__ qkv, TQ* __restrict
     const TIN* src = qkv + (size_t)t * row;
     int page = 0, off = 0;
     if (write_kv) {
-        const int slot = pl.seq_slot[pl.token_seq[t]];
-        page = pl.page_table[(size_t)slot * pl.max_pages + pos / pl.page_size];
+        if (!kv_page_of(pl, t, pos, page)) write_kv = 0;          // debug build: a bad entry is reported, nothing is written
         off = pos % pl.page_size;
     }
     const int n_rot_heads = nh + nkv;
@@ -395,8 +404,7 @@ rope_kv_write_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restri
     const float* src = qkv + (size_t)t * (nh + 2 * nkv) * hd;
     int page = 0, off = 0;
     if (write_kv) {
-        const int slot = pl.seq_slot[pl.token_seq[t]];
-        page = pl.page_table[(size_t)slot * pl.max_pages + pos / pl.page_size];
+        if (!kv_page_of(pl, t, pos, page)) write_kv = 0;          // debug build: a bad entry is reported, nothing is written
         off = pos % pl.page_size;
     }
     __shared__ float cs[2][AG_MAX_HD / 2];
@@ -444,7 +452,7 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
     if (rd < 0 || rd > hd || (rd & 1)) SP_FAIL("rope: rotary_dim %d must be even and at most head_dim %d", rd, hd);
     if (rd > AG_MAX_HD) SP_FAIL("rope: rotary_dim %d is beyond this kernel's limit %d", rd, AG_MAX_HD);
     if (rd > 0 && !inv_freq) SP_FAIL("rope: a frequency table is needed when rotary_dim > 0");
-    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     if (in_dt == SP_DT_F32 && q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16 && rd == hd && (hd % 8) == 0 &&
         ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0)) {
         rope_kv_write_bf16_kernel<<<T, 128, 0, stream>>>((const float*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool,
@@ -492,7 +500,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
     const int t = (int)(gw / nh), h = (int)(gw % nh);
     const int g = h / (nh / nkv);
     const int p = pl.positions[t];
-    const int slot = pl.seq_slot[pl.token_seq[t]];
+    const int slot = sp_checked_row(pl.seq_slot[pl.token_seq[t]], pl.rg);
     const int* pt = pl.page_table + (size_t)slot * pl.max_pages;
     const int ps = pl.page_size;
 
@@ -511,7 +519,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
         float s = -INFINITY;
         int my_page = 0, my_off = 0;
         if (valid) {
-            my_page = pt[j / ps];
+            my_page = sp_checked_page(pt[sp_checked_entry(j / ps, pl.max_pages, pl.rg)], pl.rg);
             my_off = j % ps;
             const TC* kr = kpool + (((size_t)my_page * nkv + g) * ps + my_off) * hd;
             float dot = 0.0f;
@@ -552,7 +560,7 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
     if (T <= 0) return 0;
     if (hd <= 0 || hd > AG_MAX_HD) SP_FAIL("attention: head_dim %d is beyond this kernel's limit %d", hd, AG_MAX_HD);
     if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
-    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size};
+    KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     const long long warps = (long long)T * nh;
     const long long blocks = (warps + AG_WARPS - 1) / AG_WARPS;
     if (blocks > 2147483647LL) SP_FAIL("attention: too many (token, head) pairs for one launch");
@@ -709,7 +717,7 @@ SP_API int sp_argmax_rows(const float* logits, int* out, int rows, int V, int ld
 __global__ void rope_table_kernel(const int* __restrict__ positions, const int* __restrict__ token_seq,
                                   const int* __restrict__ seq_row, const int* __restrict__ page_table, int max_pages,
                                   int page_size, const float* __restrict__ inv_freq, int half, int T,
-                                  float2* __restrict__ cs, int* __restrict__ tok_page) {
+                                  float2* __restrict__ cs, int* __restrict__ tok_page, SpRange rg) {
     const int t = blockIdx.x;
     if (t >= T) return;
     const int pos = positions[t];
@@ -717,8 +725,11 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const int* 
         const float ang = (float)pos * inv_freq[i];
         cs[(size_t)t * half + i] = make_float2(cosf(ang), sinf(ang));
     }
-    if (threadIdx.x == 0 && tok_page)
-        tok_page[t] = page_table[(size_t)seq_row[token_seq[t]] * max_pages + pos / page_size];
+    if (threadIdx.x == 0 && tok_page) {
+        const int row = sp_checked_row(seq_row[token_seq[t]], rg);
+        // a bad page is kept as it is: the kernels that use it check it again before they write
+        tok_page[t] = page_table[(size_t)row * max_pages + sp_checked_entry(pos / page_size, max_pages, rg)];
+    }
 }
 
 SP_API int sp_rope_table(const int* positions, const int* token_seq, const int* seq_row, const int* page_table,
@@ -728,7 +739,7 @@ SP_API int sp_rope_table(const int* positions, const int* token_seq, const int* 
     if (half <= 0 || !inv_freq) SP_FAIL("rope_table: a frequency table of at least one entry is needed");
     if (tok_page && (!page_table || page_size <= 0)) SP_FAIL("rope_table: the tokens' pages need the page table");
     rope_table_kernel<<<T, half >= 64 ? 64 : 32, 0, stream>>>(positions, token_seq, seq_row, page_table, max_pages, page_size,
-                                                            inv_freq, half, T, (float2*)cs, tok_page);
+                                                            inv_freq, half, T, (float2*)cs, tok_page, sp_range_host);
     SP_CHECK_LAUNCH("rope_table");
     return 0;
 }

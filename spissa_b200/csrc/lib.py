@@ -44,7 +44,36 @@ def load(module: str) -> ctypes.CDLL:
         getattr(lib, f"sp_{module}_last_error").restype = ctypes.c_char_p
         _LIBS[module] = lib
         _LOADED_PATHS[module] = str(path)
+        checked = getattr(lib, f"sp_{module}_range_checked", None)
+        _RANGE_CHECKED[module] = bool(checked()) if checked is not None else False
     return lib
+
+
+_RANGE_CHECKED: dict = {}
+
+
+def range_checked(module: str) -> bool:
+    """Whether ``module`` is loaded as the debug build whose kernels check table entries (see common.cuh)."""
+    load(module)
+    return _RANGE_CHECKED[module]
+
+
+def _declare_bounds(module: str, lib, n_pages: int, n_rows: int, device) -> None:
+    """Debug build only: the bounds the next launches of ``module`` check page and row indices against."""
+    if _RANGE_CHECKED.get(module):
+        getattr(lib, f"sp_{module}_set_bounds")(int(n_pages), int(n_rows), c_void_p(_ptr(status_word(device))))
+
+
+def _table_rows(meta, pt) -> int:
+    declared = getattr(meta, "declared_rows", None)
+    return int(declared) if declared is not None else int(pt.shape[0])
+
+
+def _pool_pages(meta, k_pool) -> int:
+    """Pages of the pools; a harness may declare fewer than it allocated (``meta.declared_pages``) to see a check fire
+    on an index that still lies inside allocated memory."""
+    declared = getattr(meta, "declared_pages", None)
+    return int(declared) if declared is not None else (int(k_pool.shape[0]) if k_pool is not None else 0)
 
 
 def loaded_libraries() -> dict:
@@ -133,6 +162,8 @@ def rope_kv_write(qkv, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd, rd, w
     T = qkv.shape[0]
     _need_contig(qkv, q_out)
     pt = meta.page_table
+    if pt is not None:
+        _declare_bounds("generic", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), qkv.device)
     _check("generic", lib.sp_rope_kv_write(
         c_void_p(_ptr(qkv)), dt_code(qkv), c_void_p(_ptr(q_out)), dt_code(q_out),
         c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool) if k_pool is not None else 0,
@@ -147,6 +178,7 @@ def attention_generic(q, k_pool, v_pool, out, meta, nh, nkv, hd, window, scale):
     T = q.shape[0]
     _need_contig(q, out)
     pt = meta.page_table
+    _declare_bounds("generic", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
     _check("generic", lib.sp_attention_generic(
         c_void_p(_ptr(q)), dt_code(q), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), dt_code(k_pool),
         c_void_p(_ptr(out)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.positions)),
@@ -305,6 +337,9 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                116: "attention: the softmax warps waited too long for the previous block's output",
                117: "attention: the softmax warps waited too long for the last block's output",
                301: "embedding: a token id outside the vocabulary",
+               401: "range check: a page index from a page table lies beyond the pools",
+               402: "range check: a sequence's row lies beyond the page table",
+               403: "range check: a position lies beyond the page table's width",
                900: "a wait that was meant to run out (test of the fault path)"}
 
 
@@ -411,6 +446,7 @@ def tc_gemm_fused(a, w, out, mode, bn, row_ssq=None, norm_width=0, eps=0.0, xw=N
         ep.cs, ep.tok_page, ep.positions = _ptr(r["cs"]), _ptr(r["tok_page"]), _ptr(r["positions"])
         ep.q_out, ep.kpool, ep.vpool = _ptr(r["q_out"]), _ptr(r["k_pool"]), _ptr(r["v_pool"])
         ep.nh, ep.nkv, ep.hd, ep.page_size = int(r["nh"]), int(r["nkv"]), int(r["hd"]), int(r["page_size"])
+        _declare_bounds("tc_gemm", lib, r.get("declared_pages", r["k_pool"].shape[0]), 0, a.device)
         c_ptr, c_dt, ldc = None, BF16, 0
     else:
         want_cols = N // 2 if mode == TC_SILU_MUL else N
@@ -430,6 +466,7 @@ def rope_table(meta, inv_freq, half, cs, tok_page):
     T = cs.shape[0]
     pt = meta.page_table
     _need_contig(cs, tok_page, inv_freq)
+    _declare_bounds("generic", lib, _pool_pages(meta, getattr(meta, "k_pool", None)), _table_rows(meta, pt), cs.device)
     _check("generic", lib.sp_rope_table(
         c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.token_seq)), c_void_p(_ptr(meta.seq_slot)),
         c_void_p(_ptr(pt)), pt.shape[1], meta.page_size, c_void_p(_ptr(inv_freq)), int(half), T, c_void_p(_ptr(cs)),
@@ -478,6 +515,7 @@ def flash_prefill(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles, nh
     lib = load("attention")
     _need_contig(q, out)
     pt = meta.page_table
+    _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
     _check("attention", lib.sp_flash_prefill(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.seq_slot)),
@@ -522,6 +560,7 @@ def flash_decode(q, k_pool, v_pool, out, meta, seq_len, nh, nkv, hd, window, sca
     n_seqs = q.shape[0]
     if counters is not None and (counters.dtype != torch.int32 or counters.numel() < n_seqs * nkv):
         raise KernelError("flash_decode: counters must be int32 with a word per (sequence, kv head)")
+    _declare_bounds("attention", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
     _check("attention", lib.sp_flash_decode(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), dt_code(out), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_void_p(_ptr(seq_len)), c_void_p(_ptr(meta.seq_slot)), c_void_p(_ptr(pt)), pt.shape[1], meta.page_size,
@@ -570,6 +609,7 @@ def gemv_qkv_rope(x, w, q_out, k_pool, v_pool, meta, inv_freq, nh, nkv, hd):
     pt = meta.page_table
     if q_out.dtype != torch.bfloat16 or k_pool.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemv_qkv_rope works on bfloat16 weights, queries and cache")
+    _declare_bounds("gemv", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), x.device)
     _check("gemv", lib.sp_gemv_qkv_rope(
         c_void_p(_ptr(x)), x.stride(0), c_void_p(_ptr(w)), w.stride(0), M, K, nh, nkv, hd, c_void_p(_ptr(q_out)),
         c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)), c_void_p(_ptr(meta.positions)), c_void_p(_ptr(meta.token_seq)),
@@ -592,6 +632,7 @@ def flash_prefill_tc(q, k_pool, v_pool, out, meta, seq_start, n_seqs, n_q_tiles,
     lib = load("flash_tc")
     _need_contig(q, out, k_pool, v_pool)
     pt = meta.page_table
+    _declare_bounds("flash_tc", lib, _pool_pages(meta, k_pool), _table_rows(meta, pt), q.device)
     _check("flash_tc", lib.sp_flash_prefill_tc(
         c_void_p(_ptr(q)), c_void_p(_ptr(out)), c_void_p(_ptr(k_pool)), c_void_p(_ptr(v_pool)),
         c_longlong(k_pool.shape[0]), q.shape[0], c_void_p(_ptr(seq_start)), c_void_p(_ptr(meta.positions)),
@@ -633,7 +674,7 @@ def decode_layers_encode_map(w: torch.Tensor, pair: int) -> bytes:
 
 
 def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, part_o, part_ml, positions, seq_row, page_table,
-                  page_size, len_pages, max_nkv, max_heads_per_kv, sync, plan=None):
+                  page_size, len_pages, max_nkv, max_heads_per_kv, sync, plan=None, n_pages=0):
     """Every layer of a decode step (one token per sequence, T ≤ 16) on the residual ``x`` [T, H] float32, in place.
 
     ``table``: the layers' descriptors on the device (``decode_layers_desc_bytes()`` each). One cooperative launch;
@@ -644,6 +685,7 @@ def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, par
     _need_contig(x, q, attn, act, page_table)
     if x.dtype != torch.float32 or x.shape[0] != T or x.shape[1] != H:
         raise KernelError(f"decode_layers: the residual must be float32 [{T}, {H}], got {x.dtype} {tuple(x.shape)}")
+    _declare_bounds("decode_layers", lib, n_pages, page_table.shape[0], x.device)
     _check("decode_layers", lib.sp_decode_layers(
         c_void_p(_ptr(table)), c_void_p(_ptr(maps)), int(n_layers), int(T), int(H), int(hd), c_void_p(_ptr(x)), c_void_p(_ptr(q)),
         c_void_p(_ptr(attn)), c_void_p(_ptr(act)), c_void_p(_ptr(xw)), c_void_p(_ptr(ssq)), c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)),

@@ -25,6 +25,7 @@
 #include "common.cuh"
 
 SP_API const char* sp_sampling_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(sampling)
 
 namespace {
 

@@ -30,6 +30,7 @@
 #include "tcgen05.cuh"
 
 SP_API const char* sp_tc_gemm_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(tc_gemm)
 
 namespace {
 
@@ -129,7 +130,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status,
-               const __grid_constant__ EpiArgs ep) {
+               const __grid_constant__ EpiArgs ep, const SpRange rg) {
     using L = SmemLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
@@ -275,10 +276,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int hh = 0; hh < heads_here; ++hh) {
                     const int col0 = n0 + hh * hd;
                     const int blk = col0 / hd;                          // q heads, then k heads, then v heads
-                    const bool live = row < M && col0 < N;
+                    bool live = row < M && col0 < N;
                     __nv_bfloat16* dst = nullptr;
                     if (live) {
                         if (blk < ep.nh) dst = ep.q_out + ((size_t)row * ep.nh + blk) * hd;
+                        else if (!sp_index_ok(page, rg.n_pages, rg, 401)) live = false;      // debug build: reported, not written
                         else {
                             const bool is_k = blk < ep.nh + ep.nkv;
                             const int kvh = is_k ? blk - ep.nh : blk - ep.nh - ep.nkv;
@@ -674,7 +676,7 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
     if (sm_count <= 0) SP_FAIL("tc_gemm: cannot read the number of SMs");
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, ep);
+    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host);
     SP_CHECK_LAUNCH("tc_gemm");
     return 0;
 }

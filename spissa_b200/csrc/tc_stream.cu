@@ -18,6 +18,7 @@
 #include "tcgen05.cuh"
 
 SP_API const char* sp_tc_stream_last_error() { return sp_error_text; }
+SP_DEFINE_RANGE_API(tc_stream)
 
 namespace {
 

@@ -157,4 +157,5 @@ class FusedDecode:
         len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
         K.decode_layers(self.table, self.maps, len(self.fields), step.n_tokens, self.H, self.hd, h, self.q, self.attn, self.act,
                         self.xw, self.ssq, self.part_o, self.part_ml, step.positions, step.seq_row, pt, cache.page_size,
-                        len_pages, self.max_nkv, self.max_group, self.sync, plan=step.key_split)
+                        len_pages, self.max_nkv, self.max_group, self.sync, plan=step.key_split,
+                        n_pages=cache.kv_groups[self.group].n_pages)

@@ -50,6 +50,7 @@ MODULES = {
     "flash_tc": "flash_tc.cu",
     "decode_layers": "decode_layers.cu",
     "tc_stream": "tc_stream.cu",
+    "host_step": "host_step.cu",
 }
 
 

@@ -36,6 +36,8 @@ class Model:
         self._fused = False            # False: not planned yet; None: the parts do not allow it
         self.fuse_prefill = True       # fold norms, rotation and cache write into a prompt step's products likewise
         self._fused_prefill = False
+        self.host_steps = True         # a short prompt step's launch sequence as one call into C++ likewise
+        self._host_step = False
 
     # ------------------------------------------------------------------ weights
     def parts(self) -> list:
@@ -67,6 +69,12 @@ class Model:
                 out[e.cache] = self.layers[e.layer].cache_request()
         return out
 
+    def _host_runner(self, step, cache) -> bool:
+        if self._host_step is False:
+            from .host_step import HostStep
+            self._host_step = HostStep.plan(self)
+        return self._host_step is not None and self._host_step.takes(step, cache)
+
     # ------------------------------------------------------------------ forward
     def forward(self, step, cache, greedy: bool = False, note=None) -> torch.Tensor:
         """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer; with
@@ -84,6 +92,8 @@ class Model:
             self._fused.run(h, step, cache)
         elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):
             self._fused_prefill.run(h, step, cache)
+        elif self.host_steps and not profiling() and self._host_runner(step, cache):
+            self._host_step.run(h, step, cache)
         else:
             for e in self.spec.schedule:
                 self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))

@@ -68,3 +68,37 @@ def test_short_prompts_and_other_models_run_part_by_part(folders):
     s = e32.acquire()
     e32.step([(s, tiny.random_prompt(777, 200, 1), [199])])
     assert e32.model._fused_prefill is None                          # the 32-bit path has no such kernels
+
+
+@pytest.mark.parametrize("name", ["E", "F"])
+def test_short_prompt_steps_through_the_host_runner_equal_the_parts_bit_for_bit(folders, name):
+    """Up to 128 tokens the layers' launch sequence runs as one call into C++ (csrc/host_step.cu): the same kernels
+    with the same arguments as part by part, so not a bit may differ; ragged batches and prompts that continue."""
+    folder, pcfg, w = folders[name]
+    V = pcfg["vocab_size"]
+    steps = [[5], [17, 3], [40], [100, 9, 19], [128]]
+    outs = {}
+    for host in (True, False):
+        engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 16)
+        engine.model.host_steps = host
+        rows = []
+        for i, counts in enumerate(steps):
+            slots = [engine.acquire() for _ in counts]
+            seqs = [tiny.random_prompt(V, n + 30, 100 * i + n) for n in counts]
+            rows.append(engine.step([(s, q[:n], [0, n - 1]) for s, q, n in zip(slots, seqs, counts)]).cpu())
+            rows.append(engine.step([(s, q[n:], [29]) for s, q, n in zip(slots, seqs, counts)]).cpu())   # 30 more each
+            for s in slots:
+                engine.release(s)
+        runner = engine.model._host_step
+        assert (runner is not False and runner is not None and runner.runs == 2 * len(steps)) if host else not runner
+        outs[host] = rows
+        engine.cache.check()
+    for a, b in zip(outs[True], outs[False]):
+        assert torch.equal(a, b)
+    # and against the plain implementation, once
+    toks = tiny.random_prompt(V, 70, 100 * 2 + 40)
+    ref = P.model_logits(pcfg, w, toks, torch.float64)
+    scale = float(ref.abs().max())
+    got = torch.cat([outs[True][4], outs[True][5]]).double()
+    want = ref[[0, 39, 69]]
+    assert float((got - want).abs().max()) / scale <= tiny.TOL["bfloat16"]

@@ -213,10 +213,11 @@ def kernel_case(name: str, reps: int) -> int:
         times = []
         for i in range(max(2, reps)):
             sl = eng.acquire()
+            toks = [rng.randrange(V) for _ in range(T)]
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             l0 = K.launches
             e0.record()
-            eng.step([(sl, [rng.randrange(V) for _ in range(T)], [T - 1])], greedy=True, check=False)
+            eng.step([(sl, toks, [T - 1])], greedy=True, check=False)
             e1.record()
             torch.cuda.synchronize()
             eng.check()

@@ -100,6 +100,9 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
     order = list(live)                             # row i of token_source belongs to order[i]
     in_flight = []                                 # [(order, pinned tokens, event)] oldest first
     steps = 0
+    # the tokens come back through three pinned buffers used in turn (two steps are in flight at most): asking the
+    # pinned allocator for a new one every step costs more than the copy
+    landing = [torch.empty(len(live), dtype=torch.int32, pin_memory=on_gpu) for _ in range(3)]
     engine_settles = hasattr(engine, "settle")
     # an engine with per-slot headers on the device: the sampler notes its tokens there and a step takes them from
     # there by slot; otherwise a step takes them from the tensor that the sampler returned, by row
@@ -142,7 +145,7 @@ def _decode_ahead(engine, sampler, params, live, results, stop, max_new_tokens, 
         else:
             logits = engine.step_device([slot for _, slot in order], token_source, rows)
             token_source = sampler.sample(logits, params, [req for req, _ in order], step_no)
-        pinned = torch.empty(len(order), dtype=torch.int32, pin_memory=on_gpu)
+        pinned = landing[steps % 3][:len(order)]
         pinned.copy_(token_source, non_blocking=True)
         event = None
         if on_gpu:

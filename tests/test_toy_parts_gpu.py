@@ -193,3 +193,89 @@ def test_routed_feed_forward_and_pair_rotation_run_through_the_engine(toy, tmp_p
         engine.release(s)
     engine.cache.check()
     assert engine.model._fused is None           # parts that offer no description of themselves run part by part
+
+
+# ------------------------------------------------------------------ an embedding that needs the tokens' positions
+class LearnedPositionEmbedding:
+    """h[t] = E[id_t] + Ppos[position_t]: absolute, learned positions live in the embedding, which therefore needs
+    more of the step than the token ids. Registered HERE under role ``embedding``."""
+    graph_safe = True
+
+    def __init__(self, vocab_size, hidden_size, max_positions, prefix="", **_):
+        self.prefix = prefix
+        self.vocab_size, self.hidden_size, self.max_positions = vocab_size, hidden_size, max_positions
+        self.rt = None
+
+    def children(self):
+        return []
+
+    def weight_specs(self):
+        return [WeightSpec(self.prefix + "weight", (self.vocab_size, self.hidden_size)),
+                WeightSpec("model.embed_positions.weight", (self.max_positions, self.hidden_size))]
+
+    def all_weight_specs(self):
+        return self.weight_specs()
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.table = tensors[self.prefix + "weight"].float()
+        self.pos = tensors["model.embed_positions.weight"].float()
+
+    def bind_all(self, tensors, rt):
+        self.bind(tensors, rt)
+
+    def forward(self, step):
+        return (self.table[step.tokens.long()] + self.pos[step.positions.long()]).contiguous()
+
+
+class ToyLearnedConfig(ToyPartsConfig):
+    def to_spec(self):
+        llama = self.base.to_spec()
+        emb = PartSpec("toy_learned_positions", dict(llama.embedding.params, max_positions=512), prefix=llama.embedding.prefix)
+        layers = tuple(LayerSpec(l.block, l.mixer.with_params(position=None), l.ffn, l.norms) for l in llama.layers)
+        return ModelSpec(**{**llama.__dict__, "architecture": "ToyLearnedForCausalLM", "embedding": emb, "layers": layers})
+
+
+def test_an_embedding_with_learned_positions_gets_the_step(tmp_path):
+    """The model hands the embedding the whole step, so positions can enter there; the layers then use no position
+    encoding at all. Whole prompts, a prompt that continues, and decode steps against the same arithmetic in float64."""
+    register_part("embedding", "toy_learned_positions", LearnedPositionEmbedding)
+    register_architecture("ToyLearnedForCausalLM", ToyLearnedConfig)
+    try:
+        cfg = config_from_dict(dict(architectures=["ToyLearnedForCausalLM"]))
+        write_random_model(cfg, tmp_path, seed=13, std=0.05)
+        pcfg, w = P.read_model_folder(tmp_path)
+        assert tuple(w["model.embed_positions.weight"].shape) == (512, BASE["hidden_size"])
+        engine = Engine.from_folder(tmp_path, dtype="float32", max_tokens=64 * 8, max_seqs=2)
+        n = P.config_numbers(BASE)
+
+        def plain(ids):
+            wd = {k: v.double() for k, v in w.items()}
+            T = len(ids)
+            h = P.embedding(wd["model.embed_tokens.weight"], ids) + wd["model.embed_positions.weight"][:T]
+            for i in range(2):
+                p = f"model.layers.{i}."
+                a = P.rms_norm(h, wd[p + "input_layernorm.weight"], n["eps"])
+                q = P.linear(a, wd[p + "self_attn.q_proj.weight"]).view(T, n["nh"], n["hd"])
+                k = P.linear(a, wd[p + "self_attn.k_proj.weight"]).view(T, n["nkv"], n["hd"])
+                v = P.linear(a, wd[p + "self_attn.v_proj.weight"]).view(T, n["nkv"], n["hd"])
+                h = h + P.linear(P.causal_attention(q, k, v).reshape(T, -1), wd[p + "self_attn.o_proj.weight"])
+                m = P.rms_norm(h, wd[p + "post_attention_layernorm.weight"], n["eps"])
+                h = h + P.swiglu(m, wd, p + "mlp.")
+            return P.linear(P.rms_norm(h, wd["model.norm.weight"], n["eps"]), wd["lm_head.weight"])
+
+        reqs = [tiny.random_prompt(300, m, 3 * m) for m in (40, 75)]
+        refs = [plain(r) for r in reqs]
+        scale = max(float(r.abs().max()) for r in refs)
+        slots = [engine.acquire() for _ in reqs]
+        got = engine.step([(s, r[:-5], [0, len(r) - 6]) for s, r in zip(slots, reqs)]).cpu().double()
+        want = torch.stack([refs[0][0], refs[0][34], refs[1][0], refs[1][69]])
+        assert float((got - want).abs().max()) / scale <= tiny.TOL["float32"]
+        for i in range(5, 0, -1):                                    # positions keep counting across steps
+            rows = engine.step([(s, [r[-i]], [0]) for s, r in zip(slots, reqs)]).cpu().double()
+            for b, ref in enumerate(refs):
+                assert float((rows[b] - ref[len(reqs[b]) - i]).abs().max()) / scale <= tiny.TOL["float32"]
+        engine.cache.check()
+    finally:
+        unregister_architecture("ToyLearnedForCausalLM")
+        unregister_part("embedding", "toy_learned_positions")

@@ -203,7 +203,7 @@ def kernel_case(name: str, reps: int) -> int:
         return 0
     if name == "prefill":
         # prompts of 2,048 tokens one after another through the engine's own step (the launch list of this run is
-        # what profiles/prefill_launches.md summarises)
+        # what profiles/prefill_step_fused_launches.md summarises)
         from spissa_b200 import Engine, LlamaConfig
         cfg = dict(CONFIG_1B)
         if KERNEL_CASE_LAYERS:
@@ -254,9 +254,14 @@ def kernel_case(name: str, reps: int) -> int:
         lib.sp_decode_layers_set_trace(ctypes.c_void_p(0))
         K.check_status(dev)
         t = trace.cpu().tolist()
-        names = ["input statistics"] + ["qkv", "attention", "combine", "output projection", "gate/up", "down"] * nl
+        # six grid barriers per layer, or five where the chunks are combined inside the attention phase by CTA pairs
+        # (the last layer's last barrier does not exist: the kernel ends there)
+        per_layer = ["qkv", "attention", "combine", "output projection", "gate/up", "down"]
+        if t[2 * 6 * nl] == 0:
+            per_layer = ["qkv", "attention+combine", "output projection", "gate/up", "down"]
+        names = ["input statistics"] + per_layer * nl
         work, wait = {}, {}
-        for e in range(1, 6 * nl + 1):              # barrier e: entered at t[2e], left at t[2e + 1]
+        for e in range(1, len(per_layer) * nl + 1):              # barrier e: entered at t[2e], left at t[2e + 1]
             work.setdefault(names[e - 1], []).append(t[2 * e] - t[2 * e - 1])
             wait.setdefault(names[e - 1], []).append(t[2 * e + 1] - t[2 * e])
         med = lambda v: sorted(v)[len(v) // 2] / 1e3

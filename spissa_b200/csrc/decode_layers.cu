@@ -22,7 +22,12 @@
 //   * attention runs inside: the keys of every (sequence, kv head) in chunks over the CTAs (the split comes as
 //     launch arguments or, for a launch replayed from a CUDA graph, as two words on the device), two groups of
 //     four warps per CTA with cp.async double buffering, the keys as the M of mma.sync and the query heads of
-//     the kv head as its N (flash_common.cuh: decode_step_t), then one warp per (token, head) combines the chunks;
+//     the kv head as its N (flash_common.cuh: decode_step_t), then one warp per (token, head) combines the chunks.
+//     Where the split is into 1, 2 or 4 chunks (about as many items as warp groups: eight sequences of eight kv
+//     heads, for instance) the CTAs are launched as pairs (a thread-block cluster of two) and all chunks of a
+//     (sequence, kv head) sit in one pair: the groups leave their partial results in shared memory, the pair's first
+//     CTA reads its partner's through distributed shared memory behind a cluster-scope mbarrier and writes the
+//     heads' outputs itself, so the combination costs neither a phase of its own nor its grid barrier;
 //   * phases that need every CTA's result are separated by a grid barrier (cooperative launch; an atomic
 //     counter; bounded spin).
 // RMSNorm costs no pass of its own: whoever adds into the residual also stores it multiplied by the next norm's
@@ -100,6 +105,8 @@ struct Params {
     unsigned long long* trace;      // optional: the global timer at each grid barrier, see sp_decode_layers_set_trace
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
     const int* plan;                // optional, on the device: {chunk_pages, n_chunks} instead of the two above
+    int pairs;                      // 1: launched as clusters of two CTAs (the pair-wise combination is possible)
+    int pad2;
     SpRange rg;                     // what the debug build checks table entries against
 };
 
@@ -194,7 +201,9 @@ struct Shared {
     int ptc[2][64];        // per attention group: page-table entries of its last item (the table is the same in every layer)
     int ptc_key[2][3];     // whose they are: sequence, first and last page
     int aborted;
+    uint64_t pair_bar;     // arrivals of the four attention groups of a CTA pair (used in the pair's first CTA)
 };
+static_assert(sizeof(Shared) <= STATIC_SMEM, "the static shared memory is counted as STATIC_SMEM bytes");
 
 // Grid-barrier arrivals are counted in sync[0]; an abort sets ABORT_BIT there, which lets every waiter through.
 constexpr unsigned ABORT_BIT = 0x40000000u;
@@ -431,9 +440,13 @@ __device__ __forceinline__ void publish_ssq(Shared* sh, float mine, float* dst, 
 
 // ---------------------------------------------------------------- attention: chunks of keys, then their combination
 // GROUPS groups of four warps, each with tiles of its own, work on different (sequence, kv head, chunk) items.
-template <int HD, int ST, int GROUPS, int NH>
+// PAIRED: there is at most one item per group, all chunks of a (sequence, kv head) lie in one CTA pair, and the
+// groups' partial results go to ``xch`` ([group][8 heads][HD + 2] floats in this CTA's shared memory) instead of global
+// memory; a single chunk is finished here (divided by its sum and stored).
+constexpr int XCH_ROWS = 8;
+template <int HD, int ST, int GROUPS, int NH, bool PAIRED>
 __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const LayerDesc& L, uint8_t* scratch_all,
-                                              int chunk_pages, int n_chunks) {
+                                              int chunk_pages, int n_chunks, float* xch) {
     using TL = Tile<HD>;
     constexpr int GROUP_BYTES = 16 * TL::ROW + 2 * ST * TL::BYTES + MAX_CHUNK_PAGES * 4;
     constexpr int MS = HD + 2;
@@ -457,9 +470,15 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
         const size_t part_base = ((size_t)b * L.nh + (size_t)g * Gq) * n_chunks + chunk;
         if (j_first > j_last) {                                    // no keys in this chunk (the same for all 128 threads)
             for (int i = tid; i < Gq; i += 128) {
-                p.part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
-                p.part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
+                if (PAIRED) {
+                    xch[((size_t)wg * XCH_ROWS + i) * MS + HD] = -INFINITY;
+                    xch[((size_t)wg * XCH_ROWS + i) * MS + HD + 1] = 0.0f;
+                } else {
+                    p.part_ml[(part_base + (size_t)i * n_chunks) * 2] = -INFINITY;
+                    p.part_ml[(part_base + (size_t)i * n_chunks) * 2 + 1] = 0.0f;
+                }
             }
+            if (PAIRED) break;
             continue;
         }
         // The table entries first, all at once: a load inside the loop would stall the warp for its whole way to
@@ -576,11 +595,130 @@ __device__ __noinline__ void attention_chunks(const Params& p, Shared* sh, const
                 acc += src[d] * f;
                 ll += src[HD + 1] * f;
             }
-            const size_t pi = part_base + (size_t)row * n_chunks;
-            p.part_o[pi * HD + d] = acc;
-            if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+            if (PAIRED) {
+                if (n_chunks == 1) {
+                    // the only chunk: what the combination would do with it (factor 2^0 = 1)
+                    p.attn[((size_t)b * L.nh + (size_t)g * Gq + row) * HD + d] = __float2bfloat16_rn(acc / ll);
+                } else {
+                    float* dst = xch + ((size_t)wg * XCH_ROWS + row) * MS;
+                    dst[d] = acc;
+                    if (d == 0) { dst[HD] = mm; dst[HD + 1] = ll; }
+                }
+            } else {
+                const size_t pi = part_base + (size_t)row * n_chunks;
+                p.part_o[pi * HD + d] = acc;
+                if (d == 0) { p.part_ml[pi * 2] = mm; p.part_ml[pi * 2 + 1] = ll; }
+            }
         }
         bar_sync(bar, 128);                                        // the tiles are free for the next item
+        if (PAIRED) break;
+    }
+}
+
+// ---------------------------------------------------------------- the pair-wise combination
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local_addr, uint32_t rank) {
+    uint32_t ra;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+    return ra;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
+// After attention_chunks<PAIRED>: out[b, heads of g, :] from the chunks' partial results in the pair's shared memory,
+// with the arithmetic and the order of attention_combine. Two chunks lie in the two groups of one CTA (a barrier of
+// the CTA's consumer warps is enough); four lie in the four groups of the pair: every group announces its result on
+// the first CTA's barrier (release, cluster scope), that CTA waits (acquire) and reads its partner's two through
+// distributed shared memory. Called by all consumer warps of every CTA; ``pair_phase`` counts the uses of the barrier.
+template <int HD>
+__device__ __noinline__ void attention_pair_combine(const Params& p, Shared* sh, const LayerDesc& L, float* xch,
+                                                       int n_chunks, uint32_t& pair_phase) {
+    constexpr int MS = HD + 2;
+    const int tid = threadIdx.x;
+    const int Gq = L.nh / L.nkv;
+    const int n_items = p.T * L.nkv * n_chunks;
+    if (n_chunks == 1) return;
+    if (n_chunks == 2) {
+        const int it0 = (int)blockIdx.x * 2;
+        bar_sync(1, CTHREADS);
+        if (it0 >= n_items) return;
+        const int b = it0 / (L.nkv * 2), g = (it0 / 2) % L.nkv;
+        for (int e = tid; e < Gq * HD; e += CTHREADS) {
+            const int row = e / HD, d = e % HD;
+            const float* c0 = xch + (size_t)row * MS;
+            const float* c1 = xch + ((size_t)XCH_ROWS + row) * MS;
+            const float mm = fmaxf(c0[HD], c1[HD]);
+            const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+            float ll = 0.0f, acc = 0.0f;
+            if (c0[HD + 1] > 0.0f) { const float f = exp2f(c0[HD] - msafe); ll += c0[HD + 1] * f; acc += c0[d] * f; }
+            if (c1[HD + 1] > 0.0f) { const float f = exp2f(c1[HD] - msafe); ll += c1[HD + 1] * f; acc += c1[d] * f; }
+            p.attn[((size_t)b * L.nh + (size_t)g * Gq + row) * HD + d] = __float2bfloat16_rn(acc / ll);
+        }
+        return;
+    }
+    // four chunks: the pair's four groups
+    const uint32_t rank = cluster_rank();
+    const int it0 = ((int)blockIdx.x & ~1) * 2;
+    if (it0 >= n_items) return;                                    // an idle pair (the same decision in both CTAs)
+    const uint32_t bar_local = smem_u32(&sh->pair_bar);
+    bar_sync(1, CTHREADS);                                         // both groups of this CTA have written their results
+    if (tid == 0) {
+        const uint32_t target = map_to_rank(bar_local, 0u);
+        // one arrival per group: this thread arrives for both groups of its CTA
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0], 2;" ::"r"(target) : "memory");
+    }
+    if (rank != 0) return;
+    if (!is_aborted(sh)) {
+        const uint32_t parity = pair_phase & 1u;
+        const unsigned long long t0 = global_ns();
+        while (true) {
+            uint32_t ok;
+            asm volatile(
+                "{\n\t.reg .pred q;\n\t"
+                "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 q, [%1], %2;\n\t"
+                "selp.u32 %0, 1, 0, q;\n\t}"
+                : "=r"(ok) : "r"(bar_local), "r"(parity) : "memory");
+            if (ok || is_aborted(sh)) break;
+            if (global_ns() - t0 > WAIT_LIMIT_NS) { raise_abort(p, sh, 205); break; }
+        }
+    }
+    ++pair_phase;
+    const int b = it0 / (L.nkv * 4), g = (it0 / 4) % L.nkv;
+    const uint32_t xch_local = smem_u32(xch), xch_peer = map_to_rank(xch_local, 1u);
+    for (int e = tid; e < Gq * HD; e += CTHREADS) {
+        const int row = e / HD, d = e % HD;
+        float mc[4], lc[4], oc[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {                              // chunk c: CTA c / 2 of the pair, group c % 2
+            const uint32_t at = (uint32_t)((((c & 1) * XCH_ROWS + row) * MS) * 4);
+            if (c < 2) {
+                const float* src = xch + (size_t)((c & 1) * XCH_ROWS + row) * MS;
+                mc[c] = src[HD]; lc[c] = src[HD + 1]; oc[c] = src[d];
+            } else {
+                mc[c] = ld_cluster_f32(xch_peer + at + HD * 4);
+                lc[c] = ld_cluster_f32(xch_peer + at + (HD + 1) * 4);
+                oc[c] = ld_cluster_f32(xch_peer + at + d * 4);
+            }
+        }
+        const float mm = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
+        const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+        float ll = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if (lc[c] > 0.0f) {                                    // chunks in order
+                const float f = exp2f(mc[c] - msafe);
+                ll += lc[c] * f;
+                acc += oc[c] * f;
+            }
+        }
+        p.attn[((size_t)b * L.nh + (size_t)g * Gq + row) * HD + d] = __float2bfloat16_rn(acc / ll);
     }
 }
 
@@ -633,7 +771,7 @@ __device__ __noinline__ void attention_combine(const Params& p, const LayerDesc&
 }
 
 // ---------------------------------------------------------------- the consumer warps' walk through the layers
-template <int HD, int ST, int AG, bool WIDE>
+template <int HD, int ST, int AG, bool WIDE, bool PAIRS>
 __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red, uint8_t* uni) {
     constexpr int NF = WIDE ? 2 : 1;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -656,6 +794,9 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
             n_chunks = 1;
         }
     }
+    // all chunks of a (sequence, kv head) in one CTA pair: see attention_pair_combine
+    const bool pair_split = PAIRS && AG == 2 && chunk_pages <= 64 && (n_chunks == 1 || n_chunks == 2 || n_chunks == 4);
+    uint32_t pair_phase = 0;
     if (tid < 2) sh->ptc_key[tid][0] = -1;
     if (tid < T) {
         const int pos = p.positions[tid];
@@ -744,13 +885,21 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
         grid_sync(p, sh, epoch);
 
         // ---- attention
-        if (warp < 4 * AG) {                         // head tiles of 8: one for up to 8 query heads per kv head, else two
-            if (L.nh <= 8 * L.nkv) attention_chunks<HD, ST, AG, 1>(p, sh, L, uni, chunk_pages, n_chunks);
-            else attention_chunks<HD, ST, AG, 2>(p, sh, L, uni, chunk_pages, n_chunks);
+        const bool paired = PAIRS && pair_split && L.nh <= 8 * L.nkv && p.T * L.nkv * n_chunks <= G * AG;
+        if (PAIRS && paired) {
+            // (AG == 2: every consumer warp belongs to an attention group) partial results through shared memory
+            attention_chunks<HD, ST, AG, 1, true>(p, sh, L, uni, chunk_pages, n_chunks, red);
+            attention_pair_combine<HD>(p, sh, L, red, n_chunks, pair_phase);
+            grid_sync(p, sh, epoch);
+        } else {
+            if (warp < 4 * AG) {                     // head tiles of 8: one for up to 8 query heads per kv head, else two
+                if (L.nh <= 8 * L.nkv) attention_chunks<HD, ST, AG, 1, false>(p, sh, L, uni, chunk_pages, n_chunks, nullptr);
+                else attention_chunks<HD, ST, AG, 2, false>(p, sh, L, uni, chunk_pages, n_chunks, nullptr);
+            }
+            grid_sync(p, sh, epoch);
+            attention_combine<HD>(p, L, n_chunks);
+            grid_sync(p, sh, epoch);
         }
-        grid_sync(p, sh, epoch);
-        attention_combine<HD>(p, L, n_chunks);
-        grid_sync(p, sh, epoch);
 
         // ---- output projection into the residual
         // residual += product; its square for the next norm's statistics; residual times the next norm's weight
@@ -812,8 +961,9 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 }
 
 // ---------------------------------------------------------------- the kernel
-// HD: head size; ST: stages of the attention's key/value tiles; AG: warp groups that work on attention
-template <int HD, int ST, int AG>
+// HD: head size; ST: stages of the attention's key/value tiles; AG: warp groups that work on attention; PAIRS: launched
+// as clusters of two CTAs, with the pair-wise combination of the attention's chunks compiled in
+template <int HD, int ST, int AG, bool PAIRS>
 __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ Shared sh_;
@@ -830,6 +980,7 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
             mbar_init(smem_u32(&sh->empty[s]), CWARPS);
         }
         sh->aborted = 0;
+        mbar_init(smem_u32(&sh->pair_bar), 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -839,9 +990,9 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
     if (warp == CWARPS) {
         copy_warp<HD>(p, sh, ring, lane);
     } else if (p.T > 8) {
-        consumers<HD, ST, AG, true>(p, sh, ring, red, uni);
+        consumers<HD, ST, AG, true, PAIRS>(p, sh, ring, red, uni);
     } else {
-        consumers<HD, ST, AG, false>(p, sh, ring, red, uni);
+        consumers<HD, ST, AG, false, PAIRS>(p, sh, ring, red, uni);
     }
     __syncthreads();
     // the last CTA to finish hands the counters back at zero for the next launch
@@ -883,11 +1034,31 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// The split of the keys: about one (sequence, kv head, chunk) item per warp group of the grid.
+// The split of the keys: about one (sequence, kv head, chunk) item per warp group of the grid. Where 1, 2 or 4 chunks
+// keep at least three quarters of the groups busy (and the CTAs can be launched as pairs) that split is taken, even if
+// the last chunks of a short sequence are empty: the pair-wise combination then saves a phase and a grid barrier.
+// chunks per (sequence, kv head) for the pair-wise combination with T sequences, or 0 where it does not pay
+int pair_chunks(int G, int T, int hd, int max_nkv) {
+    if (hd != 64 || (G % 2) != 0) return 0;
+    const int groups = G * 2, items = T * (max_nkv > 0 ? max_nkv : 1);
+    const int want = groups / items;
+    const int c = want >= 4 ? 4 : (want >= 2 ? 2 : (want >= 1 ? 1 : 0));
+    return (c > 0 && 4 * items * c >= 3 * groups) ? c : 0;
+}
+
 int plan_split(int G, int T, int hd, int len_pages, int max_nkv, int* chunk_pages, int* n_chunks) {
     if (len_pages < 1) len_pages = 1;
-    int want = G * (hd == 64 ? 2 : 1) / (T * (max_nkv > 0 ? max_nkv : 1));
+    const int groups = G * (hd == 64 ? 2 : 1);
+    int want = groups / (T * (max_nkv > 0 ? max_nkv : 1));
     if (want < 1) want = 1;
+    if (const int c = pair_chunks(G, T, hd, max_nkv)) {
+        const int per = (len_pages + c - 1) / c;
+        if (per <= 64) {
+            *chunk_pages = per;
+            *n_chunks = c;
+            return 0;
+        }
+    }
     if (want > MAX_CHUNKS) want = MAX_CHUNKS;
     if (want > len_pages) want = len_pages;
     if (want * MAX_CHUNK_PAGES < len_pages) want = (len_pages + MAX_CHUNK_PAGES - 1) / MAX_CHUNK_PAGES;
@@ -992,14 +1163,17 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.n_stages = stages;
     p.plan = plan;
+    p.pairs = pair_chunks(G, T, hd, max_nkv) > 0 ? 1 : 0;      // CTA pairs only where that split can occur with T sequences
+    p.pad2 = 0;
     p.rg = sp_range_host;
     if (plan_split(G, T, hd, len_pages, max_nkv, &p.chunk_pages, &p.n_chunks)) return 1;
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;
 
     void* args[] = {(void*)&p};
-    const void* fn = hd == 64 ? (const void*)decode_layers_kernel<64, 2, 2> : (const void*)decode_layers_kernel<128, 2, 1>;
-    static SpPerDevice configured[2];
-    const int which = hd == 64 ? 0 : 1;
+    const void* fn = hd == 64 ? (p.pairs ? (const void*)decode_layers_kernel<64, 2, 2, true> : (const void*)decode_layers_kernel<64, 2, 2, false>)
+                              : (const void*)decode_layers_kernel<128, 2, 1, false>;
+    static SpPerDevice configured[3];
+    const int which = hd == 64 ? (p.pairs ? 2 : 0) : 1;
     if (!configured[which].done()) {
         cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT - STATIC_SMEM);
         if (e != cudaSuccess) SP_FAIL("decode_layers: cannot reserve shared memory: %s", cudaGetErrorString(e));
@@ -1008,6 +1182,21 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
         if (e != cudaSuccess || per_sm < 1) SP_FAIL("decode_layers: one CTA of %d bytes does not fit an SM", smem);
         configured[which].mark();
     }
-    SP_CHECK_CALL("decode_layers", cudaLaunchCooperativeKernel(fn, dim3(G), dim3(THREADS), args, (size_t)smem, stream));
+    // cooperative (the CTAs wait for one another at the grid barrier), and as clusters of two where the grid is even
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(G);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeCooperative;
+    attrs[0].val.cooperative = 1;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = p.pairs ? 2 : 1;
+    attrs[1].val.clusterDim.y = 1;
+    attrs[1].val.clusterDim.z = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 2;
+    SP_CHECK_CALL("decode_layers", cudaLaunchKernelExC(&cfg, fn, args));
     return 0;
 }

@@ -329,6 +329,7 @@ STATUS_TEXT = {101: "the TMA loader waited too long for a free pipeline stage",
                202: "decode layers: a consumer warp waited too long for a weight tile",
                203: "decode layers: a CTA waited too long at the grid barrier",
                204: "decode layers: the split of the keys read from the device is outside what the scratch holds",
+               205: "decode layers: a CTA waited too long for its partner's partial attention results",
                111: "attention: the loader waited too long for a free key/value stage",
                112: "attention: the MMA issuer waited too long for the queries",
                113: "attention: the MMA issuer waited too long for keys and values",

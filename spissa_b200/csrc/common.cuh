@@ -109,6 +109,32 @@ static inline cudaError_t sp_launch_cluster(void (*kern)(KArgs...), dim3 grid, d
     return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with sp_launch_dependent may become resident while the kernel before it in the stream is still
+// running (on SMs whose CTAs of that kernel have left): it sets up (barriers, tensor memory) and then waits in
+// sp_wait_for_predecessor() until the predecessor has finished and its writes are visible; it touches no global
+// memory before that. The predecessor allows it by sp_allow_dependents() (the launch happens once every CTA of it
+// has said so or has left, so no CTA of the predecessor is ever kept from an SM). Between long kernels this hides the
+// launch gap and the dependent's set-up.
+__device__ __forceinline__ void sp_allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void sp_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t sp_launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                              cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 #define SP_CHECK_CALL(name, call)                                                   \
     do {                                                                           \
         cudaError_t e_ = (call);                                                   \

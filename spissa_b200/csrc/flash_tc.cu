@@ -120,6 +120,9 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
+    // set up; from here on the kernel reads what its predecessor in the stream wrote (q, the cache)
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
 
     if (warp == 0) {
         if (lane == 0 && live) {
@@ -359,18 +362,18 @@ SP_API int sp_flash_prefill_tc(const void* q, void* out, const void* kpool, cons
             if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<64>::TOTAL, cudaGetErrorString(e));
             configured[0].mark();
         }
-        flash_prefill_tc_kernel<64><<<grid, 192, Smem<64>::TOTAL, stream>>>(
+        SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<64>, grid, dim3(192), (size_t)Smem<64>::TOTAL, stream,
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host);
+            scale * LOG2E, status, sp_range_host));
     } else {
         if (!configured[1].done()) {
             cudaError_t e = cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, Smem<128>::TOTAL);
             if (e != cudaSuccess) SP_FAIL("flash_tc: cannot reserve %d bytes of shared memory: %s", Smem<128>::TOTAL, cudaGetErrorString(e));
             configured[1].mark();
         }
-        flash_prefill_tc_kernel<128><<<grid, 192, Smem<128>::TOTAL, stream>>>(
+        SP_CHECK_CALL("flash_prefill_tc", sp_launch_dependent(flash_prefill_tc_kernel<128>, grid, dim3(192), (size_t)Smem<128>::TOTAL, stream,
             mq, mk, mv, (__nv_bfloat16*)out, seq_start, positions, seq_row, page_table, max_pages, n_seqs, nh, nkv,
-            scale * LOG2E, status, sp_range_host);
+            scale * LOG2E, status, sp_range_host));
     }
     SP_CHECK_LAUNCH("flash_prefill_tc");
     return 0;

@@ -168,6 +168,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    // Set up. From here on the kernel reads what its predecessor in the stream wrote (A, C, the rows' statistics).
+    // (Asking for the first W tiles before this wait, since the weights are nobody's output, changed nothing: a CTA of
+    // this kernel becomes resident only when the predecessor's CTA has left its SM.)
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -178,10 +183,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
                     const int s = kbc % STAGES;
                     const uint32_t phase = (kbc / STAGES) & 1u;
-                    ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101);
-                    if (!ok) break;
                     const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
                     const uint32_t b_dst = a_dst + L::A_BYTES;
+                    ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101);
+                    if (!ok) break;
                     mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
                     tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
                     tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
@@ -676,8 +681,8 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
     if (sm_count <= 0) SP_FAIL("tc_gemm: cannot read the number of SMs");
     const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-    tc_gemm_kernel<BN, STAGES><<<grid, 192, L::TOTAL, stream>>>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host);
-    SP_CHECK_LAUNCH("tc_gemm");
+    SP_CHECK_CALL("tc_gemm", sp_launch_dependent(tc_gemm_kernel<BN, STAGES>, dim3(grid), dim3(192), (size_t)L::TOTAL, stream, ma, mw,
+                                                 C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host));
     return 0;
 }
 

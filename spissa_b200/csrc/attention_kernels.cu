@@ -37,6 +37,8 @@ flash_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restr
     const uint32_t k_tiles = q_tile + T::BYTES;          // two stages of K, then two of V
     const uint32_t v_tiles = k_tiles + 2 * T::BYTES;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
 
     // which sequence and which 64-token tile of it. Heads run fastest over the grid and tiles from the last to the
     // first: the tiles with the most keys start first in every head, the short ones fill the end.
@@ -172,6 +174,8 @@ flash_decode_kernel(const __nv_bfloat16* __restrict__ q, PagedKV kv, const int* 
     const uint32_t k_tiles = q_tile + 16 * T::ROW;
     const uint32_t v_tiles = k_tiles + DEC_STAGES * T::BYTES;
     float* merge = (float*)(smem + 16 * T::ROW + 2 * DEC_STAGES * T::BYTES);    // [4 warps][16 rows][HD + 2]
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int chunk = blockIdx.x, n_chunks = gridDim.x, g = blockIdx.y, b = blockIdx.z;
     const int G = nh / kv.nkv;
@@ -362,12 +366,12 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     if (hd == 64) {
         static SpPerDevice ok;
         if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<64>, prefill_smem<64>(), "flash_prefill")) return 1; ok.mark(); }
-        flash_prefill_kernel<64><<<grid, 128, prefill_smem<64>(), stream>>>(
+        sp_launch_dependent(flash_prefill_kernel<64>, grid, dim3(128), (size_t)prefill_smem<64>(), stream,
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
     } else {
         static SpPerDevice ok;
         if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<128>, prefill_smem<128>(), "flash_prefill")) return 1; ok.mark(); }
-        flash_prefill_kernel<128><<<grid, 128, prefill_smem<128>(), stream>>>(
+        sp_launch_dependent(flash_prefill_kernel<128>, grid, dim3(128), (size_t)prefill_smem<128>(), stream,
             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
     }
     SP_CHECK_LAUNCH("flash_prefill");
@@ -382,8 +386,8 @@ int launch_flash_decode_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16* 
                            void* out, int out_dt) {
     static SpPerDevice ok;            // the opt-in holds for one device: asked for on each device's first launch
     if (!ok.done()) { if (opt_in_smem(flash_decode_kernel<HD, NH>, decode_smem<HD>(), "flash_decode")) return 1; ok.mark(); }
-    flash_decode_kernel<HD, NH><<<grid, 128, decode_smem<HD>(), stream>>>(q, kv, seq_len, nh, window, sl, chunk_tiles,
-                                                                         part_o, part_ml, counters, out, out_dt);
+    sp_launch_dependent(flash_decode_kernel<HD, NH>, grid, dim3(128), (size_t)decode_smem<HD>(), stream, q, kv, seq_len, nh, window, sl,
+                        chunk_tiles, part_o, part_ml, counters, out, out_dt);
     return 0;
 }
 int launch_flash_decode(int hd, dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, const PagedKV& kv,

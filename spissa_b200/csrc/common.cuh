@@ -87,6 +87,7 @@ __device__ __forceinline__ float sp_block_max(float v, float* scratch) {
 
 // ---------------------------------------------------------------- launches with a cluster dimension
 // ``cluster_x`` CTAs that follow one another in x form a thread-block cluster (1 = none).
+// negative ``cluster_x``: |cluster_x| CTAs per cluster AND launched as a programmatic dependent (see below)
 template <typename... KArgs, typename... Args>
 static inline cudaError_t sp_launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                             cudaStream_t stream, int cluster_x, Args... args) {
@@ -95,8 +96,14 @@ static inline cudaError_t sp_launch_cluster(void (*kern)(KArgs...), dim3 grid, d
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attrs[1];
+    cudaLaunchAttribute attrs[2];
     int n = 0;
+    if (cluster_x < 0) {
+        cluster_x = -cluster_x;
+        attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
     if (cluster_x > 1) {
         attrs[n].id = cudaLaunchAttributeClusterDimension;
         attrs[n].val.clusterDim.x = (unsigned)cluster_x;

@@ -118,6 +118,8 @@ template <int NV, bool WBF16>
 __global__ void __launch_bounds__(256)
 rmsnorm_warp_kernel(const float* __restrict__ x, const void* __restrict__ w, int w_dt, void* __restrict__ out,
                     int out_dt, const int* __restrict__ rows, int n_rows, int H, float eps) {
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + warp;
     if (r >= n_rows) return;
@@ -174,9 +176,9 @@ SP_API int sp_rmsnorm(const float* x, const void* w, int w_dt, void* out, int ou
 #define SP_NORM_WARP(NV)                                                                                        \
     if (aligned && H == 128 * NV) {                                                                             \
         if (w_dt == SP_DT_BF16)                                                                                 \
-            rmsnorm_warp_kernel<NV, true><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
+            sp_launch_dependent(rmsnorm_warp_kernel<NV, true>, dim3((n_rows + 7) / 8), dim3(256), 0, stream, x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
         else                                                                                                    \
-            rmsnorm_warp_kernel<NV, false><<<(n_rows + 7) / 8, 256, 0, stream>>>(x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
+            sp_launch_dependent(rmsnorm_warp_kernel<NV, false>, dim3((n_rows + 7) / 8), dim3(256), 0, stream, x, w, w_dt, out, out_dt, rows, n_rows, H, eps); \
         SP_CHECK_LAUNCH("rmsnorm");                                                                             \
         return 0;                                                                                               \
     }
@@ -397,6 +399,8 @@ __global__ void __launch_bounds__(128)
 rope_kv_write_bf16_kernel(const float* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
                           __nv_bfloat16* __restrict__ kpool, __nv_bfloat16* __restrict__ vpool, KvPlace pl,
                           const float* __restrict__ inv_freq, int T, int nh, int nkv, int hd, int write_kv) {
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
     const int t = blockIdx.x;
     if (t >= T) return;
     const int pos = pl.positions[t];
@@ -455,7 +459,7 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     if (in_dt == SP_DT_F32 && q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16 && rd == hd && (hd % 8) == 0 &&
         ((((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0)) {
-        rope_kv_write_bf16_kernel<<<T, 128, 0, stream>>>((const float*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool,
+        sp_launch_dependent(rope_kv_write_bf16_kernel, dim3(T), dim3(128), 0, stream, (const float*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool,
                                                          (__nv_bfloat16*)vpool, pl, inv_freq, T, nh, nkv, hd, write_kv);
         SP_CHECK_LAUNCH("rope_kv_write");
         return 0;

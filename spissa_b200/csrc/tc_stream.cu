@@ -103,6 +103,9 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
+    // set up; from here on the kernel reads what its predecessor in the stream wrote
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
 
     constexpr int PARTS = GATED ? 2 : 1;
     const int q = warp & 3;                                       // epilogue warps: tensor-memory lanes 32q .. 32q+31
@@ -296,7 +299,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& ma, const Args& args, int t
         configured.mark();
     }
     SP_CHECK_CALL("tc_stream", sp_launch_cluster(tc_stream_kernel<NT, GATED>, dim3(tiles * args.pieces), dim3(192),
-                                                 (size_t)L::TOTAL, stream, args.pieces, mw, ma, args));
+                                                 (size_t)L::TOTAL, stream, -args.pieces, mw, ma, args));
     return 0;
 }
 

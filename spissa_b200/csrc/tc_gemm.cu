@@ -653,7 +653,7 @@ EncodeTiledFn encode_fn() {
 }
 
 // A [rows, K] bfloat16 matrix with leading dimension ld, fetched in boxes of box_rows x 64
-int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+int encode_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) SP_FAIL("tc_gemm: the driver does not offer cuTensorMapEncodeTiled");
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -664,6 +664,34 @@ int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) SP_FAIL("tc_gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return 0;
+}
+
+// Encoded maps are kept: a map depends on the matrix's address, shape, leading dimension and box only, the weights
+// never move and the activations come back at the same addresses step after step. Encoding takes the driver a
+// microsecond or two, which is most of what a short step's launch costs the host. A small direct-mapped table; the
+// callers are one host thread per library (two threads would at worst encode the same map twice).
+struct MapKey {
+    const void* ptr;
+    int rows, K, ld, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && K == o.K && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapSlot { MapKey key; CUtensorMap map; bool used; };
+constexpr int MAP_SLOTS = 1024;
+MapSlot map_cache[MAP_SLOTS];
+
+int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int ld, int box_rows) {
+    const MapKey key{ptr, rows, K, ld, box_rows};
+    size_t h = (size_t)((uintptr_t)ptr >> 4) * 1000003u + (size_t)rows * 8191u + (size_t)K * 131u + (size_t)ld * 31u + (size_t)box_rows;
+    MapSlot& slot = map_cache[h % MAP_SLOTS];
+    if (slot.used && slot.key == key) {
+        *map = slot.map;
+        return 0;
+    }
+    if (encode_map(map, ptr, rows, K, ld, box_rows)) return 1;
+    slot.key = key;
+    slot.map = *map;
+    slot.used = true;
     return 0;
 }
 

@@ -336,8 +336,14 @@ int opt_in_smem(Kern kern, int bytes, const char* name) {
     return 0;
 }
 
+// Head sizes the kernels are instantiated for: every multiple of 16 up to 128 (the fragments of mma.sync are 16 wide;
+// beyond 128 a thread's output row no longer fits its registers and the generic kernel runs).
+#define SP_FLASH_HEAD_SIZES(X) X(16) X(32) X(48) X(64) X(80) X(96) X(112) X(128)
+
+bool head_size_built(int hd) { return hd >= 16 && hd <= 128 && hd % 16 == 0; }
+
 int check_common(int hd, int nh, int nkv, int page_size) {
-    if (hd != 64 && hd != 128) SP_FAIL("flash attention: head_dim %d is not built (64 and 128 are)", hd);
+    if (!head_size_built(hd)) SP_FAIL("flash attention: head_dim %d is not built (multiples of 16 up to 128 are)", hd);
     if (nkv <= 0 || nh % nkv) SP_FAIL("flash attention: %d heads are no multiple of %d kv heads", nh, nkv);
     if (page_size != KT) SP_FAIL("flash attention: pages of %d tokens, this kernel walks pages of %d", page_size, KT);
     return 0;
@@ -350,8 +356,20 @@ int check_common(int hd, int nh, int nkv, int page_size) {
 SP_API int sp_flash_query_tile() { return KT; }
 
 SP_API int sp_flash_supported(int hd, int nh, int nkv, int page_size) {
-    return (hd == 64 || hd == 128) && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && page_size == KT;
+    return head_size_built(hd) && nkv > 0 && nh % nkv == 0 && nh / nkv <= 16 && page_size == KT;
 }
+
+namespace {
+template <int HD>
+int launch_flash_prefill_as(dim3 grid, cudaStream_t stream, const __nv_bfloat16* q, __nv_bfloat16* out, const PagedKV& kv,
+                            const int* seq_start, const int* positions, int n_seqs, int nh, int window, float sl) {
+    static SpPerDevice ok;            // the opt-in holds for one device: asked for on each device's first launch
+    if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<HD>, prefill_smem<HD>(), "flash_prefill")) return 1; ok.mark(); }
+    sp_launch_dependent(flash_prefill_kernel<HD>, grid, dim3(128), (size_t)prefill_smem<HD>(), stream, q, out, kv, seq_start,
+                        positions, n_seqs, nh, window, sl);
+    return 0;
+}
+}  // namespace
 
 SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const void* vpool, const int* seq_start,
                             const int* positions, const int* seq_row, const int* page_table, int max_pages,
@@ -363,16 +381,14 @@ SP_API int sp_flash_prefill(const void* q, void* out, const void* kpool, const v
     if (n_q_tiles > 65535) SP_FAIL("flash_prefill: %d query tiles are beyond this kernel's grid", n_q_tiles);
     dim3 grid(nh, n_q_tiles);
     const float sl = scale * LOG2E;
-    if (hd == 64) {
-        static SpPerDevice ok;
-        if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<64>, prefill_smem<64>(), "flash_prefill")) return 1; ok.mark(); }
-        sp_launch_dependent(flash_prefill_kernel<64>, grid, dim3(128), (size_t)prefill_smem<64>(), stream,
-            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
-    } else {
-        static SpPerDevice ok;
-        if (!ok.done()) { if (opt_in_smem(flash_prefill_kernel<128>, prefill_smem<128>(), "flash_prefill")) return 1; ok.mark(); }
-        sp_launch_dependent(flash_prefill_kernel<128>, grid, dim3(128), (size_t)prefill_smem<128>(), stream,
-            (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start, positions, n_seqs, nh, window, sl);
+    switch (hd) {
+#define X(n)                                                                                                        \
+    case n:                                                                                                         \
+        if (launch_flash_prefill_as<n>(grid, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, kv, seq_start,   \
+                                       positions, n_seqs, nh, window, sl)) return 1;                                \
+        break;
+        SP_FLASH_HEAD_SIZES(X)
+#undef X
     }
     SP_CHECK_LAUNCH("flash_prefill");
     return 0;
@@ -394,11 +410,15 @@ int launch_flash_decode(int hd, dim3 grid, cudaStream_t stream, const __nv_bfloa
                         const int* seq_len, int nh, int window, float sl, int chunk_tiles, float* part_o, float* part_ml,
                         int* counters, void* out, int out_dt) {
     const bool one = nh <= 8 * kv.nkv;
-    if (hd == 64)
-        return one ? launch_flash_decode_as<64, 1>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt)
-                   : launch_flash_decode_as<64, 2>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
-    return one ? launch_flash_decode_as<128, 1>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt)
-               : launch_flash_decode_as<128, 2>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+    switch (hd) {
+#define X(n)                                                                                                              \
+    case n:                                                                                                               \
+        return one ? launch_flash_decode_as<n, 1>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt) \
+                   : launch_flash_decode_as<n, 2>(grid, stream, q, kv, seq_len, nh, window, sl, chunk_tiles, part_o, part_ml, counters, out, out_dt);
+        SP_FLASH_HEAD_SIZES(X)
+#undef X
+    }
+    SP_FAIL("flash decode: head_dim %d is not built", hd);
 }
 
 }  // namespace

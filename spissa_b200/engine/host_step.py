@@ -95,7 +95,8 @@ class HostStep:
             return None
         for f in fields:
             m = f["mixer"]
-            if m["head_dim"] not in (64, 128) or m["num_heads"] // m["num_kv_heads"] > 16:
+            hd = m["head_dim"]
+            if hd % 16 or not 16 <= hd <= 128 or m["num_heads"] // m["num_kv_heads"] > 16:
                 return None                              # the prompt attention kernel's sizes
         return cls(model, fields)
 

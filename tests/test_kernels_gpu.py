@@ -360,7 +360,8 @@ def flash_decode_fn(K, chunk_tiles=None, fused=True):
     return fn
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (6, 3, 128)])
+@pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (6, 3, 128),
+                                       (4, 2, 16), (3, 1, 32), (3, 3, 48), (6, 2, 80), (5, 1, 96), (4, 2, 112)])
 def test_flash_prefill(K, nh, nkv, hd):
     fn = flash_prefill_fn(K)
     attention_case(K, fn, nh, nkv, hd, torch.bfloat16, [7, 1, 65, 33], [0, 199, 64, 31], None, hd, 6e-3)
@@ -374,7 +375,8 @@ def test_flash_prefill_window(K, window):
 
 
 @pytest.mark.parametrize("nh,nkv,hd", [(8, 2, 64), (4, 4, 64), (3, 1, 64), (4, 1, 128), (16, 1, 128), (32, 8, 64), (10, 1, 64),
-                                       (16, 2, 64), (9, 1, 128)])
+                                       (16, 2, 64), (9, 1, 128), (4, 2, 16), (3, 1, 32), (3, 3, 48), (6, 2, 80), (10, 1, 96),
+                                       (4, 2, 112)])
 @pytest.mark.parametrize("chunk_tiles", [None, 1, 3])
 @pytest.mark.parametrize("fused", [True, False])
 def test_flash_decode(K, nh, nkv, hd, chunk_tiles, fused):
@@ -394,6 +396,15 @@ def test_flash_finds_a_far_key(K, which, length, needle):
     out, v = needle_case(K, fn, torch.bfloat16, length, needle)
     for h in range(4):
         assert torch.allclose(out[h], v[needle, h // 2], atol=2e-2), f"head {h} missed key {needle} of {length}"
+
+
+@pytest.mark.parametrize("which", ["prefill", "decode"])
+@pytest.mark.parametrize("hd", [16, 48, 96, 112])
+def test_flash_finds_a_far_key_at_other_head_sizes(K, which, hd):
+    fn = flash_prefill_fn(K) if which == "prefill" else flash_decode_fn(K)
+    out, v = needle_case(K, fn, torch.bfloat16, 700, 640, hd=hd)
+    for h in range(4):
+        assert torch.allclose(out[h], v[640, h // 2], atol=2e-2), f"head {h} of size {hd} missed key 640 of 700"
 
 
 @pytest.mark.parametrize("which", ["prefill", "decode"])

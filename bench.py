@@ -134,13 +134,13 @@ class ClockSampler:
                     reasons=sorted(reasons), samples=len(sm))
 
 
-def model_numbers(cfg):
+def model_numbers(cfg, elem_bytes=2):
     H, I, L = cfg.hidden_size, cfg.intermediate_size, cfg.num_hidden_layers
     nh, nkv, hd, V = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.vocab_size
     per_layer = H * nh * hd * 2 + H * nkv * hd * 2 + 3 * H * I
     head = V * H
-    return dict(per_layer=per_layer, head=head, kv_bytes_per_token=2 * nkv * hd * 2 * L,
-                weight_bytes=(per_layer * L + head) * 2)
+    return dict(per_layer=per_layer, head=head, kv_bytes_per_token=2 * nkv * hd * elem_bytes * L,
+                weight_bytes=(per_layer * L + head) * elem_bytes)
 
 
 def prefill_flops(cfg, T):
@@ -420,6 +420,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="1b", choices=sorted(WORKLOADS), help="the headline workload (1b) or a secondary one")
     ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"],
+                    help="float32: the true 32-bit path of the whole model (FFMA products, no tensor cores); its prefill "
+                         "fraction is of the nominal FFMA rate (148 SMs x 128 lanes x 2 x the maximum SM clock)")
     ap.add_argument("--context", type=int, default=None,
                     help="mean prompt length of the decode runs (the cache holds twice as much per sequence)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
@@ -471,11 +474,12 @@ def main() -> int:
     if args.layers:
         cfg_dict["num_hidden_layers"] = args.layers
     cfg = LlamaConfig.from_dict(cfg_dict)
-    nums = model_numbers(cfg)
+    fp32 = args.dtype == "float32"
+    nums = model_numbers(cfg, 4 if fp32 else 2)
     points = [int(x) for x in args.points.split(",") if x.strip()]
     max_batch = max([args.batch] + points)
     torch.cuda.set_device(0)
-    engine = Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_batch * CONTEXT,
+    engine = Engine.from_config(cfg, seed=0, dtype=args.dtype, max_tokens=max_batch * CONTEXT,
                                 max_seqs=max_batch, device="cuda:0")
     rng = random.Random(1234)
     V = cfg.vocab_size
@@ -581,8 +585,11 @@ def main() -> int:
         prefill_once()
     pre_ms = sorted(prefill_once() for _ in range(5))[2]
     flops = prefill_flops(cfg, PREFILL_TOKENS)
+    flop_peak = peaks["bf16_tflops"] * 1e12
+    if fp32:
+        flop_peak = 148 * 128 * 2 * (clock_info.get("sm_max_mhz") or 1965) * 1e6
     prefill = dict(value=round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), tokens=PREFILL_TOKENS, ms=round(pre_ms, 3),
-                   frac=round(flops / (pre_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4))
+                   frac=round(flops / (pre_ms * 1e-3) / flop_peak, 4))
 
     # ---------------------------------------------------------------- other batch sizes
     pts = {}
@@ -621,7 +628,7 @@ def main() -> int:
         "metric": "decode tokens/s (%s, batch %d, ~%d-token prompts)" % (work["model"], args.batch, PROMPT),
         "value": round(value, 2), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic token ids, random N(0,0.02) weights", "impl": "ours",
+        "dtype": "fp32" if fp32 else "bf16", "data": "synthetic token ids, random N(0,0.02) weights", "impl": "ours",
         "config": {
             "model": work["model"], "layers": cfg.num_hidden_layers, "layers_full": full_layers,
             "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,

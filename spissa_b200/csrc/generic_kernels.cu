@@ -255,12 +255,92 @@ gemm_generic_kernel(const TA* __restrict__ A, const TW* __restrict__ W, void* __
     }
 }
 
+// The same product for a few rows of A (a decode step of the 32-bit path): W is streamed once with 16-byte loads,
+// a CTA of four warps owns eight rows of W (two per warp), the rows of A pass through shared memory in slices of
+// 512 columns. Each lane sums its columns k = 4·lane + 128·i in order, the lanes' sums are added by a shuffle tree:
+// the order is fixed and the same for every row of A, whatever M is, but it is another order than the tiled
+// kernel's, so a token's result differs between a decode step and a prompt step by 32-bit rounding.
+#define GS_KC 512
+#define GS_ROWS 2
+template <int MT>
+__global__ void __launch_bounds__(128)
+gemm_stream_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, void* __restrict__ C, int c_dt,
+                       int M, int N, int K, int lda, int ldw, int ldc, int accumulate) {
+    __shared__ __align__(16) float xs[MT][GS_KC];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = (blockIdx.x * 4 + warp) * GS_ROWS;
+    float acc[GS_ROWS][MT];
+#pragma unroll
+    for (int r = 0; r < GS_ROWS; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0.0f;
+    const float* wrow[GS_ROWS];
+#pragma unroll
+    for (int r = 0; r < GS_ROWS; ++r) wrow[r] = W + (size_t)min(n0 + r, N - 1) * ldw;
+
+    for (int k0 = 0; k0 < K; k0 += GS_KC) {
+        __syncthreads();                                     // the slice before has been used by every warp
+        for (int e = threadIdx.x; e < MT * (GS_KC / 4); e += 128) {
+            const int m = e / (GS_KC / 4), c = (e % (GS_KC / 4)) * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < M && k0 + c < K) v = *(const float4*)(A + (size_t)m * lda + k0 + c);     // K is a multiple of 4
+            *(float4*)&xs[m][c] = v;
+        }
+        __syncthreads();
+        float4 w[GS_ROWS][GS_KC / 128];
+#pragma unroll
+        for (int r = 0; r < GS_ROWS; ++r)
+#pragma unroll
+            for (int i = 0; i < GS_KC / 128; ++i) {
+                const int k = k0 + i * 128 + lane * 4;
+                w[r][i] = k < K ? __ldcs((const float4*)(wrow[r] + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+        for (int i = 0; i < GS_KC / 128; ++i)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const float4 x = *(const float4*)&xs[m][i * 128 + lane * 4];
+#pragma unroll
+                for (int r = 0; r < GS_ROWS; ++r) {
+                    acc[r][m] = fmaf(w[r][i].x, x.x, acc[r][m]);
+                    acc[r][m] = fmaf(w[r][i].y, x.y, acc[r][m]);
+                    acc[r][m] = fmaf(w[r][i].z, x.z, acc[r][m]);
+                    acc[r][m] = fmaf(w[r][i].w, x.w, acc[r][m]);
+                }
+            }
+    }
+#pragma unroll
+    for (int r = 0; r < GS_ROWS; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float v = sp_warp_sum(acc[r][m]);
+            if (lane == 0 && m < M && n0 + r < N) {
+                const size_t o = (size_t)m * ldc + n0 + r;
+                sp_st_dt(C, c_dt, o, accumulate ? v + ((float*)C)[o] : v);
+            }
+        }
+}
+
 SP_API int sp_gemm_generic(const void* A, int a_dt, const void* W, int w_dt, void* C, int c_dt,
                            int M, int N, int K, int lda, int ldw, int ldc, int accumulate,
                            cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0) SP_FAIL("gemm: K must be positive, got %d", K);
     if (accumulate && c_dt != SP_DT_F32) SP_FAIL("gemm: accumulation needs a 32-bit output");
+    if (M <= 16 && a_dt == SP_DT_F32 && w_dt == SP_DT_F32 && ((K | lda | ldw) & 3) == 0 &&
+        ((((uintptr_t)A) | ((uintptr_t)W)) & 15) == 0) {
+        const unsigned blocks = (unsigned)((N + 4 * GS_ROWS - 1) / (4 * GS_ROWS));
+#define GS_LAUNCH(MT) \
+        gemm_stream_f32_kernel<MT><<<blocks, 128, 0, stream>>>((const float*)A, (const float*)W, C, c_dt, M, N, K, lda, ldw, ldc, accumulate)
+        if (M <= 1) GS_LAUNCH(1);
+        else if (M <= 2) GS_LAUNCH(2);
+        else if (M <= 4) GS_LAUNCH(4);
+        else if (M <= 8) GS_LAUNCH(8);
+        else GS_LAUNCH(16);
+#undef GS_LAUNCH
+        SP_CHECK_LAUNCH("gemm_stream_f32");
+        return 0;
+    }
     dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM);
     if (grid.y > 65535) SP_FAIL("gemm: M=%d is beyond this kernel's grid", M);
 #define GG_LAUNCH(TA, TW) \
@@ -492,14 +572,50 @@ SP_API int sp_rope_kv_write(const void* qkv, int in_dt, void* q_out, int q_dt, v
 // lo = max(0, p-window+1) when window > 0, else 0. All keys, this step's included,
 // are read from the cache.
 
-template <typename TQ, typename TC>
+// q · k over hd dims for one key row; 16-byte loads where the row allows them
+__device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const float* __restrict__ kr, int hd) {
+    float dot = 0.0f;
+    if ((hd & 3) == 0 && (((uintptr_t)kr) & 15) == 0) {
+        int d = 0;
+        for (; d + 16 <= hd; d += 16) {                      // four loads in flight, then their products in order
+            float4 k4[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) k4[u] = *(const float4*)(kr + d + 4 * u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float4 q4 = *(const float4*)(qv + d + 4 * u);
+                dot = fmaf(q4.x, k4[u].x, dot); dot = fmaf(q4.y, k4[u].y, dot);
+                dot = fmaf(q4.z, k4[u].z, dot); dot = fmaf(q4.w, k4[u].w, dot);
+            }
+        }
+        for (; d < hd; d += 4) {
+            const float4 k4 = *(const float4*)(kr + d);
+            const float4 q4 = *(const float4*)(qv + d);
+            dot = fmaf(q4.x, k4.x, dot); dot = fmaf(q4.y, k4.y, dot);
+            dot = fmaf(q4.z, k4.z, dot); dot = fmaf(q4.w, k4.w, dot);
+        }
+    } else {
+        for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], kr[d], dot);
+    }
+    return dot;
+}
+__device__ __forceinline__ float ag_dot(const float* __restrict__ qv, const __nv_bfloat16* __restrict__ kr, int hd) {
+    float dot = 0.0f;
+    for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], __bfloat162float(kr[d]), dot);
+    return dot;
+}
+
+// SPLIT: the CTA's warps share ONE (token, head) and take the chunks of 32 keys in turn (few pairs, many keys: a
+// decode step); their partial results are merged in warp order through shared memory.
+template <typename TQ, typename TC, bool SPLIT>
 __global__ void __launch_bounds__(AG_WARPS * 32)
 attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool, const TC* __restrict__ vpool,
                          TQ* __restrict__ out, KvPlace pl, int T, int nh, int nkv, int hd, int window,
                          float scale) {
-    __shared__ float qs[AG_WARPS][AG_MAX_HD];
+    __shared__ __align__(16) float qs[AG_WARPS][AG_MAX_HD];
+    __shared__ float part_ml[AG_WARPS][2];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long gw = (long long)blockIdx.x * AG_WARPS + warp;
+    const long long gw = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * AG_WARPS + warp;
     if (gw >= (long long)T * nh) return;
     const int t = (int)(gw / nh), h = (int)(gw % nh);
     const int g = h / (nh / nkv);
@@ -517,7 +633,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.0f;
 
-    for (int j0 = lo; j0 <= p; j0 += 32) {
+    for (int j0 = lo + (SPLIT ? 32 * warp : 0); j0 <= p; j0 += SPLIT ? 32 * AG_WARPS : 32) {
         const int j = j0 + lane;
         const bool valid = j <= p;
         float s = -INFINITY;
@@ -526,9 +642,7 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
             my_page = sp_checked_page(pt[sp_checked_entry(j / ps, pl.max_pages, pl.rg)], pl.rg);
             my_off = j % ps;
             const TC* kr = kpool + (((size_t)my_page * nkv + g) * ps + my_off) * hd;
-            float dot = 0.0f;
-            for (int d = 0; d < hd; ++d) dot = fmaf(qs[warp][d], sp_ld(kr, d), dot);
-            s = dot * scale;
+            s = ag_dot(qs[warp], kr, hd) * scale;
         }
         const float m_new = fmaxf(m, sp_warp_max(s));
         const float e = valid ? expf(s - m_new) : 0.0f;
@@ -537,18 +651,58 @@ attention_generic_kernel(const TQ* __restrict__ q, const TC* __restrict__ kpool,
 #pragma unroll
         for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] *= corr;
         const int n_valid = min(32, p - j0 + 1);
-        for (int jj = 0; jj < n_valid; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, e, jj);
-            const int pg = __shfl_sync(0xffffffffu, my_page, jj);
-            const int of = __shfl_sync(0xffffffffu, my_off, jj);
-            const TC* vr = vpool + (((size_t)pg * nkv + g) * ps + of) * hd;
+        // eight keys at a time: their value rows are asked for together, then added in key order
+        for (int jj0 = 0; jj0 < n_valid; jj0 += 8) {
+            float pj[8];
+            const TC* vr[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                pj[u] = __shfl_sync(0xffffffffu, e, jj0 + u);
+                const int pg = __shfl_sync(0xffffffffu, my_page, jj0 + u);
+                const int of = __shfl_sync(0xffffffffu, my_off, jj0 + u);
+                vr[u] = vpool + (((size_t)pg * nkv + g) * ps + of) * hd;
+            }
 #pragma unroll
             for (int i = 0; i < AG_MAX_HD / 32; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) acc[i] = fmaf(pj, sp_ld(vr, d), acc[i]);
+                if (d < hd) {
+                    float v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) v[u] = jj0 + u < n_valid ? sp_ld(vr[u], d) : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc[i] = fmaf(pj[u], v[u], acc[i]);
+                }
             }
         }
         m = m_new;
+    }
+    if (SPLIT) {
+        // every warp leaves (m, l, acc) in shared memory (its query row is no longer needed); warp 0 merges in warp order
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) qs[warp][d] = acc[i];
+        }
+        if (lane == 0) { part_ml[warp][0] = m; part_ml[warp][1] = l; }
+        __syncthreads();
+        if (warp != 0) return;
+        float mm = -INFINITY;
+        for (int w = 0; w < AG_WARPS; ++w) mm = fmaxf(mm, part_ml[w][0]);
+        float ll = 0.0f;
+#pragma unroll
+        for (int i = 0; i < AG_MAX_HD / 32; ++i) acc[i] = 0.0f;
+        for (int w = 0; w < AG_WARPS; ++w) {
+            if (part_ml[w][1] <= 0.0f) continue;                 // a warp that saw no key
+            const float f = expf(part_ml[w][0] - mm);
+            ll += part_ml[w][1] * f;
+#pragma unroll
+            for (int i = 0; i < AG_MAX_HD / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < hd) acc[i] = fmaf(qs[w][d], f, acc[i]);
+            }
+        }
+        l = ll;
     }
 #pragma unroll
     for (int i = 0; i < AG_MAX_HD / 32; ++i) {
@@ -566,10 +720,17 @@ SP_API int sp_attention_generic(const void* q, int q_dt, const void* kpool, cons
     if (nkv <= 0 || nh % nkv) SP_FAIL("attention: %d heads are no multiple of %d kv heads", nh, nkv);
     KvPlace pl{token_seq, positions, seq_slot, page_table, max_pages, page_size, sp_range_host};
     const long long warps = (long long)T * nh;
-    const long long blocks = (warps + AG_WARPS - 1) / AG_WARPS;
+    // few (token, head) pairs (a decode step): a CTA per pair, its warps share the keys
+    const bool split = warps <= 4096;
+    const long long blocks = split ? warps : (warps + AG_WARPS - 1) / AG_WARPS;
     if (blocks > 2147483647LL) SP_FAIL("attention: too many (token, head) pairs for one launch");
-#define AG_LAUNCH(TQ, TC) \
-    attention_generic_kernel<TQ, TC><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale)
+#define AG_LAUNCH(TQ, TC)                                                                                              \
+    do {                                                                                                               \
+        if (split)                                                                                                     \
+            attention_generic_kernel<TQ, TC, true><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale); \
+        else                                                                                                           \
+            attention_generic_kernel<TQ, TC, false><<<(unsigned)blocks, AG_WARPS * 32, 0, stream>>>((const TQ*)q, (const TC*)kpool, (const TC*)vpool, (TQ*)out, pl, T, nh, nkv, hd, window, scale); \
+    } while (0)
     if (q_dt == SP_DT_F32 && cache_dt == SP_DT_F32) AG_LAUNCH(float, float);
     else if (q_dt == SP_DT_BF16 && cache_dt == SP_DT_BF16) AG_LAUNCH(__nv_bfloat16, __nv_bfloat16);
     else if (q_dt == SP_DT_F32 && cache_dt == SP_DT_BF16) AG_LAUNCH(float, __nv_bfloat16);

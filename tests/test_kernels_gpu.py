@@ -58,7 +58,8 @@ def test_rmsnorm(K, H, wdt, odt):
     close(out, ref[rows.long()], 2e-6 if odt == torch.float32 else 4e-3, "gathered rows")
 
 
-@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (33, 130, 72), (100, 64, 200), (5, 333, 96), (64, 64, 16)])
+@pytest.mark.parametrize("M,N,K_", [(1, 7, 5), (33, 130, 72), (100, 64, 200), (5, 333, 96), (64, 64, 16),
+                                    (1, 130, 72), (16, 1030, 520), (8, 100, 2048), (3, 7, 4), (2, 9, 1028), (17, 40, 512)])
 @pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16)])
 def test_gemm_generic(K, M, N, K_, adt, wdt):
@@ -79,14 +80,23 @@ def test_gemm_generic(K, M, N, K_, adt, wdt):
 
 
 def test_gemm_row_does_not_depend_on_batch(K):
+    """A row's result is the same bit for bit whatever else is in the batch, within the kernel for a few rows (a
+    decode step: up to 16) and within the tiled kernel; between the two it differs by 32-bit rounding only."""
     torch.manual_seed(3)
     a = torch.randn(70, 200, device=DEV)
     w = torch.randn(90, 200, device=DEV)
     full = torch.empty(70, 90, device=DEV)
     K.gemm_generic(a, w, full)
+    some = torch.empty(20, 90, device=DEV)
+    K.gemm_generic(a[30:50].contiguous(), w, some)
+    assert torch.equal(some[7], full[37])
     one = torch.empty(1, 90, device=DEV)
     K.gemm_generic(a[37:38].contiguous(), w, one)
-    assert torch.equal(one[0], full[37])
+    for rows in (2, 3, 8, 11, 16):
+        few = torch.empty(rows, 90, device=DEV)
+        K.gemm_generic(a[37:37 + rows].contiguous(), w, few)
+        assert torch.equal(few[0], one[0]), rows
+    close(one[0], full[37].double().cpu(), 2e-6, "a few rows against the tiled kernel")
 
 
 def rope_case(K, nh, nkv, hd, rd, theta, dtype, new_counts, before, seed):

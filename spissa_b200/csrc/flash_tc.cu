@@ -68,7 +68,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     constexpr uint32_t TMEM_COLS = 256;                           // S0 64 | S1 64 | O HD
     constexpr uint32_t COL_S = 0, COL_O = 128;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p[2], bar_o;
+    __shared__ __align__(8) uint64_t bar_q, bar_kv_full[KV_STAGES], bar_kv_empty[KV_STAGES], bar_s[2], bar_p[2], bar_o, bar_done;
     __shared__ uint32_t tmem_slot;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -108,6 +108,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         mbar_init(smem_u32(&bar_p[0]), 4);
         mbar_init(smem_u32(&bar_p[1]), 4);
         mbar_init(smem_u32(&bar_o), 1);
+        mbar_init(smem_u32(&bar_done), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -184,6 +185,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 }
                 tc_commit(smem_u32(&bar_kv_empty[s]));
                 tc_commit(smem_u32(&bar_o));
+                if (j == n_blocks - 1) tc_commit(smem_u32(&bar_done));      // the last product: a barrier of its own
             }
         }
     } else if (live) {
@@ -260,11 +262,11 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bar_p[j & 1]));
         }
-        // The last product. A row warp may be one block ahead of the others, so the product before the last may not
-        // even be issued yet; a wait by parity alone would take the completion of the one before that for it.
-        // Waiting for the product before the last first makes the parity of the last one unambiguous.
-        if (ok && n_blocks > 1) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 2) & 1u, status, 117);
-        if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_o), (uint32_t)(n_blocks - 1) & 1u, status, 117);
+        // The last product has a barrier of its own, with this one phase. On bar_o a wait by parity cannot tell the
+        // product before the last (a row warp may be a block ahead of the others, so that one may not even be issued)
+        // from the last (which may be complete before a slow warp, say one that misses the instruction cache on
+        // its way out of the loop, gets to wait: its parity has then come round and the wait never ends).
+        if (ok && n_blocks > 0) ok = mbar_wait(smem_u32(&bar_done), 0, status, 117);
         tc_fence_after();
         if (ok && !(status && *(volatile int*)status != 0)) {
             const float inv = 1.0f / l;

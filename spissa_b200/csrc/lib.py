@@ -424,41 +424,67 @@ def tc_gemm_fused(a, w, out, mode, bn, row_ssq=None, norm_width=0, eps=0.0, xw=N
     ``rope`` (mode TC_QKV_ROPE; ``out`` None): dict(cs, tok_page, positions, q_out, k_pool, v_pool, nh, nkv, hd,
     page_size): q and k are rotated with the (cos, sin) table, q stored, k and v written into the paged cache.
     """
-    lib = load("tc_gemm")
+    _fused_product("tc_gemm", a, w, out, mode, int(bn), tc_gemm_n_tiles(w.shape[0], bn), row_ssq, norm_width, eps, xw,
+                   next_w, ssq_out, rope)
+
+
+def tc_stream_max_tokens() -> int:
+    """Tokens up to which ``tc_stream`` and ``tc_stream_fused`` are built."""
+    return 128
+
+
+def tc_stream_n_tiles(N: int) -> int:
+    """Sums of squares per token that ``tc_stream_fused`` writes when it prepares the next norm (tiles of 128 columns)."""
+    return (int(N) + 127) // 128
+
+
+def tc_stream_fused(a, w, out, mode, pair=0, row_ssq=None, norm_width=0, eps=0.0, xw=None, next_w=None, ssq_out=None,
+                    rope=None):
+    """``tc_stream`` (17 to 128 tokens) with the epilogues of ``tc_gemm_fused``; ``ssq_out`` is
+    [M, tc_stream_n_tiles(N)] here and ``pair`` the block of gate rows for TC_SILU_MUL."""
+    _fused_product("tc_stream", a, w, out, mode, int(pair), tc_stream_n_tiles(w.shape[0]), row_ssq, norm_width, eps, xw,
+                   next_w, ssq_out, rope)
+
+
+def _fused_product(module, a, w, out, mode, width, n_tiles, row_ssq, norm_width, eps, xw, next_w, ssq_out, rope):
+    lib = load(module)
     M, K = a.shape
     N = w.shape[0]
     ep = _EpiArgs()
     if row_ssq is not None:
         if row_ssq.dtype != torch.float32 or row_ssq.dim() != 2 or row_ssq.shape[0] < M or not row_ssq.is_contiguous():
-            raise KernelError("tc_gemm_fused: the row statistics are a contiguous float32 [M, n] tensor")
+            raise KernelError(f"{module}_fused: the row statistics are a contiguous float32 [M, n] tensor")
         ep.row_ssq, ep.n_ssq, ep.norm_width, ep.eps = _ptr(row_ssq), row_ssq.shape[1], int(norm_width), float(eps)
     if xw is not None:
-        n_tiles = tc_gemm_n_tiles(N, bn)
         if (xw.dtype != torch.bfloat16 or tuple(xw.shape) != (M, N) or not xw.is_contiguous() or next_w.dtype != torch.bfloat16
                 or next_w.numel() != N or ssq_out.dtype != torch.float32 or tuple(ssq_out.shape) != (M, n_tiles)
                 or not ssq_out.is_contiguous()):
-            raise KernelError(f"tc_gemm_fused: xw [M, N] and next_w [N] are bfloat16, ssq_out float32 [M, {n_tiles}]")
+            raise KernelError(f"{module}_fused: xw [M, N] and next_w [N] are bfloat16, ssq_out float32 [M, {n_tiles}]")
         ep.xw, ep.next_w, ep.ssq_out = _ptr(xw), _ptr(next_w), _ptr(ssq_out)
+    code = int(mode)
     if mode == TC_QKV_ROPE:
         r = rope
         _need_contig(r["cs"], r["tok_page"], r["positions"], r["q_out"])
         if r["q_out"].dtype != torch.bfloat16 or r["k_pool"].dtype != torch.bfloat16 or r["cs"].dtype != torch.float32:
-            raise KernelError("tc_gemm_fused: q and the cache are bfloat16, the angle table float32")
+            raise KernelError(f"{module}_fused: q and the cache are bfloat16, the angle table float32")
         ep.cs, ep.tok_page, ep.positions = _ptr(r["cs"]), _ptr(r["tok_page"]), _ptr(r["positions"])
         ep.q_out, ep.kpool, ep.vpool = _ptr(r["q_out"]), _ptr(r["k_pool"]), _ptr(r["v_pool"])
         ep.nh, ep.nkv, ep.hd, ep.page_size = int(r["nh"]), int(r["nkv"]), int(r["hd"]), int(r["page_size"])
-        _declare_bounds("tc_gemm", lib, r.get("declared_pages", r["k_pool"].shape[0]), 0, a.device)
+        _declare_bounds(module, lib, r.get("declared_pages", r["k_pool"].shape[0]), 0, a.device)
         c_ptr, c_dt, ldc = None, BF16, 0
+        if module == "tc_stream":
+            code = 4                                   # 3 is the greedy head's mode there
     else:
         want_cols = N // 2 if mode == TC_SILU_MUL else N
         if out.shape[0] != M or out.shape[1] != want_cols or out.stride(1) != 1:
-            raise KernelError(f"tc_gemm_fused: out {tuple(out.shape)} does not fit a {tuple(a.shape)}, w {tuple(w.shape)}")
+            raise KernelError(f"{module}_fused: out {tuple(out.shape)} does not fit a {tuple(a.shape)}, w {tuple(w.shape)}")
         c_ptr, c_dt, ldc = _ptr(out), dt_code(out), out.stride(0)
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
-        raise KernelError("tc_gemm takes bfloat16 operands")
-    _check("tc_gemm", lib.sp_tc_gemm_fused(
+        raise KernelError(f"{module} takes bfloat16 operands")
+    fn = lib.sp_tc_gemm_fused if module == "tc_gemm" else lib.sp_tc_stream_fused
+    _check(module, fn(
         c_void_p(_ptr(a)), c_void_p(_ptr(w)), c_void_p(c_ptr), c_dt, M, N, K, a.stride(0), w.stride(0), ldc,
-        int(mode), int(bn), ctypes.byref(ep), c_void_p(_ptr(status_word(a.device))), c_void_p(_stream())))
+        code, width, ctypes.byref(ep), c_void_p(_ptr(status_word(a.device))), c_void_p(_stream())))
 
 
 def rope_table(meta, inv_freq, half, cs, tok_page):

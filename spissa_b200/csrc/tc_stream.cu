@@ -16,6 +16,7 @@
 // then computes the gate tile and the up tile of the same outputs into two accumulators). A row of W is a column of C: the 32 lanes of a warp write 32 neighbouring elements of one
 // token's row. Every mbarrier wait is bounded and records a code in ``status``; no load uses cluster multicast.
 #include "tcgen05.cuh"
+#include <string.h>
 
 SP_API const char* sp_tc_stream_last_error() { return sp_error_text; }
 SP_DEFINE_RANGE_API(tc_stream)
@@ -27,7 +28,32 @@ constexpr int BK = 64;                      // 64 bf16 = 128 bytes = one swizzle
 constexpr int UMMA_K = 16;
 constexpr int MAX_SPLITS = 8;
 
-enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ARGMAX = 3 };
+enum { MODE_STORE = 0, MODE_ACCUMULATE = 1, MODE_SILU_MUL = 2, MODE_ARGMAX = 3, MODE_QKV_ROPE = 4 };
+
+// What the fused epilogues need beyond C; all zero for the plain ones. The layout is the one the tile kernel
+// (tc_gemm.cu) takes, so that the host packs one structure for both. They fold a layer's RMS norms, the rotation and
+// the cache write into the products of a step of 17 to 128 tokens (crates/spissa-runtime/src/models/llama/
+// generate.rs:193-199 norm, :373-390 rotation, :410-416 cache append, :459-471 residual and second norm).
+struct EpiArgs {
+    // the rows of A are x ⊙ w of an RMS norm without its 1/rms: the result is multiplied by it here
+    const float* row_ssq;          // [M][n_ssq] partial sums of squares of the residual rows (null: no scaling)
+    int n_ssq, norm_width;         // norm_width: the residual's width H (1/rms = 1/sqrt(sum/H + eps))
+    float eps;
+    int pad0;
+    // MODE_ACCUMULATE: also prepare the next norm's input
+    __nv_bfloat16* xw;             // [M][N] new C ⊙ next_w (null: plain accumulation)
+    const __nv_bfloat16* next_w;   // [N]
+    float* ssq_out;                // [M][tiles of 128 columns] sums of squares of the new C over each tile's columns
+    // MODE_QKV_ROPE: W = [q heads | k heads | v heads] x head_dim rows
+    const float2* cs;              // [M][hd / 2] (cos, sin) of each token's angles
+    const int* tok_page;           // [M] the cache page that holds the token's position
+    const int* positions;          // [M]
+    __nv_bfloat16* q_out;          // [M][nh * hd]
+    __nv_bfloat16* kpool;          // [pages][nkv][page_size][hd]
+    __nv_bfloat16* vpool;
+    int nh, nkv, hd, page_size;
+};
+static_assert(sizeof(EpiArgs) == 112, "the host packs this layout");
 
 // MODE_ARGMAX (the greedy head): of a tile's 128 rows of W only the best (value, row) per token is kept, the lowest
 // row among equal values (crates/spissa-runtime/src/streaming/argmax.rs:30-51, :85-97); C is then a table of
@@ -62,6 +88,8 @@ struct Args {
     void* C;                // [M, ldc]: float32 or bfloat16
     int* status;
     int c_dt, M, N, K, ldc, mode, pair, pieces;
+    EpiArgs ep;
+    SpRange rg;
 };
 
 template <int NT, bool GATED>
@@ -74,6 +102,10 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __shared__ uint32_t tmem_slot;
     __shared__ uint32_t best_key[4][NT];                          // MODE_ARGMAX: each epilogue warp's best per token
     __shared__ int best_row[4][NT];
+    __shared__ float rstd_s[NT];                                  // each token's 1/rms (1 without row statistics)
+    __shared__ float ssq_w[4][NT];                                // preparing the next norm: each warp's sum of squares per token
+    __shared__ float xch[2][4][BW];                               // MODE_QKV_ROPE: four tokens' 128 columns, for the rotation partners
+    __shared__ int unhealthy;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -91,6 +123,7 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
         mbar_init(smem_u32(&bar_acc), 1);
+        unhealthy = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -113,12 +146,119 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // where this thread's row of the tile goes in C
     const int col = GATED ? tile * a.pair + row : tile * BW + row;
     const bool col_ok = GATED ? (row < a.pair && col < a.N / 2) : col < a.N;
-    auto emit = [&](int j, float g, float u) {                     // token j of this column
-        if (j >= a.M || !col_ok) return;
-        const size_t o = (size_t)j * a.ldc + col;
-        if (GATED) sp_st_dt(a.C, a.c_dt, o, (g / (1.0f + expf(-g))) * u);
-        else if (a.mode == MODE_ACCUMULATE) ((float*)a.C)[o] += g;
-        else sp_st_dt(a.C, a.c_dt, o, g);
+    const EpiArgs& ep = a.ep;
+    const bool prepares_norm = !GATED && a.mode == MODE_ACCUMULATE && ep.xw != nullptr;
+    const bool rope_mode = !GATED && a.mode == MODE_QKV_ROPE;
+    float next_w = 0.0f;
+    int rope_turn = 0;
+    // MODE_QKV_ROPE: where this thread's column lies. A tile holds whole heads; dims d and d + hd/2 of a head are
+    // rotation partners, 32 or 64 threads apart.
+    int r_head = 0, r_d = 0, r_half = 1, r_kvh = 0;
+    bool r_rot = false, r_q = false, r_k = false;
+    if (rope_mode) {
+        r_half = ep.hd >> 1;
+        r_head = col / ep.hd;
+        r_d = col - r_head * ep.hd;
+        r_q = r_head < ep.nh;
+        r_k = !r_q && r_head < ep.nh + ep.nkv;
+        r_rot = r_q || r_k;
+        r_kvh = r_k ? r_head - ep.nh : r_head - ep.nh - ep.nkv;
+    }
+    // What the epilogue of four tokens reads from global memory. A warp issues in order and such a load takes a
+    // microsecond under load, so the loads of four tokens are issued together, before the first of them is used.
+    struct Pre {
+        float oldc[4];
+        float2 cs[4];
+        int page[4], pos[4];
+    };
+    auto prefetch4 = [&](int jb, int j_end, Pre& pre) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const int j = jb + t;
+            pre.oldc[t] = 0.0f;
+            pre.cs[t] = make_float2(1.0f, 0.0f);
+            pre.page[t] = pre.pos[t] = 0;
+            if (j >= j_end || !col_ok || GATED) continue;
+            if (a.mode == MODE_ACCUMULATE) pre.oldc[t] = ((const float*)a.C)[(size_t)j * a.ldc + col];
+            if (rope_mode) {
+                if (r_rot) pre.cs[t] = __ldg(ep.cs + (size_t)j * r_half + (r_d < r_half ? r_d : r_d - r_half));
+                if (!r_q) {
+                    pre.page[t] = __ldg(ep.tok_page + j);
+                    pre.pos[t] = __ldg(ep.positions + j);
+                }
+            }
+        }
+    };
+    // Tokens jb .. jb+3 (those below j_end) of this thread's column. The 128 epilogue threads call it together (the
+    // fused epilogues add up or exchange across the threads): nothing here depends on the thread but the data.
+    auto emit4 = [&](int jb, int j_end, const float (&g)[4], const float (&u)[4], const Pre& pre) {
+        if (rope_mode) {
+            float v[4];
+            float* mine = xch[rope_turn & 1][0] + row;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                v[t] = jb + t < j_end ? g[t] * rstd_s[jb + t] : 0.0f;
+                mine[t * BW] = v[t];
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");         // two buffers: the next four tokens go to the other one
+            const float* theirs = xch[rope_turn & 1][0] + (r_d < r_half ? row + r_half : row - r_half);
+            ++rope_turn;
+            if (!col_ok) return;
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int j = jb + t;
+                if (j >= j_end) continue;
+                float outv = v[t];
+                if (r_rot) {
+                    const float other = theirs[t * BW];
+                    outv = r_d < r_half ? v[t] * pre.cs[t].x - other * pre.cs[t].y : v[t] * pre.cs[t].x + other * pre.cs[t].y;
+                }
+                if (r_q) {
+                    ep.q_out[((size_t)j * ep.nh + r_head) * ep.hd + r_d] = __float2bfloat16(outv);
+                } else if (sp_index_ok(pre.page[t], a.rg.n_pages, a.rg, 401)) {      // debug build: reported, not written
+                    (r_k ? ep.kpool : ep.vpool)[(((size_t)pre.page[t] * ep.nkv + r_kvh) * ep.page_size + pre.pos[t] % ep.page_size) * ep.hd + r_d] =
+                        __float2bfloat16(outv);
+                }
+            }
+            return;
+        }
+        float sq[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (col_ok) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int j = jb + t;
+                if (j >= j_end) continue;
+                const size_t o = (size_t)j * a.ldc + col;
+                const float rs = rstd_s[j];
+                if (GATED) {
+                    const float gg = g[t] * rs, uu = u[t] * rs;
+                    sp_st_dt(a.C, a.c_dt, o, (gg / (1.0f + expf(-gg))) * uu);
+                } else if (a.mode == MODE_ACCUMULATE) {
+                    const float hn = pre.oldc[t] + g[t];
+                    ((float*)a.C)[o] = hn;
+                    if (prepares_norm) {
+                        ep.xw[(size_t)j * a.N + col] = __float2bfloat16(hn * next_w);
+                        sq[t] = hn * hn;
+                    }
+                } else {
+                    sp_st_dt(a.C, a.c_dt, o, g[t] * rs);
+                }
+            }
+        }
+        if (prepares_norm) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const float sum = sp_warp_sum(sq[t]);
+                if (lane == 0 && jb + t < j_end) ssq_w[q][jb + t] = sum;
+            }
+        }
+    };
+    // after the tokens [j_lo, j_hi) of this CTA: the four warps' sums in warp order, one token per thread
+    auto emit_ssq = [&](int j_lo, int j_hi) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int j = (warp - 2) * 32 + lane;
+        if (j >= j_lo && j < j_hi && j < NT)
+            ep.ssq_out[(size_t)j * ((a.N + BW - 1) / BW) + tile] = ssq_w[0][j] + ssq_w[1][j] + ssq_w[2][j] + ssq_w[3][j];
     };
     bool healthy = false;
 
@@ -155,9 +295,26 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             tc_commit(smem_u32(&bar_acc));                         // also after a failed wait: the epilogue must not hang
         }
     } else {
+        {
+            // before the accumulator is waited for: each token's 1/rms from the partial sums, in their order
+            const int e = (warp - 2) * 32 + lane;
+            if (e < NT) {
+                float r = 1.0f;
+                if (ep.row_ssq && e < a.M) {
+                    float sum = 0.0f;
+                    for (int i = 0; i < ep.n_ssq; ++i) sum += __ldg(ep.row_ssq + (size_t)e * ep.n_ssq + i);
+                    r = 1.0f / sqrtf(sum / (float)ep.norm_width + ep.eps);
+                }
+                rstd_s[e] = r;
+            }
+            if (prepares_norm && col_ok) next_w = __bfloat162float(__ldg(ep.next_w + col));
+        }
         const bool ok = mbar_wait(smem_u32(&bar_acc), 0, a.status, 123);
         tc_fence_after();
-        healthy = ok && !(a.status && *(volatile int*)a.status != 0);
+        // the epilogue threads act together from here on: one verdict for all of them
+        if (!(ok && !(a.status && *(volatile int*)a.status != 0))) unhealthy = 1;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        healthy = unhealthy == 0;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         if (a.pieces == 1) {
 #pragma unroll 1
@@ -180,9 +337,20 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                     }
                 } else if (healthy) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) emit(c0 + j, __uint_as_float(rg[j]), GATED ? __uint_as_float(ru[j]) : 0.0f);
+                    for (int jb = 0; jb < 32; jb += 4) {
+                        Pre pre;
+                        prefetch4(c0 + jb, a.M, pre);
+                        float g4[4], u4[4];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) {
+                            g4[t] = __uint_as_float(rg[jb + t]);
+                            u4[t] = GATED ? __uint_as_float(ru[jb + t]) : 0.0f;
+                        }
+                        emit4(c0 + jb, a.M, g4, u4, pre);
+                    }
                 }
             }
+            if (prepares_norm && healthy) emit_ssq(0, a.M);
             if (!GATED && a.mode == MODE_ARGMAX) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
                 const int j = (warp - 2) * 32 + lane;              // one token per thread
@@ -233,14 +401,20 @@ tc_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
                             if (GATED) asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(pu[t][sp]) : "r"(at + (uint32_t)(NT * BW * 4)));
                         }
                     }
+                Pre pre;
+                prefetch4(jb, j1, pre);
+                float g4[4], u4[4];
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
                     float g = pg[t][0], u = pu[t][0];
 #pragma unroll
                     for (int sp = 1; sp < MAX_SPLITS; ++sp) { g += pg[t][sp]; u += pu[t][sp]; }
-                    if (jb + t < j1) emit(jb + t, g, u);
+                    g4[t] = g;
+                    u4[t] = u;
                 }
+                emit4(jb, j1, g4, u4, pre);
             }
+            if (prepares_norm) emit_ssq(j0, j1);
         }
         // nobody leaves (and frees its shared memory) before every CTA has read what it needs
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -359,16 +533,53 @@ SP_API int sp_tc_stream_supported(const void* A, const void* W, int M, int N, in
     return 0;
 }
 
+static int tc_stream_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                         int mode, int pair, const EpiArgs* epp, int* status, cudaStream_t stream);
+
 // mode 0: C = A·Wᵀ (bfloat16 or float32); 1: C (float32) += A·Wᵀ; 2: W interleaves ``pair`` gate rows and ``pair``
-// up rows, C [M, N/2] = silu(gate)·up.
+// up rows, C [M, N/2] = silu(gate)·up; 3: the greedy head's candidates.
 SP_API int sp_tc_stream(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
                         int mode, int pair, int* status, cudaStream_t stream) {
+    if (mode == MODE_QKV_ROPE) SP_FAIL("tc_stream: the rotate-and-store epilogue needs sp_tc_stream_fused");
+    return tc_stream_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, pair, nullptr, status, stream);
+}
+
+// Floats per token that the accumulating epilogue writes into ssq_out when it prepares the next norm.
+SP_API int sp_tc_stream_n_tiles(int N) { return (N + BW - 1) / BW; }
+
+// The product with a fused epilogue (see EpiArgs; ``ep`` null or all zero: the plain epilogues of sp_tc_stream).
+//   ep->row_ssq: the result is multiplied by each token's 1/rms (modes 0, 2 and 4);
+//   mode 1 with ep->xw: C += A·Wᵀ, and xw = new C ⊙ next_w (bfloat16) and ssq_out[token][tile of 128 columns] are written;
+//   mode 4: W = [q | k | v] heads x head_dim rows (head size 64 or 128); q and k are rotated with the per-token
+//     (cos, sin) table, q goes to q_out and k, v into the paged cache; C is not used.
+SP_API int sp_tc_stream_fused(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw,
+                              int ldc, int mode, int pair, const void* ep, int* status, cudaStream_t stream) {
+    return tc_stream_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, pair, (const EpiArgs*)ep, status, stream);
+}
+
+static int tc_stream_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
+                         int mode, int pair, const EpiArgs* epp, int* status, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (mode < 0 || mode > 3) SP_FAIL("tc_stream: unknown mode %d", mode);
+    if (mode < 0 || mode > 4) SP_FAIL("tc_stream: unknown mode %d", mode);
     if (mode == MODE_ACCUMULATE && c_dt != SP_DT_F32) SP_FAIL("tc_stream: accumulation needs a float32 C");
     if (sp_tc_stream_supported(A, W, M, N, K, lda, ldw, mode, pair)) return 1;
+    EpiArgs ep;
+    memset(&ep, 0, sizeof(ep));
+    if (epp) ep = *epp;
+    if (ep.row_ssq && (ep.n_ssq <= 0 || ep.norm_width <= 0)) SP_FAIL("tc_stream: the row statistics need their count and the norm's width");
+    if (ep.row_ssq && (mode == MODE_ACCUMULATE || mode == MODE_ARGMAX)) SP_FAIL("tc_stream: row statistics do not go with mode %d", mode);
+    if (ep.xw && (mode != MODE_ACCUMULATE || !ep.next_w || !ep.ssq_out))
+        SP_FAIL("tc_stream: preparing the next norm's input belongs to the accumulating epilogue and needs its weight and a place for the sums");
+    if (mode == MODE_QKV_ROPE) {
+        if (ep.hd != 64 && ep.hd != 128) SP_FAIL("tc_stream: the rotate-and-store epilogue is built for head sizes 64 and 128, got %d", ep.hd);
+        if (ep.nh <= 0 || ep.nkv <= 0 || N != (ep.nh + 2 * ep.nkv) * ep.hd) SP_FAIL("tc_stream: W has %d rows, %d q and %d kv heads of %d need %d", N, ep.nh, ep.nkv, ep.hd, (ep.nh + 2 * ep.nkv) * ep.hd);
+        if (!ep.cs || !ep.tok_page || !ep.positions || !ep.q_out || !ep.kpool || !ep.vpool || ep.page_size <= 0)
+            SP_FAIL("tc_stream: the rotate-and-store epilogue needs the angle table, the tokens' pages and positions, q and the cache");
+    }
     const int tiles = tiles_of(N, mode, pair);
     Args args;
+    args.ep = ep;
+    args.rg = sp_range_host;
     args.C = C; args.status = status;
     args.c_dt = c_dt; args.M = M; args.N = N; args.K = K; args.ldc = ldc; args.mode = mode; args.pair = pair;
     // the greedy head keeps candidates per tile: one CTA computes a tile over all of K

@@ -1,9 +1,11 @@
-"""A prompt step's layers with the norms, the rotation and the cache write folded into the matrix products.
+"""A step's layers with the norms, the rotation and the cache write folded into the matrix products.
 
-Part by part a layer of a prompt step is eight launches: norm, QKV, rotate-and-store, attention, output
-projection, norm, gate/up, down. When every layer's parts describe themselves through ``fused_fields()`` (the same
-pre-norm / RMS norm / rotary grouped-query attention / SwiGLU, bfloat16 description that the one-kernel decode path
-reads) a step of more than 128 tokens runs each layer as five:
+Part by part a layer is eight launches: norm, QKV, rotate-and-store, attention, output projection, norm, gate/up,
+down. When every layer's parts describe themselves through ``fused_fields()`` (the same pre-norm / RMS norm / rotary
+grouped-query attention / SwiGLU, bfloat16 description that the one-kernel decode path reads) a step of 17 tokens
+to 64 (a prompt, or a decode step of that many sequences: the kernel that streams the weights, ``tc_stream``) or of
+more than 128 (the tile kernel, ``tc_gemm``) runs each layer as five. Between them the tile kernel splits K over a
+cluster, which has no such epilogues, and is faster than either fused form (a 100-token step: 2.1 ms against 2.6):
 
 * QKV product on ``xw`` = residual ⊙ norm weight, its result multiplied by each row's 1/rms, rotated, q stored and
   k, v written into the paged cache in the product's epilogue;
@@ -22,11 +24,16 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
-from ..parts.linear import sm_count, tile_width
+from ..parts.linear import STREAM_TOKENS, sm_count, tile_width
 from .fused_decode import collect_fused_fields
 from ..phases import phase
 
-MIN_TOKENS = 129         # up to 128 tokens the products split K over a cluster instead; those steps run part by part
+MIN_TOKENS = 17          # up to 16 tokens the weight-streaming kernels (or the one-kernel decode path) run instead
+TILE_TOKENS = 129        # from here on the tile kernel's epilogues
+
+
+def fuses(n_tokens: int) -> bool:
+    return MIN_TOKENS <= n_tokens <= STREAM_TOKENS or n_tokens >= TILE_TOKENS
 
 
 class FusedPrefill:
@@ -63,7 +70,7 @@ class FusedPrefill:
         return cls(model, fields)
 
     def takes(self, step, cache) -> bool:
-        if step.all_single or step.n_tokens < MIN_TOKENS:
+        if not fuses(step.n_tokens):
             return False
         for e in self.model.spec.schedule:
             g = cache.kv_groups.get(cache.cache_group.get(e.cache))
@@ -89,7 +96,18 @@ class FusedPrefill:
         T, H, hd = step.n_tokens, self.H, self.hd
         dev, bf = h.device, torch.bfloat16
         sms = sm_count(dev)
+        stream = T <= STREAM_TOKENS                    # the kernel that streams the weights takes these few tokens
         schedule = self.model.spec.schedule
+
+        def product(a, w, out, mode, bn, pair=0, **kw):
+            if stream:
+                K.tc_stream_fused(a, w, out, mode, pair, **kw)
+            else:
+                K.tc_gemm_fused(a, w, out, mode, bn, **kw)
+
+        def res_tiles(bn):
+            return K.tc_stream_n_tiles(H) if stream else K.tc_gemm_n_tiles(H, bn)
+
         xw = torch.empty(T, H, dtype=bf, device=dev)
         ssq = torch.empty(T, 1, dtype=torch.float32, device=dev)
         with phase("attention_norm_ms"):
@@ -108,30 +126,31 @@ class FusedPrefill:
             if bn % hd:
                 bn = 256
             with phase("attention_norm+qkv_projection+rotary+kv_append_ms"):
-                K.tc_gemm_fused(xw, m["qkv"], None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H,
-                                eps=f["mixer_norm"]["eps"],
-                                rope=dict(cs=cs, tok_page=tok_page, positions=step.positions, q_out=q, k_pool=view.k_pool,
-                                          v_pool=view.v_pool, nh=nh, nkv=nkv, hd=hd, page_size=view.page_size))
+                product(xw, m["qkv"], None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H, eps=f["mixer_norm"]["eps"],
+                        rope=dict(cs=cs, tok_page=tok_page, positions=step.positions, q_out=q, k_pool=view.k_pool,
+                                  v_pool=view.v_pool, nh=nh, nkv=nkv, hd=hd, page_size=view.page_size))
             # ---- attention, then the output projection into the residual, preparing the second norm
             with phase("attention_ms"):
                 ctx = mixer.attend(q, step, view)
             bn = tile_width(T, H, sms)
             xw = torch.empty(T, H, dtype=bf, device=dev)
-            ssq = torch.empty(T, K.tc_gemm_n_tiles(H, bn), dtype=torch.float32, device=dev)
+            ssq = torch.empty(T, res_tiles(bn), dtype=torch.float32, device=dev)
             with phase("o_projection+attention_residual_ms"):
-                K.tc_gemm_fused(ctx, m["o"], h, K.TC_ACCUMULATE, bn, xw=xw, next_w=f["ffn_norm"]["weight"], ssq_out=ssq)
+                product(ctx, m["o"], h, K.TC_ACCUMULATE, bn, xw=xw, next_w=f["ffn_norm"]["weight"], ssq_out=ssq)
             # ---- gate/up with silu(gate)·up on the normed residual
             act = torch.empty(T, ff["intermediate_size"], dtype=bf, device=dev)
             with phase("mlp_norm+gate_projection+up_projection+activation_multiply_ms"):
-                K.tc_gemm_fused(xw, ff["gate_up"], act, K.TC_SILU_MUL, 2 * ff["pair"], row_ssq=ssq, norm_width=H,
-                                eps=f["ffn_norm"]["eps"])
+                product(xw, ff["gate_up"], act, K.TC_SILU_MUL, 2 * ff["pair"], ff["pair"], row_ssq=ssq, norm_width=H,
+                        eps=f["ffn_norm"]["eps"])
             # ---- down projection into the residual, preparing the next layer's first norm
             with phase("down_projection+mlp_residual_ms"):
                 if i + 1 < len(self.fields):
                     bn = tile_width(T, H, sms)
                     xw = torch.empty(T, H, dtype=bf, device=dev)
-                    ssq = torch.empty(T, K.tc_gemm_n_tiles(H, bn), dtype=torch.float32, device=dev)
-                    K.tc_gemm_fused(act, ff["down"], h, K.TC_ACCUMULATE, bn, xw=xw,
-                                    next_w=self.fields[i + 1]["mixer_norm"]["weight"], ssq_out=ssq)
+                    ssq = torch.empty(T, res_tiles(bn), dtype=torch.float32, device=dev)
+                    product(act, ff["down"], h, K.TC_ACCUMULATE, bn, xw=xw,
+                            next_w=self.fields[i + 1]["mixer_norm"]["weight"], ssq_out=ssq)
+                elif stream:
+                    K.tc_stream(act, ff["down"], h, K.TC_ACCUMULATE)
                 else:
                     K.tc_gemm(act, ff["down"], h, K.TC_ACCUMULATE, tile_width(T, H, sms))

@@ -4,9 +4,12 @@ A prompt of a few dozen tokens is bound by the host, not the GPU: part by part a
 microseconds each, and from Python each costs ten microseconds or more. When every layer's parts describe themselves
 through ``fused_fields()`` (the description the one-kernel decode path and the fused prompt path read), a prompt step
 of at most 128 tokens hands the whole sequence to ``csrc/host_step.cu``: a table of layer descriptors built once per
-cache, the step's arrays and five activation buffers. The kernels are the same as part by part, chosen by the same
-thresholds (``parts/linear.py``), so the results are bit-identical to the Python path. Anything else (another mixer,
-32-bit, a larger step, a profiled step) runs as before.
+cache, the step's arrays and its activation buffers. Up to 16 tokens the kernels are the same as part by part, chosen
+by the same thresholds (``parts/linear.py``), so the results are bit-identical to the Python path. From 17 to 64 tokens
+(head sizes 64 and 128) a layer is five launches instead of eight: the norms, the rotation and the cache write ride in
+the products' epilogues, the same kernels with the same arguments as ``engine/fused_prefill.py`` launches them, so
+those results are bit-identical to that runner's. Anything else (another mixer, 32-bit, a larger step, a profiled
+step) runs as before.
 """
 from __future__ import annotations
 
@@ -26,7 +29,7 @@ class _Kernels(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in (
         "rmsnorm", "gemv", "gemv_supported", "tc_stream", "tc_stream_supported", "tc_gemm", "tc_gemm_supported",
         "gemm_generic", "silu_mul", "rope_kv_write", "flash_prefill", "err_generic", "err_gemv", "err_tc_stream",
-        "err_tc_gemm", "err_attention")] + [("gemv_tokens", c_int), ("stream_tokens", c_int),
+        "err_tc_gemm", "err_attention", "tc_stream_fused", "rope_table", "norm_prepare")] + [("gemv_tokens", c_int), ("stream_tokens", c_int),
                                             ("flash_query_tile", c_int), ("pad", c_int)]
 
 
@@ -38,8 +41,9 @@ class _Layer(ctypes.Structure):
 
 class _Step(ctypes.Structure):
     _fields_ = [(n, c_void_p) for n in ("h", "x", "qkv", "q", "ctx", "act", "gu", "token_seq", "positions", "seq_row",
-                                        "page_table", "seq_start", "status")] + \
-               [(n, c_int) for n in ("T", "H", "n_seqs", "max_pages", "page_size", "n_q_tiles", "pad0", "pad1")]
+                                        "page_table", "seq_start", "status", "xw0", "xw1", "ssq0", "ssq1", "cs",
+                                        "tok_page")] + \
+               [(n, c_int) for n in ("T", "H", "n_seqs", "max_pages", "page_size", "n_q_tiles", "fused", "pad1")]
 
 
 def _address(lib, name) -> int:
@@ -67,6 +71,8 @@ def _bind() -> ctypes.CDLL:
     t.tc_stream, t.tc_stream_supported = _address(stream, "sp_tc_stream"), _address(stream, "sp_tc_stream_supported")
     t.tc_gemm, t.tc_gemm_supported = _address(gemm, "sp_tc_gemm"), _address(gemm, "sp_tc_gemm_supported")
     t.flash_prefill = _address(att, "sp_flash_prefill")
+    t.tc_stream_fused = _address(stream, "sp_tc_stream_fused")
+    t.rope_table, t.norm_prepare = _address(generic, "sp_rope_table"), _address(generic, "sp_norm_prepare")
     t.err_generic, t.err_gemv = _address(generic, "sp_generic_last_error"), _address(gemv, "sp_gemv_last_error")
     t.err_tc_stream, t.err_tc_gemm = _address(stream, "sp_tc_stream_last_error"), _address(gemm, "sp_tc_gemm_last_error")
     t.err_attention = _address(att, "sp_attention_last_error")
@@ -98,7 +104,10 @@ class HostStep:
             hd = m["head_dim"]
             if hd % 16 or not 16 <= hd <= 128 or m["num_heads"] // m["num_kv_heads"] > 16:
                 return None                              # the prompt attention kernel's sizes
-        return cls(model, fields)
+        runner = cls(model, fields)
+        from .fused_prefill import FusedPrefill
+        runner.can_fuse = FusedPrefill.plan(model) is not None
+        return runner
 
     def takes(self, step, cache) -> bool:
         if step.all_single or step.n_tokens > MAX_TOKENS or cache.page_size != K.flash_query_tile():
@@ -109,7 +118,7 @@ class HostStep:
 
     def _bind_cache(self, cache) -> None:
         self.cache_id, self.layers = id(cache), None
-        rows, keep = [], []
+        rows, keep, tables = [], [], []
         for e, f in zip(self.model.spec.schedule, self.fields):
             g = cache.kv_groups.get(cache.cache_group.get(e.cache))
             if g is None or g.request.window or g.k.dtype != torch.bfloat16:
@@ -118,6 +127,12 @@ class HostStep:
             i = g.index[e.cache]
             k_pool, v_pool = g.k[i], g.v[i]
             inv = m["inv_freq"].to(device=k_pool.device, dtype=torch.float32).contiguous()
+            for have in tables:                          # equal tables share one tensor: the runner compares addresses
+                if have.shape == inv.shape and torch.equal(have, inv):
+                    inv = have
+                    break
+            else:
+                tables.append(inv)
             keep += [inv, k_pool, v_pool]
             r = _Layer()
             r.w_qkv, r.w_o, r.w_gu, r.w_down = (t.data_ptr() for t in (m["qkv"], m["o"], ff["gate_up"], ff["down"]))
@@ -155,13 +170,29 @@ class HostStep:
         st.q, off = off, off + T * self.max_q * 2
         st.ctx, off = off, off + T * self.max_q * 2
         st.act = off
+        from .fused_prefill import fuses
+        fused = self.can_fuse and self.model.fuse_prefill and fuses(T)
+        if fused:
+            tiles = K.tc_stream_n_tiles(self.H)
+            hd = self.layers[0].hd
+            extra = torch.empty(2 * T * self.H * 2 + 2 * T * tiles * 4 + T * hd * 4 + T * 4 + 64, dtype=torch.uint8, device=dev)
+            off = extra.data_ptr()
+            off += (-off) % 16
+            st.xw0, off = off, off + T * self.H * 2
+            st.xw1, off = off, off + T * self.H * 2
+            st.ssq0, off = off, off + T * tiles * 4
+            st.ssq1, off = off, off + T * tiles * 4
+            st.cs, off = off, off + T * hd * 4                # (cos, sin) pairs of hd / 2 angles
+            st.tok_page = off
+            st.fused = 1
+            self.extra = extra
         pt = step.page_tables[self.group]
         st.token_seq, st.positions, st.seq_row = step.token_seq.data_ptr(), step.positions.data_ptr(), step.seq_row.data_ptr()
         st.page_table, st.seq_start = pt.data_ptr(), step.seq_start.data_ptr()
         st.status = K.status_word(dev).data_ptr()
         st.T, st.H, st.n_seqs, st.max_pages, st.page_size = T, self.H, step.n_seqs, pt.shape[1], cache.page_size
         st.n_q_tiles = K.query_tiles(step.host["new_counts"], K.flash_query_tile())
-        for module in ("generic", "attention", "gemv", "tc_gemm"):        # the debug build's bounds, library by library
+        for module in ("generic", "attention", "gemv", "tc_gemm", "tc_stream"):       # the debug build's bounds, library by library
             K._declare_bounds(module, K.load(module), cache.kv_groups[self.group].n_pages, pt.shape[0], dev)
         stream = K._stream()
         rc = host.sp_host_step_prompt_layers(self.layers, len(self.fields), ctypes.byref(st), c_void_p(stream))

@@ -90,10 +90,10 @@ class Model:
             self._fused_prefill = FusedPrefill.plan(self)
         if self.fuse_decode and self._fused is not None and not profiling() and self._fused.takes(step, cache):
             self._fused.run(h, step, cache)
+        elif self.host_steps and not profiling() and self._host_runner(step, cache):
+            self._host_step.run(h, step, cache)            # a prompt step of up to 128 tokens: launched from C++
         elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):
             self._fused_prefill.run(h, step, cache)
-        elif self.host_steps and not profiling() and self._host_runner(step, cache):
-            self._host_step.run(h, step, cache)
         else:
             for e in self.spec.schedule:
                 self.layers[e.layer].forward(h, step, cache.view(e.cache, step, e.writes_cache))

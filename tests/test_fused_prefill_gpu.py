@@ -22,12 +22,13 @@ def folders(tmp_path_factory):
     return out
 
 
+# above 128 tokens a step the tile kernel's epilogues run, from 17 to 64 those of the kernel that streams the weights
+@pytest.mark.parametrize("lens,first", [([300, 250, 40], [160, 90, 20]), ([30, 25, 9], [20, 15, 5]), ([40, 25], [20, 3])])
 @pytest.mark.parametrize("name", ["E", "F"])
-def test_fused_prompt_steps_match_plain_and_the_parts(folders, name):
+def test_fused_prompt_steps_match_plain_and_the_parts(folders, name, lens, first):
     folder, pcfg, w = folders[name]
     V, L = pcfg["vocab_size"], pcfg["num_hidden_layers"]
-    lens = [300, 250, 40]
-    first = [160, 90, 20]                              # the prompts arrive in two steps: the second reads the first's keys
+    # the prompts arrive in two steps: the second reads the first's keys
     seqs = [tiny.random_prompt(V, n, 5 * n) for n in lens]
     refs = [P.model_logits(pcfg, w, s, torch.float64) for s in seqs]
     scale = max(float(r.abs().max()) for r in refs)
@@ -35,6 +36,7 @@ def test_fused_prompt_steps_match_plain_and_the_parts(folders, name):
     launches = {}
     for fused in (True, False):
         engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 12, fuse_prefill=fused)
+        engine.model.host_steps = False                 # the same kernels from Python: the launches can be counted
         slots = [engine.acquire() for _ in seqs]
         l0 = K.launches
         a = engine.step([(s, q[:n], list(range(n))) for s, q, n in zip(slots, seqs, first)]).cpu()
@@ -58,12 +60,15 @@ def test_fused_prompt_steps_match_plain_and_the_parts(folders, name):
     assert launches[True] == launches[False] - 3 * L + 2, launches
 
 
-def test_short_prompts_and_other_models_run_part_by_part(folders):
+def test_short_prompts_run_from_cpp_and_other_models_part_by_part(folders):
     folder, pcfg, w = folders["E"]
     engine = Engine.from_folder(folder, dtype="bfloat16", max_tokens=64 * 8)
     s = engine.acquire()
-    engine.step([(s, tiny.random_prompt(777, 100, 1), [99])])         # up to 128 tokens: K is split over a cluster instead
+    engine.step([(s, tiny.random_prompt(777, 100, 1), [99])])         # up to 128 tokens: the launch sequence runs in C++
+    assert engine.model._host_step.runs == 1
     assert engine.model._fused_prefill is not None and engine.model._fused_prefill.runs == 0
+    engine.step([(s, tiny.random_prompt(777, 200, 2), [199])])        # beyond: the fused sequence from Python
+    assert engine.model._host_step.runs == 1 and engine.model._fused_prefill.runs == 1
     e32 = Engine.from_folder(folder, dtype="float32", max_tokens=64 * 8)
     s = e32.acquire()
     e32.step([(s, tiny.random_prompt(777, 200, 1), [199])])
@@ -73,7 +78,8 @@ def test_short_prompts_and_other_models_run_part_by_part(folders):
 @pytest.mark.parametrize("name", ["E", "F"])
 def test_short_prompt_steps_through_the_host_runner_equal_the_parts_bit_for_bit(folders, name):
     """Up to 128 tokens the layers' launch sequence runs as one call into C++ (csrc/host_step.cu): the same kernels
-    with the same arguments as part by part, so not a bit may differ; ragged batches and prompts that continue."""
+    with the same arguments as from Python (part by part up to 16 tokens, the fused sequence from 17), so not a bit
+    may differ; ragged batches and prompts that continue."""
     folder, pcfg, w = folders[name]
     V = pcfg["vocab_size"]
     steps = [[5], [17, 3], [40], [100, 9, 19], [128]]

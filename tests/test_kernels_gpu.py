@@ -825,10 +825,23 @@ def test_head_argmax_ignores_nan_and_rows_beyond_the_table(K):
         assert torch.equal(_head_argmax(K, x, w), logits.argmax(dim=1).cpu().int())
 
 
-# ------------------------------------------------------------------ tc_gemm with fused epilogues (prompt steps)
-@pytest.mark.parametrize("M,N,Kd,bn", [(300, 520, 264, 128), (129, 2048, 512, 256), (513, 1160, 128, 192), (2048, 256, 2048, 256)])
+# ------------------------------------------------------------------ products with fused epilogues
+# The tile kernel (tc_gemm, prompt steps above 128 tokens; its width argument is the tile width) and the kernel that
+# streams the weights (tc_stream, 17 to 128 tokens; width 0, or the block of gate rows) have the same epilogues.
+def fused_call(K, bn):
+    """(the fused product, sums of squares per row it writes for N columns) for tile width ``bn``; 0: tc_stream."""
+    if bn:
+        return (lambda a, w, out, mode, pair=0, **kw: K.tc_gemm_fused(a, w, out, mode, 2 * pair if pair else bn, **kw),
+                lambda N: K.tc_gemm_n_tiles(N, bn))
+    return (lambda a, w, out, mode, pair=0, **kw: K.tc_stream_fused(a, w, out, mode, pair, **kw), K.tc_stream_n_tiles)
+
+
+@pytest.mark.parametrize("M,N,Kd,bn", [(300, 520, 264, 128), (129, 2048, 512, 256), (513, 1160, 128, 192), (2048, 256, 2048, 256),
+                                       (17, 520, 264, 0), (64, 2048, 8192, 0), (33, 1160, 128, 0), (128, 256, 2048, 0),
+                                       (100, 2048, 2048, 0), (1, 200, 72, 0)])
 def test_tc_gemm_accumulate_prepares_the_next_norm(K, M, N, Kd, bn):
     """C += A·Wᵀ, and in the same epilogue C ⊙ w_next in bfloat16 and the rows' sums of squares per tile."""
+    fused, n_tiles = fused_call(K, bn)
     torch.manual_seed(M + N)
     a = (torch.randn(M, Kd, device=DEV) * 0.5).bfloat16()
     w = (torch.randn(N, Kd, device=DEV) * 0.1).bfloat16()
@@ -836,8 +849,8 @@ def test_tc_gemm_accumulate_prepares_the_next_norm(K, M, N, Kd, bn):
     next_w = (1 + 0.2 * torch.randn(N, device=DEV)).bfloat16()
     c = c0.clone()
     xw = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-    ssq = torch.full((M, K.tc_gemm_n_tiles(N, bn)), float("nan"), device=DEV)
-    K.tc_gemm_fused(a, w, c, K.TC_ACCUMULATE, bn, xw=xw, next_w=next_w, ssq_out=ssq)
+    ssq = torch.full((M, n_tiles(N)), float("nan"), device=DEV)
+    fused(a, w, c, K.TC_ACCUMULATE, xw=xw, next_w=next_w, ssq_out=ssq)
     ref = c0.double() + a.double() @ w.double().t()
     close(c, ref, 2e-5, "residual")
     close(xw.float(), ref * next_w.double(), 6e-3, "residual times the next norm's weight")
@@ -845,17 +858,19 @@ def test_tc_gemm_accumulate_prepares_the_next_norm(K, M, N, Kd, bn):
     # the consumer: a product on xw whose result is scaled by 1/rms equals the product on the normed rows
     w2 = (torch.randn(384, N, device=DEV) * 0.1).bfloat16()
     out = torch.empty(M, 384, dtype=torch.bfloat16, device=DEV)
-    K.tc_gemm_fused(xw, w2, out, K.TC_STORE, 128, row_ssq=ssq, norm_width=N, eps=1e-5)
+    fused_call(K, 128 if bn else 0)[0](xw, w2, out, K.TC_STORE, row_ssq=ssq, norm_width=N, eps=1e-5)
     normed = P.rms_norm(ref, next_w.double().cpu().to(ref.device), 1e-5)
     close(out.float(), normed @ w2.double().t(), 1.2e-2, "product of the normed rows")
     again = c0.clone()
     xw2, ssq2 = torch.empty_like(xw), torch.empty_like(ssq)
-    K.tc_gemm_fused(a, w, again, K.TC_ACCUMULATE, bn, xw=xw2, next_w=next_w, ssq_out=ssq2)
+    fused(a, w, again, K.TC_ACCUMULATE, xw=xw2, next_w=next_w, ssq_out=ssq2)
     assert torch.equal(again, c) and torch.equal(xw2, xw) and torch.equal(ssq2, ssq)      # a fixed order of sums
 
 
-@pytest.mark.parametrize("M,I,H,pair", [(200, 384, 264, 64), (1030, 1024, 512, 128)])
-def test_tc_gemm_silu_epilogue_with_row_scaling(K, M, I, H, pair):
+@pytest.mark.parametrize("M,I,H,pair,stream", [(200, 384, 264, 64, False), (1030, 1024, 512, 128, False),
+                                               (20, 384, 264, 64, True), (64, 8192, 2048, 128, True), (128, 1024, 512, 128, True)])
+def test_tc_gemm_silu_epilogue_with_row_scaling(K, M, I, H, pair, stream):
+    fused, _ = fused_call(K, 0 if stream else 2 * pair)
     torch.manual_seed(M)
     x = torch.randn(M, H, device=DEV)
     nw = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
@@ -865,20 +880,22 @@ def test_tc_gemm_silu_epilogue_with_row_scaling(K, M, I, H, pair):
     up = (torch.randn(I, H, device=DEV) * 0.1).bfloat16()
     wgu = torch.stack([gate.reshape(I // pair, pair, H), up.reshape(I // pair, pair, H)], dim=1).reshape(2 * I, H).contiguous()
     out = torch.empty(M, I, dtype=torch.bfloat16, device=DEV)
-    K.tc_gemm_fused(xw, wgu, out, K.TC_SILU_MUL, 2 * pair, row_ssq=ssq, norm_width=H, eps=1e-6)
+    fused(xw, wgu, out, K.TC_SILU_MUL, pair, row_ssq=ssq, norm_width=H, eps=1e-6)
     rstd = 1.0 / torch.sqrt(ssq.double() / H + 1e-6)
     g = (xw.double() @ gate.double().t()) * rstd
     u = (xw.double() @ up.double().t()) * rstd
     close(out.float(), P.silu(g) * u, 8e-3, "silu(gate)·up of scaled rows")
 
 
-@pytest.mark.parametrize("hd,nh,nkv,bn", [(64, 6, 2, 128), (64, 5, 1, 192), (64, 32, 8, 256), (128, 4, 2, 256), (128, 3, 1, 128)])
+@pytest.mark.parametrize("hd,nh,nkv,bn", [(64, 6, 2, 128), (64, 5, 1, 192), (64, 32, 8, 256), (128, 4, 2, 256), (128, 3, 1, 128),
+                                          (64, 6, 2, 0), (64, 5, 1, 0), (64, 32, 8, 0), (128, 4, 2, 0), (128, 3, 1, 0)])
 def test_tc_gemm_qkv_epilogue_rotates_and_writes_the_cache(K, hd, nh, nkv, bn):
     """q = rotate(rstd·x·Wqᵀ) stored, k rotated and v plain written into the pages of each token's position, for
     sequences that start at different lengths in one step."""
+    fused, _ = fused_call(K, bn)
     torch.manual_seed(hd + nh)
-    H = 264
-    new_counts, before = [130, 7, 70], [0, 100, 61]
+    H = 264 if bn else 2048
+    new_counts, before = ([130, 7, 70], [0, 100, 61]) if bn else ([40, 1, 7, 16], [0, 100, 61, 64])
     T = sum(new_counts)
     meta = KH.paged_meta(new_counts, before, DEV, seed=hd)
     x = torch.randn(T, H, device=DEV)
@@ -896,8 +913,8 @@ def test_tc_gemm_qkv_epilogue_rotates_and_writes_the_cache(K, hd, nh, nkv, bn):
     k_pool = torch.full((meta.n_pages, nkv, 64, hd), 7.0, dtype=torch.bfloat16, device=DEV)
     v_pool = torch.full((meta.n_pages, nkv, 64, hd), -7.0, dtype=torch.bfloat16, device=DEV)
     q = torch.full((T, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
-    K.tc_gemm_fused(xw, w, None, K.TC_QKV_ROPE, bn, row_ssq=ssq, norm_width=H, eps=1e-5,
-                    rope=dict(cs=cs, tok_page=tok_page, positions=meta.positions, q_out=q, k_pool=k_pool, v_pool=v_pool,
+    fused(xw, w, None, K.TC_QKV_ROPE, row_ssq=ssq, norm_width=H, eps=1e-5,
+          rope=dict(cs=cs, tok_page=tok_page, positions=meta.positions, q_out=q, k_pool=k_pool, v_pool=v_pool,
                               nh=nh, nkv=nkv, hd=hd, page_size=64))
     rstd = 1.0 / torch.sqrt(ssq.double() / H + 1e-5)
     qkv = (xw.double() @ w.double().t()) * rstd

@@ -284,6 +284,9 @@ gemv_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int tile = blockIdx.x * 4 + warp;
+    // launched as a programmatic dependent: x is what the kernel before wrote
+    sp_allow_dependents();
+    sp_wait_for_predecessor();
     if (tile >= tiles) return;
     constexpr int HALF = RT / 2 > 0 ? RT / 2 : 1;
     int row_base[RT];
@@ -434,11 +437,11 @@ int launch_gemv(const void* x, const void* W, void* out, int out_dt, int M, int 
     if (M <= 16 && stream_tiles >= 148 * 16 && mode != MODE_ROPE_KV) {
         // enough rows (the output head) to give every warp rows of its own and still fill every SM sixteen warps deep
         if (mode == MODE_SILU_MUL)
-            gemv_stream_kernel<2, 4><<<(stream_tiles + 3) / 4, 128, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo,
-                                                                                mode, pair, stream_tiles);
+            sp_launch_dependent(gemv_stream_kernel<2, 4>, dim3((stream_tiles + 3) / 4), dim3(128), 0, stream, xp, wp, out, out_dt, M,
+                                N, K, ldx, ldw, ldo, mode, pair, stream_tiles);
         else
-            gemv_stream_kernel<1, 8><<<(stream_tiles + 3) / 4, 128, 0, stream>>>(xp, wp, out, out_dt, M, N, K, ldx, ldw, ldo,
-                                                                                mode, pair, stream_tiles);
+            sp_launch_dependent(gemv_stream_kernel<1, 8>, dim3((stream_tiles + 3) / 4), dim3(128), 0, stream, xp, wp, out, out_dt, M,
+                                N, K, ldx, ldw, ldo, mode, pair, stream_tiles);
         SP_CHECK_LAUNCH("gemv_stream");
         return 0;
     }
@@ -504,8 +507,8 @@ SP_API int sp_gemv_argmax(const void* x, const void* W, void* cand, int M, int N
     if (sp_gemv_supported(x, W, M, K, ldx, ldw)) return 1;
     const int tiles = sp_gemv_argmax_candidates(N);
     if (ld_cand < tiles) SP_FAIL("gemv (argmax): the candidate table has %d columns, %d are needed", ld_cand, tiles);
-    gemv_stream_kernel<1, 8><<<(tiles + 3) / 4, 128, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)W, cand,
-                                                                   SP_DT_F32, M, N, K, ldx, ldw, ld_cand, MODE_ARGMAX, 0, tiles);
+    sp_launch_dependent(gemv_stream_kernel<1, 8>, dim3((tiles + 3) / 4), dim3(128), 0, stream, (const __nv_bfloat16*)x,
+                        (const __nv_bfloat16*)W, cand, (int)SP_DT_F32, M, N, K, ldx, ldw, ld_cand, (int)MODE_ARGMAX, 0, tiles);
     SP_CHECK_LAUNCH("gemv_argmax");
     return 0;
 }

@@ -946,6 +946,8 @@ __global__ void argmax_candidates_kernel(const Candidate* __restrict__ cand, int
                                          const int* __restrict__ seq_len) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    sp_allow_dependents();
+    sp_wait_for_predecessor();                                     // the candidates are the head kernel's
     const int r = blockIdx.x;
     const Candidate* row = cand + (size_t)r * ld;
     float bv = -INFINITY;
@@ -988,8 +990,8 @@ SP_API int sp_argmax_candidates(const void* cand, int rows, int n_cand, int ld, 
     if (rows <= 0) return 0;
     if (n_cand <= 0 || ld < n_cand) SP_FAIL("argmax_candidates: %d candidates in rows of %d", n_cand, ld);
     if (header && (!seq_slot || !seq_len)) SP_FAIL("argmax_candidates: noting tokens needs the step's slots and lengths");
-    argmax_candidates_kernel<<<rows, n_cand >= 4096 ? 1024 : 256, 0, stream>>>((const Candidate*)cand, n_cand, ld, out, header,
-                                                                                  n_slots, seq_slot, seq_len);
+    sp_launch_dependent(argmax_candidates_kernel, dim3(rows), dim3(n_cand >= 4096 ? 1024 : 256), 0, stream, (const Candidate*)cand,
+                        n_cand, ld, out, header, n_slots, seq_slot, seq_len);
     SP_CHECK_LAUNCH("argmax_candidates");
     return 0;
 }

@@ -70,10 +70,10 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* v) {
     return w;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int CG = 1>
 struct SmemLayout {
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int B_BYTES = (BN / CG) * BK * 2;            // a CTA of a pair holds its half of the W tile
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TRANSPOSE_BYTES = 4 * 32 * 36 * 4;        // a 32 x 32 float tile (rows padded to 36) per epilogue warp
     static constexpr int TOTAL = STAGES * STAGE_BYTES + 1024 + TRANSPOSE_BYTES;      // + slack to align to 1024
@@ -126,12 +126,56 @@ __device__ __forceinline__ void store_row32(void* C, int c_dt, size_t base, int 
 // Persistent: CTA b computes tiles b, b + gridDim.x, ... (M runs fastest over the tile index, so the
 // CTAs that run together share few tiles of W). Two accumulators in tensor memory let the epilogue
 // of one tile run while the next tile's products are issued.
-template <int BN, int STAGES>
+//
+// CG = 2: the CTAs of a cluster of two (on two SMs) work on ONE tile of 256 rows x BN columns with
+// tcgen05.mma.cta_group::2. Each CTA fetches its 128 rows of A and its HALF of the W tile (BN/2 rows) into its own
+// shared memory and keeps its 128 rows of the result in its own tensor memory; the tensor cores of both SMs read
+// both halves of W. A stage then costs a CTA 32 KB instead of 48 KB for the same products: a third less traffic
+// from L2 into each SM. The pair's first CTA issues the products; both CTAs' copies complete on its barrier
+// (cp.async.bulk.tensor with .cta_group::2, no multicast), its commits arrive on both CTAs' barriers, and the second
+// CTA's epilogue warps arrive on the first's "accumulator free" barrier through the cluster's shared window.
+__device__ __forceinline__ uint32_t pair_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t in_first_cta(uint32_t local_addr) {          // the same variable in the pair's first CTA
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(0u));
+    return a;
+}
+__device__ __forceinline__ void pair_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a tile of this CTA's own shared memory; the bytes count on the barrier ``bar_first`` of the pair's first CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_first) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar_first) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+// arrives, once the products issued so far are done, on the barrier at this address in BOTH CTAs of the pair
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_first_cta(uint32_t local_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(in_first_cta(local_bar)) : "memory");
+}
+
+template <int BN, int STAGES, int CG = 1>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                void* __restrict__ C, int c_dt, int M, int N, int K, int ldc, int mode, int* status,
                const __grid_constant__ EpiArgs ep, const SpRange rg) {
-    using L = SmemLayout<BN, STAGES>;
+    using L = SmemLayout<BN, STAGES, CG>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[STAGES];
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
@@ -142,8 +186,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (K + BK - 1) / BK;
-    const int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
+    constexpr int TM = BM * CG;                                  // rows of a tile
+    const int m_tiles = (M + TM - 1) / TM, n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
+    const int rank = CG == 2 ? (int)pair_rank() : 0;
+    const int walker = CG == 2 ? (int)blockIdx.x / 2 : (int)blockIdx.x;          // which of the tile walkers this CTA belongs to
+    const int walkers = CG == 2 ? (int)gridDim.x / 2 : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -152,7 +200,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bar_acc_full[b]), 1);
-            mbar_init(smem_u32(&bar_acc_empty[b]), 4);          // one arrival per epilogue warp
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4 * CG);     // one arrival per epilogue warp (of both CTAs of a pair)
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -160,12 +208,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // two accumulators, each at a power-of-two column (tensor memory is handed out in powers of two)
     constexpr uint32_t ACC_STRIDE = BN <= 128 ? 128u : 256u, TMEM_COLS = 2u * ACC_STRIDE;
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) pair_sync();                                   // the other CTA's barriers exist before anything arrives there
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
     // Set up. From here on the kernel reads what its predecessor in the stream wrote (A, C, the rows' statistics).
@@ -178,8 +233,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             uint32_t kbc = 0;                                   // pipeline slots used so far, over all tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            for (int tile = walker; tile < total_tiles && ok; tile += walkers) {
+                const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN + rank * (BN / CG);
                 for (int kb = 0; kb < num_kb; ++kb, ++kbc) {
                     const int s = kbc % STAGES;
                     const uint32_t phase = (kbc / STAGES) & 1u;
@@ -187,18 +242,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     const uint32_t b_dst = a_dst + L::A_BYTES;
                     ok = mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101);
                     if (!ok) break;
-                    mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
-                    tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
-                    tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+                    if (CG == 2) {
+                        // both CTAs' bytes count on the first CTA's barrier, which expects them all
+                        const uint32_t full_first = in_first_cta(smem_u32(&bar_full[s]));
+                        if (rank == 0) mbar_expect_tx(smem_u32(&bar_full[s]), 2 * L::STAGE_BYTES);
+                        tma_load_2d_pair(a_dst, &map_a, kb * BK, m0, full_first);
+                        tma_load_2d_pair(b_dst, &map_w, kb * BK, n0, full_first);
+                    } else {
+                        mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
+                        tma_load_2d(a_dst, &map_a, kb * BK, m0, smem_u32(&bar_full[s]));
+                        tma_load_2d(b_dst, &map_w, kb * BK, n0, smem_u32(&bar_full[s]));
+                    }
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16(BM, BN);
+        if (lane == 0 && rank == 0) {                           // of a pair, the first CTA issues the products of both
+            constexpr uint32_t idesc = umma_idesc_bf16(TM, BN);
             uint32_t kbc = 0, it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = walker; tile < total_tiles && ok; tile += walkers, ++it) {
                 const uint32_t buf = it & 1u, use = it >> 1;
                 ok = mbar_wait(smem_u32(&bar_acc_empty[buf]), (use & 1u) ^ 1u, status, 104);
                 if (!ok) break;
@@ -216,18 +279,26 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
                         // 16 bf16 = 32 bytes further along K inside the swizzle span: +2 in 16-byte units
-                        tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        if (CG == 2) tc_mma_bf16_pair(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else tc_mma_bf16(tmem_d, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     }
-                    tc_commit(smem_u32(&bar_empty[s]));
+                    if (CG == 2) tc_commit_pair(smem_u32(&bar_empty[s]));
+                    else tc_commit(smem_u32(&bar_empty[s]));
                 }
-                tc_commit(smem_u32(&bar_acc_full[buf]));        // also after a failed wait: the epilogue must not hang
+                // also after a failed wait: the epilogue must not hang
+                if (CG == 2) tc_commit_pair(smem_u32(&bar_acc_full[buf]));
+                else tc_commit(smem_u32(&bar_acc_full[buf]));
             }
         }
     } else {
         const int q = warp & 3;                      // this warp may touch tensor-memory lanes 32q .. 32q+31
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+        auto acc_free = [&](uint32_t buf) {          // the accumulator may be overwritten: the issuing CTA keeps count
+            if (CG == 2 && rank != 0) mbar_arrive_first_cta(smem_u32(&bar_acc_empty[buf]));
+            else mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        };
+        for (int tile = walker; tile < total_tiles; tile += walkers, ++it) {
+            const int m0 = (tile % m_tiles) * TM + rank * BM, n0 = (tile / m_tiles) * BN;
             const uint32_t buf = it & 1u, use = it >> 1;
             const int row = m0 + q * 32 + lane;
             constexpr int SPAN = 32;
@@ -309,7 +380,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         if (hh == heads_here - 1 && c + SPAN >= half) {
                             tc_fence_before();
                             __syncwarp();
-                            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                            if (lane == 0) acc_free(buf);
                         }
                         if (!live) continue;
                         float lo[32], hi[32];
@@ -356,7 +427,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (c0 + SPAN >= BN) {
                         tc_fence_before();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                        if (lane == 0) acc_free(buf);
                     }
                     // lane = row becomes (lane / 8 = row mod 4, lane % 8 = four columns): through this warp's own tile
 #pragma unroll
@@ -443,7 +514,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (c0 + SPAN >= c_end) {            // all of this tile has left tensor memory: hand the buffer back
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                    if (lane == 0) acc_free(buf);
                 }
                 if (row < M) {
                     if (mode == MODE_SILU_MUL)
@@ -456,9 +527,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) pair_sync();           // neither CTA leaves while the other's products read its shared memory or arrive on its barriers
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
     }
 }
 
@@ -714,6 +787,27 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int 
     return 0;
 }
 
+// The same tiles by pairs of CTAs (tcgen05 cta_group::2): tiles of 256 rows, one pair per two SMs.
+template <int BN, int STAGES>
+int launch_pair(const CUtensorMap& ma, const CUtensorMap& mw_half, void* C, int c_dt, int M, int N, int K, int ldc, int mode,
+                int* status, cudaStream_t stream, const EpiArgs& ep) {
+    using L = SmemLayout<BN, STAGES, 2>;
+    static_assert(L::TOTAL <= 232448, "a CTA's shared memory");
+    static SpPerDevice configured;
+    if (!configured.done()) {
+        cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
+        configured.mark();
+    }
+    const int sm_count = sp_sm_count();
+    if (sm_count < 2) SP_FAIL("tc_gemm: cannot read the number of SMs");
+    const long long tiles = (long long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
+    const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
+    SP_CHECK_CALL("tc_gemm", sp_launch_cluster(tc_gemm_kernel<BN, STAGES, 2>, dim3(2 * pairs), dim3(192), (size_t)L::TOTAL, stream,
+                                               -2, ma, mw_half, C, c_dt, M, N, K, ldc, mode, status, ep, sp_range_host));
+    return 0;
+}
+
 template <int BN, int STAGES>
 int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_dt, int M, int N, int K, int ldc,
                   int mode, int splits, int* status, cudaStream_t stream) {
@@ -765,6 +859,10 @@ SP_API int sp_tc_gemm_n_tiles(int N, int bn) { return bn > 0 ? (N + bn - 1) / bn
 static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
                        int mode, int bn, const EpiArgs* epp, int* status, cudaStream_t stream);
 
+// From this many rows of A on, tiles are computed by pairs of CTAs (cta_group::2); 0: never.
+static int pairs_from = 512;
+SP_API void sp_tc_gemm_set_pairs_from(int rows) { pairs_from = rows; }
+
 SP_API int sp_tc_gemm_fused(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw,
                             int ldc, int mode, int bn, const void* ep, int* status, cudaStream_t stream) {
     return tc_gemm_any(A, W, C, c_dt, M, N, K, lda, ldw, ldc, mode, bn, (const EpiArgs*)ep, status, stream);
@@ -804,6 +902,13 @@ static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, i
     if (mode == MODE_SILU_MUL && (N % bn)) SP_FAIL("tc_gemm: the fused silu epilogue needs N (%d) to be a multiple of the tile width %d", N, bn);
     CUtensorMap ma, mw;
     if (make_map(&ma, A, M, K, lda, BM)) return 1;
+    // a prompt's worth of rows: pairs of CTAs on tiles of 256 rows, each fetching half of the W tile
+    if (pairs_from > 0 && M >= pairs_from) {
+        if (make_map(&mw, W, N, K, ldw, bn / 2)) return 1;
+        if (bn == 128) return launch_pair<128, 8>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
+        if (bn == 192) return launch_pair<192, 7>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
+        return launch_pair<256, 6>(ma, mw, C, c_dt, M, N, K, ldc, mode, status, stream, ep);
+    }
     if (make_map(&mw, W, N, K, ldw, bn)) return 1;
     const int splits = fused ? 1 : pick_splits(M, N, K, bn);
     if (splits > 1) {

@@ -489,7 +489,11 @@ def test_gemv_is_repeatable_and_row_independent(K):
                                        (64, 3072, 2048, 128), (17, 2048, 8192, 128), (128, 200, 1000, 128),
                                        (100, 130, 520, 256), (33, 2048, 2048, 256),
                                        # 192-wide tiles: whole, ragged in M and N, many tiles per CTA, one row of tiles
-                                       (2048, 3072, 2048, 192), (300, 200, 136, 192), (129, 5120, 72, 192), (64, 3072, 2048, 192)])
+                                       (2048, 3072, 2048, 192), (300, 200, 136, 192), (129, 5120, 72, 192), (64, 3072, 2048, 192),
+                                       # from 512 rows on pairs of CTAs compute tiles of 256 rows (cta_group::2): ragged in M
+                                       # and N, a last tile whose second CTA has no rows, more tiles than pairs
+                                       (512, 256, 64, 128), (513, 520, 136, 128), (1000, 1160, 264, 192), (700, 300, 72, 256),
+                                       (640, 20480, 128, 256), (4096, 2048, 512, 256)])
 def test_tc_gemm(K, M, N, K_, bn):
     torch.manual_seed(M + N)
     a = torch.randn(M, K_).bfloat16()

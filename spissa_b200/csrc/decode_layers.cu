@@ -106,9 +106,24 @@ struct Params {
     int n_layers, T, H, n_stages, max_pages, chunk_pages, n_chunks, xn_row;
     const int* plan;                // optional, on the device: {chunk_pages, n_chunks} instead of the two above
     int pairs;                      // 1: launched as clusters of two CTAs (the pair-wise combination is possible)
-    int pad2;
+    // the output head as one more product behind the last layer (head_mode 0: none): the final RMS norm is folded in
+    // like the layers' norms; its tensor map is maps[n_layers * 4]
+    int head_mode;                  // 1: logits [T, head_ld] float32; 2: one (value, row) candidate per token and CTA, [T, head_ld]
+    const __nv_bfloat16* head_w;    // [head_rows, H]
+    const __nv_bfloat16* final_norm;   // [H]
+    void* head_out;
+    float final_eps;
+    int head_rows, head_ld, pad3;
     SpRange rg;                     // what the debug build checks table entries against
 };
+
+// MODE 2 of the head: the best (value, row) of a token among the rows a CTA computed; a second, tiny kernel takes the
+// best of each token's row of candidates (the lowest row wins among equal values, NaN never wins:
+// crates/spissa-runtime/src/streaming/argmax.rs:30-51, :85-97).
+struct Candidate { float value; int index; };
+__device__ __forceinline__ void candidate_take(float& bv, int& bi, float ov, int oi) {
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+}
 
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
     asm volatile(
@@ -245,6 +260,25 @@ __device__ void copy_warp(const Params& p, Shared* sh, uint32_t ring, int lane) 
                 }
             }
             cursor = (cursor + j.n_blocks) % G;
+        }
+    }
+    if (p.head_mode) {                                          // the head's rows, walked as the consumers walk them
+        const int n_blocks = (p.head_rows + 15) / 16, nkt = (p.H + KC - 1) / KC;
+        const CUtensorMap* map = p.maps + (size_t)p.n_layers * 4;
+        for (int rb = (cta - cursor + G) % G; rb < n_blocks; rb += G) {
+            const int o0 = rb * 8;
+            for (int kt = 0; kt < nkt; ++kt, ++n) {
+                const uint32_t full = smem_u32(&sh->full[slot]), empty = smem_u32(&sh->empty[slot]);
+                if (!is_aborted(sh) && !mbar_wait(empty, phase ^ 1u, nullptr, 0)) raise_abort(p, sh, 201);
+                if (lane == 0) {
+                    mbar_expect_tx(full, (uint32_t)STAGE_BYTES);
+#pragma unroll
+                    for (int c = 0; c < KC / BOXC; ++c)
+                        tma_load_4d(ring + slot * STAGE_BYTES + c * BOX_BYTES, map, kt * KC + c * BOXC, o0 % 8, 0, o0 / 8, full);
+                }
+                __syncwarp();
+                if (++slot == S) { slot = 0; phase ^= 1u; }
+            }
         }
     }
     // after an abort tiles may still be in flight into this CTA's shared memory: let them land
@@ -948,7 +982,7 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
 
         // ---- down projection into the residual
         ssq = 0.0f;
-        next_w = l + 1 < p.n_layers ? p.layers[l + 1].norm1 : nullptr;
+        next_w = l + 1 < p.n_layers ? p.layers[l + 1].norm1 : (p.head_mode ? p.final_norm : nullptr);
         {
             const int Kd = L.I;
             product<WIDE>(p, sh, job_of<HD>(L, 3, H), w, ring, red,
@@ -956,7 +990,51 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
                     x_pre, add_into_x);
         }
         if (warp < 4) publish_ssq(sh, ssq, ssq_b + cta, gp);
-        if (l + 1 < p.n_layers) grid_sync(p, sh, epoch);
+        if (l + 1 < p.n_layers || p.head_mode) grid_sync(p, sh, epoch);
+    }
+
+    // ---- the output head on the final norm of the residual
+    if (p.head_mode) {
+        stage_xw(p, sh, ssq_b, p.final_eps, xn);
+        Job j;
+        j.W = p.head_w; j.N = p.head_rows; j.K = H; j.pair = 0; j.n_blocks = (p.head_rows + 15) / 16;
+        float best_v = -INFINITY;                 // of this thread's token and column, over the CTA's blocks
+        int best_i = 0x7fffffff;
+        const bool logits = p.head_mode == 1;
+        product<WIDE>(p, sh, j, w, ring, red, aload_xn, no_pre,
+                [&](int rb, int m, int c, float a, float b, int rowA, int rowB, int nA, int nB, const float4&) {
+                    if (m >= T) return;
+                    a *= sh->rstd[m];
+                    b *= sh->rstd[m];
+                    if (logits) {
+                        float* out = (float*)p.head_out + (size_t)m * p.head_ld;
+                        if (c < nA) __stcs(out + rowA + c, a);
+                        if (c < nB) __stcs(out + rowB + c, b);
+                    } else {
+                        if (c < nA) candidate_take(best_v, best_i, a, rowA + c);
+                        if (c < nB) candidate_take(best_v, best_i, b, rowB + c);
+                    }
+                });
+        if (!logits) {
+            // the epilogue threads of a token (eight columns) leave their finds in shared memory; one thread per token
+            // takes the best of them: this CTA's candidate
+            Candidate* finds = (Candidate*)red;                  // [16 tokens][8 columns], the K-slice sums are spent
+            bar_sync(1, CTHREADS);
+            if (tid < 64 * NF) {
+                const int e_m = 8 * (tid >> 6) + 2 * ((tid >> 1) & 3) + (tid & 1), e_c = (tid >> 3) & 7;
+                finds[e_m * 8 + e_c] = Candidate{best_v, best_i};
+            }
+            bar_sync(1, CTHREADS);
+            if (tid < T) {
+                float bv = -INFINITY;
+                int bi = 0x7fffffff;
+                for (int c = 0; c < 8; ++c) {
+                    const Candidate f = finds[tid * 8 + c];
+                    if (f.index != 0x7fffffff) candidate_take(bv, bi, f.value, f.index);
+                }
+                ((Candidate*)p.head_out)[(size_t)tid * p.head_ld + cta] = Candidate{bv, bi};
+            }
+        }
     }
 }
 
@@ -1135,6 +1213,21 @@ SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int m
 // any layer. part_o / part_ml hold T·max(nh)·MAX_CHUNKS·(hd + 2) floats together; sync: 3 zeroed words.
 // ``plan`` (optional, two int32 on the device: what sp_decode_layers_plan gives) replaces the split made from
 // ``len_pages``: a captured launch then serves every length, the host refreshing the two words before a replay.
+// The output head for the NEXT call of sp_decode_layers only (mode 0: none): its weight [rows, H] (its tensor map is
+// the one behind the layers' in ``maps``), the final norm's weight and eps, and where the result goes: mode 1 logits
+// [T, ld] float32, mode 2 candidates [T, ld] pairs of (float32, int32), one per CTA (ld at least sp_decode_layers_ctas()).
+namespace {
+struct HeadArgs { int mode; const void* w; const void* norm; float eps; int rows; void* out; int ld; } next_head = {0, nullptr, nullptr, 0.f, 0, nullptr, 0};
+}
+SP_API int sp_decode_layers_set_head(int mode, const void* w, const void* norm, float eps, int rows, void* out, int ld) {
+    if (mode < 0 || mode > 2) SP_FAIL("decode_layers: unknown head mode %d", mode);
+    if (mode && (!w || !norm || !out || rows <= 0 || ld <= 0)) SP_FAIL("decode_layers: the head needs its weight, the final norm and a place for the result");
+    if (mode == 1 && ld < rows) SP_FAIL("decode_layers: logits rows of %d floats do not hold %d", ld, rows);
+    if (mode == 2 && ld < sm_count()) SP_FAIL("decode_layers: %d candidates per token, one per CTA (%d) are written", ld, sm_count());
+    next_head = HeadArgs{mode, w, norm, eps, rows, out, ld};
+    return 0;
+}
+
 SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, int T, int H, int hd, float* x, void* q, void* attn,
                             void* act, void* xw, float* ssq, float* part_o, float* part_ml, const int* positions,
                             const int* seq_row, const int* page_table, int max_pages, int page_size, int len_pages,
@@ -1164,7 +1257,15 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     p.n_stages = stages;
     p.plan = plan;
     p.pairs = pair_chunks(G, T, hd, max_nkv) > 0 ? 1 : 0;      // CTA pairs only where that split can occur with T sequences
-    p.pad2 = 0;
+    p.head_mode = next_head.mode;
+    p.head_w = (const __nv_bfloat16*)next_head.w;
+    p.final_norm = (const __nv_bfloat16*)next_head.norm;
+    p.head_out = next_head.out;
+    p.final_eps = next_head.eps;
+    p.head_rows = next_head.rows;
+    p.head_ld = next_head.ld;
+    p.pad3 = 0;
+    next_head.mode = 0;                                        // for this call only
     p.rg = sp_range_host;
     if (plan_split(G, T, hd, len_pages, max_nkv, &p.chunk_pages, &p.n_chunks)) return 1;
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;

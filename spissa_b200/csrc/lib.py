@@ -722,6 +722,27 @@ def decode_layers(table, maps, n_layers, T, H, hd, x, q, attn, act, xw, ssq, par
         c_void_p(_ptr(status_word(x.device))), c_void_p(_stream())))
 
 
+def decode_layers_set_head(mode: int, w, norm_w, eps: float, out, ld: int) -> None:
+    """The output head of the NEXT ``decode_layers`` call: ``mode`` 1 writes logits [T, ld] (float32), 2 one (value,
+    row) candidate per token and CTA [T, ld] (pairs of float32 and int32, for ``argmax_candidates``). The final norm
+    (weight ``norm_w``, ``eps``) is folded into the product; the head's tensor map follows the layers' in ``maps``."""
+    lib = load("decode_layers")
+    _need_contig(w, norm_w, out)
+    _check("decode_layers", lib.sp_decode_layers_set_head(
+        int(mode), c_void_p(_ptr(w)), c_void_p(_ptr(norm_w)), c_float(eps), int(w.shape[0]), c_void_p(_ptr(out)), int(ld)))
+
+
+def argmax_candidates(cand, rows: int, n_cand: int, out, note=None) -> None:
+    """out[r] = the row of the best of ``cand[r, :n_cand]`` ((value, row) pairs; the lowest row among equal values);
+    with ``note`` the tokens also go into the headers of the step's sequences."""
+    header = note.header if note is not None else None
+    _check("generic", load("generic").sp_argmax_candidates(
+        c_void_p(_ptr(cand)), int(rows), int(n_cand), int(cand.shape[1]), c_void_p(_ptr(out)), c_void_p(_ptr(header)),
+        header.shape[0] if header is not None else 0,
+        c_void_p(_ptr(note.seq_slot) if note is not None else None),
+        c_void_p(_ptr(note.seq_len) if note is not None else None), c_void_p(_stream())))
+
+
 def decode_layers_plan(T: int, hd: int, len_pages: int, max_nkv: int) -> tuple:
     """(pages per chunk, chunks) of the keys for ``T`` sequences of at most ``len_pages`` pages."""
     lib = load("decode_layers")

@@ -66,6 +66,9 @@ class FusedDecode:
         self.cache_id = None
         self.group = None
         self._splits = {}                      # (sequences, pages) -> the kernel's split of the keys
+        self.head = None                       # the final norm and the head, when the kernel can take them too
+        self.with_head = True                  # switch for comparisons: False leaves norm and head to the parts
+        self.head_runs = 0
 
     # ------------------------------------------------------------------ planning
     @classmethod
@@ -78,6 +81,12 @@ class FusedDecode:
         plan = cls(model, fields)
         if not K.decode_layers_supported(1, H, hd, model.rt.page_size, plan.max_group):
             return None
+        # the final norm and the head as the kernel's last product, when they say what they are
+        norm = model.final_norm.fused_fields() if hasattr(model.final_norm, "fused_fields") else None
+        head = model.head.fused_fields() if hasattr(model.head, "fused_fields") else None
+        if norm and head and norm.get("kind") == "rmsnorm" and head.get("kind") == "linear_head" \
+                and norm["size"] == H and head["hidden_size"] == H and head["vocab_size"] % 16 == 0:
+            plan.head = dict(weight=head["weight"], norm=norm["weight"], eps=float(norm["eps"]), vocab=head["vocab_size"])
         return plan
 
     def takes(self, step, cache) -> bool:
@@ -132,6 +141,8 @@ class FusedDecode:
                 float(m["scale"]) * 1.4426950408889634, 0))
             maps += [K.decode_layers_encode_map(m["qkv"], self.hd // 2), K.decode_layers_encode_map(m["o"], 0),
                      K.decode_layers_encode_map(ff["gate_up"], ff["pair"]), K.decode_layers_encode_map(ff["down"], 0)]
+        if self.head is not None:
+            maps.append(K.decode_layers_encode_map(self.head["weight"], 0))
         blob = b"".join(rows)
         assert len(blob) == len(rows) * K.decode_layers_desc_bytes()
         self.keep = keep
@@ -148,14 +159,32 @@ class FusedDecode:
         self.part_o = torch.empty(MAX_TOKENS * self.max_nh * chunks * self.hd, dtype=torch.float32, device=dev)
         self.part_ml = torch.empty(MAX_TOKENS * self.max_nh * chunks * 2, dtype=torch.float32, device=dev)
         self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.cand = torch.empty(MAX_TOKENS, ctas, 2, dtype=torch.float32, device=dev)
 
     # ------------------------------------------------------------------ running
-    def run(self, h: torch.Tensor, step, cache) -> None:
-        """All layers on the residual stream ``h`` [T, H] (float32), in place."""
+    def run(self, h: torch.Tensor, step, cache, greedy: bool = False, note=None):
+        """All layers on the residual stream ``h`` [T, H] (float32), in place. When the kernel can also take the final
+        norm and the head and the step wants every token's result, it does, and the result comes back: the greedy
+        tokens (int32 [T]; ``note`` as in ``LMHead.greedy``) or the logits (float32 [T, vocab]); else None."""
         self.runs += 1
         pt = step.page_tables[self.group]
         len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
+        result = None
+        T = step.n_tokens
+        if self.head is not None and self.with_head and step.n_want == T:
+            # every sequence brings one token and wants its result: the wanted rows are all rows, in order
+            self.head_runs += 1
+            hd = self.head
+            if greedy:
+                result = torch.empty(T, dtype=torch.int32, device=h.device)
+                K.decode_layers_set_head(2, hd["weight"], hd["norm"], hd["eps"], self.cand, self.cand.shape[1])
+            else:
+                result = torch.empty(T, hd["vocab"], dtype=torch.float32, device=h.device)
+                K.decode_layers_set_head(1, hd["weight"], hd["norm"], hd["eps"], result, hd["vocab"])
         K.decode_layers(self.table, self.maps, len(self.fields), step.n_tokens, self.H, self.hd, h, self.q, self.attn, self.act,
                         self.xw, self.ssq, self.part_o, self.part_ml, step.positions, step.seq_row, pt, cache.page_size,
                         len_pages, self.max_nkv, self.max_group, self.sync, plan=step.key_split,
                         n_pages=cache.kv_groups[self.group].n_pages)
+        if result is not None and greedy:
+            K.argmax_candidates(self.cand, T, self.cand.shape[1], result, note)
+        return result

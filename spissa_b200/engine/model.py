@@ -89,7 +89,9 @@ class Model:
             from .fused_prefill import FusedPrefill
             self._fused_prefill = FusedPrefill.plan(self)
         if self.fuse_decode and self._fused is not None and not profiling() and self._fused.takes(step, cache):
-            self._fused.run(h, step, cache)
+            done = self._fused.run(h, step, cache, greedy, note)
+            if done is not None:
+                return done                                # the kernel ran the final norm and the head as well
         elif self.host_steps and not profiling() and self._host_runner(step, cache):
             self._host_step.run(h, step, cache)            # a prompt step of up to 128 tokens: launched from C++
         elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):

@@ -64,6 +64,13 @@ class LMHead(Part):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return self.proj(x, out_dtype=torch.float32)
 
+    def fused_fields(self):
+        """What a runner that computes the head itself needs: the weight [vocab, hidden] (bfloat16, contiguous)."""
+        w = self.proj.weight if self.proj is not None else None
+        if w is None or w.dtype != torch.bfloat16 or not w.is_contiguous() or w.data_ptr() % 16:
+            return None
+        return dict(kind="linear_head", weight=w, vocab_size=self.vocab_size, hidden_size=self.hidden_size)
+
     def greedy(self, x: torch.Tensor, note=None):
         """The index of the largest logit of every row (int32 [rows]) without the logits, as the reference's greedy
         head keeps only (best index, best value) while it streams the rows

@@ -66,6 +66,46 @@ def test_kernel_runs_and_agrees_with_plain_and_with_the_parts(folders, name):
             assert err <= TOL, f"{name}: sequence {b}, {'one kernel' if fuse else 'part by part'}: {err:.3e}"
 
 
+@pytest.mark.parametrize("name,vocab", [("E", 784), ("F", 528), ("E", 16)])
+def test_the_kernel_takes_the_final_norm_and_the_head(tmp_path, name, vocab):
+    """With a vocabulary that is a multiple of 16 the final norm and the head are the kernel's last product: the logits
+    agree with the plain implementation and with the same kernel followed by the norm and head kernels; the greedy
+    tokens are the argmax of those logits (the lowest index among equal values), also noted in the headers."""
+    cfg, init = tiny.TINIES[name]
+    cfg = dict(cfg, vocab_size=vocab)
+    tiny.make_folder(cfg, init, tmp_path)
+    pcfg, w = P.read_model_folder(tmp_path)
+    lens = [70, 1, 63, 5, 33]
+    steps = 6
+    seqs = [tiny.random_prompt(vocab, n + steps, 13 * n + 1) for n in lens]
+    got = {}
+    for with_head in (True, False):
+        engine = Engine.from_folder(str(tmp_path), dtype="bfloat16", max_tokens=64 * 16, use_graphs=False)
+        engine.step([(engine.acquire(), [1, 2], [])])                      # plans the runners
+        engine.model._fused.with_head = with_head
+        got[with_head] = decode_rows(engine, seqs, lens, steps)
+        fused = engine.model._fused
+        assert fused.head is not None and fused.head_runs == (steps if with_head else 0)
+    for b, (q, n) in enumerate(zip(seqs, lens)):
+        ref = P.model_logits(pcfg, w, q, torch.float64)
+        scale = float(ref.abs().max())
+        for with_head in (True, False):
+            err = float((got[with_head][:, b].double() - ref[n:n + steps]).abs().max()) / scale
+            assert err <= TOL, f"{name}: sequence {b}, head in the kernel {with_head}: {err:.3e}"
+    # greedy: the tokens without logits, teacher-forced along the same sequences
+    engine = Engine.from_folder(str(tmp_path), dtype="bfloat16", max_tokens=64 * 16, use_graphs=False)
+    slots = [engine.acquire() for _ in seqs]
+    engine.step([(s, q[:n], []) for s, q, n in zip(slots, seqs, lens)])
+    for i in range(steps):
+        toks = engine.step([(s, [q[n + i]], [0]) for s, q, n in zip(slots, seqs, lens)], greedy=True).cpu()
+        want = got[True][i].argmax(dim=1).int()
+        assert torch.equal(toks, want), (i, toks.tolist(), want.tolist())
+        header = engine.cache.header.cpu()
+        for b, s in enumerate(slots):
+            assert int(header[s, 2]) == int(toks[b])
+    assert engine.model._fused.head_runs == steps
+
+
 def test_sixteen_sequences_in_one_step_and_seventeen_part_by_part(folders):
     folder, pcfg, w = folders["E"]
     V = pcfg["vocab_size"]

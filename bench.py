@@ -248,7 +248,7 @@ def kernel_case(name: str, reps: int) -> int:
         lib.sp_decode_layers_set_trace(ctypes.c_void_p(trace.data_ptr()))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        eng.step([(sl, [9], [0]) for sl in slots])
+        eng.step([(sl, [9], [0]) for sl in slots], greedy=True)
         e1.record()
         torch.cuda.synchronize()
         lib.sp_decode_layers_set_trace(ctypes.c_void_p(0))
@@ -265,7 +265,10 @@ def kernel_case(name: str, reps: int) -> int:
             work.setdefault(names[e - 1], []).append(t[2 * e] - t[2 * e - 1])
             wait.setdefault(names[e - 1], []).append(t[2 * e + 1] - t[2 * e])
         med = lambda v: sorted(v)[len(v) // 2] / 1e3
+        last = len(per_layer) * nl                                # behind the last layer: the final norm and the head, if the kernel ran them
+        head_us = round((t[1023] - t[2 * last + 1]) / 1e3, 2) if t[2 * last + 1] else None
         print(json.dumps({"kernel_case": name, "layers": nl, "kernel_us": round((t[1023] - t[1]) / 1e3, 1),
+                          "head_us": head_us,
                           "step_ms_with_host": round(e0.elapsed_time(e1), 3),
                           "phase_us_median": {k: round(med(v), 2) for k, v in work.items()},
                           "barrier_us_median": {k: round(med(v), 2) for k, v in wait.items()},

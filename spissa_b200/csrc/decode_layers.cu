@@ -113,7 +113,13 @@ struct Params {
     const __nv_bfloat16* final_norm;   // [H]
     void* head_out;
     float final_eps;
-    int head_rows, head_ld, pad3;
+    int head_rows, head_ld, n_slots;
+    // head_mode 2 with ``tokens``: the last CTA to finish takes the best of each token's candidates, writes the token
+    // and (with ``header``) notes it in the sequence's header [slots, 4]: position, draws, last token, spare
+    int* tokens;                    // [T]
+    int* header;
+    const int* seq_slot;            // [T]
+    const int* seq_len;             // [T] the sequences' lengths after this step
     SpRange rg;                     // what the debug build checks table entries against
 };
 
@@ -1074,14 +1080,49 @@ __global__ void __launch_bounds__(THREADS, 1) decode_layers_kernel(const __grid_
     }
     __syncthreads();
     // the last CTA to finish hands the counters back at zero for the next launch
+    __shared__ int is_last;
     if (tid == 0) {
         if (p.trace && cta == 0) p.trace[1023] = global_ns();
         __threadfence();
         const unsigned prev = atomicAdd(&p.sync[1], 1u);
-        if (prev == (unsigned)G - 1u) {
+        is_last = prev == (unsigned)G - 1u;
+        if (is_last) {
             p.sync[0] = 0u;
             p.sync[1] = 0u;
             __threadfence();
+        }
+    }
+    __syncthreads();
+    // ... and, for a greedy step, takes the best of every token's candidates (one per CTA, all written by now): the
+    // largest value, the lowest row among equal values, as a serial scan with a strict ``>`` would
+    // (crates/spissa-runtime/src/ops.rs:309-324)
+    if (is_last && p.head_mode == 2 && p.tokens && !is_aborted(sh)) {
+        __threadfence();
+        const Candidate* cand = (const Candidate*)p.head_out;
+        for (int m = warp; m < p.T; m += THREADS / 32) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int c = lane; c < G; c += 32) {
+                const float v = __ldcg(&cand[(size_t)m * p.head_ld + c].value);
+                const int i = __ldcg(&cand[(size_t)m * p.head_ld + c].index);
+                if (i != 0x7fffffff) candidate_take(bv, bi, v, i);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                candidate_take(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+            if (lane == 0) {
+                const int tok = bi == 0x7fffffff ? 0 : bi;
+                p.tokens[m] = tok;
+                if (p.header) {
+                    const int slot = p.seq_slot[m];
+                    if (slot >= 0 && slot < p.n_slots) {
+                        int* h = p.header + (size_t)slot * 4;
+                        h[0] = p.seq_len[m];
+                        h[1] += 1;
+                        h[2] = tok;
+                    }
+                }
+            }
         }
     }
 }
@@ -1218,6 +1259,14 @@ SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int m
 // [T, ld] float32, mode 2 candidates [T, ld] pairs of (float32, int32), one per CTA (ld at least sp_decode_layers_ctas()).
 namespace {
 struct HeadArgs { int mode; const void* w; const void* norm; float eps; int rows; void* out; int ld; } next_head = {0, nullptr, nullptr, 0.f, 0, nullptr, 0};
+struct GreedyArgs { int* tokens; int* header; int n_slots; const int* seq_slot; const int* seq_len; } next_greedy = {nullptr, nullptr, 0, nullptr, nullptr};
+}
+// With head mode 2, for the NEXT call only: the kernel's last CTA also writes the greedy tokens [T] and, with
+// ``header`` [n_slots, 4], notes them in the headers of the step's sequences (slots ``seq_slot``, lengths ``seq_len``).
+SP_API int sp_decode_layers_set_greedy_out(int* tokens, int* header, int n_slots, const int* seq_slot, const int* seq_len) {
+    if (header && (!seq_slot || !seq_len || n_slots <= 0)) SP_FAIL("decode_layers: noting tokens needs the step's slots and lengths");
+    next_greedy = GreedyArgs{tokens, header, n_slots, seq_slot, seq_len};
+    return 0;
 }
 SP_API int sp_decode_layers_set_head(int mode, const void* w, const void* norm, float eps, int rows, void* out, int ld) {
     if (mode < 0 || mode > 2) SP_FAIL("decode_layers: unknown head mode %d", mode);
@@ -1264,8 +1313,13 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     p.final_eps = next_head.eps;
     p.head_rows = next_head.rows;
     p.head_ld = next_head.ld;
-    p.pad3 = 0;
+    p.tokens = p.head_mode == 2 ? next_greedy.tokens : nullptr;
+    p.header = next_greedy.header;
+    p.n_slots = next_greedy.n_slots;
+    p.seq_slot = next_greedy.seq_slot;
+    p.seq_len = next_greedy.seq_len;
     next_head.mode = 0;                                        // for this call only
+    next_greedy = GreedyArgs{nullptr, nullptr, 0, nullptr, nullptr};
     p.rg = sp_range_host;
     if (plan_split(G, T, hd, len_pages, max_nkv, &p.chunk_pages, &p.n_chunks)) return 1;
     const int smem = stages * STAGE_BYTES + 2 * RED_FLOATS * 4 + uni;

@@ -732,6 +732,17 @@ def decode_layers_set_head(mode: int, w, norm_w, eps: float, out, ld: int) -> No
         int(mode), c_void_p(_ptr(w)), c_void_p(_ptr(norm_w)), c_float(eps), int(w.shape[0]), c_void_p(_ptr(out)), int(ld)))
 
 
+def decode_layers_set_greedy_out(tokens, note=None) -> None:
+    """With head mode 2, for the NEXT ``decode_layers`` call: the kernel's last CTA also takes the best of each token's
+    candidates and writes the tokens (int32 [T]); with ``note`` they also go into the headers of the step's sequences."""
+    lib = load("decode_layers")
+    header = note.header if note is not None else None
+    _check("decode_layers", lib.sp_decode_layers_set_greedy_out(
+        c_void_p(_ptr(tokens)), c_void_p(_ptr(header)), header.shape[0] if header is not None else 0,
+        c_void_p(_ptr(note.seq_slot) if note is not None else None),
+        c_void_p(_ptr(note.seq_len) if note is not None else None)))
+
+
 def argmax_candidates(cand, rows: int, n_cand: int, out, note=None) -> None:
     """out[r] = the row of the best of ``cand[r, :n_cand]`` ((value, row) pairs; the lowest row among equal values);
     with ``note`` the tokens also go into the headers of the step's sequences."""

@@ -178,6 +178,7 @@ class FusedDecode:
             if greedy:
                 result = torch.empty(T, dtype=torch.int32, device=h.device)
                 K.decode_layers_set_head(2, hd["weight"], hd["norm"], hd["eps"], self.cand, self.cand.shape[1])
+                K.decode_layers_set_greedy_out(result, note)       # the kernel's last CTA takes the best candidates
             else:
                 result = torch.empty(T, hd["vocab"], dtype=torch.float32, device=h.device)
                 K.decode_layers_set_head(1, hd["weight"], hd["norm"], hd["eps"], result, hd["vocab"])
@@ -185,6 +186,4 @@ class FusedDecode:
                         self.xw, self.ssq, self.part_o, self.part_ml, step.positions, step.seq_row, pt, cache.page_size,
                         len_pages, self.max_nkv, self.max_group, self.sync, plan=step.key_split,
                         n_pages=cache.kv_groups[self.group].n_pages)
-        if result is not None and greedy:
-            K.argmax_candidates(self.cand, T, self.cand.shape[1], result, note)
         return result

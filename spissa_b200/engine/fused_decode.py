@@ -9,6 +9,7 @@ compared with each other and with the plain implementation in the tests.
 """
 from __future__ import annotations
 
+import os
 import struct
 
 import torch
@@ -67,7 +68,8 @@ class FusedDecode:
         self.group = None
         self._splits = {}                      # (sequences, pages) -> the kernel's split of the keys
         self.head = None                       # the final norm and the head, when the kernel can take them too
-        self.with_head = True                  # switch for comparisons: False leaves norm and head to the parts
+        # switch for comparisons: False (or SPISSA_B200_FUSE_HEAD=0) leaves the final norm and the head to the parts
+        self.with_head = os.environ.get("SPISSA_B200_FUSE_HEAD", "1") != "0"
         self.head_runs = 0
 
     # ------------------------------------------------------------------ planning

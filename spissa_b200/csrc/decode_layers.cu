@@ -30,6 +30,10 @@
 //     heads' outputs itself, so the combination costs neither a phase of its own nor its grid barrier;
 //   * phases that need every CTA's result are separated by a grid barrier (cooperative launch; an atomic
 //     counter; bounded spin).
+//   * the output head can be the kernel's last product (crates/spissa-runtime/src/streaming/linear_argmax.rs:13: the
+//     reference's greedy head streams the rows and keeps the best): the final norm is folded in like the others,
+//     the vocabulary's rows stream through the same ring, and the result is the logits or, for a greedy step, one
+//     (value, row) candidate per token and CTA, of which the last CTA to finish takes the best.
 // RMSNorm costs no pass of its own: whoever adds into the residual also stores it multiplied by the next norm's
 // weight (bfloat16, the next product's input) and sums the squares of what it wrote, per CTA and token; the
 // next product adds the CTAs' sums in CTA order and multiplies its RESULT by 1/rms: y = rstd·(x ⊙ w)·Wᵀ.
@@ -118,6 +122,11 @@ struct Params {
     // and (with ``header``) notes it in the sequence's header [slots, 4]: position, draws, last token, spare
     int* tokens;                    // [T]
     int* header;
+    // the embedding as the kernel's first phase (null: ``x`` holds the rows already): x[m] = table[ids[m]], a zero row
+    // and code 301 for an id outside the table (crates/spissa-runtime/src/ops.rs:6-30: no scale)
+    const __nv_bfloat16* embed_w;   // [embed_rows, H]
+    const int* embed_ids;           // [T]
+    int embed_rows, pad4;
     const int* seq_slot;            // [T]
     const int* seq_len;             // [T] the sequences' lengths after this step
     SpRange rg;                     // what the debug build checks table entries against
@@ -144,13 +153,8 @@ __device__ __forceinline__ uint4 lds128(uint32_t a) {
     asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
     return v;
 }
-// produced inside this kernel by other CTAs: read at L2, never from this SM's L1
-__device__ __forceinline__ uint4 ld_cg_u4(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.cg.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-// Predicated loads that leave zeros when ``pred`` is false. The zero is set BEFORE the load and nothing reads
+// Predicated loads that leave zeros when ``pred`` is false (what other CTAs produced inside this kernel is read at L2,
+// never from this SM's L1). The zero is set BEFORE the load and nothing reads
 // the registers until their use: the warp goes on while the load is in flight.
 __device__ __forceinline__ void lds128_if(uint4& v, uint32_t a, bool pred) {
     v = make_uint4(0, 0, 0, 0);
@@ -850,8 +854,22 @@ __device__ void consumers(const Params& p, Shared* sh, uint32_t ring, float* red
         float s = 0.0f;
         if (cta < T) {
             const __nv_bfloat16* w0 = p.layers[0].norm1;
+            const __nv_bfloat16* row = nullptr;                  // the token's row of the embedding table, if the kernel embeds
+            bool embed = p.embed_w != nullptr, known = true;
+            if (embed) {
+                const int id = __ldg(p.embed_ids + cta);
+                known = id >= 0 && id < p.embed_rows;
+                if (!known && tid == 0 && p.status) atomicCAS(p.status, 0, 301);
+                row = p.embed_w + (size_t)(known ? id : 0) * H;
+            }
             for (int k = tid; k < H; k += CTHREADS) {
-                const float v = __ldcg(p.x + (size_t)cta * H + k);
+                float v;
+                if (embed) {
+                    v = known ? __bfloat162float(row[k]) : 0.0f;
+                    __stcg(p.x + (size_t)cta * H + k, v);
+                } else {
+                    v = __ldcg(p.x + (size_t)cta * H + k);
+                }
                 s = fmaf(v, v, s);
                 p.xw[(size_t)cta * H + k] = __float2bfloat16_rn(v * __bfloat162float(w0[k]));
             }
@@ -1260,6 +1278,14 @@ SP_API int sp_decode_layers_supported(int T, int H, int hd, int page_size, int m
 namespace {
 struct HeadArgs { int mode; const void* w; const void* norm; float eps; int rows; void* out; int ld; } next_head = {0, nullptr, nullptr, 0.f, 0, nullptr, 0};
 struct GreedyArgs { int* tokens; int* header; int n_slots; const int* seq_slot; const int* seq_len; } next_greedy = {nullptr, nullptr, 0, nullptr, nullptr};
+struct EmbedArgs { const void* w; const int* ids; int rows; } next_embed = {nullptr, nullptr, 0};
+}
+// For the NEXT call only: the kernel fills the residual itself, x[m] = table[ids[m]] (bfloat16 table [rows, H], ids
+// on the device); an id outside the table gives a zero row and code 301 in the status word.
+SP_API int sp_decode_layers_set_embedding(const void* table, int rows, const int* ids) {
+    if (table && (!ids || rows <= 0)) SP_FAIL("decode_layers: the embedding needs its table's rows and the token ids");
+    next_embed = EmbedArgs{table, ids, rows};
+    return 0;
 }
 // With head mode 2, for the NEXT call only: the kernel's last CTA also writes the greedy tokens [T] and, with
 // ``header`` [n_slots, 4], notes them in the headers of the step's sequences (slots ``seq_slot``, lengths ``seq_len``).
@@ -1318,6 +1344,11 @@ SP_API int sp_decode_layers(const void* layers, const void* maps, int n_layers, 
     p.n_slots = next_greedy.n_slots;
     p.seq_slot = next_greedy.seq_slot;
     p.seq_len = next_greedy.seq_len;
+    p.embed_w = (const __nv_bfloat16*)next_embed.w;
+    p.embed_ids = next_embed.ids;
+    p.embed_rows = next_embed.rows;
+    p.pad4 = 0;
+    next_embed = EmbedArgs{nullptr, nullptr, 0};
     next_head.mode = 0;                                        // for this call only
     next_greedy = GreedyArgs{nullptr, nullptr, 0, nullptr, nullptr};
     p.rg = sp_range_host;

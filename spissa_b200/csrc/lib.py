@@ -732,6 +732,16 @@ def decode_layers_set_head(mode: int, w, norm_w, eps: float, out, ld: int) -> No
         int(mode), c_void_p(_ptr(w)), c_void_p(_ptr(norm_w)), c_float(eps), int(w.shape[0]), c_void_p(_ptr(out)), int(ld)))
 
 
+def decode_layers_set_embedding(table, ids) -> None:
+    """For the NEXT ``decode_layers`` call: the kernel fills the residual itself from the bfloat16 embedding ``table``
+    [rows, H] and the token ``ids`` (int32 on the device); an id outside the table: a zero row and code 301."""
+    lib = load("decode_layers")
+    _need_contig(table, ids)
+    if table.dtype != torch.bfloat16 or ids.dtype != torch.int32:
+        raise KernelError("decode_layers: a bfloat16 embedding table and int32 token ids")
+    _check("decode_layers", lib.sp_decode_layers_set_embedding(c_void_p(_ptr(table)), int(table.shape[0]), c_void_p(_ptr(ids))))
+
+
 def decode_layers_set_greedy_out(tokens, note=None) -> None:
     """With head mode 2, for the NEXT ``decode_layers`` call: the kernel's last CTA also takes the best of each token's
     candidates and writes the tokens (int32 [T]); with ``note`` they also go into the headers of the step's sequences."""

@@ -71,6 +71,7 @@ class FusedDecode:
         # switch for comparisons: False (or SPISSA_B200_FUSE_HEAD=0) leaves the final norm and the head to the parts
         self.with_head = os.environ.get("SPISSA_B200_FUSE_HEAD", "1") != "0"
         self.head_runs = 0
+        self.embedding = None                  # the embedding table, when the kernel can gather the rows itself
 
     # ------------------------------------------------------------------ planning
     @classmethod
@@ -89,6 +90,9 @@ class FusedDecode:
         if norm and head and norm.get("kind") == "rmsnorm" and head.get("kind") == "linear_head" \
                 and norm["size"] == H and head["hidden_size"] == H and head["vocab_size"] % 16 == 0:
             plan.head = dict(weight=head["weight"], norm=norm["weight"], eps=float(norm["eps"]), vocab=head["vocab_size"])
+        emb = model.embedding.fused_fields() if hasattr(model.embedding, "fused_fields") else None
+        if emb and emb.get("kind") == "token_embedding" and emb["hidden_size"] == H:
+            plan.embedding = emb["weight"]
         return plan
 
     def takes(self, step, cache) -> bool:
@@ -162,10 +166,16 @@ class FusedDecode:
         self.part_ml = torch.empty(MAX_TOKENS * self.max_nh * chunks * 2, dtype=torch.float32, device=dev)
         self.sync = torch.zeros(4, dtype=torch.int32, device=dev)
         self.cand = torch.empty(MAX_TOKENS, ctas, 2, dtype=torch.float32, device=dev)
+        self.x = torch.empty(MAX_TOKENS, self.H, dtype=torch.float32, device=dev)
 
     # ------------------------------------------------------------------ running
-    def run(self, h: torch.Tensor, step, cache, greedy: bool = False, note=None):
-        """All layers on the residual stream ``h`` [T, H] (float32), in place. When the kernel can also take the final
+    def embeds(self) -> bool:
+        """Whether ``run`` may be given no residual: the kernel then starts from the step's token ids."""
+        return self.embedding is not None and self.with_head
+
+    def run(self, h, step, cache, greedy: bool = False, note=None):
+        """All layers on the residual stream ``h`` [T, H] (float32), in place (None: the kernel gathers the embedding
+        rows itself; the residual is then ``self.last_h``). When the kernel can also take the final
         norm and the head and the step wants every token's result, it does, and the result comes back: the greedy
         tokens (int32 [T]; ``note`` as in ``LMHead.greedy``) or the logits (float32 [T, vocab]); else None."""
         self.runs += 1
@@ -173,6 +183,10 @@ class FusedDecode:
         len_pages = (step.max_len + cache.page_size - 1) // cache.page_size
         result = None
         T = step.n_tokens
+        if h is None:                                   # the kernel gathers the embedding rows into its own residual
+            h = self.x[:T]
+            K.decode_layers_set_embedding(self.embedding, step.tokens)
+        self.last_h = h
         if self.head is not None and self.with_head and step.n_want == T:
             # every sequence brings one token and wants its result: the wanted rows are all rows, in order
             self.head_runs += 1

@@ -80,18 +80,23 @@ class Model:
         """Logits [step.n_want, vocab] (float32) after running the step's tokens through every layer; with
         ``greedy`` the indices of their largest entries instead (int32 [step.n_want]; the logits are never written
         where the head has a kernel for that). ``note``: see ``LMHead.greedy``."""
-        with phase("embedding_ms"):
-            h = self.embedding.forward(step)
         if self.fuse_decode and self._fused is False:
             from .fused_decode import FusedDecode
             self._fused = FusedDecode.plan(self)
         if self.fuse_prefill and self._fused_prefill is False:
             from .fused_prefill import FusedPrefill
             self._fused_prefill = FusedPrefill.plan(self)
-        if self.fuse_decode and self._fused is not None and not profiling() and self._fused.takes(step, cache):
+        one_kernel = self.fuse_decode and self._fused is not None and not profiling() and self._fused.takes(step, cache)
+        if one_kernel and self._fused.embeds():
+            h = None                                       # the kernel gathers the embedding rows itself
+        else:
+            with phase("embedding_ms"):
+                h = self.embedding.forward(step)
+        if one_kernel:
             done = self._fused.run(h, step, cache, greedy, note)
             if done is not None:
                 return done                                # the kernel ran the final norm and the head as well
+            h = self._fused.last_h
         elif self.host_steps and not profiling() and self._host_runner(step, cache):
             self._host_step.run(h, step, cache)            # a prompt step of up to 128 tokens: launched from C++
         elif self.fuse_prefill and self._fused_prefill is not None and self._fused_prefill.takes(step, cache):

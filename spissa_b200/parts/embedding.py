@@ -32,6 +32,12 @@ class TokenEmbedding(Part):
         super().bind(tensors, rt)
         self.weight = tensors[self.weight_name].contiguous()
 
+    def fused_fields(self):
+        """What a runner that gathers the rows itself needs: the table [vocab, hidden] (bfloat16)."""
+        if self.weight is None or self.weight.dtype != torch.bfloat16 or type(self) is not TokenEmbedding:
+            return None
+        return dict(kind="token_embedding", weight=self.weight, vocab_size=self.vocab_size, hidden_size=self.hidden_size)
+
     def forward(self, step) -> torch.Tensor:
         """The residual stream [T, H] (float32) of the step's tokens. An embedding that needs more than the token ids
         (positions, for a learned position table) finds it in ``step``. A token id outside the table gives a zero row

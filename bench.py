@@ -327,6 +327,33 @@ def kernel_case(name: str, reps: int) -> int:
                           dtype=torch.float32 if mode == K.TC_ACCUMULATE else bf, device=dev)
         run = lambda i: K.tc_stream(x, ws[i % n_buf], out, mode, pair)
         bytes_ = N * Kd * 2.0
+    elif name in ("stream_fused_qkv", "stream_fused_o", "stream_fused_gate_up", "stream_fused_down"):
+        # the same products of 64 tokens with the fused epilogues (engine/fused_prefill.py, 17 to 64 tokens)
+        N, Kd = {"stream_fused_qkv": (3072, H), "stream_fused_o": (H, H), "stream_fused_gate_up": (2 * I, H),
+                 "stream_fused_down": (H, I)}[name]
+        M = 64
+        n_buf = max(2, int(300e6 // (N * Kd * 2)) + 1)
+        ws = [rnd(N, Kd) for _ in range(n_buf)]
+        a = rnd(M, Kd)
+        ssq = torch.rand(M, 16, device=dev) + 1.0
+        bytes_ = N * Kd * 2.0
+        if name == "stream_fused_qkv":
+            kp, vp = rnd(M, nkv, 64, hd), rnd(M, nkv, 64, hd)          # every token in a page of its own: a decode step
+            q = torch.empty(M, nh * hd, dtype=bf, device=dev)
+            cs = torch.rand(M, hd // 2, 2, device=dev)
+            pos = torch.full((M,), 2047, dtype=torch.int32, device=dev)
+            tok_page = torch.arange(M, dtype=torch.int32, device=dev)
+            rope = dict(cs=cs, tok_page=tok_page, positions=pos, q_out=q, k_pool=kp, v_pool=vp, nh=nh, nkv=nkv, hd=hd, page_size=64)
+            run = lambda i: K.tc_stream_fused(a, ws[i % n_buf], None, K.TC_QKV_ROPE, 0, row_ssq=ssq, norm_width=H, eps=1e-5, rope=rope)
+        elif name == "stream_fused_gate_up":
+            out = torch.empty(M, I, dtype=bf, device=dev)
+            run = lambda i: K.tc_stream_fused(a, ws[i % n_buf], out, K.TC_SILU_MUL, 128, row_ssq=ssq, norm_width=H, eps=1e-5)
+        else:
+            out = torch.zeros(M, N, device=dev)
+            xw = torch.empty(M, N, dtype=bf, device=dev)
+            nw = rnd(N)
+            so = torch.empty(M, K.tc_stream_n_tiles(N), device=dev)
+            run = lambda i: K.tc_stream_fused(a, ws[i % n_buf], out, K.TC_ACCUMULATE, 0, xw=xw, next_w=nw, ssq_out=so)
     elif name in ("gemv_qkv", "gemv_o", "gemv_gate_up", "gemv_down", "gemv_head"):
         N, Kd, mode = {"gemv_qkv": (3072, H, K.TC_STORE), "gemv_o": (H, H, K.TC_ACCUMULATE),
                        "gemv_gate_up": (2 * I, H, K.TC_SILU_MUL), "gemv_down": (H, I, K.TC_ACCUMULATE),
@@ -434,7 +461,7 @@ def main() -> int:
                     help="add per-phase timings of one prompt step and of part-by-part decode steps")
     ap.add_argument("--kernel-case", default=None,
                     help="time one kernel alone (gemm_qkv|gemm_o|gemm_gate_up|gemm_down|gemv_qkv|gemv_o|gemv_gate_up|"
-                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
+                         "gemv_down|gemv_head|stream_qkv|stream_o|stream_gate_up|stream_down|stream_fused_qkv|stream_fused_o|stream_fused_gate_up|stream_fused_down|flash_prefill[_128]|flash_prefill_tc[_128]|flash_decode[_b64]|sample_b8|sample_b64|argmax_b8|decode_layers|step_b8|prefill|fused_qkv|fused_o|fused_gate_up|fused_down) instead of the step")
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()

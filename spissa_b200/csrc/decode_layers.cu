@@ -766,44 +766,45 @@ __device__ __noinline__ void attention_pair_combine(const Params& p, Shared* sh,
     }
 }
 
-// out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order; one warp per (token, head)
+// out[b, head, :] = sum_c o_c·2^(m_c - M) / sum_c l_c·2^(m_c - M), chunks in order; one warp per (token, head).
+// Lane c holds (m, l) of chunk c (there are at most 32 chunks) and hands them round by shuffles; the partial outputs
+// of up to CB chunks are asked for in one go, the first batch before the maximum is known: with head size 64 the
+// whole combination costs one round trip to L2.
 template <int HD>
 __device__ __noinline__ void attention_combine(const Params& p, const LayerDesc& L, int n_chunks) {
-    constexpr int CB = 16;                                         // chunks whose loads are issued together
+    static_assert(MAX_CHUNKS <= 32, "a lane per chunk");
     constexpr int DPL = HD / 32;                                   // output dims per lane
+    constexpr int CB = DPL <= 2 ? 32 : 16;                         // chunks whose loads are issued together
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nc = n_chunks;
     for (int r = blockIdx.x * CWARPS + warp; r < p.T * L.nh; r += gridDim.x * CWARPS) {
         const size_t bh = (size_t)r;
-        // lane c holds (m, l) of chunk c, c + 32, ...: the maximum over all chunks first
-        float mm = -INFINITY;
-        for (int c = lane; c < nc; c += 32) mm = fmaxf(mm, __ldcg(&p.part_ml[(bh * nc + c) * 2]));
-        mm = sp_warp_max(mm);
+        float2 ml = make_float2(-INFINITY, 0.0f);
+        if (lane < nc) ml = __ldcg((const float2*)&p.part_ml[(bh * nc + lane) * 2]);
+        float oc[CB][DPL];
+        auto ask = [&](int c0) {
+#pragma unroll
+            for (int u = 0; u < CB; ++u) {
+                const int c = c0 + u;
+#pragma unroll
+                for (int i = 0; i < DPL; ++i) oc[u][i] = c < nc ? __ldcg(&p.part_o[(bh * nc + c) * HD + lane + 32 * i]) : 0.0f;
+            }
+        };
+        ask(0);
+        const float mm = sp_warp_max(ml.x);
         const float msafe = (mm == -INFINITY) ? 0.0f : mm;
+        const float f_mine = ml.y > 0.0f ? exp2f(ml.x - msafe) : 0.0f;   // this lane's chunk: its weight, 0 if it saw no key
         float ll = 0.0f, acc[DPL];
 #pragma unroll
         for (int i = 0; i < DPL; ++i) acc[i] = 0.0f;
         for (int c0 = 0; c0 < nc; c0 += CB) {
-            float mc[CB], lc[CB], oc[CB][DPL];
+            if (c0 > 0) ask(c0);
 #pragma unroll
-            for (int u = 0; u < CB; ++u) {
-                const int c = c0 + u;
-                if (c < nc) {
-                    const float2 ml = __ldcg((const float2*)&p.part_ml[(bh * nc + c) * 2]);
-                    mc[u] = ml.x; lc[u] = ml.y;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) oc[u][i] = __ldcg(&p.part_o[(bh * nc + c) * HD + lane + 32 * i]);
-                } else {
-                    mc[u] = -INFINITY; lc[u] = 0.0f;
-#pragma unroll
-                    for (int i = 0; i < DPL; ++i) oc[u][i] = 0.0f;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < CB; ++u) {
-                if (lc[u] > 0.0f) {                                 // chunks in order
-                    const float f = exp2f(mc[u] - msafe);
-                    ll += lc[u] * f;
+            for (int u = 0; u < CB; ++u) {                          // chunks in order
+                const float f = __shfl_sync(0xffffffffu, f_mine, (c0 + u) & 31);
+                const float lc = __shfl_sync(0xffffffffu, ml.y, (c0 + u) & 31);
+                if (c0 + u < nc && lc > 0.0f) {
+                    ll += lc * f;
 #pragma unroll
                     for (int i = 0; i < DPL; ++i) acc[i] += oc[u][i] * f;
                 }

@@ -105,6 +105,23 @@ def main() -> int:
     assert code == 0
     code, kp = fused(bad)
     assert code == 401 and bool((kp[bad] == 9.0).all())
+
+    # and through the same epilogue of the kernel that streams the weights (steps of 17 to 64 tokens)
+    assert K.range_checked("tc_stream")
+
+    def streamed(declared):
+        kp = torch.full((wmeta.n_pages, nkv, 64, hd), 9.0, dtype=torch.bfloat16, device=DEV)
+        vp = torch.full_like(kp, -9.0)
+        rope = dict(cs=cs, tok_page=tok_page, positions=wmeta.positions, q_out=qo, k_pool=kp, v_pool=vp, nh=nh, nkv=nkv,
+                    hd=hd, page_size=64)
+        if declared is not None:
+            rope["declared_pages"] = declared
+        return code_of(lambda: K.tc_stream_fused(xw, w, None, K.TC_QKV_ROPE, 0, rope=rope)), kp
+    code, kp = streamed(None)
+    assert code == 0
+    code, kp = streamed(bad)
+    assert code == 401 and bool((kp[bad] == 9.0).all())
+    assert any(bool((kp[p] != 9.0).any()) for p in other)
     print("range check cases ok")
     return 0
 

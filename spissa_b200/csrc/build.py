@@ -9,12 +9,14 @@ functions and are loaded with ``ctypes``.
 """
 from __future__ import annotations
 
+import atexit
 import hashlib
 import os
 import shutil
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 from pathlib import Path
 
@@ -129,17 +131,59 @@ def find_built(module: str, range_check=None) -> Path | None:
     return None
 
 
+# Builds started ahead of their first use (``prefetch``): a model's first step needs several libraries one after the
+# other, each ten seconds or more of nvcc; started together they take as long as the slowest.
+_background: dict = {}             # (module, debug build?) -> the thread that builds it
+_background_lock = threading.Lock()
+_compilers: list = []              # nvcc processes in flight (ended with this process, should it leave first)
+
+
+def _end_compilers() -> None:
+    for proc in list(_compilers):
+        if proc.poll() is None:
+            proc.kill()
+
+
+atexit.register(_end_compilers)
+
+
+def prefetch(modules, verbose: bool = True) -> None:
+    """Start building, in the background, those of ``modules`` that have no up-to-date library yet. ``build_module``
+    waits for a build in flight instead of starting a second one; a build that fails here fails again, loudly, there."""
+    on = range_check_enabled()
+    for module in modules:
+        if module not in MODULES:
+            continue
+        with _background_lock:
+            if (module, on) in _background or find_built(module, on) is not None:
+                continue
+
+            def work(m=module):
+                try:
+                    build_module(m, verbose, range_check=on)
+                except Exception:
+                    pass
+
+            t = threading.Thread(target=work, name=f"spissa-build-{module}", daemon=True)
+            _background[(module, on)] = t
+            t.start()
+
+
 def build_module(module: str, verbose: bool = True, extra_flags=(), range_check=None) -> Path:
     """Compile ``module`` if no up-to-date library exists; return the library's path. ``range_check`` None: as the
     environment says (the regular build unless SPISSA_B200_RANGE_CHECK=1)."""
     if module not in MODULES:
         raise BuildError(f"unknown kernel module {module!r}; known: {sorted(MODULES)}")
+    on = range_check_enabled() if range_check is None else bool(range_check)
+    ahead = _background.get((module, on))
+    if ahead is not None and ahead is not threading.current_thread():
+        ahead.join()                                   # started ahead of its use: wait for it rather than build twice
     have = find_built(module, range_check)
     if have is not None:
         return have
     out = library_path(module, None, range_check)
     nvcc = find_nvcc()
-    tmp = out.with_suffix(f".tmp{os.getpid()}.so")
+    tmp = out.with_suffix(f".tmp{os.getpid()}_{threading.get_ident()}.so")
     cmd = [nvcc] + flags(range_check) + list(extra_flags) + ["-I", str(CSRC), "-o", str(tmp), str(CSRC / MODULES[module])]
     if verbose:
         kind = " (debug build with range checks)" if RANGE_CHECK_FLAG in cmd else ""
@@ -147,6 +191,7 @@ def build_module(module: str, verbose: bool = True, extra_flags=(), range_check=
     t0 = time.time()
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
                             env=dict(os.environ, TMPDIR=str(out.parent)))
+    _compilers.append(proc)
     last = t0
     while True:
         try:
@@ -156,6 +201,7 @@ def build_module(module: str, verbose: bool = True, extra_flags=(), range_check=
             if verbose and time.time() - last >= 10:
                 _say(f"  still compiling {MODULES[module]} ({time.time() - t0:.0f} s)")
                 last = time.time()
+    _compilers.remove(proc)
     if proc.returncode != 0:
         try:
             tmp.unlink()

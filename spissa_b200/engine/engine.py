@@ -19,6 +19,7 @@ import torch
 from ..cache import CacheManager
 from ..cache.manager import HEADER_LAST_TOKEN, HEADER_WORDS
 from ..config import load_config
+from ..csrc import build as kernel_build
 from ..csrc import lib as K
 from ..csrc.lib import KernelError
 from ..parts.base import Runtime
@@ -76,6 +77,7 @@ class Engine:
         self.dtype = _DTYPES[dtype]
         self.rt = Runtime(self.device, self.dtype, self.PAGE_SIZE)
         self.model = Model(config.to_spec())
+        kernel_build.prefetch(self.model.kernel_modules(self.dtype))      # in the background, while the weights go up
         self.model.fuse_decode = fuse_decode
         self.model.fuse_prefill = fuse_prefill
         with torch.cuda.device(self.device):
@@ -112,6 +114,7 @@ class Engine:
         dev = _require_gpu(device)
         config = load_config(folder)
         model = Model(config.to_spec())
+        kernel_build.prefetch(model.kernel_modules(_DTYPES[dtype]))       # in the background, while the weights are read
         tensors = load_tensors(folder, model.weight_specs(), dev, _DTYPES[dtype] == torch.float32)
         return cls(config, tensors, dtype, max_tokens, max_seqs, device, use_graphs, fuse_decode, fuse_prefill)
 

@@ -39,6 +39,17 @@ class Model:
         self.host_steps = True         # a short prompt step's launch sequence as one call into C++ likewise
         self._host_step = False
 
+    def kernel_modules(self, act_dtype) -> list:
+        """The kernel libraries that steps of this model can need, for building them ahead of their first use (a guess
+        costs processor time only: a library is still built when it is first asked for)."""
+        if act_dtype != torch.bfloat16:
+            return ["generic"]
+        mods = ["generic", "gemv", "attention", "tc_gemm", "tc_stream"]
+        head_sizes = {layer.mixer.params.get("head_dim") for layer in self.spec.layers}
+        if head_sizes & {64, 128}:                  # the tcgen05 prompt attention, the one-kernel decode path, the C++ launcher
+            mods += ["flash_tc", "decode_layers", "host_step"]
+        return mods
+
     # ------------------------------------------------------------------ weights
     def parts(self) -> list:
         return [self.embedding] + self.layers + [self.final_norm, self.head]

@@ -60,8 +60,13 @@ class BuildError(RuntimeError):
     pass
 
 
+_say_lock = threading.Lock()
+
+
 def _say(msg: str) -> None:
-    print(f"[spissa_b200] {msg}", file=sys.stderr, flush=True)
+    with _say_lock:                                    # builds run side by side: one line at a time
+        sys.stderr.write(f"[spissa_b200] {msg}\n")
+        sys.stderr.flush()
 
 
 def find_nvcc() -> str:

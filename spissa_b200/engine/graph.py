@@ -19,22 +19,7 @@ import weakref
 import torch
 
 from .batch import StepBatch
-
-
-def length_bucket(max_len: int, page_size: int) -> int:
-    """Powers of two up to 8 pages, then steps of 8 pages, steps that double while they are under a sixteenth of
-    the length: the bucket fixes how the keys are split, and a split made for a much longer bucket leaves most
-    chunks empty; a capture costs tens of milliseconds, so it should not come more often than every few hundred
-    steps either."""
-    b = 4 * page_size
-    while b < max_len and b < 8 * page_size:
-        b *= 2
-    if max_len <= b:
-        return b
-    step = 8 * page_size
-    while step * 16 < max_len:
-        step *= 2
-    return -(-max_len // step) * step
+from ..parts.attention import length_bucket  # noqa: F401  (the attention part splits the keys by it; graphs are keyed by it)
 
 
 def wide_bucket(max_len: int, page_size: int) -> int:

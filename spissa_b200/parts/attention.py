@@ -26,6 +26,22 @@ from .registry import build_part, register_part
 from ..phases import phase
 
 
+def length_bucket(max_len: int, page_size: int) -> int:
+    """Powers of two up to 8 pages, then steps of 8 pages, steps that double while they are under a sixteenth of
+    the length: the bucket fixes how the keys are split, and a split made for a much longer bucket leaves most
+    chunks empty; a capture costs tens of milliseconds, so it should not come more often than every few hundred
+    steps either."""
+    b = 4 * page_size
+    while b < max_len and b < 8 * page_size:
+        b *= 2
+    if max_len <= b:
+        return b
+    step = 8 * page_size
+    while step * 16 < max_len:
+        step *= 2
+    return -(-max_len // step) * step
+
+
 @register_part("mixer", "attention")
 class GQAAttention(Mixer):
     graph_safe = True
@@ -125,7 +141,10 @@ class GQAAttention(Mixer):
         ctx = torch.empty_like(q)
         if K.flash_supported(q, cache.k_pool, nh, nkv, hd, cache.page_size):
             if step.all_single:
-                chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, step.max_len, cache.page_size)
+                # the split is made for the length's bucket, not the length: a step run directly and the same step
+                # replayed from a graph (captured for the bucket) then add up in the same order, bit for bit
+                chunk_tiles, n_chunks = K.flash_decode_plan(T, nkv, length_bucket(step.max_len, cache.page_size),
+                                                            cache.page_size)
                 need = K.flash_decode_scratch_floats(T, nh, hd, n_chunks)
                 scratch = torch.empty(need, dtype=torch.float32, device=q.device)
                 K.flash_decode(q, cache.k_pool, cache.v_pool, ctx, cache, step.seq_len, nh, nkv, hd, self.window,

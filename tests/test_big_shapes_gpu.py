@@ -62,7 +62,7 @@ def test_real_layer_sizes_against_plain(tmp_path, name, cfg):
         assert len(got) == 4 + 2 + 1 + 8 and worst <= tol, f"{name}/{dtype}: {worst:.3e} of the largest logit"
 
 
-def _engine_and_plain_weights(cfg_dict, seed, dtype, max_tokens, max_seqs):
+def _engine_and_plain_weights(cfg_dict, seed, dtype, max_tokens, max_seqs, **engine_options):
     """An engine on random weights drawn on the device, and the same tensors for the plain implementation."""
     from spissa_b200 import Engine
     from spissa_b200.config import config_from_dict
@@ -73,7 +73,7 @@ def _engine_and_plain_weights(cfg_dict, seed, dtype, max_tokens, max_seqs):
     plain_w = {k: v.cpu() for k, v in tensors.items()}
     if dtype == "float32":
         tensors = {k: v.float() for k, v in tensors.items()}
-    return Engine(cfg, tensors, dtype, max_tokens, max_seqs), plain_w
+    return Engine(cfg, tensors, dtype, max_tokens, max_seqs, **engine_options), plain_w
 
 
 def test_the_whole_1b_model_on_a_short_prompt():
@@ -106,8 +106,10 @@ def test_the_whole_1b_model_on_a_short_prompt():
 
 @pytest.mark.parametrize("n_seqs", [33, 64])
 def test_decode_batches_beyond_the_one_kernel_path_at_real_layer_sizes(n_seqs):
-    """33 and 64 sequences decode part by part: the tensor-core weight-streaming products, the split-key attention and
-    a CUDA graph per length bucket, at the 1B layer sizes (two layers, a smaller vocabulary) against the plain run."""
+    """33 and 64 sequences decode with five launches a layer: the tensor-core weight-streaming products with the
+    norms, the rotation and the cache write in their epilogues, the split-key attention, and a CUDA graph per length
+    bucket, at the 1B layer sizes (two layers, a smaller vocabulary) against the plain run; the same steps launched
+    directly, without graphs, give the same bits."""
     cfg = {**LLAMA_1B_2L, "vocab_size": 20000}
     engine, w = _engine_and_plain_weights(cfg, 4, "bfloat16", 64 * n_seqs, n_seqs)
     V = cfg["vocab_size"]
@@ -118,12 +120,23 @@ def test_decode_batches_beyond_the_one_kernel_path_at_real_layer_sizes(n_seqs):
     slots = [engine.acquire() for _ in seqs]
     engine.step([(sl, s[:n], []) for sl, s, n in zip(slots, seqs, lens)])
     worst = 0.0
+    kept = []
     for i in range(3):                                          # the third step of a kind is replayed from its graph
-        rows = engine.step([(sl, [s[n + i]], [0]) for sl, s, n in zip(slots, seqs, lens)]).cpu().double()
+        rows = engine.step([(sl, [s[n + i]], [0]) for sl, s, n in zip(slots, seqs, lens)]).cpu()
+        kept.append(rows)
+        rows = rows.double()
         for b, (r, n) in enumerate(zip(refs, lens)):
             worst = max(worst, float((rows[b] - r[n + i]).abs().max()) / scale)
     assert worst <= tiny.TOL["bfloat16"], f"worst error {worst:.3e} of the largest logit"
     assert len(engine._graphs) >= 1 and not any(k[2] for k in engine._graphs)      # captured, and not the one-kernel path
+    assert engine.model._fused_prefill.runs >= 3                 # the five-launch sequence took the decode steps
+    direct, _ = _engine_and_plain_weights(cfg, 4, "bfloat16", 64 * n_seqs, n_seqs, use_graphs=False)
+    slots = [direct.acquire() for _ in seqs]
+    direct.step([(sl, s[:n], []) for sl, s, n in zip(slots, seqs, lens)])
+    for i in range(3):
+        rows = direct.step([(sl, [s[n + i]], [0]) for sl, s, n in zip(slots, seqs, lens)]).cpu()
+        assert torch.equal(rows, kept[i]), f"step {i}: launched directly and replayed from a graph differ"
+    del direct
     # greedy over the same step: the tensor-core head keeps candidates per tile
     engine2, _ = _engine_and_plain_weights(cfg, 4, "bfloat16", 64 * n_seqs, n_seqs)
     slots = [engine2.acquire() for _ in seqs]

@@ -17,6 +17,7 @@ import torch
 from ..csrc import lib as K
 
 MAX_TOKENS = 16
+WIDE_LAYER_BYTES = 160e6        # 9 to 16 sequences go through this kernel only while a layer's weights are smaller
 
 
 def collect_fused_fields(model):
@@ -62,6 +63,11 @@ class FusedDecode:
         self.max_nh = max(f["mixer"]["num_heads"] for f in fields)
         self.max_group = max(f["mixer"]["num_heads"] // f["mixer"]["num_kv_heads"] for f in fields)
         self.max_I = max(f["ffn"]["intermediate_size"] for f in fields)
+        # bytes of the largest layer's weights: with 9 to 16 tokens the kernel keeps the normed rows of all of them in
+        # shared memory (16 x 8 KB at width 4096: two ring stages are left of four) and has one tile's fragments in
+        # flight instead of two, and the larger the layer the more that costs (see ``takes_sizes``)
+        self.layer_bytes = max(sum(w.numel() * w.element_size() for w in (f["mixer"]["qkv"], f["mixer"]["o"], f["ffn"]["gate_up"],
+                                                                     f["ffn"]["down"])) for f in fields)
         self.table = None
         self.runs = 0                          # steps run through the kernel so far
         self.cache_id = None
@@ -102,6 +108,11 @@ class FusedDecode:
         """Whether a decode step of ``n_seqs`` sequences, the longest of ``max_len`` tokens, goes through the kernel."""
         if n_seqs > MAX_TOKENS:
             return False
+        # Measured, decode step in ms, this kernel against the five-launch sequence of the weight-streaming tcgen05
+        # product: 1B layers (122 MB) 16 sequences 1.09 / 1.37; 3B (201 MB) 12: 2.87 / 2.73, 16: 3.06 / 2.87;
+        # 8B (436 MB) 9: 4.54 / 4.45, 12: 5.17 / 4.84, 16: 6.4 / 5.06. Up to 8 sequences this kernel wins everywhere.
+        if n_seqs > 8 and self.layer_bytes > WIDE_LAYER_BYTES and self._five_launch() is not None:
+            return False
         if (max_len + cache.page_size - 1) // cache.page_size > K.decode_layers_max_pages():
             return False
         if not K.decode_layers_supported(n_seqs, self.H, self.hd, cache.page_size, self.max_group):
@@ -109,6 +120,16 @@ class FusedDecode:
         if self.cache_id != id(cache):
             self._bind_cache(cache)
         return self.table is not None
+
+    def _five_launch(self):
+        """The runner of the five-launch sequence for this model, if there is one."""
+        m = self.model
+        if not m.fuse_prefill:
+            return None
+        if m._fused_prefill is False:
+            from .fused_prefill import FusedPrefill
+            m._fused_prefill = FusedPrefill.plan(m)
+        return m._fused_prefill
 
     def key_split(self, n_seqs: int, max_len: int, page_size: int) -> tuple:
         """(pages per chunk, chunks) for a step: what a captured launch reads from the device before it runs."""

@@ -70,7 +70,8 @@ class FusedPrefill:
         return cls(model, fields)
 
     def takes(self, step, cache) -> bool:
-        if not fuses(step.n_tokens):
+        # (a decode step of 9 to 16 sequences that the one-kernel path left alone, large layers, comes here too)
+        if not (fuses(step.n_tokens) or (step.all_single and step.n_tokens > 8)):
             return False
         for e in self.model.spec.schedule:
             g = cache.kv_groups.get(cache.cache_group.get(e.cache))

@@ -17,7 +17,28 @@ import torch
 from ..csrc import lib as K
 
 MAX_TOKENS = 16
-WIDE_LAYER_BYTES = 160e6        # 9 to 16 sequences go through this kernel only while a layer's weights are smaller
+
+
+def five_launch_from(layer_bytes: float) -> int:
+    """The number of sequences from which a decode step is faster as the five-launch sequence of the weight-streaming
+    tcgen05 product (``engine/fused_prefill.py``) than in this kernel, by the bytes of a layer's weights. Measured on a
+    B200, decode step in ms, this kernel / five launches:
+
+        1B layers, 122 MB (width 2048, head 64):   8 sequences 0.95 / 1.14,  16: 1.09 / 1.37
+        3B layers, 201 MB (width 3072, head 128):  2: 2.21 / 2.08,  4: 2.32 / 2.26,  6: 2.44 / 2.35,  8: 2.57 / 2.38,
+                                                   12: 2.87 / 2.73,  16: 3.06 / 2.87
+        8B layers, 436 MB (width 4096, head 128):  4: 3.93 / 4.01,  6: 4.11 / 4.15,  7: 4.30 / 4.39,  8: 4.7 / 4.21,
+                                                   9: 4.54 / 4.45,  12: 5.17 / 4.84,  16: 6.4 / 5.06
+
+    The kernel's products walk blocks of 16 rows dealt to 148 CTAs; the 3B widths leave many CTAs a round short (192
+    blocks: two rounds for 44 of them), and with more than 8 tokens it keeps 16 rows of normed activations in shared
+    memory (128 KB at width 4096: two ring stages are left of four) and one tile's fragments in flight instead of two.
+    """
+    if layer_bytes <= 160e6:
+        return MAX_TOKENS + 1                  # never
+    if layer_bytes <= 300e6:
+        return 2
+    return 8
 
 
 def collect_fused_fields(model):
@@ -63,9 +84,7 @@ class FusedDecode:
         self.max_nh = max(f["mixer"]["num_heads"] for f in fields)
         self.max_group = max(f["mixer"]["num_heads"] // f["mixer"]["num_kv_heads"] for f in fields)
         self.max_I = max(f["ffn"]["intermediate_size"] for f in fields)
-        # bytes of the largest layer's weights: with 9 to 16 tokens the kernel keeps the normed rows of all of them in
-        # shared memory (16 x 8 KB at width 4096: two ring stages are left of four) and has one tile's fragments in
-        # flight instead of two, and the larger the layer the more that costs (see ``takes_sizes``)
+        # bytes of the largest layer's weights: decides from how many sequences on another runner is faster
         self.layer_bytes = max(sum(w.numel() * w.element_size() for w in (f["mixer"]["qkv"], f["mixer"]["o"], f["ffn"]["gate_up"],
                                                                      f["ffn"]["down"])) for f in fields)
         self.table = None
@@ -108,11 +127,8 @@ class FusedDecode:
         """Whether a decode step of ``n_seqs`` sequences, the longest of ``max_len`` tokens, goes through the kernel."""
         if n_seqs > MAX_TOKENS:
             return False
-        # Measured, decode step in ms, this kernel against the five-launch sequence of the weight-streaming tcgen05
-        # product: 1B layers (122 MB) 16 sequences 1.09 / 1.37; 3B (201 MB) 12: 2.87 / 2.73, 16: 3.06 / 2.87;
-        # 8B (436 MB) 9: 4.54 / 4.45, 12: 5.17 / 4.84, 16: 6.4 / 5.06. Up to 8 sequences this kernel wins everywhere.
-        if n_seqs > 8 and self.layer_bytes > WIDE_LAYER_BYTES and self._five_launch() is not None:
-            return False
+        if n_seqs >= five_launch_from(self.layer_bytes) and self._five_launch() is not None:
+            return False                               # faster as five launches a layer: see five_launch_from
         if (max_len + cache.page_size - 1) // cache.page_size > K.decode_layers_max_pages():
             return False
         if not K.decode_layers_supported(n_seqs, self.H, self.hd, cache.page_size, self.max_group):

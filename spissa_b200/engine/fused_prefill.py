@@ -25,7 +25,7 @@ import torch
 
 from ..csrc import lib as K
 from ..parts.linear import STREAM_TOKENS, sm_count, tile_width
-from .fused_decode import collect_fused_fields
+from .fused_decode import collect_fused_fields, five_launch_from
 from ..phases import phase
 
 MIN_TOKENS = 17          # up to 16 tokens the weight-streaming kernels (or the one-kernel decode path) run instead
@@ -43,6 +43,8 @@ class FusedPrefill:
         self.H = fields[0]["mixer"]["hidden_size"]
         self.hd = fields[0]["mixer"]["head_dim"]
         self.runs = 0
+        self.layer_bytes = max(sum(w.numel() * w.element_size() for w in (f["mixer"]["qkv"], f["mixer"]["o"], f["ffn"]["gate_up"],
+                                                                     f["ffn"]["down"])) for f in fields)
         # layers whose frequency tables are equal share one table of angles per step
         tables, self.rope_id = [], []
         for f in fields:
@@ -70,8 +72,8 @@ class FusedPrefill:
         return cls(model, fields)
 
     def takes(self, step, cache) -> bool:
-        # (a decode step of 9 to 16 sequences that the one-kernel path left alone, large layers, comes here too)
-        if not (fuses(step.n_tokens) or (step.all_single and step.n_tokens > 8)):
+        # (a decode step of up to 16 sequences comes here too where large layers make this the faster way)
+        if not (fuses(step.n_tokens) or (step.all_single and step.n_tokens >= five_launch_from(self.layer_bytes))):
             return False
         for e in self.model.spec.schedule:
             g = cache.kv_groups.get(cache.cache_group.get(e.cache))

@@ -152,10 +152,10 @@ def _end_compilers() -> None:
 atexit.register(_end_compilers)
 
 
-def prefetch(modules, verbose: bool = True) -> None:
+def prefetch(modules, verbose: bool = True, range_check=None) -> None:
     """Start building, in the background, those of ``modules`` that have no up-to-date library yet. ``build_module``
     waits for a build in flight instead of starting a second one; a build that fails here fails again, loudly, there."""
-    on = range_check_enabled()
+    on = range_check_enabled() if range_check is None else bool(range_check)
     for module in modules:
         if module not in MODULES:
             continue
@@ -227,6 +227,7 @@ def build_module(module: str, verbose: bool = True, extra_flags=(), range_check=
 
 
 def build_all(verbose: bool = True, range_check=None) -> dict:
+    prefetch(MODULES, verbose, range_check)            # side by side
     return {m: build_module(m, verbose, range_check=range_check) for m in MODULES}
 
 

@@ -409,6 +409,11 @@ class _EpiArgs(ctypes.Structure):
 TC_QKV_ROPE = 3
 
 
+def tc_gemm_splits(M: int, N: int, K: int, bn: int) -> int:
+    """CTAs that share a tile along K when ``tc_gemm`` (the plain epilogues) runs these sizes; 1: K is not split."""
+    return int(load("tc_gemm").sp_tc_gemm_splits(int(M), int(N), int(K), int(bn)))
+
+
 def tc_gemm_n_tiles(N: int, bn: int) -> int:
     return (int(N) + int(bn) - 1) // int(bn)
 

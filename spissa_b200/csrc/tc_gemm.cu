@@ -535,8 +535,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
-// ---------------------------------------------------------------- few tokens: K split over a cluster
-// With at most 128 tokens there is one row of tiles, too few CTAs to pull W from memory at full speed. Here
+// ---------------------------------------------------------------- few tiles: K split over a cluster
+// With a few hundred tokens at most there are few tiles, too few CTAs to pull W from memory at full speed, and each
+// walks all of K alone (the down projection of 256 tokens: 32 tiles of 128 blocks of K). Here
 // the CTAs of a thread-block cluster share one 128 x BN tile: each takes a slice of K, leaves its partial
 // tile in its own shared memory (over the pipeline stages, which are spent by then), and rank 0 adds the
 // partial tiles in rank order through distributed shared memory before the usual epilogue. The order of
@@ -576,7 +577,9 @@ tc_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rank = (int)cluster_rank();
-    const int n0 = (blockIdx.x / splits) * BN;
+    const int m_tiles = (M + BM - 1) / BM;
+    const int tile = blockIdx.x / splits;                     // rows run fastest: clusters that run together share few tiles of W
+    const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
     const int num_kb = (K + BK - 1) / BK;
     const int per = (num_kb + splits - 1) / splits;
     const int kb0 = min(num_kb, rank * per), kb1 = min(num_kb, kb0 + per);
@@ -609,7 +612,7 @@ tc_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (!mbar_wait(smem_u32(&bar_empty[s]), phase ^ 1u, status, 101)) break;
                 const uint32_t a_dst = smem_base + s * L::STAGE_BYTES;
                 mbar_expect_tx(smem_u32(&bar_full[s]), L::STAGE_BYTES);
-                tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, 0, smem_u32(&bar_full[s]));
+                tma_load_2d(a_dst, &map_a, (kb0 + i) * BK, m0, smem_u32(&bar_full[s]));
                 tma_load_2d(a_dst + L::A_BYTES, &map_w, (kb0 + i) * BK, n0, smem_u32(&bar_full[s]));
             }
         }
@@ -633,7 +636,8 @@ tc_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
     }
     const int q = warp & 3;
-    const int row = q * 32 + lane;
+    const int row = q * 32 + lane;                            // within the tile
+    const int grow = m0 + row;                                // of C
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16);
     const uint32_t part = smem_base;                          // [BN / 4][128 rows][4] float32
     bool ok = true;
@@ -692,9 +696,9 @@ tc_gemm_splitk_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     const float g = v[j];
                     v[j] = (g / (1.0f + expf(-g))) * b[j];
                 }
-                if (row < M) store_row32(C, c_dt, (size_t)row * ldc + n0 / 2 + c0, n0 / 2 + c0, N / 2, v, false);
-            } else if (row < M) {
-                store_row32(C, c_dt, (size_t)row * ldc + n0 + c0, n0 + c0, N, v, mode == MODE_ACCUMULATE);
+                if (grow < M) store_row32(C, c_dt, (size_t)grow * ldc + n0 / 2 + c0, n0 / 2 + c0, N / 2, v, false);
+            } else if (grow < M) {
+                store_row32(C, c_dt, (size_t)grow * ldc + n0 + c0, n0 + c0, N, v, mode == MODE_ACCUMULATE);
             }
         }
     }
@@ -818,21 +822,22 @@ int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_d
         if (e != cudaSuccess) SP_FAIL("tc_gemm: cannot reserve %d bytes of shared memory: %s", L::TOTAL, cudaGetErrorString(e));
         configured.mark();
     }
-    const int n_tiles = (N + BN - 1) / BN;
+    const int n_tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     SP_CHECK_CALL("tc_gemm_splitk", sp_launch_cluster(tc_gemm_splitk_kernel<BN, STAGES>, dim3(n_tiles * splits), dim3(192),
                                                      (size_t)L::TOTAL, stream, splits, ma, mw, C, c_dt, M, N, K, ldc,
                                                      mode, splits, status));
     return 0;
 }
 
-// How many CTAs share one tile along K: only for a single row of few tiles. Measured at 64 tokens on B200:
-// two CTAs help a little for K = 2048 (15.6 -> 13.6 us for 24 tiles), four halve the time for K = 8192
-// (41.6 -> 20.1 us for 16 tiles), eight are slower than one, and with 64 tiles or more splitting only hurts.
+// How many CTAs share one tile along K: only for few tiles. Measured at 64 tokens on B200: two CTAs help a little
+// for K = 2048 (15.6 -> 13.6 us for 24 tiles), four halve the time for K = 8192 (41.6 -> 20.1 us for 16 tiles),
+// eight are slower than one, and with 64 tiles or more splitting only hurts. Beyond one row of tiles (more than 128
+// tokens) only the long loops over K are split: the down projection of 129 to 512 tokens.
 int pick_splits(int M, int N, int K, int bn) {
-    if (M > BM) return 1;
-    const int n_tiles = (N + bn - 1) / bn;
+    const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     const int num_kb = (K + BK - 1) / BK;
-    if (n_tiles > 32) return 1;
+    if (M > BM) return (tiles <= 64 && num_kb >= 64) ? 4 : 1;
+    if (tiles > 32) return 1;
     if (num_kb >= 64) return 4;
     if (num_kb >= 16) return 2;
     return 1;
@@ -858,6 +863,10 @@ SP_API int sp_tc_gemm_n_tiles(int N, int bn) { return bn > 0 ? (N + bn - 1) / bn
 
 static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw, int ldc,
                        int mode, int bn, const EpiArgs* epp, int* status, cudaStream_t stream);
+
+// CTAs that would share a tile along K in sp_tc_gemm for these sizes (1: none): the host asks before it chooses
+// between a fused epilogue (never split) and the plain one followed by a small kernel.
+SP_API int sp_tc_gemm_splits(int M, int N, int K, int bn) { return pick_splits(M, N, K, bn == 192 ? 256 : bn); }
 
 // From this many rows of A on, tiles are computed by pairs of CTAs (cta_group::2); 0: never.
 static int pairs_from = 512;

@@ -111,6 +111,21 @@ class FusedPrefill:
         def res_tiles(bn):
             return K.tc_stream_n_tiles(H) if stream else K.tc_gemm_n_tiles(H, bn)
 
+        def into_residual(a, w, next_w):
+            """h += a·wᵀ, and the next norm's input: (residual ⊙ next_w in bfloat16, the rows' sums of squares)."""
+            bn = tile_width(T, H, sms)
+            xw = torch.empty(T, H, dtype=bf, device=dev)
+            if not stream and K.tc_gemm_splits(T, H, a.shape[1], bn) > 1:
+                # few tiles and a long K (the down projection of a few hundred tokens): the kernel that splits K over a
+                # cluster has the plain epilogues only, so the norm's input is a small kernel of its own behind it
+                ssq = torch.empty(T, 1, dtype=torch.float32, device=dev)
+                K.tc_gemm(a, w, h, K.TC_ACCUMULATE, bn)
+                K.norm_prepare(h, next_w, xw, ssq)
+            else:
+                ssq = torch.empty(T, res_tiles(bn), dtype=torch.float32, device=dev)
+                product(a, w, h, K.TC_ACCUMULATE, bn, xw=xw, next_w=next_w, ssq_out=ssq)
+            return xw, ssq
+
         xw = torch.empty(T, H, dtype=bf, device=dev)
         ssq = torch.empty(T, 1, dtype=torch.float32, device=dev)
         with phase("attention_norm_ms"):
@@ -135,11 +150,8 @@ class FusedPrefill:
             # ---- attention, then the output projection into the residual, preparing the second norm
             with phase("attention_ms"):
                 ctx = mixer.attend(q, step, view)
-            bn = tile_width(T, H, sms)
-            xw = torch.empty(T, H, dtype=bf, device=dev)
-            ssq = torch.empty(T, res_tiles(bn), dtype=torch.float32, device=dev)
             with phase("o_projection+attention_residual_ms"):
-                product(ctx, m["o"], h, K.TC_ACCUMULATE, bn, xw=xw, next_w=f["ffn_norm"]["weight"], ssq_out=ssq)
+                xw, ssq = into_residual(ctx, m["o"], f["ffn_norm"]["weight"])
             # ---- gate/up with silu(gate)·up on the normed residual
             act = torch.empty(T, ff["intermediate_size"], dtype=bf, device=dev)
             with phase("mlp_norm+gate_projection+up_projection+activation_multiply_ms"):
@@ -148,11 +160,7 @@ class FusedPrefill:
             # ---- down projection into the residual, preparing the next layer's first norm
             with phase("down_projection+mlp_residual_ms"):
                 if i + 1 < len(self.fields):
-                    bn = tile_width(T, H, sms)
-                    xw = torch.empty(T, H, dtype=bf, device=dev)
-                    ssq = torch.empty(T, res_tiles(bn), dtype=torch.float32, device=dev)
-                    product(act, ff["down"], h, K.TC_ACCUMULATE, bn, xw=xw,
-                            next_w=self.fields[i + 1]["mixer_norm"]["weight"], ssq_out=ssq)
+                    xw, ssq = into_residual(act, ff["down"], self.fields[i + 1]["mixer_norm"]["weight"])
                 elif stream:
                     K.tc_stream(act, ff["down"], h, K.TC_ACCUMULATE)
                 else:

@@ -493,7 +493,9 @@ def test_gemv_is_repeatable_and_row_independent(K):
                                        # from 512 rows on pairs of CTAs compute tiles of 256 rows (cta_group::2): ragged in M
                                        # and N, a last tile whose second CTA has no rows, more tiles than pairs
                                        (512, 256, 64, 128), (513, 520, 136, 128), (1000, 1160, 264, 192), (700, 300, 72, 256),
-                                       (640, 20480, 128, 256), (4096, 2048, 512, 256)])
+                                       (640, 20480, 128, 256), (4096, 2048, 512, 256),
+                                       # several rows of few tiles and a long K: the cluster splits K there too
+                                       (256, 2048, 8192, 128), (300, 520, 4100 - 4, 256), (129, 200, 4096, 128), (511, 1030, 4160, 128)])
 def test_tc_gemm(K, M, N, K_, bn):
     torch.manual_seed(M + N)
     a = torch.randn(M, K_).bfloat16()

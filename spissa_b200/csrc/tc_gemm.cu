@@ -832,11 +832,11 @@ int launch_splitk(const CUtensorMap& ma, const CUtensorMap& mw, void* C, int c_d
 // How many CTAs share one tile along K: only for few tiles. Measured at 64 tokens on B200: two CTAs help a little
 // for K = 2048 (15.6 -> 13.6 us for 24 tiles), four halve the time for K = 8192 (41.6 -> 20.1 us for 16 tiles),
 // eight are slower than one, and with 64 tiles or more splitting only hurts. Beyond one row of tiles (more than 128
-// tokens) only the long loops over K are split: the down projection of 129 to 512 tokens.
+// tokens) only the long loops over K are split: the down projection of 129 to 1,023 tokens.
 int pick_splits(int M, int N, int K, int bn) {
     const int tiles = ((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     const int num_kb = (K + BK - 1) / BK;
-    if (M > BM) return (tiles <= 64 && num_kb >= 64) ? 4 : 1;
+    if (M > BM) return num_kb < 64 ? 1 : tiles <= 36 ? 4 : tiles <= 72 ? 2 : 1;         // one wave of CTAs at most
     if (tiles > 32) return 1;
     if (num_kb >= 64) return 4;
     if (num_kb >= 16) return 2;
@@ -869,7 +869,7 @@ static int tc_gemm_any(const void* A, const void* W, void* C, int c_dt, int M, i
 SP_API int sp_tc_gemm_splits(int M, int N, int K, int bn) { return pick_splits(M, N, K, bn == 192 ? 256 : bn); }
 
 // From this many rows of A on, tiles are computed by pairs of CTAs (cta_group::2); 0: never.
-static int pairs_from = 512;
+static int pairs_from = 1024;
 SP_API void sp_tc_gemm_set_pairs_from(int rows) { pairs_from = rows; }
 
 SP_API int sp_tc_gemm_fused(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int lda, int ldw,

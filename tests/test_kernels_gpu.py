@@ -490,10 +490,10 @@ def test_gemv_is_repeatable_and_row_independent(K):
                                        (100, 130, 520, 256), (33, 2048, 2048, 256),
                                        # 192-wide tiles: whole, ragged in M and N, many tiles per CTA, one row of tiles
                                        (2048, 3072, 2048, 192), (300, 200, 136, 192), (129, 5120, 72, 192), (64, 3072, 2048, 192),
-                                       # from 512 rows on pairs of CTAs compute tiles of 256 rows (cta_group::2): ragged in M
+                                       # from 1,024 rows on pairs of CTAs compute tiles of 256 rows (cta_group::2): ragged in M
                                        # and N, a last tile whose second CTA has no rows, more tiles than pairs
-                                       (512, 256, 64, 128), (513, 520, 136, 128), (1000, 1160, 264, 192), (700, 300, 72, 256),
-                                       (640, 20480, 128, 256), (4096, 2048, 512, 256),
+                                       (1024, 256, 64, 128), (1025, 520, 136, 128), (1500, 1160, 264, 192), (1300, 300, 72, 256),
+                                       (1152, 20480, 128, 256), (4096, 2048, 512, 256),
                                        # several rows of few tiles and a long K: the cluster splits K there too
                                        (256, 2048, 8192, 128), (300, 520, 4100 - 4, 256), (129, 200, 4096, 128), (511, 1030, 4160, 128)])
 def test_tc_gemm(K, M, N, K_, bn):
@@ -843,6 +843,7 @@ def fused_call(K, bn):
 
 
 @pytest.mark.parametrize("M,N,Kd,bn", [(300, 520, 264, 128), (129, 2048, 512, 256), (513, 1160, 128, 192), (2048, 256, 2048, 256),
+                                       (1100, 1160, 264, 128), (1300, 520, 512, 192),
                                        (17, 520, 264, 0), (64, 2048, 8192, 0), (33, 1160, 128, 0), (128, 256, 2048, 0),
                                        (100, 2048, 2048, 0), (1, 200, 72, 0)])
 def test_tc_gemm_accumulate_prepares_the_next_norm(K, M, N, Kd, bn):
@@ -893,15 +894,21 @@ def test_tc_gemm_silu_epilogue_with_row_scaling(K, M, I, H, pair, stream):
     close(out.float(), P.silu(g) * u, 8e-3, "silu(gate)·up of scaled rows")
 
 
-@pytest.mark.parametrize("hd,nh,nkv,bn", [(64, 6, 2, 128), (64, 5, 1, 192), (64, 32, 8, 256), (128, 4, 2, 256), (128, 3, 1, 128),
-                                          (64, 6, 2, 0), (64, 5, 1, 0), (64, 32, 8, 0), (128, 4, 2, 0), (128, 3, 1, 0)])
-def test_tc_gemm_qkv_epilogue_rotates_and_writes_the_cache(K, hd, nh, nkv, bn):
+@pytest.mark.parametrize("hd,nh,nkv,bn,big", [(64, 6, 2, 128, False), (64, 5, 1, 192, False), (64, 32, 8, 256, False),
+                                              (128, 4, 2, 256, False), (128, 3, 1, 128, False),
+                                              (64, 6, 2, 128, True), (64, 5, 1, 192, True), (64, 32, 8, 256, True),
+                                              (128, 4, 2, 256, True), (128, 3, 1, 128, True),
+                                              (64, 6, 2, 0, False), (64, 5, 1, 0, False), (64, 32, 8, 0, False),
+                                              (128, 4, 2, 0, False), (128, 3, 1, 0, False)])
+def test_tc_gemm_qkv_epilogue_rotates_and_writes_the_cache(K, hd, nh, nkv, bn, big):
     """q = rotate(rstd·x·Wqᵀ) stored, k rotated and v plain written into the pages of each token's position, for
     sequences that start at different lengths in one step."""
     fused, _ = fused_call(K, bn)
     torch.manual_seed(hd + nh)
     H = 264 if bn else 2048
     new_counts, before = ([130, 7, 70], [0, 100, 61]) if bn else ([40, 1, 7, 16], [0, 100, 61, 64])
+    if big:
+        new_counts, before = [700, 7, 330, 70], [0, 100, 61, 5]          # 1,107 rows: tiles of 256 rows by pairs of CTAs
     T = sum(new_counts)
     meta = KH.paged_meta(new_counts, before, DEV, seed=hd)
     x = torch.randn(T, H, device=DEV)

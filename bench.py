@@ -163,6 +163,7 @@ def ragged_lengths(batch, seed):
 
 
 KERNEL_CASE_LAYERS = 0
+KERNEL_CASE_BATCH = 0          # sequences of --kernel-case decode_layers (0: eight)
 
 
 def kernel_case(name: str, reps: int) -> int:
@@ -235,10 +236,11 @@ def kernel_case(name: str, reps: int) -> int:
         if KERNEL_CASE_LAYERS:
             cfg["num_hidden_layers"] = KERNEL_CASE_LAYERS
         nl = cfg["num_hidden_layers"]
-        eng = Engine.from_config(LlamaConfig.from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=8 * CONTEXT,
-                                 max_seqs=8, use_graphs=False)
+        n_seqs = KERNEL_CASE_BATCH or 8
+        eng = Engine.from_config(LlamaConfig.from_dict(cfg), seed=0, dtype="bfloat16", max_tokens=n_seqs * CONTEXT,
+                                 max_seqs=n_seqs, use_graphs=False)
         rng = random.Random(0)
-        slots = [eng.acquire() for _ in range(8)]
+        slots = [eng.acquire() for _ in range(n_seqs)]
         for sl in slots:
             eng.step([(sl, [rng.randrange(V) for _ in range(T)], [T - 1])])
         for i in range(max(1, reps - 1)):
@@ -267,7 +269,7 @@ def kernel_case(name: str, reps: int) -> int:
         med = lambda v: sorted(v)[len(v) // 2] / 1e3
         last = len(per_layer) * nl                                # behind the last layer: the final norm and the head, if the kernel ran them
         head_us = round((t[1023] - t[2 * last + 1]) / 1e3, 2) if t[2 * last + 1] else None
-        print(json.dumps({"kernel_case": name, "layers": nl, "kernel_us": round((t[1023] - t[1]) / 1e3, 1),
+        print(json.dumps({"kernel_case": name, "layers": nl, "sequences": n_seqs, "kernel_us": round((t[1023] - t[1]) / 1e3, 1),
                           "head_us": head_us,
                           "step_ms_with_host": round(e0.elapsed_time(e1), 3),
                           "phase_us_median": {k: round(med(v), 2) for k, v in work.items()},
@@ -466,8 +468,9 @@ def main() -> int:
     ap.add_argument("--case-layers", type=int, default=0, help="layers of the model in --kernel-case decode_layers (0: all)")
     args = ap.parse_args()
     if args.kernel_case:
-        global KERNEL_CASE_LAYERS
+        global KERNEL_CASE_LAYERS, KERNEL_CASE_BATCH
         KERNEL_CASE_LAYERS = args.case_layers
+        KERNEL_CASE_BATCH = args.batch or 0
         return kernel_case(args.kernel_case, args.reps)
 
     if args.impl == "reference":
